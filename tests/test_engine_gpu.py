@@ -1,0 +1,179 @@
+"""The engine against the plain implementation, under every way of cutting the work:
+each request alone and whole; with its last 32 tokens one by one; in batches of unequal
+lengths whose shorter requests end earlier, one batch after another so that slots and
+blocks are used again; long decoding; the first tokens of a sequence."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from conftest import TINY, assert_close, oracle_logits, token_ids
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+NAMES = ["a", "b", "c"]
+
+
+def load(folder, dtype):
+    import thintensor_b200
+
+    return thintensor_b200.load_model(folder, dtype=dtype, device="cuda")
+
+
+def folder_for(model_folders, name, dtype):
+    # the bfloat16 engine reads bfloat16 weights; the oracle reads the same file, so
+    # both compute with identical weight values
+    return model_folders(name, "float32" if dtype == "float32" else "bfloat16")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_whole_requests_alone(model_folders, name, dtype):
+    from thintensor_b200.engine.engine import Entry
+
+    folder = folder_for(model_folders, name, dtype)
+    runtime = load(folder, dtype)
+    engine = runtime.new_engine(max_tokens=512, max_sequences=4)
+    vocab = TINY[name]["vocab_size"]
+    for seed, length in enumerate([1, 2, 5, 63, 64, 65, 130, 200]):
+        tokens = token_ids(vocab, length, 100 + seed)
+        slot = engine.open()
+        logits = engine.step([Entry(slot, tokens, list(range(length)))])
+        engine.close(slot)
+        engine.check_status()
+        assert_close(logits, oracle_logits(folder, tokens), dtype, f"{name} whole length {length}")
+    assert engine.cache.free_blocks == engine.cache.num_blocks
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_last_tokens_one_by_one(model_folders, name, dtype):
+    from thintensor_b200.engine.engine import Entry
+
+    folder = folder_for(model_folders, name, dtype)
+    runtime = load(folder, dtype)
+    engine = runtime.new_engine(max_tokens=512, max_sequences=2)
+    vocab = TINY[name]["vocab_size"]
+    for seed, length in enumerate([33, 70, 161]):
+        tokens = token_ids(vocab, length, 200 + seed)
+        want = oracle_logits(folder, tokens)
+        head = length - 32
+        slot = engine.open()
+        got = [engine.step([Entry(slot, tokens[:head], [head - 1])])]
+        for t in range(head, length):
+            got.append(engine.step([Entry(slot, [tokens[t]], [0])]))
+        engine.close(slot)
+        engine.check_status()
+        assert_close(torch.cat(got), want[head - 1:], dtype, f"{name} tail of length {length}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_first_tokens_from_empty_cache(model_folders, name, dtype):
+    """Token by token from the very first token: positions 0, 1, 2 ... of a fresh slot."""
+    from thintensor_b200.engine.engine import Entry
+
+    folder = folder_for(model_folders, name, dtype)
+    runtime = load(folder, dtype)
+    engine = runtime.new_engine(max_tokens=128, max_sequences=2)
+    tokens = token_ids(TINY[name]["vocab_size"], 20, 300)
+    slot = engine.open()
+    got = [engine.step([Entry(slot, [t], [0])]) for t in tokens]
+    engine.close(slot)
+    assert_close(torch.cat(got), oracle_logits(folder, tokens), dtype, f"{name} first tokens")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_unequal_batches_with_reuse(model_folders, name, dtype):
+    """Batches of unequal prompts; every request is then continued one token per step
+    to its own length, so shorter requests leave earlier; the next batch reuses the
+    slots and blocks.  The cache is sized so that nothing is left over."""
+    from thintensor_b200.engine.engine import Entry
+
+    folder = folder_for(model_folders, name, dtype)
+    runtime = load(folder, dtype)
+    vocab = TINY[name]["vocab_size"]
+    # (prompt length, total length) per request
+    batches = [
+        [(5, 9), (9, 40), (2, 2), (17, 30)],
+        [(70, 75), (1, 12), (40, 41)],
+        [(64, 70), (3, 67), (128, 131), (31, 33)],
+    ]
+    most = max(sum(-(-total // 64) * 64 for _, total in batch) for batch in batches)
+    engine = runtime.new_engine(max_tokens=most, max_sequences=4)
+    seed = 400
+    for batch_index, batch in enumerate(batches):
+        requests = []
+        for prompt_len, total in batch:
+            seed += 1
+            requests.append({"tokens": token_ids(vocab, total, seed), "prompt": prompt_len, "total": total,
+                             "slot": engine.open(), "got": {}})
+        logits = engine.step([Entry(r["slot"], r["tokens"][: r["prompt"]], [r["prompt"] - 1]) for r in requests])
+        for row, r in enumerate(requests):
+            r["got"][r["prompt"] - 1] = logits[row]
+            r["at"] = r["prompt"]
+        live = [r for r in requests if r["at"] < r["total"]]
+        for r in requests:
+            if r["at"] >= r["total"]:
+                engine.close(r["slot"])
+        while live:
+            logits = engine.step([Entry(r["slot"], [r["tokens"][r["at"]]], [0]) for r in live])
+            for row, r in enumerate(live):
+                r["got"][r["at"]] = logits[row]
+                r["at"] += 1
+            for r in live:
+                if r["at"] >= r["total"]:
+                    engine.close(r["slot"])
+            live = [r for r in live if r["at"] < r["total"]]
+        engine.check_status()
+        for index, r in enumerate(requests):
+            want = oracle_logits(folder, r["tokens"])
+            places = sorted(r["got"])
+            assert places == list(range(r["prompt"] - 1, r["total"]))
+            got = torch.stack([r["got"][p] for p in places])
+            assert_close(got, want[places], dtype, f"{name} batch {batch_index} request {index}")
+        assert engine.cache.free_blocks == engine.cache.num_blocks
+        assert engine.cache.slots.free_count == engine.cache.max_slots
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(model_folders, dtype):
+    """Several hundred decode steps after a short prompt: every block boundary and the
+    split of the keys over several slices are crossed."""
+    from thintensor_b200.engine.engine import Entry
+
+    name = "b"
+    folder = folder_for(model_folders, name, dtype)
+    runtime = load(folder, dtype)
+    engine = runtime.new_engine(max_tokens=1024, max_sequences=2)
+    tokens = token_ids(TINY[name]["vocab_size"], 450, 500)
+    want = oracle_logits(folder, tokens)
+    slot = engine.open()
+    got = [engine.step([Entry(slot, tokens[:3], [2])])]
+    for t in range(3, len(tokens)):
+        got.append(engine.step([Entry(slot, [tokens[t]], [0])]))
+    engine.close(slot)
+    engine.check_status()
+    assert_close(torch.cat(got), want[2:], dtype, "long decoding")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_step_cut_into_pieces(model_folders, dtype):
+    """A step with more tokens than max_step_tokens runs in pieces with the same result."""
+    from thintensor_b200.engine.engine import Entry
+
+    name = "a"
+    folder = folder_for(model_folders, name, dtype)
+    runtime = load(folder, dtype)
+    engine = runtime.new_engine(max_tokens=512, max_sequences=3, max_step_tokens=48)
+    vocab = TINY[name]["vocab_size"]
+    prompts = [token_ids(vocab, n, 600 + n) for n in (50, 7, 100)]
+    slots = [engine.open() for _ in prompts]
+    logits = engine.step([Entry(s, p, [0, len(p) - 1]) for s, p in zip(slots, prompts)])
+    for s in slots:
+        engine.close(s)
+    for i, p in enumerate(prompts):
+        want = oracle_logits(folder, p)
+        assert_close(logits[2 * i: 2 * i + 2], want[[0, len(p) - 1]], dtype, f"pieces request {i}")

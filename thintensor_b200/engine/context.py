@@ -1,0 +1,63 @@
+"""What a part sees of a step: the packed tokens, where each sequence's tokens start,
+how long each sequence was before the step, the block tables, and scratch memory.
+
+A step runs ``n_tokens`` packed tokens of ``sequences`` sequences.  Token ``t`` belongs
+to the sequence ``b`` with ``cu[b] <= t < cu[b + 1]`` and stands at position
+``len_before[b] + t - cu[b]``.  All of these live on the device, so a decode step
+captured in a CUDA graph can be replayed while a kernel advances the lengths.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+
+class Workspace:
+    """Named scratch buffers that persist between steps.  A buffer grows when a step
+    asks for more than it holds and otherwise keeps its address, so steps of a shape
+    that has run before allocate nothing (a requirement for graph replay)."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self._buffers: dict[str, torch.Tensor] = {}
+        self.generation = 0  # bumped whenever a buffer moves
+
+    def get(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        count = 1
+        for s in shape:
+            count *= int(s)
+        nbytes = count * torch.empty((), dtype=dtype).element_size()
+        buffer = self._buffers.get(name)
+        if buffer is None or buffer.numel() < nbytes:
+            grow = max(nbytes, 256)
+            buffer = torch.empty(grow, dtype=torch.uint8, device=self.device)
+            self._buffers[name] = buffer
+            self.generation += 1
+        return buffer[:nbytes].view(dtype).view(*shape)
+
+    def bytes(self) -> int:
+        return sum(b.numel() for b in self._buffers.values())
+
+
+@dataclass
+class StepContext:
+    n_tokens: int                       # packed tokens in this step
+    sequences: int                      # sequences in this step
+    decode: bool                        # every sequence brings exactly one token
+    max_new: int                        # most tokens any sequence brings
+    max_total: int                      # upper bound of any sequence's length after the step
+    tokens: torch.Tensor                # int32 [n_tokens]
+    cu: torch.Tensor                    # int32 [sequences + 1]
+    len_before: torch.Tensor            # int32 [sequences]
+    slots: torch.Tensor                 # int32 [sequences], for per-sequence state
+    tables: list[torch.Tensor]          # per KV group: int32 [sequences, width]
+    act_dtype: torch.dtype              # dtype of activations and of the cache
+    workspace: Workspace
+    status: torch.Tensor                # uint32-as-int32 [1] device status word
+    host_slots: list[int] = field(default_factory=list)
+    host_new: list[int] = field(default_factory=list)       # tokens each sequence brings
+    host_before: list[int] = field(default_factory=list)    # lengths before the step (unknown inside a replayed graph)
+
+    def scratch(self, name: str, shape: tuple[int, ...], dtype: torch.dtype | None = None) -> torch.Tensor:
+        return self.workspace.get(name, shape, dtype or self.act_dtype)

@@ -1,0 +1,122 @@
+"""A model built from a :class:`~thintensor_b200.parts.spec.ModelSpec`.
+
+The class knows nothing of any architecture: it builds the parts the spec names from
+the part registries, collects the tensors they declare under their checkpoint names,
+hands each part its tensors, tells the cache what every run of the schedule needs, and
+runs the schedule.  The reference's counterpart is the layer loop of
+ThinGpuCausalLMRuntime (thinruntime/gpu_runtime.py:10114-10392) driven by its
+execution plan.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..cache.cache import SequenceCache
+from ..parts import ARRANGEMENTS, EMBEDDINGS, HEADS, NORMS, REGISTRIES
+from ..parts.base import Delta, Part, WeightDecl
+from ..parts.spec import ModelSpec, PartSpec
+from .context import StepContext
+
+
+@dataclass
+class BuiltPart:
+    part: Part
+    prefix: str
+
+
+def _build(role_registry, spec: PartSpec) -> BuiltPart:
+    return BuiltPart(role_registry.build(spec.kind, dict(spec.params)), spec.prefix)
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec, dtype: torch.dtype, device: torch.device | str | None):
+        spec.validate()
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"the engine runs in float32 or bfloat16, not {dtype}")
+        self.spec = spec
+        self.dtype = dtype
+        self.device = torch.device(device) if device is not None else None
+        self.embedding = _build(EMBEDDINGS, spec.embedding)
+        self.final_norm = _build(NORMS, spec.final_norm)
+        self.head = _build(HEADS, spec.head)
+        self.layers = []
+        self._layer_parts: list[dict[str, BuiltPart]] = []
+        for layer in spec.layers:
+            arrangement_cls = ARRANGEMENTS._classes.get(layer.arrangement)
+            if arrangement_cls is None:
+                raise KeyError(f"no arrangement of kind {layer.arrangement!r}; registered: {', '.join(ARRANGEMENTS.kinds())}")
+            built: dict[str, BuiltPart] = {}
+            for role, registry_name in arrangement_cls.roles.items():
+                if role not in layer.parts:
+                    raise ValueError(f"arrangement {layer.arrangement!r} needs a part for role {role!r}")
+                built[role] = _build(REGISTRIES[registry_name], layer.parts[role])
+            self._layer_parts.append(built)
+            self.layers.append(arrangement_cls({role: b.part for role, b in built.items()}))
+        self.bound = False
+
+    # ------------------------------------------------------------------ weights
+    def _all_parts(self) -> list[BuiltPart]:
+        parts = [self.embedding]
+        for built in self._layer_parts:
+            parts.extend(built.values())
+        parts.extend([self.final_norm, self.head])
+        return parts
+
+    def weight_declarations(self) -> dict[str, WeightDecl]:
+        """Checkpoint name -> declaration, in the order the tensors are stored."""
+        out: dict[str, WeightDecl] = {}
+        for built in self._all_parts():
+            for local, decl in built.part.weights().items():
+                name = built.prefix + local
+                if name in out and out[name] != decl:
+                    raise ValueError(f"tensor {name!r} is declared twice with different shapes")
+                out[name] = decl
+        return out
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        """Give every part its tensors; ``tensors`` maps checkpoint names to device
+        tensors (an aliased tensor appears under the name of its source)."""
+        for built in self._all_parts():
+            mine: dict[str, torch.Tensor] = {}
+            for local, decl in built.part.weights().items():
+                name = built.prefix + local
+                if decl.alias_of is not None:
+                    name = decl.alias_of
+                if name in tensors:
+                    mine[local] = tensors[name]
+                elif not decl.optional:
+                    raise KeyError(f"tensor {name!r} was not loaded")
+            built.part.bind(mine, self.dtype, self.device)
+        self.bound = True
+
+    # -------------------------------------------------------------------- cache
+    def cache_needs(self):
+        kv, state, source = [], [], []
+        for run in self.spec.schedule:
+            mixer = self.layers[run.layer].mixer()
+            kv.append(mixer.cache_need() if mixer is not None else None)
+            state.append(mixer.state_need() if mixer is not None else None)
+            source.append(run.cache_from)
+        return kv, state, source
+
+    def new_cache(self, num_blocks: int, max_slots: int, device: torch.device | str | None = "default") -> SequenceCache:
+        kv, state, source = self.cache_needs()
+        where = self.device if device == "default" else device
+        return SequenceCache(kv, state, source, num_blocks, max_slots, self.dtype, where)
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, ctx: StepContext, cache: SequenceCache, rows: torch.Tensor) -> torch.Tensor:
+        """Run the packed tokens of ``ctx`` through the schedule and return float32
+        logits ``[len(rows), vocab]`` at the packed token indices ``rows``."""
+        if not self.bound:
+            raise RuntimeError("the model has no weights yet")
+        residual = ctx.scratch("model.residual", (ctx.n_tokens, self.spec.hidden_size), torch.float32)
+        self.embedding.part.forward(ctx, ctx.tokens, residual)
+        pending: Delta | None = None
+        for index, run in enumerate(self.spec.schedule):
+            pending = self.layers[run.layer].run(ctx, residual, pending, cache.run_cache(index), cache.run_state(index))
+        wanted = ctx.scratch("model.final", (rows.numel(), self.spec.hidden_size))
+        self.final_norm.part.forward(ctx, residual, pending, wanted, rows)
+        return self.head.part.forward(ctx, wanted)

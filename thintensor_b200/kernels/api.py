@@ -1,0 +1,210 @@
+"""Python signatures of the CUDA kernels.
+
+Each function checks what the kernel cannot check itself (device, dtype, contiguity,
+sizes it refuses), passes raw pointers and the current CUDA stream through ctypes, and
+raises on a launch error.  Nothing here computes anything and nothing falls back to
+another implementation: tensors that are not on a CUDA device are an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+BLOCK_TOKENS = 64          # tokens of one cache block (TT_BLOCK_TOKENS in csrc/common.cuh)
+MAX_HEAD_DIM = 256
+
+STATUS_BAD_TOKEN = 1
+STATUS_BAD_BLOCK = 2
+STATUS_WAIT_EXPIRED = 4
+STATUS_BAD_SHAPE = 8
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16, not {dtype}")
+
+
+def _ptr(t: torch.Tensor | None) -> c_void_p:
+    if t is None:
+        return c_void_p(0)
+    if not t.is_cuda:
+        raise KernelError("thintensor_b200 kernels run on CUDA tensors only; got a tensor on " + str(t.device))
+    return c_void_p(t.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+def _need(t: torch.Tensor, dtype: torch.dtype, name: str) -> None:
+    if t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+_prototyped: set[tuple[str, str]] = set()
+
+
+def _fn(lib: str, name: str, argtypes: list):
+    handle = build.load(lib)
+    fn = getattr(handle, name)
+    if (lib, name) not in _prototyped:
+        fn.argtypes = argtypes
+        fn.restype = c_int
+        _prototyped.add((lib, name))
+    return fn
+
+
+# ------------------------------------------------------------------------- elementwise
+def embed_gather(table: torch.Tensor, tokens: torch.Tensor, residual: torch.Tensor, scale: float, status: torch.Tensor) -> None:
+    """residual[t] = table[tokens[t]] * scale, float32 out."""
+    _need(tokens, torch.int32, "tokens")
+    _need(residual, torch.float32, "residual")
+    if not table.is_contiguous():
+        raise KernelError("embedding table must be contiguous")
+    n, hidden = tokens.numel(), table.shape[1]
+    fn = _fn("elementwise", "tt_embed_gather", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
+    _check(fn(_ptr(table), dtype_code(table.dtype), _ptr(tokens), _ptr(residual), n, hidden, table.shape[0], scale, _ptr(status), _stream()), "embed_gather")
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                rows: torch.Tensor | None = None, weight_offset: float = 0.0) -> None:
+    """residual += sum(delta over its first axis); out = rmsnorm(residual) * weight.
+    With ``rows`` (int32), out[i] comes from residual row rows[i] and residual is left
+    as it was."""
+    _need(residual, torch.float32, "residual")
+    _need(weight, torch.float32, "norm weight")
+    if not out.is_contiguous():
+        raise KernelError("norm output must be contiguous")
+    hidden = residual.shape[-1]
+    splits, stride = 0, 0
+    if delta is not None:
+        _need(delta, torch.float32, "delta")
+        splits = delta.shape[0]
+        stride = delta.stride(0)
+    n_rows = rows.numel() if rows is not None else residual.shape[0]
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+    fn = _fn("elementwise", "tt_add_rmsnorm", [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_float, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(_ptr(residual), _ptr(delta), splits, stride, _ptr(weight), weight_offset, eps, _ptr(out), dtype_code(out.dtype), _ptr(rows), n_rows, hidden, _stream()), "add_rmsnorm")
+
+
+def rope_append(qkv: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, attention_scaling: float, q_out: torch.Tensor,
+                k_pool: torch.Tensor | None, v_pool: torch.Tensor | None, table: torch.Tensor | None, cu: torch.Tensor,
+                len_before: torch.Tensor, sequences: int, n_tokens: int, heads: int, kv_heads: int, head_dim: int,
+                status: torch.Tensor) -> None:
+    """Rotate q and k of float32 partial sums ``qkv`` [splits, tokens, cols], write q in
+    the activation dtype and append k and v to the block pools.  Without pools the
+    projection holds queries only."""
+    _need(qkv, torch.float32, "qkv")
+    _need(inv_freq, torch.float32, "inv_freq")
+    write = k_pool is not None
+    cols = heads * head_dim + (2 * kv_heads * head_dim if write else 0)
+    if qkv.shape[-1] != cols:
+        raise KernelError(f"qkv has {qkv.shape[-1]} columns, expected {cols}")
+    if write and (k_pool.dtype != q_out.dtype or v_pool.dtype != q_out.dtype):
+        raise KernelError("cache pools and activations must share a dtype")
+    fn = _fn("elementwise", "tt_rope_append", [c_void_p, c_int, c_longlong, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int,
+                                               c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(qkv), qkv.shape[0], qkv.stride(0), _ptr(inv_freq), rotary_dim, attention_scaling, _ptr(q_out), _ptr(k_pool), _ptr(v_pool),
+              dtype_code(q_out.dtype), _ptr(table), table.shape[1] if table is not None else 0,
+              k_pool.shape[0] if write else 0, _ptr(cu), _ptr(len_before), sequences, n_tokens, heads, kv_heads, head_dim,
+              1 if write else 0, _ptr(status), _stream()), "rope_append")
+
+
+def swiglu(gate_up: torch.Tensor, act: torch.Tensor) -> None:
+    """act = silu(gate) * up from float32 partial sums [splits, tokens, 2 * inter]."""
+    _need(gate_up, torch.float32, "gate_up")
+    inter = gate_up.shape[-1] // 2
+    fn = _fn("elementwise", "tt_swiglu", [c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(gate_up), gate_up.shape[0], gate_up.stride(0), _ptr(act), dtype_code(act.dtype), gate_up.shape[1], inter, _stream()), "swiglu")
+
+
+def advance_lengths(lengths: torch.Tensor, cu: torch.Tensor, sequences: int) -> None:
+    fn = _fn("elementwise", "tt_advance_lengths", [c_void_p, c_void_p, c_int, c_void_p])
+    _check(fn(_ptr(lengths), _ptr(cu), sequences, _stream()), "advance_lengths")
+
+
+# --------------------------------------------------------------------------- attention
+def check_head_dim(head_dim: int) -> None:
+    if head_dim <= 0 or head_dim % 16 or head_dim > MAX_HEAD_DIM:
+        raise KernelError(f"attention kernels take head sizes that are multiples of 16 up to {MAX_HEAD_DIM}, not {head_dim}")
+
+
+def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor, cu: torch.Tensor,
+              len_before: torch.Tensor, sequences: int, n_tokens: int, heads: int, kv_heads: int, head_dim: int,
+              scale: float, window: int, splits: int, out: torch.Tensor, part_acc: torch.Tensor | None,
+              part_ml: torch.Tensor | None, status: torch.Tensor) -> None:
+    """Exact causal attention of ``n_tokens`` packed query tokens over the block cache."""
+    check_head_dim(head_dim)
+    if heads % kv_heads:
+        raise KernelError(f"{heads} query heads are not a multiple of {kv_heads} key/value heads")
+    if not (q.dtype == k_pool.dtype == v_pool.dtype == out.dtype):
+        raise KernelError("queries, cache and output must share a dtype")
+    fn = _fn("attention", "tt_attention", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
+                                           c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(q), _ptr(k_pool), _ptr(v_pool), dtype_code(q.dtype), _ptr(table), table.shape[1], k_pool.shape[0], _ptr(cu),
+              _ptr(len_before), sequences, n_tokens, heads, kv_heads, head_dim, scale, window, splits, _ptr(out),
+              _ptr(part_acc), _ptr(part_ml), _ptr(status), _stream()), "attention")
+
+
+# -------------------------------------------------------------------------------- gemm
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor) -> None:
+    """out[s] = x @ w[:, k-slice s].T in float32 FMA; ``out`` is float32
+    [splits, m, n]; bias (float32 [n]) goes into slice 0."""
+    _need(out, torch.float32, "gemm output")
+    if x.stride(-1) != 1 or w.stride(-1) != 1:
+        raise KernelError("gemm operands must be contiguous along k")
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k or out.shape[1:] != (m, n):
+        raise KernelError(f"gemm shapes do not fit: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+    fn = _fn("gemm_simt", "tt_gemm_simt", [c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_longlong,
+                                           c_longlong, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(x), dtype_code(x.dtype), x.stride(0), _ptr(w), dtype_code(w.dtype), w.stride(0), _ptr(bias), _ptr(out), out.stride(1),
+              out.stride(0), m, n, k, out.shape[0], _stream()), "gemm_simt")
+
+
+# ---------------------------------------------------------------------------- sampling
+def argmax_rows(logits: torch.Tensor, out: torch.Tensor) -> None:
+    _need(logits, torch.float32, "logits")
+    _need(out, torch.int32, "token output")
+    fn = _fn("sampling", "tt_argmax_rows", [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(out), _stream()), "argmax_rows")
+
+
+def sample_rows(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, seed: int, request: torch.Tensor,
+                step: torch.Tensor, out: torch.Tensor) -> None:
+    _need(logits, torch.float32, "logits")
+    _need(request, torch.int32, "request ids")
+    _need(step, torch.int32, "step ids")
+    _need(out, torch.int32, "token output")
+    fn = _fn("sampling", "tt_sample_rows", [c_void_p, c_longlong, c_int, c_int, c_float, c_int, c_float, c_ulonglong, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], temperature, top_k, top_p, seed & ((1 << 64) - 1),
+              _ptr(request), _ptr(step), _ptr(out), _stream()), "sample_rows")
+
+
+# ----------------------------------------------------------------- tensor-core kernels
+def tcgen05_ready() -> bool:
+    """Whether the tcgen05 matrix product is part of this build."""
+    return "gemm_tcgen05" in build.SOURCES

@@ -1,0 +1,99 @@
+"""Causal grouped-query attention over the block cache.
+
+For each token: q, k, v projections of the normed hidden state (one fused matrix),
+position encoding on q and k, k and v appended to the sequence's cache, softmax
+attention of q over every cached key of its sequence (or the last ``window`` of them)
+with query head h reading key/value head ``h // (heads / kv_heads)`` and scores scaled
+by ``head_dim ** -0.5``, then the output projection
+(thinruntime/gpu_runtime.py:10151-10249 and 8913-8961).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import api
+from .base import MIXERS, POSITION_ENCODINGS, Delta, KVNeed, Mixer, WeightDecl
+from .linear import Linear
+from .spec import PartSpec
+
+
+def kv_splits(ctx, heads: int, sm_count: int = 148) -> int:
+    """Into how many slices the keys of a decode step are cut so that the grid fills the
+    GPU.  Depends only on the step's shape, not on the lengths on the device."""
+    rows = ctx.n_tokens * heads
+    if not ctx.decode or rows >= 4 * sm_count:
+        return 1
+    want = -(-4 * sm_count * 4 // max(rows, 1))           # 4 warps per block, ~4 blocks per SM
+    most = max(1, ctx.max_total // 256)                    # at least 256 keys per slice
+    return max(1, min(want, most, 64))
+
+
+@MIXERS.register("attention")
+class CausalAttention(Mixer):
+    def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, position: PartSpec | None = None,
+                 bias: bool = False, window: int | None = None, scale: float | None = None):
+        self.hidden, self.heads, self.kv_heads, self.head_dim = int(hidden), int(heads), int(kv_heads), int(head_dim)
+        if self.heads % self.kv_heads:
+            raise ValueError(f"{heads} query heads are not a multiple of {kv_heads} key/value heads")
+        api.check_head_dim(self.head_dim)
+        self.bias = bool(bias)
+        self.window = None if not window else int(window)
+        self.scale = float(scale) if scale is not None else self.head_dim ** -0.5
+        position = position or PartSpec("none", {"head_dim": self.head_dim})
+        self.position = POSITION_ENCODINGS.build(position.kind, dict(position.params))
+        self.qkv: Linear | None = None
+        self.q_only: Linear | None = None
+        self.out: Linear | None = None
+
+    # -------------------------------------------------------------- declarations
+    def weights(self) -> dict[str, WeightDecl]:
+        q, kv = self.heads * self.head_dim, self.kv_heads * self.head_dim
+        out = {
+            "q_proj.weight": WeightDecl((q, self.hidden)),
+            "k_proj.weight": WeightDecl((kv, self.hidden)),
+            "v_proj.weight": WeightDecl((kv, self.hidden)),
+            "o_proj.weight": WeightDecl((self.hidden, q)),
+        }
+        if self.bias:
+            out.update({
+                "q_proj.bias": WeightDecl((q,)), "k_proj.bias": WeightDecl((kv,)), "v_proj.bias": WeightDecl((kv,)),
+                "o_proj.bias": WeightDecl((self.hidden,)),
+            })
+        return out
+
+    def cache_need(self) -> KVNeed:
+        return KVNeed(self.kv_heads, self.head_dim, self.window)
+
+    def bind(self, tensors, dtype, device) -> None:
+        self.position.bind({}, dtype, device)
+        weight = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]], dim=0)
+        bias = None
+        if self.bias:
+            bias = torch.cat([tensors["q_proj.bias"].float(), tensors["k_proj.bias"].float(), tensors["v_proj.bias"].float()])
+        self.qkv = Linear(weight, bias)
+        self.q_only = self.qkv.rows(0, self.heads * self.head_dim)
+        self.out = Linear(tensors["o_proj.weight"], tensors["o_proj.bias"] if self.bias else None)
+
+    # ------------------------------------------------------------------- running
+    def forward(self, ctx, x, cache, state) -> Delta:
+        if cache is None or cache.k_pool is None:
+            raise RuntimeError("attention needs a cache with storage")
+        table = ctx.tables[cache.group]
+        q_cols = self.heads * self.head_dim
+        projection = (self.qkv if cache.writes else self.q_only)(ctx, x, "attention.qkv")
+        q = ctx.scratch("attention.q", (ctx.n_tokens, q_cols))
+        api.rope_append(projection, self.position.inv_freq, self.position.rotary_dim, self.position.attention_scaling, q,
+                        cache.k_pool if cache.writes else None, cache.v_pool if cache.writes else None, table, ctx.cu,
+                        ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads, self.kv_heads, self.head_dim, ctx.status)
+        mixed = ctx.scratch("attention.mixed", (ctx.n_tokens, q_cols))
+        self.attend(ctx, q, cache, table, mixed)
+        return Delta(self.out(ctx, mixed, "attention.out"))
+
+    def attend(self, ctx, q, cache, table, mixed) -> None:
+        splits = kv_splits(ctx, self.heads)
+        part_acc = part_ml = None
+        if splits > 1:
+            part_acc = ctx.scratch("attention.part_acc", (ctx.n_tokens * self.heads * splits * self.head_dim,), torch.float32)
+            part_ml = ctx.scratch("attention.part_ml", (ctx.n_tokens * self.heads * splits * 2,), torch.float32)
+        api.attention(q, cache.k_pool, cache.v_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads,
+                      self.kv_heads, self.head_dim, self.scale, self.window or 0, splits, mixed, part_acc, part_ml, ctx.status)

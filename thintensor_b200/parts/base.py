@@ -1,0 +1,185 @@
+"""Interfaces of the parts a layer is made of, and one registry for each role.
+
+A part is built from the parameters of its :class:`~thintensor_b200.parts.spec.PartSpec`
+alone.  It declares the tensors it needs under names of its own, is handed those
+tensors once, and is then run with a :class:`~thintensor_b200.engine.context.StepContext`.
+No part knows which model it is in, which layer it is, or what the checkpoint calls
+its tensors.
+
+Roles and what each must provide:
+
+* ``Norm``: ``forward(ctx, residual, delta, out, rows=None)`` adds ``delta`` (the not
+  yet added output of the part before it, possibly several partial sums) into the
+  float32 residual stream and writes the normalised rows to ``out``.
+* ``PositionEncoding``: an object a mixer is given at construction; for rotary
+  encodings a float32 table of inverse frequencies that the mixer's kernels use.
+* ``Mixer``: ``forward(ctx, x, cache, state) -> Delta``; declares with
+  ``cache_need()`` / ``state_need()`` what the cache must hold for it.
+* ``FeedForward``: ``forward(ctx, x) -> Delta``.
+* ``Embedding``: ``forward(ctx, tokens, residual)``; ``Head``: ``forward(ctx, x) -> logits``.
+* ``Arrangement``: wires norms, mixer and feed-forward around the residual stream.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable
+
+import torch
+
+
+@dataclass(frozen=True)
+class WeightDecl:
+    """A tensor a part needs.  ``init`` tells the random-weights mode how to draw it:
+    ``normal`` is N(0, 0.02), ``norm`` is 1 + N(0, 0.1), ``zeros`` is zero.
+    ``alias_of`` names a checkpoint tensor (full name) to use instead when this one is
+    absent from the checkpoint; with ``prefer_alias`` it is used even when this one is
+    stored (a tied output head, whose stored copy is ignored)."""
+
+    shape: tuple[int, ...]
+    init: str = "normal"
+    optional: bool = False
+    alias_of: str | None = None
+    prefer_alias: bool = False
+    integer: bool = False
+
+
+@dataclass(frozen=True)
+class KVNeed:
+    """Keys and values a mixer wants kept for each sequence: ``kv_heads`` heads of
+    ``head_dim`` numbers per token; ``window`` = only the last so many tokens."""
+
+    kv_heads: int
+    head_dim: int
+    window: int | None = None
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """Per-sequence state of fixed size: one tensor of ``shape`` and ``dtype`` for each
+    sequence, zero when the sequence starts."""
+
+    shape: tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class Delta:
+    """What a mixer or feed-forward adds to the residual stream: float32
+    ``[splits, tokens, hidden]``; the sum over ``splits`` is the value.  The norm that
+    follows does the sum and the addition."""
+
+    tensor: torch.Tensor
+
+    @property
+    def splits(self) -> int:
+        return self.tensor.shape[0]
+
+
+class Part:
+    """Common behaviour: declared weights and binding."""
+
+    def weights(self) -> dict[str, WeightDecl]:
+        return {}
+
+    def bind(self, tensors: dict[str, torch.Tensor], dtype: torch.dtype, device: torch.device) -> None:
+        """Receive the declared tensors (already on ``device``, in their stored dtype
+        unless the engine runs in float32, ``dtype`` being the activation dtype) and
+        prepare what kernels need."""
+
+
+class Norm(Part):
+    def forward(self, ctx, residual: torch.Tensor, delta: Delta | None, out: torch.Tensor, rows: torch.Tensor | None = None) -> None:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    pass
+
+
+class Mixer(Part):
+    def cache_need(self) -> KVNeed | None:
+        return None
+
+    def state_need(self) -> StateNeed | None:
+        return None
+
+    def forward(self, ctx, x: torch.Tensor, cache, state) -> Delta:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, ctx, x: torch.Tensor) -> Delta:
+        raise NotImplementedError
+
+
+class Embedding(Part):
+    def forward(self, ctx, tokens: torch.Tensor, residual: torch.Tensor) -> None:
+        raise NotImplementedError
+
+
+class Head(Part):
+    def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Arrangement:
+    """How one layer's parts are wired.  ``roles`` lists the part roles it needs and
+    the registry each comes from; ``run`` returns the delta still to be added."""
+
+    roles: dict[str, str] = {}
+
+    def __init__(self, parts: dict[str, Part]):
+        self.parts = parts
+
+    def mixer(self) -> Mixer | None:
+        return None
+
+    def run(self, ctx, residual: torch.Tensor, pending: Delta | None, cache, state) -> Delta | None:
+        raise NotImplementedError
+
+
+class Registry:
+    """kind -> class, for one role."""
+
+    def __init__(self, role: str):
+        self.role = role
+        self._classes: dict[str, Callable[..., Any]] = {}
+
+    def register(self, kind: str):
+        def decorate(cls):
+            if kind in self._classes:
+                raise ValueError(f"{self.role} {kind!r} is already registered")
+            self._classes[kind] = cls
+            return cls
+
+        return decorate
+
+    def unregister(self, kind: str) -> None:
+        self._classes.pop(kind, None)
+
+    def build(self, kind: str, params: dict[str, Any]):
+        if kind not in self._classes:
+            raise KeyError(f"no {self.role} of kind {kind!r}; registered: {', '.join(sorted(self._classes))}")
+        return self._classes[kind](**params)
+
+    def kinds(self) -> list[str]:
+        return sorted(self._classes)
+
+
+NORMS = Registry("norm")
+POSITION_ENCODINGS = Registry("position encoding")
+MIXERS = Registry("mixer")
+FEED_FORWARDS = Registry("feed-forward")
+EMBEDDINGS = Registry("embedding")
+HEADS = Registry("head")
+ARRANGEMENTS = Registry("arrangement")
+
+REGISTRIES = {
+    "norm": NORMS,
+    "position": POSITION_ENCODINGS,
+    "mixer": MIXERS,
+    "ffn": FEED_FORWARDS,
+    "embedding": EMBEDDINGS,
+    "head": HEADS,
+    "arrangement": ARRANGEMENTS,
+}

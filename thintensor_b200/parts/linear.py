@@ -1,0 +1,66 @@
+"""A weight matrix ``[out_features, in_features]`` and the product ``x @ W.T``.
+
+The result is always float32 partial sums ``[splits, tokens, out_features]`` whose sum
+over ``splits`` is the product: the kernel that consumes it (the norm that adds it to
+the residual stream, the rotary/append kernel, SwiGLU) does that sum, so a projection
+whose few output tiles could not fill the GPU may cut its ``in_features`` into slices
+without a reduction kernel of its own.
+
+Which kernel runs is decided by the operands' dtypes alone: bfloat16 activations with
+a bfloat16 weight use the tcgen05 tensor-core kernel; everything else (the true 32-bit
+path, or a weight that the checkpoint stores in float32) uses the exact FMA kernel.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import api
+
+
+class Linear:
+    def __init__(self, weight: torch.Tensor, bias: torch.Tensor | None = None):
+        if weight.dim() != 2:
+            raise ValueError(f"a projection weight must be a matrix, got shape {tuple(weight.shape)}")
+        self.weight = weight.contiguous()
+        self.bias = None if bias is None else bias.to(torch.float32).contiguous()
+        self.out_features, self.in_features = self.weight.shape
+
+    def rows(self, begin: int, end: int) -> "Linear":
+        """The projection onto output features begin..end-1 (shares storage)."""
+        return Linear(self.weight[begin:end], None if self.bias is None else self.bias[begin:end])
+
+    def __call__(self, ctx, x: torch.Tensor, name: str) -> torch.Tensor:
+        tokens = x.shape[0]
+        if x.shape[1] != self.in_features:
+            raise ValueError(f"{name}: input has {x.shape[1]} features, the weight takes {self.in_features}")
+        if x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16 and api.tcgen05_ready():
+            splits = api.gemm_tcgen05_splits(tokens, self.out_features, self.in_features)
+            out = ctx.scratch(name, (splits, tokens, self.out_features), torch.float32)
+            api.gemm_tcgen05(x, self.weight, self.bias, out, ctx.status)
+            return out
+        out = ctx.scratch(name, (1, tokens, self.out_features), torch.float32)
+        api.gemm_simt(x, self.weight, self.bias, out)
+        return out
+
+
+class GatedLinear:
+    """gate and up projections as one ``[2 * inter, in]`` matrix (gate rows first) and
+    ``silu(gate) * up`` in the activation dtype."""
+
+    def __init__(self, gate: torch.Tensor, up: torch.Tensor, gate_bias: torch.Tensor | None, up_bias: torch.Tensor | None):
+        self.inter = gate.shape[0]
+        bias = None
+        if gate_bias is not None or up_bias is not None:
+            zeros = torch.zeros(self.inter, dtype=torch.float32, device=gate.device)
+            bias = torch.cat([(gate_bias if gate_bias is not None else zeros).float(), (up_bias if up_bias is not None else zeros).float()])
+        self.fused = Linear(torch.cat([gate, up], dim=0), bias)
+
+    def __call__(self, ctx, x: torch.Tensor, name: str) -> torch.Tensor:
+        tokens = x.shape[0]
+        act = ctx.scratch(name + ".act", (tokens, self.inter))
+        w = self.fused
+        if x.dtype == torch.bfloat16 and w.weight.dtype == torch.bfloat16 and w.bias is None and api.tcgen05_ready():
+            api.gemm_tcgen05_swiglu(x, w.weight, act, ctx.status)
+            return act
+        api.swiglu(w(ctx, x, name), act)
+        return act
