@@ -1,0 +1,105 @@
+"""Generation through the Python entry point against the plain implementation:
+greedy tokens, stop tokens, sequences that end earlier, several batches one after
+another, sampling with temperature / top-k / top-p, and that graph replay changes nothing."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+import plain_llama
+from conftest import TINY, token_ids
+
+pytestmark = pytest.mark.gpu
+
+
+def oracle_generate(folder, prompts, max_new, stop_ids=(), **sampling):
+    cfg, weights = plain_llama.read_model(folder)
+    return [plain_llama.generate(cfg, weights, p, max_new, stop_ids=stop_ids, request=i, **sampling) for i, p in enumerate(prompts)]
+
+
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_greedy_matches_plain(model_folders, name):
+    import thintensor_b200
+
+    folder = model_folders(name, "float32")
+    runtime = thintensor_b200.load_model(folder, dtype="fp32")
+    vocab = TINY[name]["vocab_size"]
+    lengths = [5, 9, 2] if name == "a" else [17, 1, 40, 70]
+    prompts = [token_ids(vocab, n, 700 + n) for n in lengths]
+    steps = 8 if name == "a" else 12
+    got = runtime.generate(prompts, max_new_tokens=steps, stop_ids=(), batch_size=4)
+    assert got == oracle_generate(folder, prompts, steps)
+    # the same without graph replay, and in smaller batches so that slots are reused
+    assert runtime.generate(prompts, max_new_tokens=steps, stop_ids=(), batch_size=2, use_graph=False) == got
+    # the per-step path (host reads every token) gives the same tokens as the run without host reads
+    assert runtime.generate(prompts, max_new_tokens=steps, stop_ids=(-1,), batch_size=3) == got
+
+
+def test_stop_tokens_end_sequences_early(model_folders):
+    import thintensor_b200
+    from thintensor_b200.engine.generate import GenerationStats
+
+    name = "b"
+    folder = model_folders(name, "float32")
+    runtime = thintensor_b200.load_model(folder, dtype="fp32")
+    vocab = TINY[name]["vocab_size"]
+    prompts = [token_ids(vocab, n, 800 + n) for n in (6, 30, 3, 11, 19)]
+    free_run = oracle_generate(folder, prompts, 24)
+    # stop ids taken from what the model actually produces, so that sequences end at different steps
+    stop = {free_run[0][3], free_run[1][10], free_run[3][1]}
+    want = oracle_generate(folder, prompts, 24, stop_ids=stop)
+    assert len({len(w) for w in want}) > 1, "the stop ids should end sequences at different lengths"
+    stats = GenerationStats()
+    got = runtime.generate(prompts, max_new_tokens=24, stop_ids=tuple(stop), batch_size=3, stats=stats)
+    assert got == want
+    assert stats.batches == 2 and stats.batch_sizes == [3, 2]
+    engine = runtime._engine
+    assert engine.cache.free_blocks == engine.cache.num_blocks
+    assert engine.cache.slots.free_count == engine.cache.max_slots
+
+
+@pytest.mark.parametrize("sampling", [
+    {"temperature": 0.8, "seed": 4},
+    {"temperature": 1.3, "top_k": 5, "seed": 9},
+    {"temperature": 0.7, "top_p": 0.6, "seed": 1},
+    {"temperature": 1.0, "top_k": 20, "top_p": 0.9, "seed": 123456789012},
+])
+def test_sampling_matches_plain(model_folders, sampling):
+    """Tiny B with temperature sampling: the same counter-based uniform numbers on both
+    sides give the same tokens, whatever the batch a request runs in."""
+    import thintensor_b200
+
+    name = "b"
+    folder = model_folders(name, "float32")
+    runtime = thintensor_b200.load_model(folder, dtype="fp32")
+    vocab = TINY[name]["vocab_size"]
+    prompts = [token_ids(vocab, n, 900 + n) for n in (17, 1, 40, 70)]
+    want = oracle_generate(folder, prompts, 12, **sampling)
+    got = runtime.generate(prompts, max_new_tokens=12, stop_ids=(), batch_size=4, **sampling)
+    assert got == want
+    assert runtime.generate(prompts, max_new_tokens=12, stop_ids=(), batch_size=1, **sampling) == got
+
+
+def test_bfloat16_greedy_follows_float32(model_folders):
+    """bfloat16 generation is the same model: teacher-forced on the float32 tokens its
+    argmax agrees wherever the float32 margin is clear."""
+    import thintensor_b200
+    from thintensor_b200.engine.engine import Entry
+
+    name = "a"
+    folder = model_folders(name, "bfloat16")
+    exact = thintensor_b200.load_model(folder, dtype="fp32")
+    fast = thintensor_b200.load_model(folder, dtype="bf16")
+    prompt = token_ids(TINY[name]["vocab_size"], 12, 1000)
+    new = exact.generate([prompt], max_new_tokens=20, stop_ids=())[0]
+    tokens = prompt + new
+    outs = []
+    for runtime in (exact, fast):
+        engine = runtime.new_engine(max_tokens=128, max_sequences=1)
+        slot = engine.open()
+        outs.append(engine.step([Entry(slot, tokens, list(range(len(tokens))))]))
+        engine.close(slot)
+    top2 = outs[0].topk(2, dim=-1).values
+    clear = (top2[:, 0] - top2[:, 1]) > 0.25
+    assert int(clear.sum()) > 5
+    assert bool((outs[0].argmax(-1) == outs[1].argmax(-1))[clear].all())

@@ -13,6 +13,7 @@ __version__ = "0.1.0"
 _EXPORTS = {
     "load_model": ("thintensor_b200.runtime", "load_model"),
     "save_random_model": ("thintensor_b200.runtime", "save_random_model"),
+    "random_model": ("thintensor_b200.runtime", "random_model"),
     "Runtime": ("thintensor_b200.runtime", "Runtime"),
     "Engine": ("thintensor_b200.engine.engine", "Engine"),
     "Entry": ("thintensor_b200.engine.engine", "Entry"),

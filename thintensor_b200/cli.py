@@ -1,0 +1,191 @@
+"""Command line: ``python -m thintensor_b200 {run,bench,validate,random} ...``
+
+Option names and meanings follow the reference's ``thintensor`` command
+(thinruntime/cli.py:165-264 for ``run``, :305-403 for ``bench``, :405-431 for
+``validate``): ``--prompt``, ``--context`` (most prompt + new tokens), ``--max-new-tokens``
+/ ``--steps``, ``--temperature``, ``--top-p``, ``--top-k``, ``--seed``, ``--device``,
+``--dtype``, ``--tokenizer``, ``--json``; ``bench`` has ``--steps``, ``--warmup``,
+``--prompt-token-ids``, ``--out``; ``validate`` has ``--require-tier``.  What the
+reference's flags select among engines, profiles, quantisation and residency has no
+counterpart here.  Unlike the reference, which refuses anything but greedy decoding
+(thinruntime/cli.py:1940-1945), sampling options are honoured.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+import time
+from pathlib import Path
+
+
+def build_parser() -> argparse.ArgumentParser:
+    parser = argparse.ArgumentParser(prog="thintensor_b200", description="Llama dense decoder on one B200")
+    sub = parser.add_subparsers(dest="command", required=True)
+
+    run = sub.add_parser("run", help="Generate tokens", formatter_class=argparse.ArgumentDefaultsHelpFormatter)
+    run.add_argument("model", help="model folder (config.json + safetensors)")
+    run.add_argument("--prompt", default="Hello", help="Input prompt (needs a tokenizer in the model folder or --tokenizer)")
+    run.add_argument("--prompt-token-ids", action="append", help="Comma-separated prompt token ids; repeat for a batch")
+    run.add_argument("--prompts-file", help="JSON file holding a list of token-id lists")
+    run.add_argument("--context", type=int, default=512, help="Context length: most prompt + new tokens of a sequence")
+    run.add_argument("--max-new-tokens", "--steps", dest="max_new_tokens", type=int, default=200, help="Maximum generated tokens")
+    run.add_argument("--temperature", type=float, default=0.0, help="Sampling temperature; 0 is greedy")
+    run.add_argument("--top-p", type=float, default=1.0, help="Nucleus mass; 1 switches it off")
+    run.add_argument("--top-k", type=int, default=0, help="Keep the k most likely tokens; 0 switches it off")
+    run.add_argument("--seed", type=int, default=0, help="Random seed")
+    run.add_argument("--device", choices=["cuda"], default="cuda")
+    run.add_argument("--dtype", choices=["bf16", "fp32"], default="bf16")
+    run.add_argument("--tokenizer", help="Tokenizer directory")
+    run.add_argument("--batch-size", type=int, default=8, help="Most sequences decoded together")
+    run.add_argument("--ignore-eos", action="store_true", help="Always generate --max-new-tokens tokens")
+    run.add_argument("--json", action="store_true", help="JSON output")
+
+    bench = sub.add_parser("bench", help="Benchmark prefill and decode", formatter_class=argparse.ArgumentDefaultsHelpFormatter)
+    bench.add_argument("model", help="model folder")
+    bench.add_argument("--steps", type=int, default=200, help="Timed decode steps")
+    bench.add_argument("--warmup", type=int, default=10, help="Warmup decode steps")
+    bench.add_argument("--prompt-token-ids", help="Comma-separated explicit prompt token ids used by every sequence")
+    bench.add_argument("--prompt-len", type=int, default=128, help="Length of the synthetic prompt when no ids are given")
+    bench.add_argument("--batch", type=int, default=1, help="Sequences decoded together")
+    bench.add_argument("--seed", type=int, default=0)
+    bench.add_argument("--device", choices=["cuda"], default="cuda")
+    bench.add_argument("--dtype", choices=["bf16", "fp32"], default="bf16")
+    bench.add_argument("--json", action="store_true")
+    bench.add_argument("--out", help="Write JSON results to this file")
+
+    validate = sub.add_parser("validate", help="Compare the engine's ways of running with its 32-bit path",
+                              formatter_class=argparse.ArgumentDefaultsHelpFormatter)
+    validate.add_argument("model", help="model folder")
+    validate.add_argument("--require-tier", choices=["ranking", "exact"], default="ranking", help="Minimum accepted correctness tier")
+    validate.add_argument("--prompt-token-ids", help="Comma-separated token ids; default is a seeded synthetic sequence")
+    validate.add_argument("--length", type=int, default=96, help="Length of the synthetic sequence")
+    validate.add_argument("--seed", type=int, default=0)
+    validate.add_argument("--device", choices=["cuda"], default="cuda")
+    validate.add_argument("--dtype", choices=["bf16", "fp32"], default="bf16")
+    validate.add_argument("--json", action="store_true")
+
+    random = sub.add_parser("random", help="Write a model folder with random weights",
+                            formatter_class=argparse.ArgumentDefaultsHelpFormatter)
+    random.add_argument("out", help="folder to write config.json and model.safetensors into")
+    random.add_argument("--config", required=True, help="config.json (or a folder holding one) that gives every size")
+    random.add_argument("--seed", type=int, default=0)
+    random.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16", help="stored dtype")
+    return parser
+
+
+def parse_ids(text: str) -> list[int]:
+    try:
+        return [int(part) for part in text.replace(" ", "").split(",") if part]
+    except ValueError as exc:
+        raise SystemExit(f"token ids must be comma-separated integers: {exc}")
+
+
+def load_tokenizer(model: Path, override: str | None):
+    """A tokenizer found next to the model or at ``--tokenizer``; used as a black box,
+    as the reference does (thinruntime/cli.py:4661-4721)."""
+    where = Path(override) if override else model
+    if not any((where / name).is_file() for name in ("tokenizer.json", "tokenizer.model", "tokenizer_config.json")):
+        raise SystemExit(f"no tokenizer files in {where}; pass --prompt-token-ids or --tokenizer DIR")
+    from transformers import AutoTokenizer
+
+    return AutoTokenizer.from_pretrained(str(where))
+
+
+def cmd_run(args) -> int:
+    import thintensor_b200
+
+    if args.max_new_tokens <= 0:
+        raise SystemExit("--max-new-tokens must be positive")
+    if args.context <= 0:
+        raise SystemExit("--context must be positive")
+    tokenizer = None
+    if args.prompts_file:
+        prompts = json.loads(Path(args.prompts_file).read_text())
+    elif args.prompt_token_ids:
+        prompts = [parse_ids(p) for p in args.prompt_token_ids]
+    else:
+        tokenizer = load_tokenizer(Path(args.model), args.tokenizer)
+        prompts = [tokenizer(args.prompt)["input_ids"]]
+    runtime = thintensor_b200.load_model(args.model, dtype=args.dtype, device=args.device)
+    started = time.perf_counter()
+    outputs = runtime.generate(
+        prompts, max_new_tokens=args.max_new_tokens, temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
+        seed=args.seed, stop_ids=() if args.ignore_eos else None, context=args.context, batch_size=args.batch_size,
+    )
+    elapsed = time.perf_counter() - started
+    new_tokens = sum(len(o) for o in outputs)
+    if args.json:
+        print(json.dumps({
+            "prompt_token_ids": prompts, "generated_token_ids": outputs, "new_tokens": new_tokens,
+            "seconds": elapsed, "tokens_per_s": new_tokens / elapsed if elapsed > 0 else None,
+            "dtype": args.dtype, "temperature": args.temperature, "top_p": args.top_p, "top_k": args.top_k, "seed": args.seed,
+        }))
+    else:
+        for prompt, output in zip(prompts, outputs):
+            print(tokenizer.decode(output) if tokenizer is not None else ",".join(str(t) for t in output))
+        print(f"[{new_tokens} tokens in {elapsed:.3f} s]", file=sys.stderr)
+    return 0
+
+
+def cmd_bench(args) -> int:
+    import torch
+
+    import thintensor_b200
+    from thintensor_b200.benchmark import measure_decode, measure_prefill
+
+    runtime = thintensor_b200.load_model(args.model, dtype=args.dtype, device=args.device)
+    vocab = runtime.model.spec.vocab_size
+    if args.prompt_token_ids:
+        prompt = parse_ids(args.prompt_token_ids)
+    else:
+        g = torch.Generator().manual_seed(args.seed)
+        prompt = torch.randint(0, vocab, (args.prompt_len,), generator=g).tolist()
+    context = len(prompt) + args.warmup + args.steps + 1
+    prefill = measure_prefill(runtime, prompt, repeats=3)
+    decode = measure_decode(runtime, [prompt] * args.batch, context, args.warmup, args.steps)
+    result = {
+        "model": str(args.model), "dtype": args.dtype, "batch_size": args.batch, "prompt_tokens": len(prompt),
+        "steps": args.steps, "warmup_steps": args.warmup,
+        "tokens_per_s": decode["tokens_per_s"], "ms_per_token": decode["ms_per_step"],
+        "prefill_tokens_per_s": prefill["tokens_per_s"], "prefill_ms": prefill["ms"],
+    }
+    text = json.dumps(result, indent=None if args.json else 2)
+    if args.out:
+        Path(args.out).write_text(text + "\n")
+    print(text)
+    return 0
+
+
+def cmd_validate(args) -> int:
+    from thintensor_b200.validate import validate_model
+
+    ids = parse_ids(args.prompt_token_ids) if args.prompt_token_ids else None
+    report = validate_model(args.model, dtype=args.dtype, tokens=ids, length=args.length, seed=args.seed)
+    print(json.dumps(report) if args.json else json.dumps(report, indent=2))
+    order = {"fail": 0, "ranking_pass": 1, "exact_pass": 2}
+    needed = {"ranking": 1, "exact": 2}[args.require_tier]
+    return 0 if order[report["tier"]] >= needed else 1
+
+
+def cmd_random(args) -> int:
+    import thintensor_b200
+    from thintensor_b200.config.base import read_config_json
+
+    folder = thintensor_b200.save_random_model(args.out, read_config_json(args.config), seed=args.seed, dtype=args.dtype)
+    print(str(folder))
+    return 0
+
+
+def main(argv: list[str] | None = None) -> int:
+    args = build_parser().parse_args(argv)
+    handler = {"run": cmd_run, "bench": cmd_bench, "validate": cmd_validate, "random": cmd_random}[args.command]
+    try:
+        return handler(args)
+    except (ValueError, RuntimeError) as exc:
+        print(f"error: {exc}", file=sys.stderr)
+        return 2
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -15,6 +15,7 @@ when there are no stop tokens.
 """
 from __future__ import annotations
 
+import time
 from dataclasses import dataclass, field
 from typing import Protocol, Sequence
 
@@ -59,6 +60,9 @@ class GenerationStats:
     prompt_tokens: int = 0
     new_tokens: int = 0
     batch_sizes: list[int] = field(default_factory=list)
+    prefill_seconds: float = 0.0            # host clock; every phase ends with tokens read on the host
+    decode_seconds: float = 0.0
+    decoded_tokens: int = 0                 # tokens produced by decode steps (the first of each request excluded)
 
 
 def plan_batch(pending: list[int], totals: list[int], batch_size: int, backend: Backend) -> list[int]:
@@ -107,7 +111,10 @@ def run_generation(backend: Backend, prompts: Sequence[Sequence[int]], max_new_t
         stats.batch_sizes.append(len(batch))
         stats.prefill_steps += 1
         stats.prompt_tokens += sum(len(prompts[i]) for i in batch)
+        clock = time.perf_counter()
         first = backend.start_batch(batch, [prompts[i] for i in batch], [totals[i] for i in batch])
+        stats.prefill_seconds += time.perf_counter() - clock
+        clock = time.perf_counter()
         live: list[int] = []                      # positions in the batch still running
         for position, (index, token) in enumerate(zip(batch, first)):
             results[index].append(int(token))
@@ -124,12 +131,14 @@ def run_generation(backend: Backend, prompts: Sequence[Sequence[int]], max_new_t
                     for position, token in zip(live, tokens):
                         results[batch[position]].append(int(token))
                 stats.decode_steps += steps
+                stats.decoded_tokens += steps * len(live)
                 for position in live:
                     backend.finish(position)
                 live = []
                 break
             tokens = backend.decode_step(live)
             stats.decode_steps += 1
+            stats.decoded_tokens += len(live)
             produced += 1
             still: list[int] = []
             for position, token in zip(live, tokens):
@@ -139,6 +148,7 @@ def run_generation(backend: Backend, prompts: Sequence[Sequence[int]], max_new_t
                 else:
                     still.append(position)
             live = still
+        stats.decode_seconds += time.perf_counter() - clock
     stats.new_tokens = sum(len(r) for r in results)
     return results
 
@@ -189,6 +199,7 @@ class _DecodeState:
         self.max_total = max(totals)
         self.graph: torch.cuda.CUDAGraph | None = None
         self.warm = False
+        self.launches_per_step = 0              # kernels of this library in one decode step
 
     def context(self) -> StepContext:
         e = self.engine
@@ -209,10 +220,10 @@ class _DecodeState:
 
     def step(self, params: SamplingParams, use_graph: bool) -> None:
         e = self.engine
-        if not use_graph:
-            self.body(params)
-        elif not self.warm:
-            self.body(params)                   # first run allocates scratch and compiles
+        if not use_graph or not self.warm:
+            before = api.launch_count()
+            self.body(params)                   # the first run also allocates scratch and compiles
+            self.launches_per_step = api.launch_count() - before
             self.warm = True
         else:
             if self.graph is None:
@@ -243,6 +254,7 @@ class EngineBackend:
         self._steps: list[int] = []
         self._state: _DecodeState | None = None
         self._state_live: tuple[int, ...] = ()
+        self._pinned: torch.Tensor | None = None
 
     def fits(self, totals: Sequence[int]) -> bool:
         cache = self.engine.cache
@@ -277,7 +289,14 @@ class EngineBackend:
         return self._state
 
     def decode_step(self, live) -> list[int]:
+        """The host is the authority on what each sequence is fed: the last tokens go up
+        from pinned memory, the new ones come back, every step."""
         state = self._state_for(live)
+        if self._pinned is None or self._pinned.numel() < len(live):
+            self._pinned = torch.empty(max(64, len(live)), dtype=torch.int32, pin_memory=True)
+        feed = self._pinned[: len(live)]
+        feed.copy_(torch.tensor([self._last[p] for p in live], dtype=torch.int32))
+        state.tokens.copy_(feed, non_blocking=True)
         state.step(self.params, self.use_graph)
         tokens = state.tokens.tolist()
         for position, token in zip(live, tokens):

@@ -82,7 +82,7 @@ class DecoderModel:
             mine: dict[str, torch.Tensor] = {}
             for local, decl in built.part.weights().items():
                 name = built.prefix + local
-                if decl.alias_of is not None:
+                if decl.alias_of is not None and (decl.prefer_alias or name not in tensors):
                     name = decl.alias_of
                 if name in tensors:
                     mine[local] = tensors[name]

@@ -48,9 +48,20 @@ def _stream() -> c_void_p:
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def _check(code: int, what: str) -> None:
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many of this library's kernels have been launched (or captured into a graph)
+    by this process so far."""
+    return _launches
+
+
+def _check(code: int, what: str, kernels: int = 1) -> None:
+    global _launches
     if code != 0:
         raise KernelError(f"{what}: CUDA error {code} at launch")
+    _launches += kernels
 
 
 def _need(t: torch.Tensor, dtype: torch.dtype, name: str) -> None:
@@ -163,7 +174,7 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table
                                            c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
     _check(fn(_ptr(q), _ptr(k_pool), _ptr(v_pool), dtype_code(q.dtype), _ptr(table), table.shape[1], k_pool.shape[0], _ptr(cu),
               _ptr(len_before), sequences, n_tokens, heads, kv_heads, head_dim, scale, window, splits, _ptr(out),
-              _ptr(part_acc), _ptr(part_ml), _ptr(status), _stream()), "attention")
+              _ptr(part_acc), _ptr(part_ml), _ptr(status), _stream()), "attention", 2 if splits > 1 else 1)
 
 
 # -------------------------------------------------------------------------------- gemm

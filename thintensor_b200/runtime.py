@@ -127,3 +127,28 @@ def save_random_model(folder: str | Path, config, seed: int = 0, dtype: str = "b
         arch, _ = load_config(config.to_dict())
     declared = DecoderModel(arch.describe(config), torch.float32, None).weight_declarations()
     return write_model_folder(folder, config, declared, seed, dtype)
+
+
+def random_model(config, seed: int = 0, dtype="bf16", device="cuda") -> Runtime:
+    """A runtime whose weights are drawn on the device (N(0, 0.02), norm weights
+    1 + N(0, 0.1)) without writing a folder: for benchmarks at sizes whose files would
+    take minutes to write.  ``config`` is a config.json dict or a typed configuration."""
+    torch_dtype = parse_dtype(dtype)
+    device = require_cuda(device)
+    arch, config = load_config(config if isinstance(config, dict) else config.to_dict())
+    model = DecoderModel(arch.describe(config), torch_dtype, device)
+    generator = torch.Generator(device=device)
+    generator.manual_seed(int(seed))
+    tensors: dict[str, torch.Tensor] = {}
+    for name, decl in model.weight_declarations().items():
+        if decl.alias_of is not None and decl.prefer_alias:
+            continue
+        if decl.integer:
+            tensors[name] = torch.zeros(decl.shape, dtype=torch.int32, device=device)
+            continue
+        noise = torch.randn(decl.shape, generator=generator, device=device, dtype=torch.float32)
+        value = 1.0 + 0.1 * noise if decl.init == "norm" else (noise * 0.02 if decl.init == "normal" else noise * 0.0)
+        tensors[name] = value.to(torch_dtype)
+        del noise, value
+    model.bind(tensors)
+    return Runtime(Path("."), arch, config, model)
