@@ -181,7 +181,7 @@ def main() -> int:
             "hidden_size": raw["hidden_size"], "heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"],
             "head_dim": raw["head_dim"], "intermediate_size": raw["intermediate_size"], "vocab_size": vocab,
             "tied_embeddings": True, "rope": "llama3 factor 32", "global_batch": BATCH, "prompt_len": PROMPT,
-            "seq_len": CONTEXT, "parallelism": "none (1 GPU)", "cache": "bf16, blocks of 64 tokens",
+            "seq_len": CONTEXT, "parallelism": "none (1 GPU)",
             "l2": "every step reads all weights (2.47 GB > 126 MB L2)", "peaks": pk["source"],
         },
         "clocks": clocks.summary(),
