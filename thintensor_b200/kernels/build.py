@@ -31,6 +31,7 @@ SOURCES: dict[str, list[str]] = {
     "attention": [],
     "gemm_simt": [],
     "sampling": [],
+    "attention_static_scratch": [],
     # "gemm_tcgen05": [],
     # "attention_mma": [],
 }
@@ -100,7 +101,7 @@ def _choose_build_dir() -> Path:
 def _digest(name: str) -> str:
     h = hashlib.sha256()
     h.update((CSRC / f"{name}.cu").read_bytes())
-    for header in sorted(CSRC.glob("*.cuh")):
+    for header in sorted(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))):
         h.update(header.read_bytes())
     h.update(" ".join(ARCH_FLAGS + COMMON_FLAGS + SOURCES[name]).encode())
     return h.hexdigest()[:16]
