@@ -1,0 +1,122 @@
+"""The generation loop's decisions with a scripted backend: batches, stop tokens,
+sequences that end earlier, budgets, and that every sequence is finished exactly once."""
+from __future__ import annotations
+
+import pytest
+
+from thintensor_b200.engine.generate import GenerationError, GenerationStats, run_generation
+from thintensor_b200.sampling import SamplingParams
+
+
+class ScriptedBackend:
+    """Request r produces script[r][0], script[r][1], ...; records every call."""
+
+    def __init__(self, script, capacity_tokens=10_000, capacity_sequences=100):
+        self.script = script
+        self.capacity_tokens, self.capacity_sequences = capacity_tokens, capacity_sequences
+        self.calls: list[tuple] = []
+        self.live_now: set[int] = set()
+        self.finished: list[int] = []
+        self.batch: list[int] = []
+        self.at: dict[int, int] = {}
+
+    def fits(self, totals):
+        return sum(totals) + sum(0 for _ in self.live_now) <= self.capacity_tokens and len(totals) <= self.capacity_sequences
+
+    def start_batch(self, requests, prompts, totals):
+        assert not self.live_now, "a batch started while the previous one still had live sequences"
+        self.calls.append(("start", tuple(requests), tuple(len(p) for p in prompts), tuple(totals)))
+        self.batch = list(requests)
+        self.live_now = set(range(len(requests)))
+        out = []
+        for r in requests:
+            self.at[r] = 1
+            out.append(self.script[r][0])
+        return out
+
+    def decode_step(self, live):
+        assert set(live) <= self.live_now
+        self.calls.append(("step", tuple(live)))
+        out = []
+        for position in live:
+            r = self.batch[position]
+            out.append(self.script[r][self.at[r]])
+            self.at[r] += 1
+        return out
+
+    def decode_run(self, live, steps):
+        self.calls.append(("run", tuple(live), steps))
+        return [self.decode_step(live) for _ in range(steps)]
+
+    def finish(self, position):
+        assert position in self.live_now, "finished twice, or never started"
+        self.live_now.remove(position)
+        self.finished.append(self.batch[position])
+
+
+def test_stop_tokens_and_early_finish():
+    script = {0: [5, 6, 99, 1, 1, 1], 1: [99, 2, 2, 2, 2, 2], 2: [7, 7, 7, 7, 7, 7], 3: [8, 99, 0, 0, 0, 0], 4: [4, 4, 4, 99, 0, 0]}
+    backend = ScriptedBackend(script)
+    stats = GenerationStats()
+    out = run_generation(backend, [[1]] * 5, max_new_tokens=5, stop_ids=[99], batch_size=3, stats=stats)
+    assert out == [[5, 6, 99], [99], [7, 7, 7, 7, 7], [8, 99], [4, 4, 4, 99]]        # the stop token is kept
+    assert sorted(backend.finished) == [0, 1, 2, 3, 4] and not backend.live_now
+    steps = [c for c in backend.calls if c[0] == "step"]
+    assert steps[:4] == [("step", (0, 2)), ("step", (0, 2)), ("step", (2,)), ("step", (2,))]   # request 1 left after its first token
+    assert [c[1] for c in backend.calls if c[0] == "start"] == [(0, 1, 2), (3, 4)]             # no request joins a running batch
+    assert stats.batches == 2 and stats.batch_sizes == [3, 2] and stats.new_tokens == 15
+    assert stats.decoded_tokens == 15 - 5
+
+
+def test_without_stop_ids_runs_to_the_budget_without_reading_tokens():
+    script = {r: list(range(10)) for r in range(3)}
+    backend = ScriptedBackend(script)
+    out = run_generation(backend, [[1, 2], [3], [4, 5, 6]], max_new_tokens=6, stop_ids=(), batch_size=8)
+    assert out == [list(range(6))] * 3
+    assert ("run", (0, 1, 2), 5) in backend.calls and sorted(backend.finished) == [0, 1, 2]
+    assert backend.calls[0] == ("start", (0, 1, 2), (2, 1, 3), (8, 7, 9))
+    backend = ScriptedBackend(script)
+    assert run_generation(backend, [[1]], max_new_tokens=1) == [[0]] and backend.finished == [0]
+    assert not [c for c in backend.calls if c[0] in ("run", "step")]
+
+
+def test_batches_follow_the_cache_capacity():
+    script = {r: [1] * 10 for r in range(5)}
+    backend = ScriptedBackend(script, capacity_tokens=40)
+    prompts = [[0] * 10, [0] * 10, [0] * 30, [0] * 5, [0] * 5]
+    run_generation(backend, prompts, max_new_tokens=4, stop_ids=(), batch_size=4)
+    assert [c[1] for c in backend.calls if c[0] == "start"] == [(0, 1), (2,), (3, 4)]
+    with pytest.raises(GenerationError, match="more than the cache can hold"):
+        run_generation(ScriptedBackend(script, capacity_tokens=20), prompts, max_new_tokens=4)
+
+
+def test_argument_errors():
+    backend = ScriptedBackend({0: [1, 1, 1]})
+    with pytest.raises(GenerationError, match="max_new_tokens"):
+        run_generation(backend, [[1]], max_new_tokens=0)
+    with pytest.raises(GenerationError, match="empty"):
+        run_generation(backend, [[]], max_new_tokens=2)
+    with pytest.raises(GenerationError, match="exceeds the context"):
+        run_generation(backend, [[1] * 10], max_new_tokens=3, context=12)
+    with pytest.raises(GenerationError, match="batch_size"):
+        run_generation(backend, [[1]], max_new_tokens=2, batch_size=0)
+    assert run_generation(backend, [], max_new_tokens=3) == []
+
+
+def test_sampling_params_are_checked():
+    assert SamplingParams().greedy and not SamplingParams(temperature=0.7).greedy
+    for bad in ({"temperature": -1.0}, {"top_k": -1}, {"top_p": 0.0}, {"top_p": 1.5}):
+        with pytest.raises(ValueError):
+            SamplingParams(**bad)
+
+
+def test_no_cpu_path():
+    import thintensor_b200
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    with pytest.raises(RuntimeError, match="CUDA"):
+        thintensor_b200.load_model(".", dtype="bf16", device="cuda")
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        thintensor_b200.load_model(".", dtype="bf16", device="cpu")

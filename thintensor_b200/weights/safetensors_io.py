@@ -171,4 +171,4 @@ def write_safetensors(path: str | Path, tensors: dict[str, torch.Tensor], metada
         out.write(encoded)
         for tensor in blobs:
             if tensor.numel():
-                out.write(tensor.view(torch.uint8).reshape(-1).numpy().tobytes())
+                out.write(tensor.reshape(-1).view(torch.uint8).numpy().tobytes())
