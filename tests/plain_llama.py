@@ -191,24 +191,37 @@ def causal_attention(q, k, v, window: int | None = None) -> torch.Tensor:
     return out.reshape(T, heads * d)
 
 
-def attention_block(x, w: dict, prefix: str, cfg: dict, positions, inv_freq, window=None) -> torch.Tensor:
-    """q, k, v projections (+ optional biases), rotary on q and k, causal attention,
-    output projection (thinruntime/gpu_runtime.py:10151-10249).  Weights are
-    [out_features, in_features] applied as W @ x."""
+def projections(x, w: dict, prefix: str, cfg: dict, positions, inv_freq):
+    """q, k, v of one sequence after the rotary encoding: [T, heads, d], [T, kv_heads, d]
+    twice (thinruntime/gpu_runtime.py:10151-10209).  Weights are [out_features,
+    in_features] applied as W @ x, with optional biases (:10179-10188)."""
     T = x.shape[0]
     heads, kv_heads, d = cfg["heads"], cfg["kv_heads"], cfg["head_dim"]
 
-    def proj(name, value):
-        y = value @ w[prefix + name + ".weight"].T
+    def proj(name):
+        y = x @ w[prefix + name + ".weight"].T
         bias = w.get(prefix + name + ".bias")
         return y if bias is None else y + bias
 
-    q = proj("q_proj", x).reshape(T, heads, d)
-    k = proj("k_proj", x).reshape(T, kv_heads, d)
-    v = proj("v_proj", x).reshape(T, kv_heads, d)
+    q = proj("q_proj").reshape(T, heads, d)
+    k = proj("k_proj").reshape(T, kv_heads, d)
+    v = proj("v_proj").reshape(T, kv_heads, d)
     cos, sin = rope_cos_sin(inv_freq, positions, x.dtype)
-    q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
-    return proj("o_proj", causal_attention(q, k, v, window))
+    return apply_rope(q, cos, sin), apply_rope(k, cos, sin), v
+
+
+def output_projection(mixed, w: dict, prefix: str) -> torch.Tensor:
+    """a = Wo @ o (+ bias) (thinruntime/gpu_runtime.py:10221-10231)."""
+    y = mixed @ w[prefix + "o_proj.weight"].T
+    bias = w.get(prefix + "o_proj.bias")
+    return y if bias is None else y + bias
+
+
+def attention_block(x, w: dict, prefix: str, cfg: dict, positions, inv_freq, window=None) -> torch.Tensor:
+    """Projections, rotary on q and k, causal attention, output projection
+    (thinruntime/gpu_runtime.py:10151-10249)."""
+    q, k, v = projections(x, w, prefix, cfg, positions, inv_freq)
+    return output_projection(causal_attention(q, k, v, window), w, prefix)
 
 
 def swiglu(x, w: dict, prefix: str) -> torch.Tensor:

@@ -1,0 +1,272 @@
+"""Each part alone against the plain implementation's function for it, and the
+generality of the assembly: a schedule that names a layer twice and lets a run read
+another run's cache, a windowed mixer beside full ones, and a toy mixer with state of
+its own that is defined here, registered, built and stepped without touching the
+library's files."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+import plain_llama
+from conftest import TINY, token_ids
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def make_engine(spec, dtype=torch.float32, seed=0, blocks=16, slots=4, scale=None):
+    from thintensor_b200.engine.engine import Engine
+    from thintensor_b200.engine.model import DecoderModel
+    from thintensor_b200.weights.random_init import random_tensors
+
+    model = DecoderModel(spec, dtype, DEV)
+    tensors = random_tensors(model.weight_declarations(), seed, torch.float32)
+    for key in tensors:
+        if scale and any(key.endswith(s) for s in scale):
+            tensors[key] = tensors[key] * scale[[s for s in scale if key.endswith(s)][0]]
+    host = {k: v.clone() for k, v in tensors.items()}
+    model.bind({k: v.to(DEV).to(dtype if v.is_floating_point() else v.dtype) for k, v in tensors.items()})
+    return Engine(model, model.new_cache(blocks, slots)), host
+
+
+def context_for(engine, slots, news):
+    """A StepContext for sequences that bring ``news`` tokens each (cache reserved)."""
+    from thintensor_b200.engine.engine import Entry
+
+    entries = [Entry(s, [0] * n, []) for s, n in zip(slots, news)]
+    for e in entries:
+        engine.cache.reserve(e.slot, engine.cache.length(e.slot) + len(e.tokens))
+    ctx, _, _ = engine._prepare(entries, [(i, 0, n) for i, n in enumerate(news)], [0] * len(news))
+    return ctx
+
+
+SHARP = {"q_proj.weight": 8.0, "k_proj.weight": 8.0, "embed_tokens.weight": 20.0, "lm_head.weight": 20.0}
+
+
+def llama_spec(name):
+    from thintensor_b200.config import load_config
+
+    arch, config = load_config(TINY[name])
+    return arch.describe(config)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_part(dtype):
+    from thintensor_b200.parts import NORMS
+    from thintensor_b200.parts.base import Delta
+
+    engine, _ = make_engine(llama_spec("a"), dtype)
+    norm = NORMS.build("rmsnorm", {"dim": 200, "eps": 1e-5})
+    weight = torch.randn(200) * 0.1 + 1
+    norm.bind({"weight": weight.to(DEV)}, dtype, torch.device(DEV))
+    ctx = context_for(engine, [engine.open()], [6])
+    residual = torch.randn(6, 200, device=DEV)
+    delta = torch.randn(2, 6, 200, device=DEV)
+    want_residual = residual.double() + delta.double().sum(0)
+    out = torch.empty(6, 200, dtype=dtype, device=DEV)
+    norm.forward(ctx, residual, Delta(delta), out)
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    torch.testing.assert_close(out.double(), plain_llama.rms_norm(want_residual, weight.double().to(DEV), 1e-5), rtol=tol, atol=tol)
+    torch.testing.assert_close(residual.double(), want_residual, rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["b", "c"])
+def test_attention_and_ffn_parts(name, dtype):
+    """The mixer and the feed-forward of layer 0, run alone on packed sequences (one of
+    them in two steps), against plain_llama.attention_block and plain_llama.swiglu."""
+    spec = llama_spec(name)
+    engine, host = make_engine(spec, dtype, seed=3, scale=SHARP)
+    cfg = plain_llama.normalise_config(TINY[name])
+    weights = {k: (v.to(dtype).double() if v.is_floating_point() else v) for k, v in host.items()}
+    inv_freq = plain_llama.rope_inv_freq(cfg["head_dim"], cfg["theta"], cfg["scaling"])
+    arrangement = engine.model.layers[0]
+    mixer, ffn = arrangement.parts["mixer"], arrangement.parts["ffn"]
+    lengths = [70, 3, 130]
+    g = torch.Generator().manual_seed(5)
+    xs = [torch.randn(n, cfg["hidden"], generator=g).to(dtype) for n in lengths]
+    slots = [engine.open() for _ in lengths]
+    tol = 3e-5 if dtype == torch.float32 else 3e-2
+
+    # step 1: all but the last 2 tokens of sequence 2; step 2: its last 2 tokens alone
+    first = [70, 3, 128]
+    ctx = context_for(engine, slots, first)
+    x = torch.cat([xs[i][: first[i]] for i in range(3)]).to(DEV)
+    got = mixer.forward(ctx, x, engine.cache.run_cache(0), None).tensor.sum(0).double().cpu()
+    for s, n in zip(slots, first):
+        engine.cache.advance(s, n)
+    wants = [plain_llama.attention_block(xs[i].double(), weights, "model.layers.0.self_attn.", cfg, torch.arange(lengths[i]), inv_freq)
+             for i in range(3)]
+    torch.testing.assert_close(got, torch.cat([wants[i][: first[i]] for i in range(3)]), rtol=tol, atol=tol)
+    ctx = context_for(engine, [slots[2]], [2])
+    got = mixer.forward(ctx, xs[2][128:].to(DEV), engine.cache.run_cache(0), None).tensor.sum(0).double().cpu()
+    torch.testing.assert_close(got, wants[2][128:], rtol=tol, atol=tol)
+
+    ctx = context_for(engine, [slots[1]], [5])
+    x = torch.randn(5, cfg["hidden"], generator=g).to(dtype)
+    got = ffn.forward(ctx, x.to(DEV)).tensor.sum(0).double().cpu()
+    torch.testing.assert_close(got, plain_llama.swiglu(x.double(), weights, "model.layers.0.mlp."), rtol=tol, atol=tol)
+    engine.check_status()
+
+
+def test_position_encoding_and_embedding_parts():
+    from thintensor_b200.parts import EMBEDDINGS, POSITION_ENCODINGS
+
+    scaling = TINY["c"]["rope_scaling"]
+    rope = POSITION_ENCODINGS.build("rope", {"head_dim": 48, "theta": 250000.0, "scaling": scaling})
+    torch.testing.assert_close(rope.inv_freq_host, plain_llama.rope_inv_freq(48, 250000.0, scaling), rtol=2e-7, atol=0)
+    partial = POSITION_ENCODINGS.build("rope", {"head_dim": 64, "theta": 10000.0, "rotary_dim": 32})
+    torch.testing.assert_close(partial.inv_freq_host, plain_llama.rope_inv_freq(32, 10000.0, None))
+    with pytest.raises(ValueError):
+        POSITION_ENCODINGS.build("rope", {"head_dim": 64, "theta": 10000.0, "rotary_dim": 33})
+    engine, _ = make_engine(llama_spec("a"))
+    table = torch.randn(50, 24)
+    embedding = EMBEDDINGS.build("table", {"vocab": 50, "hidden": 24, "scale": 2.0})
+    embedding.bind({"weight": table.to(DEV)}, torch.float32, torch.device(DEV))
+    ctx = context_for(engine, [engine.open()], [4])
+    tokens = torch.tensor([3, 49, 0, 3], dtype=torch.int32, device=DEV)
+    residual = torch.empty(4, 24, device=DEV)
+    embedding.forward(ctx, tokens, residual)
+    torch.testing.assert_close(residual.cpu(), plain_llama.embed(table, [3, 49, 0, 3]) * 2.0)
+
+
+def plain_schedule(cfg, w, tokens, schedule, windows):
+    """The plain implementation's parts run in the order of ``schedule``: entries are
+    (layer, cache_from); a run that reads another run's cache attends over that run's
+    keys and values with its own queries."""
+    positions = torch.arange(len(tokens))
+    inv_freq = plain_llama.rope_inv_freq(cfg["head_dim"], cfg["theta"], cfg["scaling"])
+    h = plain_llama.embed(w["model.embed_tokens.weight"], tokens)
+    kept = {}
+    for index, (layer, source) in enumerate(schedule):
+        p = f"model.layers.{layer}."
+        x = plain_llama.rms_norm(h, w[p + "input_layernorm.weight"], cfg["eps"])
+        q, k, v = plain_llama.projections(x, w, p + "self_attn.", cfg, positions, inv_freq)
+        if source is not None:
+            k, v = kept[source]
+        kept[index] = (k, v)
+        h = h + plain_llama.output_projection(plain_llama.causal_attention(q, k, v, windows.get(layer)), w, p + "self_attn.")
+        h = h + plain_llama.swiglu(plain_llama.rms_norm(h, w[p + "post_attention_layernorm.weight"], cfg["eps"]), w, p + "mlp.")
+    return plain_llama.head(plain_llama.rms_norm(h, w["model.norm.weight"], cfg["eps"]), w)
+
+
+def test_schedule_repeats_layers_shares_caches_and_mixes_windows():
+    """Layer 1 has a window of 40 keys, layers 0 and 2 see everything; the schedule runs
+    layer 0 twice and ends with a run of layer 2 that reads the first run's cache.  Whole
+    sequences and token-by-token decoding agree with the plain parts run in that order."""
+    from dataclasses import replace
+
+    from thintensor_b200.engine.engine import Entry
+    from thintensor_b200.parts.spec import PartSpec, Run
+
+    spec = llama_spec("b")
+    layers = list(spec.layers)
+    mixer = layers[1].parts["mixer"]
+    layers[1] = replace(layers[1], parts={**layers[1].parts, "mixer": PartSpec(mixer.kind, {**mixer.params, "window": 40}, mixer.prefix)})
+    schedule = (Run(0), Run(1), Run(0), Run(2, cache_from=0))
+    spec = replace(spec, layers=tuple(layers), schedule=schedule)
+    engine, host = make_engine(spec, torch.float32, seed=7, scale=SHARP, blocks=24)
+    assert [g.need.window for g in engine.cache.kv_groups] == [None, 40]
+    cfg = plain_llama.normalise_config(TINY["b"])
+    weights = {k: v.double() for k, v in host.items()}
+    tokens = token_ids(cfg["vocab"], 150, 77)
+    want = plain_schedule(cfg, weights, tokens, [(0, None), (1, None), (0, None), (2, 0)], {1: 40})
+    slot = engine.open()
+    whole = engine.step([Entry(slot, tokens, list(range(len(tokens))))])
+    engine.close(slot)
+    scale = float(want.abs().max())
+    assert float((whole.double().cpu() - want).abs().max()) <= 2e-4 * scale
+    slot = engine.open()
+    got = [engine.step([Entry(slot, tokens[:100], [99])])]
+    for t in range(100, 150):
+        got.append(engine.step([Entry(slot, [tokens[t]], [0])]))
+    windowed = engine.cache.kv_groups[1].table
+    assert windowed.row(slot)[0] == -1 and windowed.pool.held_count < 3      # blocks that slid out of the window went back
+    engine.close(slot)
+    engine.check_status()
+    assert float((torch.cat(got).double().cpu() - want[99:]).abs().max()) <= 2e-4 * scale
+    assert engine.cache.free_blocks == engine.cache.num_blocks
+
+
+def test_toy_mixer_with_state_of_its_own():
+    """A mixer that keeps, per sequence, the running sum of its inputs and their count
+    (fixed-size state, no keys) and outputs W @ (mean of the inputs so far).  Defined
+    here, registered here, used for one layer next to an attention layer."""
+    from dataclasses import replace
+
+    from thintensor_b200.engine.engine import Entry
+    from thintensor_b200.parts import MIXERS
+    from thintensor_b200.parts.base import Delta, Mixer, StateNeed, WeightDecl
+    from thintensor_b200.parts.spec import PartSpec
+
+    @MIXERS.register("toy_running_mean")
+    class RunningMean(Mixer):
+        def __init__(self, hidden):
+            self.hidden = hidden
+
+        def weights(self):
+            return {"mix.weight": WeightDecl((self.hidden, self.hidden))}
+
+        def state_need(self):
+            return StateNeed((self.hidden + 1,), torch.float32)
+
+        def bind(self, tensors, dtype, device):
+            self.w = tensors["mix.weight"].float()
+
+        def forward(self, ctx, x, cache, state):
+            out = torch.empty(1, ctx.n_tokens, self.hidden, dtype=torch.float32, device=x.device)
+            at = 0
+            for slot, new in zip(ctx.host_slots, ctx.host_new):
+                xs = x[at: at + new].float()
+                sums = state[slot, : self.hidden] + xs.cumsum(0)
+                counts = state[slot, self.hidden] + torch.arange(1, new + 1, device=x.device)
+                out[0, at: at + new] = (sums / counts[:, None]) @ self.w.T
+                state[slot, : self.hidden] = sums[-1]
+                state[slot, self.hidden] = counts[-1]
+                at += new
+            return Delta(out)
+
+    try:
+        spec = llama_spec("a")
+        layers = list(spec.layers)
+        layers[0] = replace(layers[0], parts={**layers[0].parts, "mixer": PartSpec("toy_running_mean", {"hidden": 64}, "model.layers.0.toy.")})
+        spec = replace(spec, layers=tuple(layers))
+        engine, host = make_engine(spec, torch.float32, seed=9, scale=SHARP)
+        assert "model.layers.0.toy.mix.weight" in host and "model.layers.0.self_attn.q_proj.weight" not in host
+        assert len(engine.cache.state_groups) == 1 and len(engine.cache.kv_groups) == 1
+        cfg = plain_llama.normalise_config(TINY["a"])
+        w = {k: v.double() for k, v in host.items()}
+
+        def plain(tokens):
+            positions = torch.arange(len(tokens))
+            inv_freq = plain_llama.rope_inv_freq(cfg["head_dim"], cfg["theta"], cfg["scaling"])
+            h = plain_llama.embed(w["model.embed_tokens.weight"], tokens)
+            x = plain_llama.rms_norm(h, w["model.layers.0.input_layernorm.weight"], cfg["eps"])
+            mean = x.cumsum(0) / torch.arange(1, len(tokens) + 1)[:, None]
+            h = h + mean @ w["model.layers.0.toy.mix.weight"].T
+            h = h + plain_llama.swiglu(plain_llama.rms_norm(h, w["model.layers.0.post_attention_layernorm.weight"], cfg["eps"]), w, "model.layers.0.mlp.")
+            h = plain_llama.decoder_layer(h, w, 1, cfg, positions, inv_freq)
+            return plain_llama.head(plain_llama.rms_norm(h, w["model.norm.weight"], cfg["eps"]), w)
+
+        prompts = [token_ids(256, n, 90 + n) for n in (30, 7, 75)]
+        wants = [plain(p) for p in prompts]
+        slots = [engine.open() for _ in prompts]
+        heads = [20, 7, 10]
+        logits = engine.step([Entry(s, p[:h], [h - 1]) for s, p, h in zip(slots, prompts, heads)])
+        for i in range(3):
+            assert float((logits[i].double().cpu() - wants[i][heads[i] - 1]).abs().max()) <= 2e-4 * float(wants[i].abs().max())
+        engine.close(slots[1])
+        for t in range(10):                       # sequences 0 and 2 go on one token at a time
+            logits = engine.step([Entry(slots[0], [prompts[0][20 + t]], [0]), Entry(slots[2], [prompts[2][10 + t]], [0])])
+            for row, (i, place) in enumerate([(0, 20 + t), (2, 10 + t)]):
+                assert float((logits[row].double().cpu() - wants[i][place]).abs().max()) <= 2e-4 * float(wants[i].abs().max())
+        engine.close(slots[0])
+        engine.close(slots[2])
+        # a slot that is used again starts from zero state
+        slot = engine.open()
+        logits = engine.step([Entry(slot, prompts[1], [6])])
+        assert float((logits[0].double().cpu() - wants[1][6]).abs().max()) <= 2e-4 * float(wants[1].abs().max())
+        engine.close(slot)
+    finally:
+        MIXERS.unregister("toy_running_mean")
