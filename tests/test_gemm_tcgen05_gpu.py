@@ -1,0 +1,96 @@
+"""The tcgen05 matrix product alone, against a float64 product of the same bfloat16
+numbers: all three forms (tokens on the 128-row side, with and without the fused
+SwiGLU, and features on the 128-row side), sizes that are no multiples of any tile,
+k cut into slices, and bias."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def randn(*shape, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(torch.bfloat16).to(DEV)
+
+
+def run(tokens, features, k, splits, with_bias, seed=0):
+    from thintensor_b200.kernels import api
+
+    x, w = randn(tokens, k, seed=seed), randn(features, k, seed=seed + 1)
+    bias = torch.randn(features, device=DEV) if with_bias else None
+    out = torch.full((splits, tokens, features), float("nan"), dtype=torch.float32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    api.gemm_tcgen05(x, w, bias, out, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, "a bounded wait ran out"
+    want = x.double() @ w.double().T + (bias.double() if with_bias else 0)
+    got = out.double().sum(0)
+    assert torch.isfinite(got).all()
+    # float32 accumulation of exact bfloat16 products: the error grows like sqrt(k) * eps
+    torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-4 * k ** 0.5)
+
+
+@pytest.mark.parametrize("tokens", [1, 8, 16, 17, 33, 64, 100, 128])
+@pytest.mark.parametrize("features,k,splits", [(128, 64, 1), (311, 72, 1), (2048, 2048, 4), (200, 1000, 3), (128256 // 16, 256, 1)])
+def test_features_on_m(tokens, features, k, splits):
+    run(tokens, features, k, splits, with_bias=(tokens % 2 == 0))
+
+
+@pytest.mark.parametrize("tokens", [129, 256, 300, 1000])
+@pytest.mark.parametrize("features,k,splits", [(128, 64, 1), (311, 72, 1), (3072, 2048, 1), (200, 1000, 2), (2048, 8192, 4)])
+def test_tokens_on_m(tokens, features, k, splits):
+    run(tokens, features, k, splits, with_bias=(features % 2 == 1))
+
+
+def test_split_policy_and_refusals():
+    from thintensor_b200.kernels import api
+
+    assert api.gemm_tcgen05_splits(8, 2048, 2048) == 8          # 16 tiles, 32 k-blocks: four blocks per slice
+    assert api.gemm_tcgen05_splits(8, 2048, 8192) == 16
+    assert api.gemm_tcgen05_splits(8, 128256, 2048) == 1
+    assert api.gemm_tcgen05_splits(2048, 3072, 2048) == 1
+    x, w = randn(4, 70, seed=1), randn(32, 70, seed=2)             # k = 70 is no multiple of 8
+    assert not api.gemm_tcgen05_usable(x, w)
+    with pytest.raises(api.KernelError):
+        api.gemm_tcgen05(x, w, None, torch.empty(1, 4, 32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV))
+
+
+@pytest.mark.parametrize("tokens,inter,k", [(129, 128, 64), (300, 200, 72), (2048, 1024, 512), (257, 8192, 2048)])
+def test_fused_swiglu(tokens, inter, k):
+    from thintensor_b200.kernels import api
+
+    x = randn(tokens, k, seed=5)
+    w = randn(2 * inter, k, seed=6, scale=0.1)
+    act = torch.full((tokens, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    api.gemm_tcgen05_swiglu(x, w, act, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    y = x.double() @ w.double().T
+    g, u = y[:, :inter], y[:, inter:]
+    want = g / (1 + torch.exp(-g)) * u
+    torch.testing.assert_close(act.double(), want, rtol=2e-2, atol=2e-2)
+
+
+def test_linear_uses_it_and_matches_exact_kernel():
+    """The projection helper takes the tensor-core kernel for bfloat16 and agrees with
+    the exact FMA kernel on the same operands."""
+    from thintensor_b200.engine.context import StepContext, Workspace
+    from thintensor_b200.kernels import api
+    from thintensor_b200.parts.linear import Linear
+
+    ws = Workspace(torch.device(DEV))
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    empty = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ctx = StepContext(n_tokens=40, sequences=1, decode=False, max_new=40, max_total=40, tokens=empty, cu=empty, len_before=empty,
+                      slots=empty, tables=[], act_dtype=torch.bfloat16, workspace=ws, status=status)
+    x, w = randn(40, 2048, seed=8), randn(512, 2048, seed=9, scale=0.05)
+    before = api.launch_count()
+    got = Linear(w)(ctx, x, "t").sum(0)
+    exact = torch.empty(1, 40, 512, device=DEV)
+    api.gemm_simt(x, w, None, exact)
+    torch.testing.assert_close(got, exact[0], rtol=1e-4, atol=1e-3)
+    assert api.launch_count() - before == 2

@@ -1,0 +1,373 @@
+// bfloat16 matrix products on the 5th-generation tensor cores of sm_100a:
+//   out = x @ w^T,  x [tokens, k] and w [features, k] both bfloat16 with k contiguous,
+// accumulated in float32 in tensor memory.
+//
+// One CTA computes one 128-row accumulator tile.  Operand tiles of 64 k-elements (128
+// bytes per row) travel global -> shared memory by TMA (cp.async.bulk.tensor, 128-byte
+// swizzle) through a ring of stages guarded by full/empty mbarriers; one elected thread
+// issues tcgen05.mma (M = 128, K = 16 per instruction) on shared-memory descriptors;
+// tcgen05.commit releases stages and finally signals the epilogue warps, which read the
+// accumulator with tcgen05.ld and store.  Warp 0 loads, warp 1 owns tensor memory and
+// issues, warps 2-5 are the epilogue (each reads the 32 lanes its warp index allows).
+//
+// Three forms:
+//   TOKENS_ON_M            tile = 128 tokens x BN features; float32 partial sums
+//                          out[split][token][feature] (+ bias in split 0).  Prompts.
+//   TOKENS_ON_M + SWIGLU   the weight holds gate rows then up rows; each k-block issues
+//                          two products (gate tile, up tile) into two column ranges and
+//                          the epilogue writes silu(gate) * up in bfloat16.
+//   FEATURES_ON_M          tile = 128 features x BN tokens (BN = 16..128): the weights sit
+//                          on the 128-row side so that a decode step with few tokens
+//                          wastes no tensor-core rows and streams each weight exactly
+//                          once; the output is written transposed.  k may be cut into
+//                          `splits` slices (grid.z) so that few output tiles still fill
+//                          148 SMs; consumers sum the slices.
+//
+// Every wait is bounded: when one runs out the kernel raises TT_STATUS_WAIT_EXPIRED,
+// drains its outstanding copies, frees its tensor memory and returns.
+//
+// Counterparts in random-unknown-username/Thintensor: the Triton matvec kernels
+// thinruntime/triton_kernels.py:484-535, 2074-2185 (multi_matvec), 3022-3083 (split-k)
+// and _fused_gate_up_silu_kernel :3155-3239; all SIMT, one token.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;          // accumulator rows (UMMA M)
+constexpr int BK = 64;           // k elements per stage: 128 bytes, one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr uint32_t SPIN_LIMIT = 1u << 24;
+
+enum Form { TOKENS_ON_M = 0, TOKENS_ON_M_SWIGLU = 1, FEATURES_ON_M = 2 };
+
+// ---------------------------------------------------------------- small PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_load16(uint32_t addr, float* v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(addr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a k-major bfloat16 tile whose rows are 128 bytes
+// apart and swizzled in 1024-byte groups of eight rows (what TMA writes with
+// CU_TENSOR_MAP_SWIZZLE_128B): start address, stride between eight-row groups = 1024
+// bytes, descriptor version 1, layout type 2 (128-byte swizzle).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(1024u >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor: float32 accumulator, bfloat16 a and b, both k-major, M x N.
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <int FORM, int BN> struct Shape {
+    static constexpr bool dual = FORM == TOKENS_ON_M_SWIGLU;
+    static constexpr int a_bytes = BM * BK * 2;
+    static constexpr int b_bytes = BN * BK * 2 * (dual ? 2 : 1);
+    static constexpr int stage_bytes = a_bytes + b_bytes;
+    static constexpr int acc_cols = BN * (dual ? 2 : 1);
+    static constexpr int tmem_cols = acc_cols < 32 ? 32 : acc_cols;
+};
+
+struct Args {
+    const float* bias;       // float32 [features] or null
+    void* out;               // float32 partial sums, or bfloat16 activations (SWIGLU)
+    long long ld_out;        // elements between token rows of out
+    long long split_stride;  // elements between k-slices of out
+    int tokens, features, k;
+    int k_blocks_per_split;
+    int up_row_offset;       // SWIGLU: row of w where the up projection starts (= features of the output)
+    unsigned* status;
+};
+
+template <int FORM, int BN, int STAGES>
+__global__ void __launch_bounds__(THREADS)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Args args) {
+    using S = Shape<FORM, BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle groups need 1024-byte alignment
+    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
+    __shared__ uint32_t tmem_base_shared;
+    __shared__ int aborted;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_m = blockIdx.y, tile_n = blockIdx.x, split = blockIdx.z;
+    const int k_blocks_total = (args.k + BK - 1) / BK;
+    const int kb_begin = split * args.k_blocks_per_split;
+    const int kb_end = min(k_blocks_total, kb_begin + args.k_blocks_per_split);
+    const int n_kb = max(0, kb_end - kb_begin);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
+        mbar_init(smem_u32(&acc_bar), 1);
+        aborted = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(&tmem_base_shared), S::tmem_cols);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_shared;
+
+    // rows of the two operands this tile reads
+    const int a_row = tile_m * BM;                      // tokens (TOKENS_ON_M*) or features (FEATURES_ON_M)
+    const int b_row = tile_n * BN;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int issued = 0;
+            for (int i = 0; i < n_kb; ++i) {
+                const int s = i % STAGES;
+                const uint32_t parity = ((i / STAGES) & 1) ^ 1;
+                if (!mbar_wait(smem_u32(&empty_bar[s]), parity)) { atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); aborted = 1; break; }
+                const uint32_t bar = smem_u32(&full_bar[s]);
+                mbar_expect_tx(bar, S::stage_bytes);
+                uint8_t* stage = smem + (size_t)s * S::stage_bytes;
+                const int kx = (kb_begin + i) * BK;
+                tma_load_2d(smem_u32(stage), &map_a, kx, a_row, bar);
+                tma_load_2d(smem_u32(stage + S::a_bytes), &map_b, kx, b_row, bar);
+                if (S::dual) tma_load_2d(smem_u32(stage + S::a_bytes + BN * BK * 2), &map_b, kx, args.up_row_offset + b_row, bar);
+                ++issued;
+            }
+            // drain: every copy issued must have landed before shared memory is given up
+            for (int i = max(0, issued - STAGES); i < issued; ++i)
+                if (!mbar_wait(smem_u32(&full_bar[i % STAGES]), (i / STAGES) & 1)) { atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); break; }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(BM, BN);
+            bool ok = true;
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int s = i % STAGES;
+                if (!mbar_wait(smem_u32(&full_bar[s]), (i / STAGES) & 1)) { atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); aborted = 1; ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = smem_u32(smem + (size_t)s * S::stage_bytes);
+                const uint32_t b_addr = a_addr + S::a_bytes;
+#pragma unroll
+                for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                    const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
+                    const uint64_t da = smem_desc(a_addr + kk * UMMA_K * 2);
+                    umma_bf16(tmem_base, da, smem_desc(b_addr + kk * UMMA_K * 2), idesc, acc);
+                    if (S::dual) umma_bf16(tmem_base + BN, da, smem_desc(b_addr + BN * BK * 2 + kk * UMMA_K * 2), idesc, acc);
+                }
+                umma_commit(smem_u32(&empty_bar[s]));     // the stage is free once these products have read it
+            }
+            if (ok) umma_commit(smem_u32(&acc_bar));      // the accumulator is complete once all products are done
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const int quarter = warp & 3;                      // the 32 tensor-memory lanes this warp may read
+        const int row = quarter * 32 + lane;               // accumulator row owned by this thread
+        bool ok = n_kb == 0 ? true : mbar_wait(smem_u32(&acc_bar), 0);
+        if (!ok && lane == 0) { atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); aborted = 1; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        if (ok) {
+            if (FORM == TOKENS_ON_M) {
+                const int token = a_row + row;
+                float* out = (float*)args.out + (size_t)split * args.split_stride + (size_t)token * args.ld_out;
+                for (int c = 0; c < BN; c += 16) {
+                    float v[16];
+                    if (n_kb > 0) tmem_load16(lane_addr + c, v);
+                    else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+                    }
+                    const int f0 = b_row + c;
+                    if (token < args.tokens) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int f = f0 + j;
+                            if (f < args.features) out[f] = v[j] + ((args.bias && split == 0) ? args.bias[f] : 0.0f);
+                        }
+                    }
+                }
+            } else if (FORM == TOKENS_ON_M_SWIGLU) {
+                const int token = a_row + row;
+                __nv_bfloat16* out = (__nv_bfloat16*)args.out + (size_t)token * args.ld_out;
+                for (int c = 0; c < BN; c += 16) {
+                    float g[16], u[16];
+                    tmem_load16(lane_addr + c, g);
+                    tmem_load16(lane_addr + BN + c, u);
+                    const int f0 = b_row + c;
+                    if (token < args.tokens) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int f = f0 + j;
+                            if (f < args.features) out[f] = __float2bfloat16_rn(g[j] / (1.0f + __expf(-g[j])) * u[j]);
+                        }
+                    }
+                }
+            } else {
+                const int feature = a_row + row;
+                float* out = (float*)args.out + (size_t)split * args.split_stride;
+                const float bias = (args.bias && split == 0 && feature < args.features) ? args.bias[feature] : 0.0f;
+                for (int c = 0; c < BN; c += 16) {
+                    float v[16];
+                    if (n_kb > 0) tmem_load16(lane_addr + c, v);
+                    else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+                    }
+                    if (feature < args.features) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int token = b_row + c + j;
+                            if (token < args.tokens) out[(size_t)token * args.ld_out + feature] = v[j] + bias;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, S::tmem_cols);
+}
+
+// ------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    }
+    return fn;
+}
+
+// A [rows, k] bfloat16 matrix with `ld` elements between rows, read in boxes of box_rows x 64.
+bool make_map(CUtensorMap* map, const void* base, long long rows, long long k, long long ld, int box_rows) {
+    EncodeTiled fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int FORM, int BN, int STAGES>
+int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const Args& args, dim3 grid, cudaStream_t stream) {
+    constexpr int shared = Shape<FORM, BN>::stage_bytes * STAGES + 1024;
+    static bool configured = false;
+    auto kernel = gemm_tcgen05_kernel<FORM, BN, STAGES>;
+    if (!configured) {
+        const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
+        if (err != cudaSuccess) return (int)err;
+        configured = true;
+    }
+    kernel<<<grid, THREADS, shared, stream>>>(map_a, map_b, args);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+// How many tokens the features-on-m form takes at most.
+extern "C" int tt_gemm_tcgen05_max_skinny_tokens() { return 128; }
+
+// Operands must be 16-byte aligned with row strides that are multiples of 8 elements.
+// form: 0 float32 partial sums out[splits][tokens][features]; 1 SwiGLU, out bfloat16
+// [tokens][features] with w holding `features` gate rows then `features` up rows.
+// Returns a cudaError_t value, or -1 if the driver's tensor-map encoder is unavailable
+// or refused the operands.
+extern "C" int tt_gemm_tcgen05(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* out,
+                               long long ld_out, long long split_stride, int tokens, int features, int k, int splits,
+                               int form, unsigned* status, cudaStream_t stream) {
+    if (tokens <= 0 || features <= 0) return 0;
+    if (k <= 0 || (k % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || splits < 1)
+        return (int)cudaErrorInvalidValue;
+    const int k_blocks = (k + BK - 1) / BK;
+    if (splits > k_blocks) splits = k_blocks;
+    Args args;
+    args.bias = bias; args.out = out; args.ld_out = ld_out; args.split_stride = split_stride;
+    args.tokens = tokens; args.features = features; args.k = k;
+    args.k_blocks_per_split = (k_blocks + splits - 1) / splits;
+    args.up_row_offset = features; args.status = status;
+    CUtensorMap map_a, map_b;
+    if (form == 1) {
+        if (splits != 1 || bias) return (int)cudaErrorInvalidValue;
+        if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, 2LL * features, k, ldw, 128)) return -1;
+        const dim3 grid((features + 127) / 128, (tokens + BM - 1) / BM, 1);
+        return launch<TOKENS_ON_M_SWIGLU, 128, 4>(map_a, map_b, args, grid, stream);
+    }
+    if (tokens > 128) {
+        if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, features, k, ldw, 128)) return -1;
+        const dim3 grid((features + 127) / 128, (tokens + BM - 1) / BM, splits);
+        return launch<TOKENS_ON_M, 128, 3>(map_a, map_b, args, grid, stream);
+    }
+    const int bn = tokens <= 16 ? 16 : tokens <= 32 ? 32 : tokens <= 64 ? 64 : 128;
+    if (!make_map(&map_a, w, features, k, ldw, BM) || !make_map(&map_b, x, tokens, k, ldx, bn)) return -1;
+    const dim3 grid(1, (features + BM - 1) / BM, splits);
+    switch (bn) {
+        case 16: return launch<FEATURES_ON_M, 16, 6>(map_a, map_b, args, grid, stream);
+        case 32: return launch<FEATURES_ON_M, 32, 5>(map_a, map_b, args, grid, stream);
+        case 64: return launch<FEATURES_ON_M, 64, 4>(map_a, map_b, args, grid, stream);
+        default: return launch<FEATURES_ON_M, 128, 3>(map_a, map_b, args, grid, stream);
+    }
+}

@@ -216,6 +216,58 @@ def sample_rows(logits: torch.Tensor, temperature: float, top_k: int, top_p: flo
 
 
 # ----------------------------------------------------------------- tensor-core kernels
+SM_COUNT = 148              # B200
+SKINNY_TOKENS = 128         # up to this many tokens the weights go on the 128-row side of the tile
+
+
 def tcgen05_ready() -> bool:
     """Whether the tcgen05 matrix product is part of this build."""
     return "gemm_tcgen05" in build.SOURCES
+
+
+def gemm_tcgen05_usable(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """TMA needs 16-byte aligned bases and row strides, i.e. k and both leading
+    dimensions must be multiples of 8 bfloat16 numbers."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+            and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and x.stride(1) == 1 and w.stride(1) == 1)
+
+
+def gemm_tcgen05_splits(tokens: int, features: int, k: int) -> int:
+    """Into how many slices k is cut so that few output tiles still fill the GPU: about
+    two CTAs per SM, at least four 64-wide k-blocks per slice, at most 16 slices."""
+    tiles = -(-features // 128) * (1 if tokens <= SKINNY_TOKENS else -(-tokens // 128))
+    k_blocks = -(-k // 64)
+    return max(1, min(2 * SM_COUNT // tiles, k_blocks // 4, 16))
+
+
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor, status: torch.Tensor) -> None:
+    """out[s] = x @ w[:, k-slice s].T on the tensor cores; bfloat16 operands, float32
+    ``out`` [splits, tokens, features]; bias (float32) goes into slice 0."""
+    _need(out, torch.float32, "gemm output")
+    tokens, k = x.shape
+    features = w.shape[0]
+    if not gemm_tcgen05_usable(x, w) or w.shape[1] != k or tuple(out.shape[1:]) != (tokens, features):
+        raise KernelError(f"tcgen05 gemm cannot take x {tuple(x.shape)} / w {tuple(w.shape)} / out {tuple(out.shape)} (k and strides must be multiples of 8)")
+    if out.shape[0] > -(-k // 64):
+        raise KernelError(f"{out.shape[0]} k-slices for k = {k}: a slice needs at least one block of 64")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+    fn = _fn("gemm_tcgen05", "tt_gemm_tcgen05", [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_longlong,
+                                                 c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(bias), _ptr(out), out.stride(1), out.stride(0), tokens, features, k,
+              out.shape[0], 0, _ptr(status), _stream()), "gemm_tcgen05")
+
+
+def gemm_tcgen05_swiglu(x: torch.Tensor, w: torch.Tensor, act: torch.Tensor, status: torch.Tensor) -> None:
+    """act = silu(x @ gate.T) * (x @ up.T) in bfloat16, where ``w`` [2 * inter, k] holds
+    the gate rows followed by the up rows; the activation never exists in float32 in
+    global memory."""
+    _need(act, torch.bfloat16, "activation output")
+    tokens, k = x.shape
+    inter = w.shape[0] // 2
+    if not gemm_tcgen05_usable(x, w) or w.shape[1] != k or tuple(act.shape) != (tokens, inter):
+        raise KernelError(f"tcgen05 swiglu gemm cannot take x {tuple(x.shape)} / w {tuple(w.shape)} / act {tuple(act.shape)}")
+    fn = _fn("gemm_tcgen05", "tt_gemm_tcgen05", [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_longlong,
+                                                 c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(None), _ptr(act), act.stride(0), 0, tokens, inter, k, 1, 1,
+              _ptr(status), _stream()), "gemm_tcgen05_swiglu")

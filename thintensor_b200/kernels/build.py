@@ -32,7 +32,7 @@ SOURCES: dict[str, list[str]] = {
     "gemm_simt": [],
     "sampling": [],
     "attention_static_scratch": [],
-    # "gemm_tcgen05": [],
+    "gemm_tcgen05": [],
     # "attention_mma": [],
 }
 

@@ -6,9 +6,10 @@ the residual stream, the rotary/append kernel, SwiGLU) does that sum, so a proje
 whose few output tiles could not fill the GPU may cut its ``in_features`` into slices
 without a reduction kernel of its own.
 
-Which kernel runs is decided by the operands' dtypes alone: bfloat16 activations with
-a bfloat16 weight use the tcgen05 tensor-core kernel; everything else (the true 32-bit
-path, or a weight that the checkpoint stores in float32) uses the exact FMA kernel.
+Which kernel runs is decided by the operands alone: bfloat16 activations with a
+bfloat16 weight whose rows TMA can address (k a multiple of 8) use the tcgen05
+tensor-core kernel; everything else (the true 32-bit path, a weight that the checkpoint
+stores in float32, an odd k) uses the exact FMA kernel.
 """
 from __future__ import annotations
 
@@ -33,7 +34,7 @@ class Linear:
         tokens = x.shape[0]
         if x.shape[1] != self.in_features:
             raise ValueError(f"{name}: input has {x.shape[1]} features, the weight takes {self.in_features}")
-        if x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16 and api.tcgen05_ready():
+        if api.tcgen05_ready() and api.gemm_tcgen05_usable(x, self.weight):
             splits = api.gemm_tcgen05_splits(tokens, self.out_features, self.in_features)
             out = ctx.scratch(name, (splits, tokens, self.out_features), torch.float32)
             api.gemm_tcgen05(x, self.weight, self.bias, out, ctx.status)
@@ -59,8 +60,8 @@ class GatedLinear:
         tokens = x.shape[0]
         act = ctx.scratch(name + ".act", (tokens, self.inter))
         w = self.fused
-        if x.dtype == torch.bfloat16 and w.weight.dtype == torch.bfloat16 and w.bias is None and api.tcgen05_ready():
-            api.gemm_tcgen05_swiglu(x, w.weight, act, ctx.status)
+        if tokens > api.SKINNY_TOKENS and w.bias is None and api.tcgen05_ready() and api.gemm_tcgen05_usable(x, w.weight):
+            api.gemm_tcgen05_swiglu(x, w.weight, act, ctx.status)       # prompts: the float32 gate/up never reach global memory
             return act
         api.swiglu(w(ctx, x, name), act)
         return act
