@@ -120,6 +120,8 @@ def main() -> int:
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration has (both numbers are reported)")
     parser.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64")
+    parser.add_argument("--only", choices=["decode", "prefill"], help="run one phase only and print its numbers (for profiling)")
+    parser.add_argument("--batch", type=int, default=BATCH, help="with --only decode: sequences decoded together")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -142,6 +144,13 @@ def main() -> int:
     vocab = raw["vocab_size"]
     g = torch.Generator().manual_seed(1)
     prompts = [torch.randint(0, vocab, (PROMPT,), generator=g).tolist() for _ in range(64)]
+
+    if args.only == "decode":
+        print(json.dumps(measure_decode(runtime, prompts[:args.batch], CONTEXT, args.warmup, args.steps)))
+        return 0
+    if args.only == "prefill":
+        print(json.dumps(measure_prefill(runtime, prompts[0], repeats=max(1, args.steps), warmup=args.warmup)))
+        return 0
 
     with ClockSampler() as clocks:
         decode = measure_decode(runtime, prompts[:BATCH], CONTEXT, args.warmup, args.steps)

@@ -84,7 +84,7 @@ def make_cache(sequences_len, kv_heads, head_dim, dtype, seed, extra_blocks=3):
     width = max(blocks_per)
     table = torch.full((len(sequences_len), width), -1, dtype=torch.int32)
     k_pool = torch.zeros(total, kv_heads, 64, head_dim)
-    v_pool = torch.zeros(total, kv_heads, 64, head_dim)
+    v_pool = torch.zeros(total, kv_heads, head_dim, 64)          # values lie transposed inside a block
     keys, values = [], []
     at = 0
     for b, n in enumerate(sequences_len):
@@ -98,7 +98,7 @@ def make_cache(sequences_len, kv_heads, head_dim, dtype, seed, extra_blocks=3):
             table[b, j] = block
             chunk = slice(j * 64, min(n, (j + 1) * 64))
             k_pool[block, :, : chunk.stop - chunk.start] = k[chunk].transpose(0, 1)
-            v_pool[block, :, : chunk.stop - chunk.start] = v[chunk].transpose(0, 1)
+            v_pool[block, :, :, : chunk.stop - chunk.start] = v[chunk].permute(1, 2, 0)
     return k_pool.to(dtype).to(DEV), v_pool.to(dtype).to(DEV), table.to(DEV), keys, values
 
 
@@ -183,6 +183,61 @@ def test_attention_decode_splits_and_window(dtype, splits, window):
     assert int(st.item()) == 0
 
 
+@pytest.mark.parametrize("heads,kv_heads,head_dim", [(8, 2, 64), (4, 4, 32), (6, 2, 96), (16, 1, 128), (5, 1, 64), (32, 8, 64), (12, 2, 128)])
+def test_attention_mma_prompts_with_cached_prefix(heads, kv_heads, head_dim):
+    """The tensor-core kernel on packed prompts of unequal length (tiles that end inside a
+    sequence, groups that do not divide 16, a cached prefix)."""
+    from thintensor_b200.kernels import api
+
+    dtype = torch.bfloat16
+    totals, news = [70, 5, 200, 64, 130], [70, 2, 9, 1, 130]
+    k_pool, v_pool, table, keys, values = make_cache(totals, kv_heads, head_dim, dtype, seed=12)
+    tokens = sum(news)
+    q = randn(tokens, heads, head_dim, dtype=dtype, seed=13)
+    cu = torch.tensor([0] + list(torch.tensor(news).cumsum(0)), dtype=torch.int32, device=DEV)
+    before = torch.tensor([t - n for t, n in zip(totals, news)], dtype=torch.int32, device=DEV)
+    out = torch.full((tokens, heads * head_dim), float("nan"), dtype=dtype, device=DEV)
+    st = status()
+    scale = head_dim ** -0.5
+    api.attention_mma(q.view(tokens, -1), k_pool, v_pool, table, cu, before, len(totals), tokens, heads, kv_heads, head_dim, scale, 0, 1,
+                      out, None, None, st)
+    want = attention_reference(q.float().cpu(), keys, values, news, heads, kv_heads, scale, 0)
+    torch.testing.assert_close(out.double().cpu().view(tokens, heads, head_dim), want, **tol(dtype))
+    assert int(st.item()) == 0
+
+
+@pytest.mark.parametrize("splits", [1, 2, 5, 16])
+@pytest.mark.parametrize("window", [0, 100])
+@pytest.mark.parametrize("heads,kv_heads,head_dim", [(8, 2, 64), (3, 1, 128)])
+def test_attention_mma_decode_splits_and_window(splits, window, heads, kv_heads, head_dim):
+    """The tensor-core kernel in decoding: the same far-key construction as for the exact kernel."""
+    from thintensor_b200.kernels import api
+
+    dtype = torch.bfloat16
+    totals = [700, 1, 65, 300]
+    k_pool, v_pool, table, keys, values = make_cache(totals, kv_heads, head_dim, dtype, seed=20)
+    q = randn(len(totals), heads, head_dim, dtype=dtype, seed=21)
+    far = 3 if not window else totals[0] - window
+    spike = (q[0, 0].float() * (24.0 * head_dim ** 0.5 / float(q[0, 0].float().norm()) ** 2)).to(dtype)
+    block, offset = int(table[0, far // 64]), far % 64
+    k_pool[block, 0, offset] = spike
+    keys[0][far, 0] = spike.float().cpu()
+    cu = torch.arange(len(totals) + 1, dtype=torch.int32, device=DEV)
+    before = torch.tensor([t - 1 for t in totals], dtype=torch.int32, device=DEV)
+    out = torch.full((len(totals), heads * head_dim), float("nan"), dtype=dtype, device=DEV)
+    rows = len(totals) * heads
+    part_acc = torch.full((rows * splits * head_dim,), float("nan"), dtype=torch.float32, device=DEV)
+    part_ml = torch.full((rows * splits * 2,), float("nan"), dtype=torch.float32, device=DEV)
+    st = status()
+    scale = head_dim ** -0.5
+    api.attention_mma(q.view(len(totals), -1), k_pool, v_pool, table, cu, before, len(totals), len(totals), heads, kv_heads, head_dim,
+                      scale, window, splits, out, part_acc, part_ml, st)
+    want = attention_reference(q.float().cpu(), keys, values, [1] * len(totals), heads, kv_heads, scale, window)
+    torch.testing.assert_close(out.double().cpu().view(len(totals), heads, head_dim), want, **tol(dtype))
+    assert torch.allclose(want[0, 0], values[0][far, 0].double(), atol=0.35)
+    assert int(st.item()) == 0
+
+
 def test_attention_refuses_bad_sizes():
     from thintensor_b200.kernels import api
 
@@ -190,6 +245,8 @@ def test_attention_refuses_bad_sizes():
         api.check_head_dim(24)
     with pytest.raises(api.KernelError):
         api.check_head_dim(272)
+    assert not api.attention_mma_supports(torch.bfloat16, 4, 2, 48) and not api.attention_mma_supports(torch.float32, 4, 2, 64)
+    assert not api.attention_mma_supports(torch.bfloat16, 34, 2, 64) and api.attention_mma_supports(torch.bfloat16, 32, 8, 64)
 
 
 # ----------------------------------------------------------------------------------- rope
@@ -234,7 +291,7 @@ def test_rope_append(dtype, heads, kv_heads, head_dim, rotary_dim):
             pos = start + i
             block, off = int(table_cpu[b, pos // 64]), pos % 64
             torch.testing.assert_close(k_pool[block, :, off].double().cpu(), rotate(k)[t], **tol(dtype))
-            torch.testing.assert_close(v_pool[block, :, off].double().cpu(), v[t], **tol(dtype))
+            torch.testing.assert_close(v_pool[block, :, :, off].double().cpu(), v[t], **tol(dtype))
             t += 1
 
 

@@ -55,7 +55,7 @@ def problem(dtype, lengths, heads, kv_heads, head_dim, seed):
             table[b, j] = order[at]
             at += 1
     k_pool = torch.randn(total, kv_heads, 64, head_dim, generator=g).to(dtype).to(DEV)
-    v_pool = torch.randn(total, kv_heads, 64, head_dim, generator=g).to(dtype).to(DEV)
+    v_pool = torch.randn(total, kv_heads, head_dim, 64, generator=g).to(dtype).to(DEV)
     q = torch.randn(len(lengths), heads * head_dim, generator=g).to(dtype).to(DEV)
     cu = torch.arange(len(lengths) + 1, dtype=torch.int32, device=DEV)
     before = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=DEV)

@@ -2,8 +2,9 @@
 of the schedule that keeps any, and per-sequence state of fixed size.
 
 Runs with the same need (kv heads, head size, window) form a *group* with storage of
-its own: one pool ``[runs, 2, blocks, kv_heads, block_tokens, head_dim]`` (keys at index
-0, values at 1) and one block table, so that, say, windowed layers give blocks back
+its own: one pool ``[runs, 2, blocks, kv_heads * block_tokens * head_dim]`` (keys at index
+0 laid out ``[kv_heads, block_tokens, head_dim]`` inside a block, values at 1 laid out
+transposed, ``[kv_heads, head_dim, block_tokens]``) and one block table, so that, say, windowed layers give blocks back
 while full-attention layers keep theirs.  State needs are grouped the same way into
 ``[runs, slots, *shape]`` tensors, zeroed when a slot is handed out.
 
@@ -29,7 +30,7 @@ class KVGroup:
     need: KVNeed
     runs: list[int]                 # schedule entries that own a cache in this group
     table: BlockTable
-    storage: torch.Tensor | None    # [runs, 2, blocks, kv_heads, BLOCK_TOKENS, head_dim]
+    storage: torch.Tensor | None    # [runs, 2, blocks, kv_heads * BLOCK_TOKENS * head_dim]
 
     def bytes(self) -> int:
         return 0 if self.storage is None else self.storage.numel() * self.storage.element_size()
@@ -48,7 +49,7 @@ class RunCache:
 
     group: int | None               # index of its KV group, None if it keeps no keys
     k_pool: torch.Tensor | None     # [blocks, kv_heads, BLOCK_TOKENS, head_dim]
-    v_pool: torch.Tensor | None
+    v_pool: torch.Tensor | None     # [blocks, kv_heads, head_dim, BLOCK_TOKENS]
     writes: bool                    # False when the run reads another run's cache
     window: int | None
 
@@ -113,8 +114,10 @@ class SequenceCache:
 
         if self.device is not None:
             for group in self.kv_groups:
-                shape = (len(group.runs), 2, self.num_blocks, group.need.kv_heads, BLOCK_TOKENS, group.need.head_dim)
-                group.storage = torch.empty(shape, dtype=dtype, device=self.device)
+                shape = (len(group.runs), 2, self.num_blocks, group.need.kv_heads * BLOCK_TOKENS * group.need.head_dim)
+                # zeros, not empty: a tensor-core product multiplies the unused tail of a block by a
+                # probability of exactly zero, which must not meet a NaN left in fresh memory
+                group.storage = torch.zeros(shape, dtype=dtype, device=self.device)
             for sgroup in self.state_groups:
                 shape = (len(sgroup.runs), self.max_slots, *sgroup.need.shape)
                 sgroup.storage = torch.zeros(shape, dtype=sgroup.need.dtype, device=self.device)
@@ -183,7 +186,9 @@ class SequenceCache:
         index = self._run_index[run]
         k = v = None
         if g.storage is not None:
-            k, v = g.storage[index, 0], g.storage[index, 1]
+            need = g.need
+            k = g.storage[index, 0].view(self.num_blocks, need.kv_heads, BLOCK_TOKENS, need.head_dim)
+            v = g.storage[index, 1].view(self.num_blocks, need.kv_heads, need.head_dim, BLOCK_TOKENS)
         return RunCache(group, k, v, self._cache_from[run] is None, g.need.window)
 
     def run_state(self, run: int) -> torch.Tensor | None:

@@ -80,11 +80,14 @@ __global__ void attention_rows_kernel(const T* __restrict__ q, const T* __restri
 
     for (int base = begin; base < end; base += 32) {
         const int key = base + lane;
-        long long off = -1;
+        long long off = -1, voff = -1;
         float score = -INFINITY;
         if (key < end) {
             off = tt_cache_offset(table_row, key, kh, kv_heads, head_dim, pool_blocks, status);
-            if (off >= 0) score = dot16<T>(k_pool + off, qs, head_dim);
+            if (off >= 0) {
+                score = dot16<T>(k_pool + off, qs, head_dim);
+                voff = tt_value_offset(table_row, key, kh, kv_heads, head_dim, pool_blocks, nullptr);
+            }
         }
         const float m_tile = tt_warp_max(score);
         if (m_tile == -INFINITY) continue;  // nothing readable in this tile
@@ -98,13 +101,13 @@ __global__ void attention_rows_kernel(const T* __restrict__ q, const T* __restri
         const int count = min(32, end - base);
         for (int j = 0; j < count; ++j) {
             const float pj = __shfl_sync(0xffffffffu, p, j);
-            const long long oj = __shfl_sync(0xffffffffu, off, j);
+            const long long oj = __shfl_sync(0xffffffffu, voff, j);
             if (oj < 0) continue;
-            const T* vrow = v_pool + oj;
+            const T* vcol = v_pool + oj;               // dimension d of this key lies d * 64 elements on
 #pragma unroll
             for (int i = 0; i < ATTN_MAX_HEAD_DIM / 32; ++i) {
                 const int d = lane + 32 * i;
-                if (d < head_dim) acc[i] = fmaf(pj, tt_to_float(vrow[d]), acc[i]);
+                if (d < head_dim) acc[i] = fmaf(pj, tt_to_float(vcol[(size_t)d * TT_BLOCK_TOKENS]), acc[i]);
             }
         }
     }

@@ -1,0 +1,271 @@
+// Causal grouped-query attention over the block cache on tensor cores, bfloat16, for head
+// sizes 32, 64, 96 and 128 and up to 16 query heads per key/value head.  One kernel for
+// prompts and for decoding.
+//
+// A warp owns a tile of 16 query rows that share one sequence and one key/value head:
+// rows are (token, head of the group) pairs, 16 / group tokens by `group` heads, so a
+// decode step puts all heads of a group into one tile and reads each key and value once
+// for the whole group.  The warp walks the sequence's cache blocks (64 keys each) within
+// its slice of the keys; per block S = Q K^T and O += P V run as m16n8k16 mma.sync with a
+// running softmax in float32.
+//
+// No shared memory and no transposes: both products read their B operand straight from
+// global memory with 16-byte loads.  That works because (1) a dot product does not care in
+// which order its terms are added, so the k index of each product is permuted such that a
+// thread's four fragment registers are 16 contiguous bytes of a cache row (for Q K^T the
+// head dimension is permuted identically in Q and K; for P V the key index is permuted
+// identically in P's columns and V's rows, by choosing which key each score column
+// stands for), and (2) values are stored transposed inside a cache block
+// ([head_dim][64 tokens], see common.cuh), which is the "k contiguous" order P V needs.
+// The four warps of a CTA take neighbouring tiles, so their loads of the same keys meet in L1.
+//
+// With splits > 1 (decode) grid.z cuts the blocks of keys into slices; partial (max, sum,
+// accumulator) results go to scratch and attention_merge_kernel combines them.
+//
+// Counterparts in random-unknown-username/Thintensor: _single_token_gqa_attention_kernel and
+// the split pair, thinruntime/triton_kernels.py:14-245 (one token, one program per query
+// head, SIMT); prompts are fed token by token there.
+#include "attention_kernels.cuh"
+
+namespace {
+
+constexpr int MMA_WARPS = 4;
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__device__ __forceinline__ uint4 load16(const __nv_bfloat16* p) { return *reinterpret_cast<const uint4*>(p); }
+
+// Which key of a 64-key block score column n of score tile j stands for (see the header).
+__device__ __forceinline__ int key_of(int j, int n) { return 32 * (j >> 2) + 8 * (n >> 1) + 2 * (j & 3) + (n & 1); }
+
+template <int HD>
+__global__ void __launch_bounds__(MMA_WARPS * 32)
+attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
+                     const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ table, int table_width,
+                     int pool_blocks, const int* __restrict__ cu, const int* __restrict__ len_before, int sequences,
+                     int heads, int kv_heads, float scale_log2, int window, int splits, int tokens_per_tile,
+                     __nv_bfloat16* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml,
+                     unsigned* status) {
+    constexpr int KC = HD / 32;          // 32-wide chunks of the head dimension
+    constexpr int NT = HD / 8;           // 8-wide output tiles
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int kh = blockIdx.y, split = blockIdx.z;
+    const int group = heads / kv_heads;
+
+    // which sequence and which of its tiles this warp has
+    int tile = blockIdx.x * MMA_WARPS + warp;
+    int b = 0;
+    for (; b < sequences; ++b) {
+        const int tiles_b = (cu[b + 1] - cu[b] + tokens_per_tile - 1) / tokens_per_tile;
+        if (tile < tiles_b) break;
+        tile -= tiles_b;
+    }
+    if (b >= sequences) return;
+    const int seq_begin = cu[b], seq_new = cu[b + 1] - seq_begin, before = len_before[b];
+    const int tok0 = tile * tokens_per_tile;
+    const int tile_tokens = min(tokens_per_tile, seq_new - tok0);
+
+    // this thread's two rows: g and g + 8
+    int row_pos[2], row_first[2];
+    size_t row_q[2];
+    bool row_ok[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = g + 8 * i;
+        const int local = r / group;
+        row_ok[i] = local < tile_tokens;
+        const int token = seq_begin + tok0 + local, head = kh * group + (r - local * group);
+        row_q[i] = ((size_t)token * heads + head) * HD;
+        row_pos[i] = row_ok[i] ? before + tok0 + local : -1;
+        row_first[i] = (window > 0 && row_pos[i] - window + 1 > 0) ? row_pos[i] - window + 1 : 0;
+    }
+
+    // the blocks of keys this tile needs, and this slice's share of them
+    const int lo_pos = before + tok0, hi_pos = before + tok0 + tile_tokens - 1;
+    const int lo_key = (window > 0 && lo_pos - window + 1 > 0) ? lo_pos - window + 1 : 0;
+    const int block0 = lo_key / TT_BLOCK_TOKENS, block1 = hi_pos / TT_BLOCK_TOKENS;
+    const int per = (block1 - block0 + 1 + splits - 1) / splits;
+    const int my_begin = block0 + split * per, my_end = min(block1 + 1, my_begin + per);
+
+    // Q fragments, head dimension permuted: chunk c, registers 0..3 = dims 32c + 8t + {0,1},{2,3},{4,5},{6,7}
+    uint32_t qa[KC][4], qb[KC][4];
+#pragma unroll
+    for (int c = 0; c < KC; ++c) {
+        const uint4 zero = make_uint4(0, 0, 0, 0);
+        const uint4 va = row_ok[0] ? load16(q + row_q[0] + 32 * c + 8 * t) : zero;
+        const uint4 vb = row_ok[1] ? load16(q + row_q[1] + 32 * c + 8 * t) : zero;
+        qa[c][0] = va.x; qa[c][1] = va.y; qa[c][2] = va.z; qa[c][3] = va.w;
+        qb[c][0] = vb.x; qb[c][1] = vb.y; qb[c][2] = vb.z; qb[c][3] = vb.w;
+    }
+
+    float o[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f; }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+    const int* table_row = table + (size_t)b * table_width;
+
+    for (int kb = my_begin; kb < my_end; ++kb) {
+        const int block = table_row[kb];
+        if (block < 0 || block >= pool_blocks) {
+            if (lane == 0) atomicOr(status, TT_STATUS_BAD_BLOCK);
+            continue;
+        }
+        const __nv_bfloat16* kbase = k_pool + ((size_t)block * kv_heads + kh) * TT_BLOCK_TOKENS * HD;
+        const __nv_bfloat16* vbase = v_pool + ((size_t)block * kv_heads + kh) * HD * TT_BLOCK_TOKENS;
+
+        // S = Q K^T for the block's 64 keys: 8 tiles of 8 keys
+        float s[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+            const __nv_bfloat16* krow = kbase + (size_t)key_of(j, g) * HD + 8 * t;
+#pragma unroll
+            for (int c = 0; c < KC; ++c) {
+                const uint4 kr = load16(krow + 32 * c);
+                mma_bf16(s[j], qa[c][0], qb[c][0], qa[c][1], qb[c][1], kr.x, kr.y);
+                mma_bf16(s[j], qa[c][2], qb[c][2], qa[c][3], qb[c][3], kr.z, kr.w);
+            }
+        }
+
+        // scale, mask (causal, window), running softmax; rows g (i = 0) and g + 8 (i = 1)
+        const int key_base = kb * TT_BLOCK_TOKENS;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int key = key_base + key_of(j, 2 * t + e);
+                    const bool seen = key <= row_pos[i] && key >= row_first[i];
+                    const float v = seen ? s[j][2 * i + e] * scale_log2 : -INFINITY;
+                    s[j][2 * i + e] = v;
+                    mx = fmaxf(mx, v);
+                }
+            }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m_run[i], mx);
+            const float corr = (m_new == -INFINITY) ? 1.0f : exp2f(m_run[i] - m_new);
+            const float base = (m_new == -INFINITY) ? 0.0f : m_new;
+            float sum = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const float p = exp2f(s[j][2 * i + e] - base);
+                    s[j][2 * i + e] = p;
+                    sum += p;
+                }
+            }
+            l_run[i] = l_run[i] * corr + sum;
+            m_run[i] = m_new;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) { o[n][2 * i] *= corr; o[n][2 * i + 1] *= corr; }
+        }
+
+        // O += P V: four products of 16 keys each per output tile
+        uint32_t pa[4][4];
+#pragma unroll
+        for (int mm = 0; mm < 4; ++mm) {
+            pa[mm][0] = pack_bf16(s[2 * mm][0], s[2 * mm][1]);
+            pa[mm][1] = pack_bf16(s[2 * mm][2], s[2 * mm][3]);
+            pa[mm][2] = pack_bf16(s[2 * mm + 1][0], s[2 * mm + 1][1]);
+            pa[mm][3] = pack_bf16(s[2 * mm + 1][2], s[2 * mm + 1][3]);
+        }
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+            const __nv_bfloat16* vrow = vbase + (size_t)(8 * n + g) * TT_BLOCK_TOKENS + 8 * t;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const uint4 vr = load16(vrow + 32 * half);
+                mma_bf16(o[n], pa[2 * half][0], pa[2 * half][1], pa[2 * half][2], pa[2 * half][3], vr.x, vr.y);
+                mma_bf16(o[n], pa[2 * half + 1][0], pa[2 * half + 1][1], pa[2 * half + 1][2], pa[2 * half + 1][3], vr.z, vr.w);
+            }
+        }
+    }
+
+    // row sums live spread over the four threads of a quad
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        if (!row_ok[i]) continue;
+        if (splits == 1) {
+            const float inv = l_run[i] > 0.0f ? 1.0f / l_run[i] : 0.0f;
+            __nv_bfloat16* dst = out + row_q[i] + 2 * t;
+#pragma unroll
+            for (int n = 0; n < NT; ++n)
+                *reinterpret_cast<uint32_t*>(dst + 8 * n) = pack_bf16(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
+        } else {
+            const size_t slot = (row_q[i] / HD) * splits + split;          // (token * heads + head) * splits + split
+            float* dst = part_acc + slot * HD + 2 * t;
+#pragma unroll
+            for (int n = 0; n < NT; ++n)
+                *reinterpret_cast<float2*>(dst + 8 * n) = make_float2(o[n][2 * i], o[n][2 * i + 1]);
+            if (t == 0) {
+                part_ml[slot * 2] = m_run[i] * 0.6931471805599453f;          // the merge works with natural exponents
+                part_ml[slot * 2 + 1] = l_run[i];
+            }
+        }
+    }
+}
+
+template <int HD>
+int launch(const void* q, const void* k_pool, const void* v_pool, const int* table, int table_width, int pool_blocks,
+           const int* cu, const int* len_before, int sequences, int n_tokens, int heads, int kv_heads, float scale,
+           int window, int splits, void* out, float* part_acc, float* part_ml, unsigned* status, cudaStream_t stream) {
+    const int group = heads / kv_heads;
+    const int tokens_per_tile = 16 / group;
+    const int tiles = (n_tokens + tokens_per_tile - 1) / tokens_per_tile + sequences;   // upper bound; spare warps leave at once
+    const dim3 grid((tiles + MMA_WARPS - 1) / MMA_WARPS, kv_heads, splits);
+    attention_mma_kernel<HD><<<grid, MMA_WARPS * 32, 0, stream>>>(
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, table, table_width, pool_blocks, cu,
+        len_before, sequences, heads, kv_heads, scale * 1.4426950408889634f, window, splits, tokens_per_tile,
+        (__nv_bfloat16*)out, part_acc, part_ml, status);
+    if (splits > 1) {
+        const long long rows = (long long)n_tokens * heads;
+        attention_merge_kernel<__nv_bfloat16><<<(unsigned)((rows + ATTN_WARPS - 1) / ATTN_WARPS), ATTN_WARPS * 32, 0, stream>>>(
+            part_acc, part_ml, splits, HD, rows, (__nv_bfloat16*)out);
+    }
+    return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+// 1 if this kernel takes the sizes, 0 if the exact kernel has to serve them.
+extern "C" int tt_attention_mma_supports(int heads, int kv_heads, int head_dim) {
+    if (kv_heads <= 0 || heads % kv_heads || heads / kv_heads > 16) return 0;
+    return head_dim == 32 || head_dim == 64 || head_dim == 96 || head_dim == 128;
+}
+
+extern "C" int tt_attention_mma(const void* q, const void* k_pool, const void* v_pool, const int* table, int table_width,
+                                int pool_blocks, const int* cu, const int* len_before, int sequences, int n_tokens,
+                                int heads, int kv_heads, int head_dim, float scale, int window, int splits, void* out,
+                                float* part_acc, float* part_ml, unsigned* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (!tt_attention_mma_supports(heads, kv_heads, head_dim) || splits < 1 || splits > 65535 || kv_heads > 65535)
+        return (int)cudaErrorInvalidValue;
+    if (splits > 1 && (!part_acc || !part_ml)) return (int)cudaErrorInvalidValue;
+#define TT_LAUNCH(HD) return launch<HD>(q, k_pool, v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, scale, window, splits, out, part_acc, part_ml, status, stream)
+    switch (head_dim) {
+        case 32: TT_LAUNCH(32);
+        case 64: TT_LAUNCH(64);
+        case 96: TT_LAUNCH(96);
+        default: TT_LAUNCH(128);
+    }
+#undef TT_LAUNCH
+}

@@ -78,9 +78,14 @@ __device__ __forceinline__ int tt_find_sequence(const int* __restrict__ cu, int 
     return lo;
 }
 
-// Address of token `position` of a sequence in a block pool laid out
-// [block][kv_head][TT_BLOCK_TOKENS][head_dim]; returns -1 and raises the status bit
-// when the table entry is outside the pool.
+// The cache of one layer is two block pools.  Keys:   [block][kv_head][TT_BLOCK_TOKENS][head_dim]
+// (a token's head vector is contiguous).  Values: [block][kv_head][head_dim][TT_BLOCK_TOKENS]
+// (transposed: the 64 tokens of one head dimension are contiguous, which is the operand
+// order the P @ V tensor-core product reads straight from global memory).
+//
+// tt_cache_offset: element offset of a key vector; tt_value_offset: element offset of
+// value dimension 0 of a token, dimension d lies d * TT_BLOCK_TOKENS elements further.
+// Both return -1 and raise the status bit when the table entry is outside the pool.
 __device__ __forceinline__ long long tt_cache_offset(const int* __restrict__ table_row, int position, int kv_head,
                                                      int kv_heads, int head_dim, int pool_blocks,
                                                      unsigned* status) {
@@ -90,4 +95,15 @@ __device__ __forceinline__ long long tt_cache_offset(const int* __restrict__ tab
         return -1;
     }
     return (((long long)block * kv_heads + kv_head) * TT_BLOCK_TOKENS + (position % TT_BLOCK_TOKENS)) * head_dim;
+}
+
+__device__ __forceinline__ long long tt_value_offset(const int* __restrict__ table_row, int position, int kv_head,
+                                                     int kv_heads, int head_dim, int pool_blocks,
+                                                     unsigned* status) {
+    const int block = table_row[position / TT_BLOCK_TOKENS];
+    if (block < 0 || block >= pool_blocks) {
+        if (status) atomicOr(status, TT_STATUS_BAD_BLOCK);
+        return -1;
+    }
+    return ((long long)block * kv_heads + kv_head) * head_dim * TT_BLOCK_TOKENS + (position % TT_BLOCK_TOKENS);
 }

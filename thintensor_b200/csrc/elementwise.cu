@@ -103,7 +103,8 @@ extern "C" int tt_add_rmsnorm(float* residual, const float* delta, int splits, l
 // rotary encoding + cache append.
 // qkv: float32 [splits][tokens][q_cols + 2 * kv_cols] partial sums of the projection.
 // For token t of sequence b at position p = len_before[b] + (t - cu[b]):
-//   q' -> q_out[t] (activation dtype), k' -> key pool at p, v -> value pool at p.
+//   q' -> q_out[t] (activation dtype), k' -> key pool at p, v -> value pool at p
+//   (values are stored transposed inside a block, see common.cuh).
 // Rotation on the first rotary_dim numbers of each head, halves convention:
 //   a' = a cos - b sin, b' = b cos + a sin, angle = inv_freq[i] * float(p) in float32.
 // kv_cols == 0: the projection holds queries only and nothing is appended (a layer that
@@ -179,8 +180,8 @@ __global__ void rope_append_kernel(const float* __restrict__ qkv, int splits, si
         const int col = q_cols + kv_cols + w;
         float a = 0.0f;
         for (int s = 0; s < splits; ++s) a += row[s * split_stride + col];
-        const long long off = tt_cache_offset(table_row, pos, kh, kv_heads, head_dim, pool_blocks, status);
-        if (off >= 0) v_pool[off + i] = tt_from_float<TAct>(a);
+        const long long off = tt_value_offset(table_row, pos, kh, kv_heads, head_dim, pool_blocks, status);
+        if (off >= 0) v_pool[off + (long long)i * TT_BLOCK_TOKENS] = tt_from_float<TAct>(a);
     }
 }
 

@@ -177,6 +177,28 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table
               _ptr(part_acc), _ptr(part_ml), _ptr(status), _stream()), "attention", 2 if splits > 1 else 1)
 
 
+def attention_mma_supports(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int) -> bool:
+    """Whether the tensor-core attention kernel takes these sizes (bfloat16, head size 32,
+    64, 96 or 128, at most 16 query heads per key/value head)."""
+    return dtype == torch.bfloat16 and head_dim in (32, 64, 96, 128) and heads % kv_heads == 0 and heads // kv_heads <= 16
+
+
+def attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor, cu: torch.Tensor,
+                  len_before: torch.Tensor, sequences: int, n_tokens: int, heads: int, kv_heads: int, head_dim: int,
+                  scale: float, window: int, splits: int, out: torch.Tensor, part_acc: torch.Tensor | None,
+                  part_ml: torch.Tensor | None, status: torch.Tensor) -> None:
+    """Causal attention of packed bfloat16 query tokens over the block cache on tensor cores."""
+    if not attention_mma_supports(q.dtype, heads, kv_heads, head_dim):
+        raise KernelError(f"the tensor-core attention kernel does not take {q.dtype}, {heads}/{kv_heads} heads of size {head_dim}")
+    if not (k_pool.dtype == v_pool.dtype == out.dtype == torch.bfloat16):
+        raise KernelError("queries, cache and output must all be bfloat16")
+    fn = _fn("attention_mma", "tt_attention_mma", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
+                                                   c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(table), table.shape[1], k_pool.shape[0], _ptr(cu), _ptr(len_before), sequences,
+              n_tokens, heads, kv_heads, head_dim, scale, window, splits, _ptr(out), _ptr(part_acc), _ptr(part_ml), _ptr(status),
+              _stream()), "attention_mma", 2 if splits > 1 else 1)
+
+
 # -------------------------------------------------------------------------------- gemm
 def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor) -> None:
     """out[s] = x @ w[:, k-slice s].T in float32 FMA; ``out`` is float32

@@ -33,7 +33,7 @@ SOURCES: dict[str, list[str]] = {
     "sampling": [],
     "attention_static_scratch": [],
     "gemm_tcgen05": [],
-    # "attention_mma": [],
+    "attention_mma": [],
 }
 
 

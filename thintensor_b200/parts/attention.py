@@ -17,14 +17,14 @@ from .linear import Linear
 from .spec import PartSpec
 
 
-def kv_splits(ctx, heads: int, sm_count: int = 148) -> int:
+def kv_splits(ctx, parallel_units: int, keys_per_slice: int, sm_count: int = 148) -> int:
     """Into how many slices the keys of a decode step are cut so that the grid fills the
-    GPU.  Depends only on the step's shape, not on the lengths on the device."""
-    rows = ctx.n_tokens * heads
-    if not ctx.decode or rows >= 4 * sm_count:
+    GPU: ``parallel_units`` is how many warps the step has without slicing.  Depends only
+    on the step's shape and the length bound, never on the lengths on the device."""
+    if not ctx.decode:
         return 1
-    want = -(-4 * sm_count * 4 // max(rows, 1))           # 4 warps per block, ~4 blocks per SM
-    most = max(1, ctx.max_total // 256)                    # at least 256 keys per slice
+    want = -(-8 * sm_count // max(parallel_units, 1))       # about eight warps per SM
+    most = max(1, ctx.max_total // keys_per_slice)
     return max(1, min(want, most, 64))
 
 
@@ -90,10 +90,17 @@ class CausalAttention(Mixer):
         return Delta(self.out(ctx, mixed, "attention.out"))
 
     def attend(self, ctx, q, cache, table, mixed) -> None:
-        splits = kv_splits(ctx, self.heads)
+        """Tensor cores where the kernel takes the sizes (bfloat16, head size 32/64/96/128,
+        groups up to 16), the exact kernel otherwise."""
+        tensor_cores = api.attention_mma_supports(q.dtype, self.heads, self.kv_heads, self.head_dim)
+        if tensor_cores:
+            splits = kv_splits(ctx, ctx.sequences * self.kv_heads, 128)
+        else:
+            splits = kv_splits(ctx, ctx.n_tokens * self.heads, 256)
         part_acc = part_ml = None
         if splits > 1:
             part_acc = ctx.scratch("attention.part_acc", (ctx.n_tokens * self.heads * splits * self.head_dim,), torch.float32)
             part_ml = ctx.scratch("attention.part_ml", (ctx.n_tokens * self.heads * splits * 2,), torch.float32)
-        api.attention(q, cache.k_pool, cache.v_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads,
-                      self.kv_heads, self.head_dim, self.scale, self.window or 0, splits, mixed, part_acc, part_ml, ctx.status)
+        kernel = api.attention_mma if tensor_cores else api.attention
+        kernel(q, cache.k_pool, cache.v_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads,
+               self.kv_heads, self.head_dim, self.scale, self.window or 0, splits, mixed, part_acc, part_ml, ctx.status)
