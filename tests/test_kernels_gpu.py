@@ -48,7 +48,7 @@ def test_embed_gather(dtype):
 
 # ----------------------------------------------------------------------------------- norm
 @pytest.mark.parametrize("out_dtype", DTYPES)
-@pytest.mark.parametrize("hidden,splits", [(72, 0), (1000, 1), (2048, 3), (12000, 2)])
+@pytest.mark.parametrize("hidden,splits", [(72, 0), (1000, 1), (1002, 5), (2048, 3), (2048, 16), (12000, 2), (20000, 1)])
 def test_add_rmsnorm(out_dtype, hidden, splits):
     from thintensor_b200.kernels import api
 
@@ -325,7 +325,7 @@ def test_gemm_simt(x_dtype, w_dtype, m, n, k, splits):
 
 
 # ------------------------------------------------------------------------------- sampling
-@pytest.mark.parametrize("vocab", [311, 1000, 128256])
+@pytest.mark.parametrize("vocab", [311, 1000, 8192, 128256])
 def test_argmax_lowest_id_on_ties(vocab):
     from thintensor_b200.kernels import api
 

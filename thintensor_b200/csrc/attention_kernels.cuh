@@ -134,28 +134,42 @@ __global__ void attention_rows_kernel(const T* __restrict__ q, const T* __restri
 }
 
 // out[t, h, :] = sum_s acc_s * exp(m_s - M) / sum_s l_s * exp(m_s - M), M = max_s m_s.
+// One warp per row.  Lanes first take one slice each to find M and the weights, then all
+// lanes walk the slices' accumulators with independent loads; the additions run in slice
+// order, so the result does not depend on the grid.
 template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                        int splits, int head_dim, long long rows, T* __restrict__ out) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long row = (long long)blockIdx.x * ATTN_WARPS + warp;
     if (row >= rows) return;
+    const float* ml = part_ml + (size_t)row * splits * 2;
     float m = -INFINITY;
-    for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[((size_t)row * splits + s) * 2]);
+    for (int s = lane; s < splits; s += 32) m = fmaxf(m, __ldg(ml + 2 * s));
+    m = tt_warp_max(m);
     float l = 0.0f;
     float acc[ATTN_MAX_HEAD_DIM / 32];
 #pragma unroll
     for (int i = 0; i < ATTN_MAX_HEAD_DIM / 32; ++i) acc[i] = 0.0f;
-    for (int s = 0; s < splits; ++s) {
-        const size_t slot = (size_t)row * splits + s;
-        const float ms = part_ml[slot * 2];
-        if (ms == -INFINITY) continue;
-        const float w = expf(ms - m);
-        l += part_ml[slot * 2 + 1] * w;
+    for (int s0 = 0; s0 < splits; s0 += 32) {
+        // this lane's slice of the group of 32: its weight and its share of the denominator
+        const int mine = s0 + lane;
+        float w_mine = 0.0f, l_mine = 0.0f;
+        if (mine < splits) {
+            const float ms = __ldg(ml + 2 * mine);
+            if (ms != -INFINITY) { w_mine = expf(ms - m); l_mine = __ldg(ml + 2 * mine + 1) * w_mine; }
+        }
+        const int count = min(32, splits - s0);
+        for (int j = 0; j < count; ++j) l += __shfl_sync(0xffffffffu, l_mine, j);
+#pragma unroll 4
+        for (int j = 0; j < count; ++j) {
+            const float w = __shfl_sync(0xffffffffu, w_mine, j);
+            const float* a = part_acc + ((size_t)row * splits + s0 + j) * head_dim;
 #pragma unroll
-        for (int i = 0; i < ATTN_MAX_HEAD_DIM / 32; ++i) {
-            const int d = lane + 32 * i;
-            if (d < head_dim) acc[i] = fmaf(part_acc[slot * head_dim + d], w, acc[i]);
+            for (int i = 0; i < ATTN_MAX_HEAD_DIM / 32; ++i) {
+                const int d = lane + 32 * i;
+                if (d < head_dim) acc[i] = fmaf(__ldg(a + d), w, acc[i]);
+            }
         }
     }
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;

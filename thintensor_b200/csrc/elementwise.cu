@@ -84,14 +84,84 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __
     }
 }
 
+// The same for hidden sizes that are multiples of 4 up to 16384: every thread keeps its
+// (up to four) float4 pieces of the row in registers, all loads of the k-slices are
+// independent, and the order of additions is the one of the kernel above.
+#define NORM_VEC_MAX 4
+template <typename TOut>
+__global__ void __launch_bounds__(1024)
+add_rmsnorm_vec_kernel(float* __restrict__ residual, const float* __restrict__ delta, int splits, size_t split_stride,
+                       const float* __restrict__ weight, float weight_offset, float eps, TOut* __restrict__ out,
+                       const int* __restrict__ rows, int hidden) {
+    __shared__ float reduce[32];
+    const int i = blockIdx.x;
+    const int r = rows ? rows[i] : i;
+    const int quads = hidden >> 2;
+    float4* res = reinterpret_cast<float4*>(residual + (size_t)r * hidden);
+    const float4* del = delta ? reinterpret_cast<const float4*>(delta + (size_t)r * hidden) : nullptr;
+    const size_t stride4 = split_stride >> 2;
+    float4 x[NORM_VEC_MAX];
+    float sumsq = 0.0f;
+#pragma unroll
+    for (int v = 0; v < NORM_VEC_MAX; ++v) {
+        const int j = threadIdx.x + v * blockDim.x;
+        if (j < quads) {
+            float4 a = res[j];
+            int s = 0;
+            for (; s + 4 <= splits; s += 4) {
+                const float4 d0 = __ldg(del + (size_t)s * stride4 + j), d1 = __ldg(del + (size_t)(s + 1) * stride4 + j);
+                const float4 d2 = __ldg(del + (size_t)(s + 2) * stride4 + j), d3 = __ldg(del + (size_t)(s + 3) * stride4 + j);
+                a.x = (((a.x + d0.x) + d1.x) + d2.x) + d3.x;
+                a.y = (((a.y + d0.y) + d1.y) + d2.y) + d3.y;
+                a.z = (((a.z + d0.z) + d1.z) + d2.z) + d3.z;
+                a.w = (((a.w + d0.w) + d1.w) + d2.w) + d3.w;
+            }
+            for (; s < splits; ++s) {
+                const float4 d0 = __ldg(del + (size_t)s * stride4 + j);
+                a.x += d0.x; a.y += d0.y; a.z += d0.z; a.w += d0.w;
+            }
+            if (!rows && splits > 0) res[j] = a;
+            x[v] = a;
+            sumsq += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+        }
+    }
+    const float total = tt_block_sum(sumsq, reduce);
+    const float rstd = rsqrtf(total / (float)hidden + eps);
+    TOut* o = out + (size_t)i * hidden;
+    const float4* w4 = reinterpret_cast<const float4*>(weight);
+#pragma unroll
+    for (int v = 0; v < NORM_VEC_MAX; ++v) {
+        const int j = threadIdx.x + v * blockDim.x;
+        if (j < quads) {
+            const float4 w = __ldg(w4 + j);
+            const float y0 = x[v].x * rstd * (w.x + weight_offset), y1 = x[v].y * rstd * (w.y + weight_offset);
+            const float y2 = x[v].z * rstd * (w.z + weight_offset), y3 = x[v].w * rstd * (w.w + weight_offset);
+            o[4 * j] = tt_from_float<TOut>(y0);
+            o[4 * j + 1] = tt_from_float<TOut>(y1);
+            o[4 * j + 2] = tt_from_float<TOut>(y2);
+            o[4 * j + 3] = tt_from_float<TOut>(y3);
+        }
+    }
+}
+
 extern "C" int tt_add_rmsnorm(float* residual, const float* delta, int splits, long long split_stride,
                               const float* weight, float weight_offset, float eps, void* out, int out_dtype,
                               const int* rows, int n_rows, int hidden, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
+    if (!delta) splits = 0;
+    if (hidden % 4 == 0 && hidden <= 4096 * NORM_VEC_MAX && split_stride % 4 == 0 && ((uintptr_t)residual & 15) == 0 &&
+        ((uintptr_t)delta & 15) == 0 && ((uintptr_t)weight & 15) == 0) {
+        int threads = ((hidden / 4 + 31) / 32) * 32;
+        if (threads > 1024) threads = 1024;
+        if (out_dtype == TT_F32)
+            add_rmsnorm_vec_kernel<float><<<n_rows, threads, 0, stream>>>(residual, delta, splits, (size_t)split_stride, weight, weight_offset, eps, (float*)out, rows, hidden);
+        else
+            add_rmsnorm_vec_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(residual, delta, splits, (size_t)split_stride, weight, weight_offset, eps, (__nv_bfloat16*)out, rows, hidden);
+        TT_LAUNCH_CHECK();
+    }
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     const int row_cache = hidden <= 11264 ? hidden : 11264;  // 44 KB of the default 48 KB
     const size_t shared = (size_t)(row_cache + 32) * sizeof(float);
-    if (!delta) splits = 0;
     if (out_dtype == TT_F32)
         add_rmsnorm_kernel<float><<<n_rows, threads, shared, stream>>>(residual, delta, splits, (size_t)split_stride, weight, weight_offset, eps, (float*)out, rows, hidden, row_cache);
     else
@@ -110,6 +180,21 @@ extern "C" int tt_add_rmsnorm(float* residual, const float* delta, int splits, l
 // kv_cols == 0: the projection holds queries only and nothing is appended (a layer that
 // reads another layer's cache).
 // ------------------------------------------------------------------------------------
+// sum of one element over the k-slices of a projection: independent loads, fixed order of additions
+__device__ __forceinline__ float sum_slices(const float* __restrict__ p, int splits, size_t split_stride) {
+    float total = 0.0f;
+    int s = 0;
+    for (; s + 4 <= splits; s += 4) {
+        const float a = __ldg(p + (size_t)s * split_stride), b = __ldg(p + (size_t)(s + 1) * split_stride);
+        const float c = __ldg(p + (size_t)(s + 2) * split_stride), d = __ldg(p + (size_t)(s + 3) * split_stride);
+        total = (((total + a) + b) + c) + d;
+    }
+    for (; s < splits; ++s) total += __ldg(p + (size_t)s * split_stride);
+    return total;
+}
+
+// One thread per item of a token: a rotated pair of q or k, a number beyond the rotary
+// part, or a value.  grid = (tokens, ceil(items / blockDim.x)).
 template <typename TAct>
 __global__ void rope_append_kernel(const float* __restrict__ qkv, int splits, size_t split_stride,
                                    const float* __restrict__ inv_freq,
@@ -118,19 +203,10 @@ __global__ void rope_append_kernel(const float* __restrict__ qkv, int splits, si
                                    const int* __restrict__ table, int table_width, int pool_blocks,
                                    const int* __restrict__ cu, const int* __restrict__ len_before, int sequences,
                                    int heads, int kv_heads, int head_dim, int write_cache, unsigned* status) {
-    extern __shared__ float cs[];  // cos[rotary_dim / 2], sin[rotary_dim / 2]
     const int t = blockIdx.x;
     const int b = tt_find_sequence(cu, sequences, t);
     const int pos = len_before[b] + (t - cu[b]);
     const int half = rotary_dim >> 1;
-    for (int i = threadIdx.x; i < half; i += blockDim.x) {
-        const float angle = inv_freq[i] * (float)pos;
-        float s, c;
-        sincosf(angle, &s, &c);
-        cs[i] = c * attention_scaling;
-        cs[half + i] = s * attention_scaling;
-    }
-    __syncthreads();
     const int q_cols = heads * head_dim;
     const int kv_cols = write_cache ? kv_heads * head_dim : 0;
     const int cols = q_cols + 2 * kv_cols;
@@ -138,48 +214,47 @@ __global__ void rope_append_kernel(const float* __restrict__ qkv, int splits, si
     const int* table_row = table + (size_t)b * table_width;
     const int rot_heads = heads + (write_cache ? kv_heads : 0);
     const int pass = head_dim - rotary_dim;  // numbers of a head that are not rotated
-    // rotated pairs of q and k
-    for (int w = threadIdx.x; w < rot_heads * half; w += blockDim.x) {
+    const int n_rot = rot_heads * half, n_pass = rot_heads * pass;
+    int w = blockIdx.y * blockDim.x + threadIdx.x;
+    if (w < n_rot) {
         const int head = w / half, i = w - head * half;
         const int col = head * head_dim + i;  // k heads follow q heads in the row
-        float a = 0.0f, c2 = 0.0f;
-        for (int s = 0; s < splits; ++s) {
-            a += row[s * split_stride + col];
-            c2 += row[s * split_stride + col + half];
-        }
-        const float co = cs[i], si = cs[half + i];
+        const float a = sum_slices(row + col, splits, split_stride);
+        const float c2 = sum_slices(row + col + half, splits, split_stride);
+        float si, co;
+        sincosf(inv_freq[i] * (float)pos, &si, &co);
+        co *= attention_scaling;
+        si *= attention_scaling;
         const float ra = a * co - c2 * si, rb = c2 * co + a * si;
         if (head < heads) {
             q_out[(size_t)t * q_cols + col] = tt_from_float<TAct>(ra);
             q_out[(size_t)t * q_cols + col + half] = tt_from_float<TAct>(rb);
         } else {
-            const int kh = head - heads;
-            const long long off = tt_cache_offset(table_row, pos, kh, kv_heads, head_dim, pool_blocks, status);
+            const long long off = tt_cache_offset(table_row, pos, head - heads, kv_heads, head_dim, pool_blocks, status);
             if (off >= 0) {
                 k_pool[off + i] = tt_from_float<TAct>(ra);
                 k_pool[off + i + half] = tt_from_float<TAct>(rb);
             }
         }
+        return;
     }
-    // numbers beyond the rotary part pass through
-    for (int w = threadIdx.x; w < rot_heads * pass; w += blockDim.x) {
+    w -= n_rot;
+    if (w < n_pass) {
         const int head = w / pass, i = rotary_dim + (w - head * pass);
         const int col = head * head_dim + i;
-        float a = 0.0f;
-        for (int s = 0; s < splits; ++s) a += row[s * split_stride + col];
+        const float a = sum_slices(row + col, splits, split_stride);
         if (head < heads) {
             q_out[(size_t)t * q_cols + col] = tt_from_float<TAct>(a);
         } else {
             const long long off = tt_cache_offset(table_row, pos, head - heads, kv_heads, head_dim, pool_blocks, status);
             if (off >= 0) k_pool[off + i] = tt_from_float<TAct>(a);
         }
+        return;
     }
-    // values
-    for (int w = threadIdx.x; w < kv_cols; w += blockDim.x) {
+    w -= n_pass;
+    if (w < kv_cols) {
         const int kh = w / head_dim, i = w - kh * head_dim;
-        const int col = q_cols + kv_cols + w;
-        float a = 0.0f;
-        for (int s = 0; s < splits; ++s) a += row[s * split_stride + col];
+        const float a = sum_slices(row + q_cols + kv_cols + w, splits, split_stride);
         const long long off = tt_value_offset(table_row, pos, kh, kv_heads, head_dim, pool_blocks, status);
         if (off >= 0) v_pool[off + (long long)i * TT_BLOCK_TOKENS] = tt_from_float<TAct>(a);
     }
@@ -193,13 +268,15 @@ extern "C" int tt_rope_append(const float* qkv, int splits, long long split_stri
                               cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return (int)cudaErrorInvalidValue;
-    const int work = (heads + kv_heads) * head_dim / 2;
-    const int threads = work >= 512 ? 256 : 128;
-    const size_t shared = (size_t)(rotary_dim > 0 ? rotary_dim : 2) * sizeof(float);
+    const int rot_heads = heads + (write_cache ? kv_heads : 0);
+    const int items = rot_heads * (rotary_dim / 2) + rot_heads * (head_dim - rotary_dim) + (write_cache ? kv_heads * head_dim : 0);
+    const int threads = 128;
+    const dim3 grid(n_tokens, (items + threads - 1) / threads);
+    if (grid.y > 65535) return (int)cudaErrorInvalidValue;
     if (act_dtype == TT_F32)
-        rope_append_kernel<float><<<n_tokens, threads, shared, stream>>>(qkv, splits, (size_t)split_stride, inv_freq, rotary_dim, attention_scaling, (float*)q_out, (float*)k_pool, (float*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, heads, kv_heads, head_dim, write_cache, status);
+        rope_append_kernel<float><<<grid, threads, 0, stream>>>(qkv, splits, (size_t)split_stride, inv_freq, rotary_dim, attention_scaling, (float*)q_out, (float*)k_pool, (float*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, heads, kv_heads, head_dim, write_cache, status);
     else
-        rope_append_kernel<__nv_bfloat16><<<n_tokens, threads, shared, stream>>>(qkv, splits, (size_t)split_stride, inv_freq, rotary_dim, attention_scaling, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, heads, kv_heads, head_dim, write_cache, status);
+        rope_append_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(qkv, splits, (size_t)split_stride, inv_freq, rotary_dim, attention_scaling, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, heads, kv_heads, head_dim, write_cache, status);
     TT_LAUNCH_CHECK();
 }
 

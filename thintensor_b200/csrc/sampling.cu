@@ -56,9 +56,75 @@ argmax_rows_kernel(const float* __restrict__ logits, long long ld, int vocab, in
     }
 }
 
-extern "C" int tt_argmax_rows(const float* logits, long long ld, int n_rows, int vocab, int* out, cudaStream_t stream) {
+// Two stages for large vocabularies: ARGMAX_CHUNKS blocks per row each reduce a slice to
+// (value, id) in `scratch`, then one warp per row reduces those; the comparison rule
+// (larger value, lower id on ties) is the same at every level.
+#define ARGMAX_CHUNKS 32
+
+__global__ void __launch_bounds__(256)
+argmax_stage1_kernel(const float* __restrict__ logits, long long ld, int vocab, float* __restrict__ scratch_v,
+                     int* __restrict__ scratch_i) {
+    __shared__ float best_v[8];
+    __shared__ int best_i[8];
+    const float* row = logits + (size_t)blockIdx.y * ld;
+    const int per = (vocab + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS;
+    const int lo = blockIdx.x * per, hi = min(vocab, lo + per);
+    float v = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int j = lo + threadIdx.x; j < hi; j += blockDim.x) {
+        const float x = row[j];
+        if (idx == 0x7fffffff || x > v) { v = x; idx = j; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (oi != 0x7fffffff && (idx == 0x7fffffff || ov > v || (ov == v && oi < idx))) { v = ov; idx = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { best_v[warp] = v; best_i[warp] = idx; }
+    __syncthreads();
+    if (warp == 0) {
+        v = lane < 8 ? best_v[lane] : -INFINITY;
+        idx = lane < 8 ? best_i[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (oi != 0x7fffffff && (idx == 0x7fffffff || ov > v || (ov == v && oi < idx))) { v = ov; idx = oi; }
+        }
+        if (lane == 0) {
+            scratch_v[blockIdx.y * ARGMAX_CHUNKS + blockIdx.x] = v;
+            scratch_i[blockIdx.y * ARGMAX_CHUNKS + blockIdx.x] = idx;
+        }
+    }
+}
+
+__global__ void argmax_stage2_kernel(const float* __restrict__ scratch_v, const int* __restrict__ scratch_i, int n_rows,
+                                     int* __restrict__ out) {
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= n_rows) return;
+    float v = scratch_v[row * ARGMAX_CHUNKS + lane];
+    int idx = scratch_i[row * ARGMAX_CHUNKS + lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (oi != 0x7fffffff && (idx == 0x7fffffff || ov > v || (ov == v && oi < idx))) { v = ov; idx = oi; }
+    }
+    if (lane == 0) out[row] = idx == 0x7fffffff ? 0 : idx;
+}
+
+// scratch: room for n_rows * 32 floats and n_rows * 32 ints (may be null: one block per row then).
+extern "C" int tt_argmax_rows(const float* logits, long long ld, int n_rows, int vocab, int* out, float* scratch_v,
+                              int* scratch_i, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (vocab <= 0) return (int)cudaErrorInvalidValue;
+    if (scratch_v && scratch_i && vocab >= 8192 && n_rows <= 65535) {
+        argmax_stage1_kernel<<<dim3(ARGMAX_CHUNKS, n_rows), 256, 0, stream>>>(logits, ld, vocab, scratch_v, scratch_i);
+        argmax_stage2_kernel<<<(n_rows + 3) / 4, 128, 0, stream>>>(scratch_v, scratch_i, n_rows, out);
+        TT_LAUNCH_CHECK();
+    }
     argmax_rows_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, out);
     TT_LAUNCH_CHECK();
 }

@@ -219,11 +219,24 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, out: 
 
 
 # ---------------------------------------------------------------------------- sampling
+_argmax_scratch: dict[torch.device, tuple[torch.Tensor, torch.Tensor]] = {}
+
+
 def argmax_rows(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """out[i] = argmax of logits[i], lowest id on ties.  Large vocabularies are reduced in
+    two stages through a small scratch buffer kept per device."""
     _need(logits, torch.float32, "logits")
     _need(out, torch.int32, "token output")
-    fn = _fn("sampling", "tt_argmax_rows", [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p])
-    _check(fn(_ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(out), _stream()), "argmax_rows")
+    rows = logits.shape[0]
+    scratch = _argmax_scratch.get(logits.device)
+    if scratch is None or scratch[0].numel() < rows * 32:
+        count = max(rows, 256) * 32
+        scratch = (torch.empty(count, dtype=torch.float32, device=logits.device), torch.empty(count, dtype=torch.int32, device=logits.device))
+        _argmax_scratch[logits.device] = scratch
+    fn = _fn("sampling", "tt_argmax_rows", [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    two_stage = logits.shape[1] >= 8192
+    _check(fn(_ptr(logits), logits.stride(0), rows, logits.shape[1], _ptr(out), _ptr(scratch[0]), _ptr(scratch[1]), _stream()),
+           "argmax_rows", 2 if two_stage else 1)
 
 
 def sample_rows(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, seed: int, request: torch.Tensor,
