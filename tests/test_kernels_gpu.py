@@ -63,7 +63,8 @@ def test_add_rmsnorm(out_dtype, hidden, splits):
     before = residual.clone()
     api.add_rmsnorm(residual, delta, weight, eps, out)
     torch.testing.assert_close(out.double(), want, **tol(out_dtype))
-    torch.testing.assert_close(residual.double(), x, rtol=1e-6, atol=1e-6)
+    # float32 summation of splits + 1 numbers of order one
+    torch.testing.assert_close(residual.double(), x, rtol=1e-6, atol=5e-7 * (splits + 1))
     # gather form: chosen rows, residual left alone
     pick = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
     residual2 = before.clone()
