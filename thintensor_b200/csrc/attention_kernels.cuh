@@ -51,6 +51,8 @@ __global__ void attention_rows_kernel(const T* __restrict__ q, const T* __restri
                                       int sequences, int n_tokens, int heads, int kv_heads, int head_dim, float scale,
                                       int window, int splits, T* __restrict__ out, float* __restrict__ part_acc,
                                       float* __restrict__ part_ml, unsigned* status) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
     extern __shared__ float q_shared[];  // ATTN_WARPS * head_dim
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long row = (long long)blockIdx.x * ATTN_WARPS + warp;  // (token, head)
@@ -140,6 +142,8 @@ __global__ void attention_rows_kernel(const T* __restrict__ q, const T* __restri
 template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                        int splits, int head_dim, long long rows, T* __restrict__ out) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long row = (long long)blockIdx.x * ATTN_WARPS + warp;
     if (row >= rows) return;

@@ -56,6 +56,8 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
                      int heads, int kv_heads, float scale_log2, int window, int splits, int tokens_per_tile,
                      __nv_bfloat16* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml,
                      unsigned* status) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
     constexpr int KC = HD / 32;          // 32-wide chunks of the head dimension
     constexpr int NT = HD / 8;           // 8-wide output tiles
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -232,13 +234,13 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* tab
     const int tokens_per_tile = 16 / group;
     const int tiles = (n_tokens + tokens_per_tile - 1) / tokens_per_tile + sequences;   // upper bound; spare warps leave at once
     const dim3 grid((tiles + MMA_WARPS - 1) / MMA_WARPS, kv_heads, splits);
-    attention_mma_kernel<HD><<<grid, MMA_WARPS * 32, 0, stream>>>(
+    tt_launch_pdl(attention_mma_kernel<HD>, dim3(grid), dim3(MMA_WARPS * 32), 0, stream, 
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, table, table_width, pool_blocks, cu,
         len_before, sequences, heads, kv_heads, scale * 1.4426950408889634f, window, splits, tokens_per_tile,
         (__nv_bfloat16*)out, part_acc, part_ml, status);
     if (splits > 1) {
         const long long rows = (long long)n_tokens * heads;
-        attention_merge_kernel<__nv_bfloat16><<<(unsigned)((rows + ATTN_WARPS - 1) / ATTN_WARPS), ATTN_WARPS * 32, 0, stream>>>(
+        tt_launch_pdl(attention_merge_kernel<__nv_bfloat16>, dim3((unsigned)((rows + ATTN_WARPS - 1) / ATTN_WARPS)), dim3(ATTN_WARPS * 32), 0, stream, 
             part_acc, part_ml, splits, HD, rows, (__nv_bfloat16*)out);
     }
     return (int)cudaGetLastError();

@@ -22,6 +22,32 @@
 
 #define TT_LAUNCH_CHECK() return (int)cudaGetLastError()
 
+// Programmatic dependent launch.  A kernel started through tt_launch_pdl may begin while
+// the kernel before it in the stream is still running; it must call tt_pdl_wait() before
+// it touches anything that kernel (or any earlier one) wrote, and it calls
+// tt_pdl_launch_dependents() as early as it can so that the kernel after it may in turn
+// start its own preamble (for a matrix product: fetching weights, which no kernel of the
+// step writes).  tt_pdl_wait() returns only when every earlier kernel has finished and
+// its writes are visible, so the chain of dependencies stays intact.  Both are no-ops in
+// a kernel that was launched the ordinary way.
+__device__ __forceinline__ void tt_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void tt_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename Kernel, typename... Args>
+static inline cudaError_t tt_launch_pdl(Kernel kernel, dim3 grid, dim3 block, size_t shared, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = shared;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, kernel, args...);
+}
+
 template <typename T> __device__ __forceinline__ float tt_to_float(T v);
 template <> __device__ __forceinline__ float tt_to_float<float>(float v) { return v; }
 template <> __device__ __forceinline__ float tt_to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

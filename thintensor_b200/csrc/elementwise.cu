@@ -16,6 +16,8 @@ template <typename TW>
 __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
                                     float* __restrict__ residual, int hidden, int vocab, float scale,
                                     unsigned* status) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
     const int t = blockIdx.x;
     int id = tokens[t];
     if (id < 0 || id >= vocab) {
@@ -33,9 +35,9 @@ extern "C" int tt_embed_gather(const void* table, int table_dtype, const int* to
     if (n_tokens <= 0) return 0;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (table_dtype == TT_F32)
-        embed_gather_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, tokens, residual, hidden, vocab, scale, status);
+        tt_launch_pdl(embed_gather_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)table, tokens, residual, hidden, vocab, scale, status);
     else
-        embed_gather_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, tokens, residual, hidden, vocab, scale, status);
+        tt_launch_pdl(embed_gather_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, (const __nv_bfloat16*)table, tokens, residual, hidden, vocab, scale, status);
     TT_LAUNCH_CHECK();
 }
 
@@ -53,6 +55,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __
                                    size_t split_stride, const float* __restrict__ weight, float weight_offset,
                                    float eps, TOut* __restrict__ out, const int* __restrict__ rows, int hidden,
                                    int row_cache) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
     extern __shared__ float row_shared[];  // row_cache floats, then 32 for the reduction
     float* reduce = row_shared + row_cache;
     const int i = blockIdx.x;
@@ -93,6 +97,8 @@ __global__ void __launch_bounds__(1024)
 add_rmsnorm_vec_kernel(float* __restrict__ residual, const float* __restrict__ delta, int splits, size_t split_stride,
                        const float* __restrict__ weight, float weight_offset, float eps, TOut* __restrict__ out,
                        const int* __restrict__ rows, int hidden) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
     __shared__ float reduce[32];
     const int i = blockIdx.x;
     const int r = rows ? rows[i] : i;
@@ -154,18 +160,18 @@ extern "C" int tt_add_rmsnorm(float* residual, const float* delta, int splits, l
         int threads = ((hidden / 4 + 31) / 32) * 32;
         if (threads > 1024) threads = 1024;
         if (out_dtype == TT_F32)
-            add_rmsnorm_vec_kernel<float><<<n_rows, threads, 0, stream>>>(residual, delta, splits, (size_t)split_stride, weight, weight_offset, eps, (float*)out, rows, hidden);
+            tt_launch_pdl(add_rmsnorm_vec_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, residual, delta, splits, (size_t)split_stride, weight, weight_offset, eps, (float*)out, rows, hidden);
         else
-            add_rmsnorm_vec_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(residual, delta, splits, (size_t)split_stride, weight, weight_offset, eps, (__nv_bfloat16*)out, rows, hidden);
+            tt_launch_pdl(add_rmsnorm_vec_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, residual, delta, splits, (size_t)split_stride, weight, weight_offset, eps, (__nv_bfloat16*)out, rows, hidden);
         TT_LAUNCH_CHECK();
     }
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     const int row_cache = hidden <= 11264 ? hidden : 11264;  // 44 KB of the default 48 KB
     const size_t shared = (size_t)(row_cache + 32) * sizeof(float);
     if (out_dtype == TT_F32)
-        add_rmsnorm_kernel<float><<<n_rows, threads, shared, stream>>>(residual, delta, splits, (size_t)split_stride, weight, weight_offset, eps, (float*)out, rows, hidden, row_cache);
+        tt_launch_pdl(add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), shared, stream, residual, delta, splits, (size_t)split_stride, weight, weight_offset, eps, (float*)out, rows, hidden, row_cache);
     else
-        add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, shared, stream>>>(residual, delta, splits, (size_t)split_stride, weight, weight_offset, eps, (__nv_bfloat16*)out, rows, hidden, row_cache);
+        tt_launch_pdl(add_rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), shared, stream, residual, delta, splits, (size_t)split_stride, weight, weight_offset, eps, (__nv_bfloat16*)out, rows, hidden, row_cache);
     TT_LAUNCH_CHECK();
 }
 
@@ -203,6 +209,8 @@ __global__ void rope_append_kernel(const float* __restrict__ qkv, int splits, si
                                    const int* __restrict__ table, int table_width, int pool_blocks,
                                    const int* __restrict__ cu, const int* __restrict__ len_before, int sequences,
                                    int heads, int kv_heads, int head_dim, int write_cache, unsigned* status) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
     const int t = blockIdx.x;
     const int b = tt_find_sequence(cu, sequences, t);
     const int pos = len_before[b] + (t - cu[b]);
@@ -274,9 +282,9 @@ extern "C" int tt_rope_append(const float* qkv, int splits, long long split_stri
     const dim3 grid(n_tokens, (items + threads - 1) / threads);
     if (grid.y > 65535) return (int)cudaErrorInvalidValue;
     if (act_dtype == TT_F32)
-        rope_append_kernel<float><<<grid, threads, 0, stream>>>(qkv, splits, (size_t)split_stride, inv_freq, rotary_dim, attention_scaling, (float*)q_out, (float*)k_pool, (float*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, heads, kv_heads, head_dim, write_cache, status);
+        tt_launch_pdl(rope_append_kernel<float>, dim3(grid), dim3(threads), 0, stream, qkv, splits, (size_t)split_stride, inv_freq, rotary_dim, attention_scaling, (float*)q_out, (float*)k_pool, (float*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, heads, kv_heads, head_dim, write_cache, status);
     else
-        rope_append_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(qkv, splits, (size_t)split_stride, inv_freq, rotary_dim, attention_scaling, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, heads, kv_heads, head_dim, write_cache, status);
+        tt_launch_pdl(rope_append_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), 0, stream, qkv, splits, (size_t)split_stride, inv_freq, rotary_dim, attention_scaling, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, heads, kv_heads, head_dim, write_cache, status);
     TT_LAUNCH_CHECK();
 }
 
@@ -287,6 +295,8 @@ extern "C" int tt_rope_append(const float* qkv, int splits, long long split_stri
 template <typename TAct>
 __global__ void swiglu_kernel(const float* __restrict__ gate_up, int splits, size_t split_stride,
                               TAct* __restrict__ act, int inter, size_t total) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const size_t t = idx / inter;
@@ -307,9 +317,9 @@ extern "C" int tt_swiglu(const float* gate_up, int splits, long long split_strid
     const int threads = 256;
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);
     if (act_dtype == TT_F32)
-        swiglu_kernel<float><<<blocks, threads, 0, stream>>>(gate_up, splits, (size_t)split_stride, (float*)act, inter, total);
+        tt_launch_pdl(swiglu_kernel<float>, dim3(blocks), dim3(threads), 0, stream, gate_up, splits, (size_t)split_stride, (float*)act, inter, total);
     else
-        swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(gate_up, splits, (size_t)split_stride, (__nv_bfloat16*)act, inter, total);
+        tt_launch_pdl(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, gate_up, splits, (size_t)split_stride, (__nv_bfloat16*)act, inter, total);
     TT_LAUNCH_CHECK();
 }
 
@@ -317,12 +327,14 @@ extern "C" int tt_swiglu(const float* gate_up, int splits, long long split_strid
 // after a step: len[b] += cu[b + 1] - cu[b]
 // ------------------------------------------------------------------------------------
 __global__ void advance_lengths_kernel(int* __restrict__ len, const int* __restrict__ cu, int sequences) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b < sequences) len[b] += cu[b + 1] - cu[b];
 }
 
 extern "C" int tt_advance_lengths(int* len, const int* cu, int sequences, cudaStream_t stream) {
     if (sequences <= 0) return 0;
-    advance_lengths_kernel<<<(sequences + 127) / 128, 128, 0, stream>>>(len, cu, sequences);
+    tt_launch_pdl(advance_lengths_kernel, dim3((sequences + 127) / 128), dim3(128), 0, stream, len, cu, sequences);
     TT_LAUNCH_CHECK();
 }

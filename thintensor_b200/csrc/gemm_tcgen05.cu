@@ -145,6 +145,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __shared__ uint32_t tmem_base_shared;
     __shared__ int aborted;
 
+    tt_pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_m = blockIdx.y, tile_n = blockIdx.x, split = blockIdx.z;
     const int k_blocks_total = (args.k + BK - 1) / BK;
@@ -170,9 +171,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
+        // The weight operand is written by no kernel of the step, so the first ring of
+        // weight tiles is fetched before waiting for the kernel that produces the
+        // activations; under programmatic dependent launch that fetch overlaps the
+        // tail of the previous kernel.
         if (lane == 0) {
-            int issued = 0;
-            for (int i = 0; i < n_kb; ++i) {
+            constexpr bool weights_are_a = FORM == FEATURES_ON_M;
+            const int first = min(n_kb, STAGES);
+            for (int i = 0; i < first; ++i) {               // stages are empty: nothing to wait for
+                const uint32_t bar = smem_u32(&full_bar[i]);
+                mbar_expect_tx(bar, S::stage_bytes);
+                uint8_t* stage = smem + (size_t)i * S::stage_bytes;
+                const int kx = (kb_begin + i) * BK;
+                if (weights_are_a) {
+                    tma_load_2d(smem_u32(stage), &map_a, kx, a_row, bar);
+                } else {
+                    tma_load_2d(smem_u32(stage + S::a_bytes), &map_b, kx, b_row, bar);
+                    if (S::dual) tma_load_2d(smem_u32(stage + S::a_bytes + BN * BK * 2), &map_b, kx, args.up_row_offset + b_row, bar);
+                }
+            }
+            tt_pdl_wait();
+            for (int i = 0; i < first; ++i) {
+                const uint32_t bar = smem_u32(&full_bar[i]);
+                uint8_t* stage = smem + (size_t)i * S::stage_bytes;
+                const int kx = (kb_begin + i) * BK;
+                if (weights_are_a) tma_load_2d(smem_u32(stage + S::a_bytes), &map_b, kx, b_row, bar);
+                else tma_load_2d(smem_u32(stage), &map_a, kx, a_row, bar);
+            }
+            int issued = first;
+            for (int i = first; i < n_kb; ++i) {
                 const int s = i % STAGES;
                 const uint32_t parity = ((i / STAGES) & 1) ^ 1;
                 if (!mbar_wait(smem_u32(&empty_bar[s]), parity)) { atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); aborted = 1; break; }
@@ -213,6 +240,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
     } else {
         // ------------------------------------------------------------ epilogue
+        tt_pdl_wait();                                      // nothing is stored before every earlier kernel is done
         const int quarter = warp & 3;                      // the 32 tensor-memory lanes this warp may read
         const int row = quarter * 32 + lane;               // accumulator row owned by this thread
         bool ok = n_kb == 0 ? true : mbar_wait(smem_u32(&acc_bar), 0);
@@ -322,7 +350,7 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const Args& args,
         if (err != cudaSuccess) return (int)err;
         configured = true;
     }
-    kernel<<<grid, THREADS, shared, stream>>>(map_a, map_b, args);
+    tt_launch_pdl(kernel, grid, dim3(THREADS), shared, stream, map_a, map_b, args);
     return (int)cudaGetLastError();
 }
 

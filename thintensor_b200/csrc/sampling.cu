@@ -23,6 +23,8 @@ __device__ __forceinline__ unsigned order_key(float v) {
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_rows_kernel(const float* __restrict__ logits, long long ld, int vocab, int* __restrict__ out) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
     __shared__ float best_v[32];
     __shared__ int best_i[32];
     const float* row = logits + (size_t)blockIdx.x * ld;
@@ -64,6 +66,8 @@ argmax_rows_kernel(const float* __restrict__ logits, long long ld, int vocab, in
 __global__ void __launch_bounds__(256)
 argmax_stage1_kernel(const float* __restrict__ logits, long long ld, int vocab, float* __restrict__ scratch_v,
                      int* __restrict__ scratch_i) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
     __shared__ float best_v[8];
     __shared__ int best_i[8];
     const float* row = logits + (size_t)blockIdx.y * ld;
@@ -102,6 +106,8 @@ argmax_stage1_kernel(const float* __restrict__ logits, long long ld, int vocab, 
 
 __global__ void argmax_stage2_kernel(const float* __restrict__ scratch_v, const int* __restrict__ scratch_i, int n_rows,
                                      int* __restrict__ out) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= n_rows) return;
     float v = scratch_v[row * ARGMAX_CHUNKS + lane];
@@ -121,11 +127,11 @@ extern "C" int tt_argmax_rows(const float* logits, long long ld, int n_rows, int
     if (n_rows <= 0) return 0;
     if (vocab <= 0) return (int)cudaErrorInvalidValue;
     if (scratch_v && scratch_i && vocab >= 8192 && n_rows <= 65535) {
-        argmax_stage1_kernel<<<dim3(ARGMAX_CHUNKS, n_rows), 256, 0, stream>>>(logits, ld, vocab, scratch_v, scratch_i);
-        argmax_stage2_kernel<<<(n_rows + 3) / 4, 128, 0, stream>>>(scratch_v, scratch_i, n_rows, out);
+        tt_launch_pdl(argmax_stage1_kernel, dim3(dim3(ARGMAX_CHUNKS, n_rows)), dim3(256), 0, stream, logits, ld, vocab, scratch_v, scratch_i);
+        tt_launch_pdl(argmax_stage2_kernel, dim3((n_rows + 3) / 4), dim3(128), 0, stream, scratch_v, scratch_i, n_rows, out);
         TT_LAUNCH_CHECK();
     }
-    argmax_rows_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, out);
+    tt_launch_pdl(argmax_rows_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, stream, logits, ld, vocab, out);
     TT_LAUNCH_CHECK();
 }
 
@@ -162,6 +168,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_rows_kernel(const float* __restrict__ logits, long long ld, int vocab, float temperature, int top_k,
                    float top_p, unsigned long long seed, const int* __restrict__ request,
                    const int* __restrict__ step, int* __restrict__ out) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
     __shared__ float red[32];
     __shared__ int redi[32];
     __shared__ float prefix[SAMPLE_THREADS];
@@ -257,6 +265,6 @@ extern "C" int tt_sample_rows(const float* logits, long long ld, int n_rows, int
                               cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (vocab <= 0 || !(temperature > 0.0f) || !(top_p > 0.0f)) return (int)cudaErrorInvalidValue;
-    sample_rows_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, temperature, top_k, top_p, seed, request, step, out);
+    tt_launch_pdl(sample_rows_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, stream, logits, ld, vocab, temperature, top_k, top_p, seed, request, step, out);
     TT_LAUNCH_CHECK();
 }
