@@ -102,13 +102,16 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def reference_arm() -> int:
-    print(json.dumps({
-        "impl": "reference",
-        "unavailable": "the reference engine runs one sequence, one token per call (scripts/thin_runtime.py:1115-1117: batch_size 1) "
-                       "and loads only .thin archives made by its Rust converter, which cannot be built here (no cargo); "
-                       "it has no batch-8 decode to measure",
-    }))
+def reference_arm(steps: int, warmup: int) -> int:
+    """The unmodified reference from baseline/_ref on the same shape and workload."""
+    sys.path.insert(0, str(ROOT / "baseline"))
+    try:
+        import reference_arm as arm
+
+        line = arm.run(LLAMA_1B, METRIC, BATCH, PROMPT, CONTEXT, steps, max(warmup, 3))
+    except Exception as exc:  # noqa: BLE001 - the arm must always print a line and exit 0
+        line = {"impl": "reference", "unavailable": f"the reference failed to run: {type(exc).__name__}: {str(exc)[:300]}"}
+    print(json.dumps(line))
     return 0
 
 
@@ -124,7 +127,7 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=BATCH, help="with --only decode: sequences decoded together")
     args = parser.parse_args()
     if args.impl == "reference":
-        return reference_arm()
+        return reference_arm(min(args.steps, 128), args.warmup)
     if args.gpus != 1:
         print("bench.py measures one GPU only: this library does not run on several GPUs")
         return 2
