@@ -207,10 +207,11 @@ def test_attention_mma_prompts_with_cached_prefix(heads, kv_heads, head_dim):
     assert int(st.item()) == 0
 
 
+@pytest.mark.parametrize("shared_tile", [False, True])
 @pytest.mark.parametrize("splits", [1, 2, 5, 16])
 @pytest.mark.parametrize("window", [0, 100])
-@pytest.mark.parametrize("heads,kv_heads,head_dim", [(8, 2, 64), (3, 1, 128)])
-def test_attention_mma_decode_splits_and_window(splits, window, heads, kv_heads, head_dim):
+@pytest.mark.parametrize("heads,kv_heads,head_dim", [(8, 2, 64), (3, 1, 128), (5, 1, 96)])
+def test_attention_mma_decode_splits_and_window(splits, window, heads, kv_heads, head_dim, shared_tile):
     """The tensor-core kernel in decoding: the same far-key construction as for the exact kernel."""
     from thintensor_b200.kernels import api
 
@@ -232,7 +233,7 @@ def test_attention_mma_decode_splits_and_window(splits, window, heads, kv_heads,
     st = status()
     scale = head_dim ** -0.5
     api.attention_mma(q.view(len(totals), -1), k_pool, v_pool, table, cu, before, len(totals), len(totals), heads, kv_heads, head_dim,
-                      scale, window, splits, out, part_acc, part_ml, st)
+                      scale, window, splits, out, part_acc, part_ml, st, one_token_each=shared_tile)
     want = attention_reference(q.float().cpu(), keys, values, [1] * len(totals), heads, kv_heads, scale, window)
     torch.testing.assert_close(out.double().cpu().view(len(totals), heads, head_dim), want, **tol(dtype))
     assert torch.allclose(want[0, 0], values[0][far, 0].double(), atol=0.35)

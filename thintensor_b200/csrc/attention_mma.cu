@@ -19,8 +19,13 @@
 // ([head_dim][64 tokens], see common.cuh), which is the "k contiguous" order P V needs.
 // The four warps of a CTA take neighbouring tiles, so their loads of the same keys meet in L1.
 //
-// With splits > 1 (decode) grid.z cuts the blocks of keys into slices; partial (max, sum,
-// accumulator) results go to scratch and attention_merge_kernel combines them.
+// Two ways to map tiles (template TILE_WARPS).  Prompts: every warp has a tile of its own.
+// Decoding: a tile has too few rows to share keys between warps, so the TILE_WARPS warps of
+// a CTA share ONE tile and split its blocks of keys among themselves (warp w takes blocks
+// w, w + TILE_WARPS, ...), then combine their (max, sum, accumulator) through shared memory.
+//
+// With splits > 1 (decode) grid.z cuts the blocks of keys into slices as well; partial
+// results go to scratch and attention_merge_kernel combines them.
 //
 // Counterparts in random-unknown-username/Thintensor: _single_token_gqa_attention_kernel and
 // the split pair, thinruntime/triton_kernels.py:14-245 (one token, one program per query
@@ -29,7 +34,8 @@
 
 namespace {
 
-constexpr int MMA_WARPS = 4;
+constexpr int MMA_WARPS = 4;          // warps of a CTA when every warp has its own tile (prompts)
+constexpr int DECODE_WARPS = 8;       // warps that share one tile (decoding)
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -48,8 +54,8 @@ __device__ __forceinline__ uint4 load16(const __nv_bfloat16* p) { return *reinte
 // Which key of a 64-key block score column n of score tile j stands for (see the header).
 __device__ __forceinline__ int key_of(int j, int n) { return 32 * (j >> 2) + 8 * (n >> 1) + 2 * (j & 3) + (n & 1); }
 
-template <int HD>
-__global__ void __launch_bounds__(MMA_WARPS * 32)
+template <int HD, int TILE_WARPS>
+__global__ void __launch_bounds__((TILE_WARPS > 1 ? TILE_WARPS : MMA_WARPS) * 32)
 attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                      const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ table, int table_width,
                      int pool_blocks, const int* __restrict__ cu, const int* __restrict__ len_before, int sequences,
@@ -64,15 +70,29 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     const int kh = blockIdx.y, split = blockIdx.z;
     const int group = heads / kv_heads;
 
-    // which sequence and which of its tiles this warp has
-    int tile = blockIdx.x * MMA_WARPS + warp;
-    int b = 0;
-    for (; b < sequences; ++b) {
-        const int tiles_b = (cu[b + 1] - cu[b] + tokens_per_tile - 1) / tokens_per_tile;
-        if (tile < tiles_b) break;
-        tile -= tiles_b;
+    // which sequence and which of its tiles this warp (prompts) or this CTA (decoding) has:
+    // lanes look at 32 sequences at a time, a warp scan of their tile counts finds the owner
+    int tile = TILE_WARPS > 1 ? (int)blockIdx.x : (int)blockIdx.x * MMA_WARPS + warp;
+    int b = -1;
+    for (int base = 0; base < sequences && b < 0; base += 32) {
+        const int mine = base + lane;
+        const int count = mine < sequences ? (cu[mine + 1] - cu[mine] + tokens_per_tile - 1) / tokens_per_tile : 0;
+        int prefix = count;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, prefix, o);
+            if (lane >= o) prefix += up;
+        }
+        const unsigned owner = __ballot_sync(0xffffffffu, tile < prefix);
+        if (owner) {
+            const int first = __ffs(owner) - 1;
+            b = base + first;
+            tile -= __shfl_sync(0xffffffffu, prefix - count, first);
+        } else {
+            tile -= __shfl_sync(0xffffffffu, prefix, 31);
+        }
     }
-    if (b >= sequences) return;
+    if (b < 0) return;                 // a spare warp (prompts) or a spare CTA (decoding): uniform, so nobody waits for it
     const int seq_begin = cu[b], seq_new = cu[b + 1] - seq_begin, before = len_before[b];
     const int tok0 = tile * tokens_per_tile;
     const int tile_tokens = min(tokens_per_tile, seq_new - tok0);
@@ -116,8 +136,12 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
     const int* table_row = table + (size_t)b * table_width;
 
-    for (int kb = my_begin; kb < my_end; ++kb) {
-        const int block = table_row[kb];
+    constexpr int STEP = TILE_WARPS > 1 ? TILE_WARPS : 1;
+    const int kb_first = my_begin + (TILE_WARPS > 1 ? warp : 0);
+    int next_block = kb_first < my_end ? table_row[kb_first] : -1;
+    for (int kb = kb_first; kb < my_end; kb += STEP) {
+        const int block = next_block;
+        if (kb + STEP < my_end) next_block = table_row[kb + STEP];      // the next entry travels while this block is worked on
         if (block < 0 || block >= pool_blocks) {
             if (lane == 0) atomicOr(status, TT_STATUS_BAD_BLOCK);
             continue;
@@ -203,6 +227,54 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
     }
+
+    if (TILE_WARPS > 1) {
+        // the warps' partial results meet in shared memory; then every thread finishes a few (row, dim) pairs
+        constexpr int PITCH = HD + 4;
+        extern __shared__ float shared[];                 // [TILE_WARPS][16][PITCH] accumulators, [TILE_WARPS][16] max, [TILE_WARPS][16] sum
+        float* sh_o = shared;
+        float* sh_m = shared + TILE_WARPS * 16 * PITCH;
+        float* sh_l = sh_m + TILE_WARPS * 16;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int r = g + 8 * i;
+            float* dst = sh_o + ((size_t)warp * 16 + r) * PITCH + 2 * t;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) { dst[8 * n] = o[n][2 * i]; dst[8 * n + 1] = o[n][2 * i + 1]; }
+            if (t == 0) { sh_m[warp * 16 + r] = m_run[i]; sh_l[warp * 16 + r] = l_run[i]; }
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < 16 * HD; idx += TILE_WARPS * 32) {
+            const int r = idx / HD, d = idx - r * HD;
+            const int local = r / group;
+            if (local >= tile_tokens) continue;
+            float m = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < TILE_WARPS; ++w) m = fmaxf(m, sh_m[w * 16 + r]);
+            float l = 0.0f, acc = 0.0f;
+            if (m != -INFINITY) {
+#pragma unroll
+                for (int w = 0; w < TILE_WARPS; ++w) {
+                    const float scale_w = exp2f(sh_m[w * 16 + r] - m);     // 0 for a warp that saw no key of this row
+                    l = fmaf(sh_l[w * 16 + r], scale_w, l);
+                    acc = fmaf(sh_o[((size_t)w * 16 + r) * PITCH + d], scale_w, acc);
+                }
+            }
+            const size_t row_index = (size_t)(seq_begin + tok0 + local) * heads + kh * group + (r - local * group);
+            if (splits == 1) {
+                out[row_index * HD + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+            } else {
+                const size_t slot = row_index * splits + split;
+                part_acc[slot * HD + d] = acc;
+                if (d == 0) {
+                    part_ml[slot * 2] = m * 0.6931471805599453f;             // the merge works with natural exponents
+                    part_ml[slot * 2 + 1] = l;
+                }
+            }
+        }
+        return;
+    }
+
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         if (!row_ok[i]) continue;
@@ -229,18 +301,36 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
 template <int HD>
 int launch(const void* q, const void* k_pool, const void* v_pool, const int* table, int table_width, int pool_blocks,
            const int* cu, const int* len_before, int sequences, int n_tokens, int heads, int kv_heads, float scale,
-           int window, int splits, void* out, float* part_acc, float* part_ml, unsigned* status, cudaStream_t stream) {
+           int window, int splits, int shared_tiles, void* out, float* part_acc, float* part_ml, unsigned* status,
+           cudaStream_t stream) {
     const int group = heads / kv_heads;
     const int tokens_per_tile = 16 / group;
     const int tiles = (n_tokens + tokens_per_tile - 1) / tokens_per_tile + sequences;   // upper bound; spare warps leave at once
-    const dim3 grid((tiles + MMA_WARPS - 1) / MMA_WARPS, kv_heads, splits);
-    tt_launch_pdl(attention_mma_kernel<HD>, dim3(grid), dim3(MMA_WARPS * 32), 0, stream, 
-        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, table, table_width, pool_blocks, cu,
-        len_before, sequences, heads, kv_heads, scale * 1.4426950408889634f, window, splits, tokens_per_tile,
-        (__nv_bfloat16*)out, part_acc, part_ml, status);
+    cudaError_t err;
+    if (shared_tiles) {
+        constexpr int shared = DECODE_WARPS * 16 * (HD + 4 + 2) * (int)sizeof(float);
+        static bool configured = false;
+        auto kernel = attention_mma_kernel<HD, DECODE_WARPS>;
+        if (!configured) {
+            err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
+            if (err != cudaSuccess) return (int)err;
+            configured = true;
+        }
+        const int exact_tiles = shared_tiles;      // decoding: the caller knows the tile count (one per sequence)
+        err = tt_launch_pdl(kernel, dim3(exact_tiles, kv_heads, splits), dim3(DECODE_WARPS * 32), shared, stream,
+            (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, table, table_width, pool_blocks, cu,
+            len_before, sequences, heads, kv_heads, scale * 1.4426950408889634f, window, splits, tokens_per_tile,
+            (__nv_bfloat16*)out, part_acc, part_ml, status);
+    } else {
+        err = tt_launch_pdl(attention_mma_kernel<HD, 1>, dim3((tiles + MMA_WARPS - 1) / MMA_WARPS, kv_heads, splits), dim3(MMA_WARPS * 32), 0, stream,
+            (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, table, table_width, pool_blocks, cu,
+            len_before, sequences, heads, kv_heads, scale * 1.4426950408889634f, window, splits, tokens_per_tile,
+            (__nv_bfloat16*)out, part_acc, part_ml, status);
+    }
+    if (err != cudaSuccess) return (int)err;
     if (splits > 1) {
         const long long rows = (long long)n_tokens * heads;
-        tt_launch_pdl(attention_merge_kernel<__nv_bfloat16>, dim3((unsigned)((rows + ATTN_WARPS - 1) / ATTN_WARPS)), dim3(ATTN_WARPS * 32), 0, stream, 
+        tt_launch_pdl(attention_merge_kernel<__nv_bfloat16>, dim3((unsigned)((rows + ATTN_WARPS - 1) / ATTN_WARPS)), dim3(ATTN_WARPS * 32), 0, stream,
             part_acc, part_ml, splits, HD, rows, (__nv_bfloat16*)out);
     }
     return (int)cudaGetLastError();
@@ -248,6 +338,8 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* tab
 
 }  // namespace
 
+// shared_tiles: 0 = every warp has a tile of its own (prompts); otherwise the number of
+// tiles (sequences, when each brings one token) and the warps of a CTA share a tile.
 // 1 if this kernel takes the sizes, 0 if the exact kernel has to serve them.
 extern "C" int tt_attention_mma_supports(int heads, int kv_heads, int head_dim) {
     if (kv_heads <= 0 || heads % kv_heads || heads / kv_heads > 16) return 0;
@@ -256,13 +348,14 @@ extern "C" int tt_attention_mma_supports(int heads, int kv_heads, int head_dim) 
 
 extern "C" int tt_attention_mma(const void* q, const void* k_pool, const void* v_pool, const int* table, int table_width,
                                 int pool_blocks, const int* cu, const int* len_before, int sequences, int n_tokens,
-                                int heads, int kv_heads, int head_dim, float scale, int window, int splits, void* out,
-                                float* part_acc, float* part_ml, unsigned* status, cudaStream_t stream) {
+                                int heads, int kv_heads, int head_dim, float scale, int window, int splits,
+                                int shared_tiles, void* out, float* part_acc, float* part_ml, unsigned* status,
+                                cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (!tt_attention_mma_supports(heads, kv_heads, head_dim) || splits < 1 || splits > 65535 || kv_heads > 65535)
         return (int)cudaErrorInvalidValue;
     if (splits > 1 && (!part_acc || !part_ml)) return (int)cudaErrorInvalidValue;
-#define TT_LAUNCH(HD) return launch<HD>(q, k_pool, v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, scale, window, splits, out, part_acc, part_ml, status, stream)
+#define TT_LAUNCH(HD) return launch<HD>(q, k_pool, v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, scale, window, splits, shared_tiles, out, part_acc, part_ml, status, stream)
     switch (head_dim) {
         case 32: TT_LAUNCH(32);
         case 64: TT_LAUNCH(64);

@@ -186,16 +186,20 @@ def attention_mma_supports(dtype: torch.dtype, heads: int, kv_heads: int, head_d
 def attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor, cu: torch.Tensor,
                   len_before: torch.Tensor, sequences: int, n_tokens: int, heads: int, kv_heads: int, head_dim: int,
                   scale: float, window: int, splits: int, out: torch.Tensor, part_acc: torch.Tensor | None,
-                  part_ml: torch.Tensor | None, status: torch.Tensor) -> None:
-    """Causal attention of packed bfloat16 query tokens over the block cache on tensor cores."""
+                  part_ml: torch.Tensor | None, status: torch.Tensor, one_token_each: bool = False) -> None:
+    """Causal attention of packed bfloat16 query tokens over the block cache on tensor cores.
+    ``one_token_each`` (decoding): the warps of a CTA share a sequence's tile and split its keys."""
     if not attention_mma_supports(q.dtype, heads, kv_heads, head_dim):
         raise KernelError(f"the tensor-core attention kernel does not take {q.dtype}, {heads}/{kv_heads} heads of size {head_dim}")
     if not (k_pool.dtype == v_pool.dtype == out.dtype == torch.bfloat16):
         raise KernelError("queries, cache and output must all be bfloat16")
+    if one_token_each and n_tokens != sequences:
+        raise KernelError("one_token_each needs exactly one token per sequence")
     fn = _fn("attention_mma", "tt_attention_mma", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
-                                                   c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+                                                   c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
     _check(fn(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(table), table.shape[1], k_pool.shape[0], _ptr(cu), _ptr(len_before), sequences,
-              n_tokens, heads, kv_heads, head_dim, scale, window, splits, _ptr(out), _ptr(part_acc), _ptr(part_ml), _ptr(status),
+              n_tokens, heads, kv_heads, head_dim, scale, window, splits, sequences if one_token_each else 0, _ptr(out), _ptr(part_acc),
+              _ptr(part_ml), _ptr(status),
               _stream()), "attention_mma", 2 if splits > 1 else 1)
 
 

@@ -17,13 +17,14 @@ from .linear import Linear
 from .spec import PartSpec
 
 
-def kv_splits(ctx, parallel_units: int, keys_per_slice: int, sm_count: int = 148) -> int:
+def kv_splits(ctx, parallel_units: int, keys_per_slice: int, target_units: int) -> int:
     """Into how many slices the keys of a decode step are cut so that the grid fills the
-    GPU: ``parallel_units`` is how many warps the step has without slicing.  Depends only
-    on the step's shape and the length bound, never on the lengths on the device."""
+    GPU: ``parallel_units`` is how many independent units (warps or CTAs) the step has
+    without slicing, ``target_units`` how many the GPU wants.  Depends only on the step's
+    shape and the length bound, never on the lengths on the device."""
     if not ctx.decode:
         return 1
-    want = -(-8 * sm_count // max(parallel_units, 1))       # about eight warps per SM
+    want = -(-target_units // max(parallel_units, 1))
     most = max(1, ctx.max_total // keys_per_slice)
     return max(1, min(want, most, 64))
 
@@ -94,13 +95,18 @@ class CausalAttention(Mixer):
         groups up to 16), the exact kernel otherwise."""
         tensor_cores = api.attention_mma_supports(q.dtype, self.heads, self.kv_heads, self.head_dim)
         if tensor_cores:
-            splits = kv_splits(ctx, ctx.sequences * self.kv_heads, 128)
+            # decoding: one CTA of eight warps per (sequence, kv head, slice); about one CTA per SM
+            splits = kv_splits(ctx, ctx.sequences * self.kv_heads, 512, 128)
         else:
-            splits = kv_splits(ctx, ctx.n_tokens * self.heads, 256)
+            splits = kv_splits(ctx, ctx.n_tokens * self.heads, 256, 8 * 148)
         part_acc = part_ml = None
         if splits > 1:
             part_acc = ctx.scratch("attention.part_acc", (ctx.n_tokens * self.heads * splits * self.head_dim,), torch.float32)
             part_ml = ctx.scratch("attention.part_ml", (ctx.n_tokens * self.heads * splits * 2,), torch.float32)
-        kernel = api.attention_mma if tensor_cores else api.attention
-        kernel(q, cache.k_pool, cache.v_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads,
-               self.kv_heads, self.head_dim, self.scale, self.window or 0, splits, mixed, part_acc, part_ml, ctx.status)
+        if tensor_cores:
+            api.attention_mma(q, cache.k_pool, cache.v_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads,
+                              self.kv_heads, self.head_dim, self.scale, self.window or 0, splits, mixed, part_acc, part_ml, ctx.status,
+                              one_token_each=ctx.decode)
+        else:
+            api.attention(q, cache.k_pool, cache.v_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads,
+                          self.kv_heads, self.head_dim, self.scale, self.window or 0, splits, mixed, part_acc, part_ml, ctx.status)
