@@ -19,13 +19,18 @@
 // ([head_dim][64 tokens], see common.cuh), which is the "k contiguous" order P V needs.
 // The four warps of a CTA take neighbouring tiles, so their loads of the same keys meet in L1.
 //
-// Two ways to map tiles (template TILE_WARPS).  Prompts: every warp has a tile of its own.
-// Decoding: a tile has too few rows to share keys between warps, so the TILE_WARPS warps of
-// a CTA share ONE tile and split its blocks of keys among themselves (warp w takes blocks
-// w, w + TILE_WARPS, ...), then combine their (max, sum, accumulator) through shared memory.
-//
-// With splits > 1 (decode) grid.z cuts the blocks of keys into slices as well; partial
-// results go to scratch and attention_merge_kernel combines them.
+// Two kernels share the per-block arithmetic.  Prompts (attention_mma_kernel): every warp has
+// a tile of its own and loads fragments with plain 16-byte loads; the four warps of a CTA
+// take neighbouring tiles, so their loads of the same keys meet in L1.  Decoding
+// (attention_decode_kernel): one token per sequence, a tile is one CTA; its warps split
+// the tile's blocks of keys among themselves (warp w takes blocks w, w + WARPS, ...).  The
+// step is bound by reading the cache once, so every thread streams exactly the 16-byte
+// pieces it will later use as fragments into private shared-memory slots with cp.async,
+// several blocks ahead of the arithmetic (no registers held, no synchronisation needed: a
+// thread reads only what it copied itself); copies of blocks that the step does not
+// write start before the wait for the previous kernel.  The warps' (max, sum,
+// accumulator) meet in shared memory at the end.  grid.z may cut the keys into slices as
+// well; then partial results go to scratch and attention_merge_kernel combines them.
 //
 // Counterparts in random-unknown-username/Thintensor: _single_token_gqa_attention_kernel and
 // the split pair, thinruntime/triton_kernels.py:14-245 (one token, one program per query
@@ -34,8 +39,7 @@
 
 namespace {
 
-constexpr int MMA_WARPS = 4;          // warps of a CTA when every warp has its own tile (prompts)
-constexpr int DECODE_WARPS = 8;       // warps that share one tile (decoding)
+constexpr int MMA_WARPS = 4;          // warps of a CTA of the prompt kernel
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -54,8 +58,106 @@ __device__ __forceinline__ uint4 load16(const __nv_bfloat16* p) { return *reinte
 // Which key of a 64-key block score column n of score tile j stands for (see the header).
 __device__ __forceinline__ int key_of(int j, int n) { return 32 * (j >> 2) + 8 * (n >> 1) + 2 * (j & 3) + (n & 1); }
 
-template <int HD, int TILE_WARPS>
-__global__ void __launch_bounds__((TILE_WARPS > 1 ? TILE_WARPS : MMA_WARPS) * 32)
+// The rows a thread owns (g and g + 8 of a 16-row tile) and the running softmax state.
+template <int HD> struct TileState {
+    static constexpr int KC = HD / 32;   // 32-wide chunks of the head dimension
+    static constexpr int NT = HD / 8;    // 8-wide output tiles
+    uint32_t qa[KC][4], qb[KC][4];       // Q fragments of rows g and g + 8, head dimension permuted
+    float o[NT][4];
+    float m_run[2], l_run[2];
+    int row_pos[2], row_first[2];
+};
+
+// One block of 64 keys: S = Q K^T, scale, mask, running softmax, O += P V.
+// load_k(j, c) returns the 16 bytes of key key_of(j, g) at dims 32c + 8t .. + 7;
+// load_v(n, half) returns the 16 bytes of value dimension 8n + g at keys 32 * half + 8t .. + 7.
+template <int HD, typename LoadK, typename LoadV>
+__device__ __forceinline__ void block_math(TileState<HD>& st, int key_base, int t, float scale_log2, LoadK load_k, LoadV load_v) {
+    constexpr int KC = TileState<HD>::KC, NT = TileState<HD>::NT;
+    float s[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < KC; ++c) {
+            const uint4 kr = load_k(j, c);
+            mma_bf16(s[j], st.qa[c][0], st.qb[c][0], st.qa[c][1], st.qb[c][1], kr.x, kr.y);
+            mma_bf16(s[j], st.qa[c][2], st.qb[c][2], st.qa[c][3], st.qb[c][3], kr.z, kr.w);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int key = key_base + key_of(j, 2 * t + e);
+                const bool seen = key <= st.row_pos[i] && key >= st.row_first[i];
+                const float v = seen ? s[j][2 * i + e] * scale_log2 : -INFINITY;
+                s[j][2 * i + e] = v;
+                mx = fmaxf(mx, v);
+            }
+        }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(st.m_run[i], mx);
+        const float corr = (m_new == -INFINITY) ? 1.0f : exp2f(st.m_run[i] - m_new);
+        const float base = (m_new == -INFINITY) ? 0.0f : m_new;
+        float sum = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const float p = exp2f(s[j][2 * i + e] - base);
+                s[j][2 * i + e] = p;
+                sum += p;
+            }
+        }
+        st.l_run[i] = st.l_run[i] * corr + sum;
+        st.m_run[i] = m_new;
+#pragma unroll
+        for (int n = 0; n < NT; ++n) { st.o[n][2 * i] *= corr; st.o[n][2 * i + 1] *= corr; }
+    }
+    uint32_t pa[4][4];
+#pragma unroll
+    for (int mm = 0; mm < 4; ++mm) {
+        pa[mm][0] = pack_bf16(s[2 * mm][0], s[2 * mm][1]);
+        pa[mm][1] = pack_bf16(s[2 * mm][2], s[2 * mm][3]);
+        pa[mm][2] = pack_bf16(s[2 * mm + 1][0], s[2 * mm + 1][1]);
+        pa[mm][3] = pack_bf16(s[2 * mm + 1][2], s[2 * mm + 1][3]);
+    }
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const uint4 vr = load_v(n, half);
+            mma_bf16(st.o[n], pa[2 * half][0], pa[2 * half][1], pa[2 * half][2], pa[2 * half][3], vr.x, vr.y);
+            mma_bf16(st.o[n], pa[2 * half + 1][0], pa[2 * half + 1][1], pa[2 * half + 1][2], pa[2 * half + 1][3], vr.z, vr.w);
+        }
+    }
+}
+
+template <int HD>
+__device__ __forceinline__ void load_queries(TileState<HD>& st, const __nv_bfloat16* __restrict__ q, const size_t (&row_q)[2],
+                                             const bool (&row_ok)[2], int t) {
+#pragma unroll
+    for (int c = 0; c < TileState<HD>::KC; ++c) {
+        const uint4 zero = make_uint4(0, 0, 0, 0);
+        const uint4 va = row_ok[0] ? load16(q + row_q[0] + 32 * c + 8 * t) : zero;
+        const uint4 vb = row_ok[1] ? load16(q + row_q[1] + 32 * c + 8 * t) : zero;
+        st.qa[c][0] = va.x; st.qa[c][1] = va.y; st.qa[c][2] = va.z; st.qa[c][3] = va.w;
+        st.qb[c][0] = vb.x; st.qb[c][1] = vb.y; st.qb[c][2] = vb.z; st.qb[c][3] = vb.w;
+    }
+#pragma unroll
+    for (int n = 0; n < TileState<HD>::NT; ++n) { st.o[n][0] = st.o[n][1] = st.o[n][2] = st.o[n][3] = 0.0f; }
+    st.m_run[0] = st.m_run[1] = -INFINITY;
+    st.l_run[0] = st.l_run[1] = 0.0f;
+}
+
+// ------------------------------------------------------------------------------ prompts
+template <int HD>
+__global__ void __launch_bounds__(MMA_WARPS * 32)
 attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                      const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ table, int table_width,
                      int pool_blocks, const int* __restrict__ cu, const int* __restrict__ len_before, int sequences,
@@ -64,15 +166,14 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
                      unsigned* status) {
     tt_pdl_launch_dependents();
     tt_pdl_wait();
-    constexpr int KC = HD / 32;          // 32-wide chunks of the head dimension
-    constexpr int NT = HD / 8;           // 8-wide output tiles
+    constexpr int NT = HD / 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int kh = blockIdx.y, split = blockIdx.z;
     const int group = heads / kv_heads;
 
-    // which sequence and which of its tiles this warp (prompts) or this CTA (decoding) has:
-    // lanes look at 32 sequences at a time, a warp scan of their tile counts finds the owner
-    int tile = TILE_WARPS > 1 ? (int)blockIdx.x : (int)blockIdx.x * MMA_WARPS + warp;
+    // which sequence and which of its tiles this warp has: lanes look at 32 sequences at a
+    // time, a warp scan of their tile counts finds the owner
+    int tile = (int)blockIdx.x * MMA_WARPS + warp;
     int b = -1;
     for (int base = 0; base < sequences && b < 0; base += 32) {
         const int mine = base + lane;
@@ -92,13 +193,12 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
             tile -= __shfl_sync(0xffffffffu, prefix, 31);
         }
     }
-    if (b < 0) return;                 // a spare warp (prompts) or a spare CTA (decoding): uniform, so nobody waits for it
+    if (b < 0) return;                 // a spare warp
     const int seq_begin = cu[b], seq_new = cu[b + 1] - seq_begin, before = len_before[b];
     const int tok0 = tile * tokens_per_tile;
     const int tile_tokens = min(tokens_per_tile, seq_new - tok0);
 
-    // this thread's two rows: g and g + 8
-    int row_pos[2], row_first[2];
+    TileState<HD> st;
     size_t row_q[2];
     bool row_ok[2];
 #pragma unroll
@@ -108,8 +208,8 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
         row_ok[i] = local < tile_tokens;
         const int token = seq_begin + tok0 + local, head = kh * group + (r - local * group);
         row_q[i] = ((size_t)token * heads + head) * HD;
-        row_pos[i] = row_ok[i] ? before + tok0 + local : -1;
-        row_first[i] = (window > 0 && row_pos[i] - window + 1 > 0) ? row_pos[i] - window + 1 : 0;
+        st.row_pos[i] = row_ok[i] ? before + tok0 + local : -1;
+        st.row_first[i] = (window > 0 && st.row_pos[i] - window + 1 > 0) ? st.row_pos[i] - window + 1 : 0;
     }
 
     // the blocks of keys this tile needs, and this slice's share of them
@@ -119,180 +219,195 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     const int per = (block1 - block0 + 1 + splits - 1) / splits;
     const int my_begin = block0 + split * per, my_end = min(block1 + 1, my_begin + per);
 
-    // Q fragments, head dimension permuted: chunk c, registers 0..3 = dims 32c + 8t + {0,1},{2,3},{4,5},{6,7}
-    uint32_t qa[KC][4], qb[KC][4];
-#pragma unroll
-    for (int c = 0; c < KC; ++c) {
-        const uint4 zero = make_uint4(0, 0, 0, 0);
-        const uint4 va = row_ok[0] ? load16(q + row_q[0] + 32 * c + 8 * t) : zero;
-        const uint4 vb = row_ok[1] ? load16(q + row_q[1] + 32 * c + 8 * t) : zero;
-        qa[c][0] = va.x; qa[c][1] = va.y; qa[c][2] = va.z; qa[c][3] = va.w;
-        qb[c][0] = vb.x; qb[c][1] = vb.y; qb[c][2] = vb.z; qb[c][3] = vb.w;
-    }
-
-    float o[NT][4];
-#pragma unroll
-    for (int n = 0; n < NT; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f; }
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+    load_queries<HD>(st, q, row_q, row_ok, t);
     const int* table_row = table + (size_t)b * table_width;
-
-    constexpr int STEP = TILE_WARPS > 1 ? TILE_WARPS : 1;
-    const int kb_first = my_begin + (TILE_WARPS > 1 ? warp : 0);
-    int next_block = kb_first < my_end ? table_row[kb_first] : -1;
-    for (int kb = kb_first; kb < my_end; kb += STEP) {
+    int next_block = my_begin < my_end ? table_row[my_begin] : -1;
+    for (int kb = my_begin; kb < my_end; ++kb) {
         const int block = next_block;
-        if (kb + STEP < my_end) next_block = table_row[kb + STEP];      // the next entry travels while this block is worked on
+        if (kb + 1 < my_end) next_block = table_row[kb + 1];      // the next entry travels while this block is worked on
         if (block < 0 || block >= pool_blocks) {
             if (lane == 0) atomicOr(status, TT_STATUS_BAD_BLOCK);
             continue;
         }
-        const __nv_bfloat16* kbase = k_pool + ((size_t)block * kv_heads + kh) * TT_BLOCK_TOKENS * HD;
-        const __nv_bfloat16* vbase = v_pool + ((size_t)block * kv_heads + kh) * HD * TT_BLOCK_TOKENS;
-
-        // S = Q K^T for the block's 64 keys: 8 tiles of 8 keys
-        float s[8][4];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
-            const __nv_bfloat16* krow = kbase + (size_t)key_of(j, g) * HD + 8 * t;
-#pragma unroll
-            for (int c = 0; c < KC; ++c) {
-                const uint4 kr = load16(krow + 32 * c);
-                mma_bf16(s[j], qa[c][0], qb[c][0], qa[c][1], qb[c][1], kr.x, kr.y);
-                mma_bf16(s[j], qa[c][2], qb[c][2], qa[c][3], qb[c][3], kr.z, kr.w);
-            }
-        }
-
-        // scale, mask (causal, window), running softmax; rows g (i = 0) and g + 8 (i = 1)
-        const int key_base = kb * TT_BLOCK_TOKENS;
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            float mx = -INFINITY;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int key = key_base + key_of(j, 2 * t + e);
-                    const bool seen = key <= row_pos[i] && key >= row_first[i];
-                    const float v = seen ? s[j][2 * i + e] * scale_log2 : -INFINITY;
-                    s[j][2 * i + e] = v;
-                    mx = fmaxf(mx, v);
-                }
-            }
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            const float m_new = fmaxf(m_run[i], mx);
-            const float corr = (m_new == -INFINITY) ? 1.0f : exp2f(m_run[i] - m_new);
-            const float base = (m_new == -INFINITY) ? 0.0f : m_new;
-            float sum = 0.0f;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const float p = exp2f(s[j][2 * i + e] - base);
-                    s[j][2 * i + e] = p;
-                    sum += p;
-                }
-            }
-            l_run[i] = l_run[i] * corr + sum;
-            m_run[i] = m_new;
-#pragma unroll
-            for (int n = 0; n < NT; ++n) { o[n][2 * i] *= corr; o[n][2 * i + 1] *= corr; }
-        }
-
-        // O += P V: four products of 16 keys each per output tile
-        uint32_t pa[4][4];
-#pragma unroll
-        for (int mm = 0; mm < 4; ++mm) {
-            pa[mm][0] = pack_bf16(s[2 * mm][0], s[2 * mm][1]);
-            pa[mm][1] = pack_bf16(s[2 * mm][2], s[2 * mm][3]);
-            pa[mm][2] = pack_bf16(s[2 * mm + 1][0], s[2 * mm + 1][1]);
-            pa[mm][3] = pack_bf16(s[2 * mm + 1][2], s[2 * mm + 1][3]);
-        }
-#pragma unroll
-        for (int n = 0; n < NT; ++n) {
-            const __nv_bfloat16* vrow = vbase + (size_t)(8 * n + g) * TT_BLOCK_TOKENS + 8 * t;
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                const uint4 vr = load16(vrow + 32 * half);
-                mma_bf16(o[n], pa[2 * half][0], pa[2 * half][1], pa[2 * half][2], pa[2 * half][3], vr.x, vr.y);
-                mma_bf16(o[n], pa[2 * half + 1][0], pa[2 * half + 1][1], pa[2 * half + 1][2], pa[2 * half + 1][3], vr.z, vr.w);
-            }
-        }
+        const __nv_bfloat16* kbase = k_pool + ((size_t)block * kv_heads + kh) * TT_BLOCK_TOKENS * HD + 8 * t;
+        const __nv_bfloat16* vbase = v_pool + ((size_t)block * kv_heads + kh) * HD * TT_BLOCK_TOKENS + (size_t)g * TT_BLOCK_TOKENS + 8 * t;
+        block_math<HD>(st, kb * TT_BLOCK_TOKENS, t, scale_log2,
+                       [&](int j, int c) { return load16(kbase + (size_t)key_of(j, g) * HD + 32 * c); },
+                       [&](int n, int half) { return load16(vbase + (size_t)(8 * n) * TT_BLOCK_TOKENS + 32 * half); });
     }
 
     // row sums live spread over the four threads of a quad
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
-        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+        st.l_run[i] += __shfl_xor_sync(0xffffffffu, st.l_run[i], 1);
+        st.l_run[i] += __shfl_xor_sync(0xffffffffu, st.l_run[i], 2);
     }
-
-    if (TILE_WARPS > 1) {
-        // the warps' partial results meet in shared memory; then every thread finishes a few (row, dim) pairs
-        constexpr int PITCH = HD + 4;
-        extern __shared__ float shared[];                 // [TILE_WARPS][16][PITCH] accumulators, [TILE_WARPS][16] max, [TILE_WARPS][16] sum
-        float* sh_o = shared;
-        float* sh_m = shared + TILE_WARPS * 16 * PITCH;
-        float* sh_l = sh_m + TILE_WARPS * 16;
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int r = g + 8 * i;
-            float* dst = sh_o + ((size_t)warp * 16 + r) * PITCH + 2 * t;
-#pragma unroll
-            for (int n = 0; n < NT; ++n) { dst[8 * n] = o[n][2 * i]; dst[8 * n + 1] = o[n][2 * i + 1]; }
-            if (t == 0) { sh_m[warp * 16 + r] = m_run[i]; sh_l[warp * 16 + r] = l_run[i]; }
-        }
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < 16 * HD; idx += TILE_WARPS * 32) {
-            const int r = idx / HD, d = idx - r * HD;
-            const int local = r / group;
-            if (local >= tile_tokens) continue;
-            float m = -INFINITY;
-#pragma unroll
-            for (int w = 0; w < TILE_WARPS; ++w) m = fmaxf(m, sh_m[w * 16 + r]);
-            float l = 0.0f, acc = 0.0f;
-            if (m != -INFINITY) {
-#pragma unroll
-                for (int w = 0; w < TILE_WARPS; ++w) {
-                    const float scale_w = exp2f(sh_m[w * 16 + r] - m);     // 0 for a warp that saw no key of this row
-                    l = fmaf(sh_l[w * 16 + r], scale_w, l);
-                    acc = fmaf(sh_o[((size_t)w * 16 + r) * PITCH + d], scale_w, acc);
-                }
-            }
-            const size_t row_index = (size_t)(seq_begin + tok0 + local) * heads + kh * group + (r - local * group);
-            if (splits == 1) {
-                out[row_index * HD + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
-            } else {
-                const size_t slot = row_index * splits + split;
-                part_acc[slot * HD + d] = acc;
-                if (d == 0) {
-                    part_ml[slot * 2] = m * 0.6931471805599453f;             // the merge works with natural exponents
-                    part_ml[slot * 2 + 1] = l;
-                }
-            }
-        }
-        return;
-    }
-
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         if (!row_ok[i]) continue;
         if (splits == 1) {
-            const float inv = l_run[i] > 0.0f ? 1.0f / l_run[i] : 0.0f;
+            const float inv = st.l_run[i] > 0.0f ? 1.0f / st.l_run[i] : 0.0f;
             __nv_bfloat16* dst = out + row_q[i] + 2 * t;
 #pragma unroll
             for (int n = 0; n < NT; ++n)
-                *reinterpret_cast<uint32_t*>(dst + 8 * n) = pack_bf16(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
+                *reinterpret_cast<uint32_t*>(dst + 8 * n) = pack_bf16(st.o[n][2 * i] * inv, st.o[n][2 * i + 1] * inv);
         } else {
             const size_t slot = (row_q[i] / HD) * splits + split;          // (token * heads + head) * splits + split
             float* dst = part_acc + slot * HD + 2 * t;
 #pragma unroll
             for (int n = 0; n < NT; ++n)
-                *reinterpret_cast<float2*>(dst + 8 * n) = make_float2(o[n][2 * i], o[n][2 * i + 1]);
+                *reinterpret_cast<float2*>(dst + 8 * n) = make_float2(st.o[n][2 * i], st.o[n][2 * i + 1]);
             if (t == 0) {
-                part_ml[slot * 2] = m_run[i] * 0.6931471805599453f;          // the merge works with natural exponents
-                part_ml[slot * 2 + 1] = l_run[i];
+                part_ml[slot * 2] = st.m_run[i] * 0.6931471805599453f;       // the merge works with natural exponents
+                part_ml[slot * 2 + 1] = st.l_run[i];
+            }
+        }
+    }
+}
+
+// ----------------------------------------------------------------------------- decoding
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* src) {
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// How many warps share a tile and how many blocks each keeps in flight, so that the
+// slots fit one CTA per SM: warps * stages * (HD * 256 bytes) <= 192 KB.
+template <int HD> struct DecodeShape;
+template <> struct DecodeShape<32> { static constexpr int WARPS = 8, STAGES = 3; };
+template <> struct DecodeShape<64> { static constexpr int WARPS = 4, STAGES = 3; };
+template <> struct DecodeShape<96> { static constexpr int WARPS = 4, STAGES = 2; };
+template <> struct DecodeShape<128> { static constexpr int WARPS = 3, STAGES = 2; };
+
+template <int HD>
+__global__ void __launch_bounds__(DecodeShape<HD>::WARPS * 32)
+attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
+                        const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ table, int table_width,
+                        int pool_blocks, const int* __restrict__ len_before, int heads, int kv_heads, float scale_log2,
+                        int window, int splits, __nv_bfloat16* __restrict__ out, float* __restrict__ part_acc,
+                        float* __restrict__ part_ml, unsigned* status) {
+    constexpr int WARPS = DecodeShape<HD>::WARPS, STAGES = DecodeShape<HD>::STAGES;
+    constexpr int KC = HD / 32, NT = HD / 8;
+    constexpr int K_LOADS = 8 * KC, V_LOADS = NT * 2, LOADS = K_LOADS + V_LOADS;    // 16-byte pieces per thread and block
+    extern __shared__ uint4 slots[];                  // [WARPS][STAGES][LOADS][32 lanes]
+    tt_pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int b = blockIdx.x, kh = blockIdx.y, split = blockIdx.z;
+    const int group = heads / kv_heads;
+    // Lengths and tables were written before the previous kernel started (by the step before
+    // this one, or by the host), so they may be read ahead of the wait.
+    const int pos = len_before[b];                    // position of this step's token = keys 0 .. pos
+    const int lo_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int block0 = lo_key / TT_BLOCK_TOKENS, block1 = pos / TT_BLOCK_TOKENS;
+    const int per = (block1 - block0 + 1 + splits - 1) / splits;
+    const int my_begin = block0 + split * per, my_end = min(block1 + 1, my_begin + per);
+    const int n_mine = my_begin + warp < my_end ? (my_end - my_begin - warp + WARPS - 1) / WARPS : 0;   // blocks of this warp
+    const int* table_row = table + (size_t)b * table_width;
+    uint4* my_slots = slots + (size_t)warp * STAGES * LOADS * 32 + lane;
+    bool waited = false;
+    unsigned valid = 0;                                // bit i % 32: block i of this warp has usable data
+
+    auto issue = [&](int i) {                          // start the copies of this warp's i-th block (or an empty group)
+        if (i < n_mine) {
+            const int kb = my_begin + warp + i * WARPS;
+            if (kb == block1 && !waited) { tt_pdl_wait(); waited = true; }     // the block this step's token was written into
+            const int block = table_row[kb];
+            if (block >= 0 && block < pool_blocks) {
+                const __nv_bfloat16* kbase = k_pool + ((size_t)block * kv_heads + kh) * TT_BLOCK_TOKENS * HD + 8 * t;
+                const __nv_bfloat16* vbase = v_pool + ((size_t)block * kv_heads + kh) * HD * TT_BLOCK_TOKENS + (size_t)g * TT_BLOCK_TOKENS + 8 * t;
+                uint4* dst = my_slots + (size_t)(i % STAGES) * LOADS * 32;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+#pragma unroll
+                    for (int c = 0; c < KC; ++c) cp_async16(dst + (j * KC + c) * 32, kbase + (size_t)key_of(j, g) * HD + 32 * c);
+#pragma unroll
+                for (int n = 0; n < NT; ++n)
+#pragma unroll
+                    for (int half = 0; half < 2; ++half)
+                        cp_async16(dst + (K_LOADS + n * 2 + half) * 32, vbase + (size_t)(8 * n) * TT_BLOCK_TOKENS + 32 * half);
+                valid |= 1u << (i & 31);
+            } else {
+                valid &= ~(1u << (i & 31));
+                if (lane == 0) atomicOr(status, TT_STATUS_BAD_BLOCK);
+            }
+        }
+        cp_async_commit();
+    };
+
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; ++i) issue(i);
+    if (!waited) { tt_pdl_wait(); waited = true; }     // the queries come from the previous kernel
+
+    TileState<HD> st;
+    size_t row_q[2];
+    bool row_ok[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = g + 8 * i;
+        row_ok[i] = r < group;                         // one token: the tile's rows are the heads of the group
+        row_q[i] = ((size_t)b * heads + kh * group + r) * HD;
+        st.row_pos[i] = row_ok[i] ? pos : -1;
+        st.row_first[i] = lo_key;
+    }
+    load_queries<HD>(st, q, row_q, row_ok, t);
+
+    for (int i = 0; i < n_mine; ++i) {
+        issue(i + STAGES - 1);
+        cp_async_wait<STAGES - 1>();                   // all but the newest STAGES - 1 groups are done: block i has landed
+        if (!((valid >> (i & 31)) & 1u)) continue;
+        const uint4* src = my_slots + (size_t)(i % STAGES) * LOADS * 32;
+        const int kb = my_begin + warp + i * WARPS;
+        block_math<HD>(st, kb * TT_BLOCK_TOKENS, t, scale_log2,
+                       [&](int j, int c) { return src[(j * KC + c) * 32]; },
+                       [&](int n, int half) { return src[(K_LOADS + n * 2 + half) * 32]; });
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        st.l_run[i] += __shfl_xor_sync(0xffffffffu, st.l_run[i], 1);
+        st.l_run[i] += __shfl_xor_sync(0xffffffffu, st.l_run[i], 2);
+    }
+
+    // the warps' partial results meet in shared memory (the slots are free now)
+    __syncthreads();
+    constexpr int PITCH = HD + 4;
+    float* sh_o = reinterpret_cast<float*>(slots);     // [WARPS][16][PITCH]
+    float* sh_m = sh_o + WARPS * 16 * PITCH;           // [WARPS][16]
+    float* sh_l = sh_m + WARPS * 16;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = g + 8 * i;
+        float* dst = sh_o + ((size_t)warp * 16 + r) * PITCH + 2 * t;
+#pragma unroll
+        for (int n = 0; n < NT; ++n) { dst[8 * n] = st.o[n][2 * i]; dst[8 * n + 1] = st.o[n][2 * i + 1]; }
+        if (t == 0) { sh_m[warp * 16 + r] = st.m_run[i]; sh_l[warp * 16 + r] = st.l_run[i]; }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < group * HD; idx += WARPS * 32) {
+        const int r = idx / HD, d = idx - r * HD;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) m = fmaxf(m, sh_m[w * 16 + r]);
+        float l = 0.0f, acc = 0.0f;
+        if (m != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                const float weight = exp2f(sh_m[w * 16 + r] - m);       // 0 for a warp that saw no key
+                l = fmaf(sh_l[w * 16 + r], weight, l);
+                acc = fmaf(sh_o[((size_t)w * 16 + r) * PITCH + d], weight, acc);
+            }
+        }
+        const size_t row_index = (size_t)b * heads + kh * group + r;
+        if (splits == 1) {
+            out[row_index * HD + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+        } else {
+            const size_t slot = row_index * splits + split;
+            part_acc[slot * HD + d] = acc;
+            if (d == 0) {
+                part_ml[slot * 2] = m * 0.6931471805599453f;            // the merge works with natural exponents
+                part_ml[slot * 2 + 1] = l;
             }
         }
     }
@@ -301,30 +416,31 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
 template <int HD>
 int launch(const void* q, const void* k_pool, const void* v_pool, const int* table, int table_width, int pool_blocks,
            const int* cu, const int* len_before, int sequences, int n_tokens, int heads, int kv_heads, float scale,
-           int window, int splits, int shared_tiles, void* out, float* part_acc, float* part_ml, unsigned* status,
+           int window, int splits, int one_token_each, void* out, float* part_acc, float* part_ml, unsigned* status,
            cudaStream_t stream) {
     const int group = heads / kv_heads;
-    const int tokens_per_tile = 16 / group;
-    const int tiles = (n_tokens + tokens_per_tile - 1) / tokens_per_tile + sequences;   // upper bound; spare warps leave at once
+    const float scale_log2 = scale * 1.4426950408889634f;
     cudaError_t err;
-    if (shared_tiles) {
-        constexpr int shared = DECODE_WARPS * 16 * (HD + 4 + 2) * (int)sizeof(float);
+    if (one_token_each) {
+        using D = DecodeShape<HD>;
+        constexpr int shared = D::WARPS * D::STAGES * (8 * (HD / 32) + (HD / 8) * 2) * 32 * 16;
+        static_assert(shared >= D::WARPS * 16 * (HD + 6) * 4, "the slots must also hold the warps' partial results");
         static bool configured = false;
-        auto kernel = attention_mma_kernel<HD, DECODE_WARPS>;
+        auto kernel = attention_decode_kernel<HD>;
         if (!configured) {
             err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
             if (err != cudaSuccess) return (int)err;
             configured = true;
         }
-        const int exact_tiles = shared_tiles;      // decoding: the caller knows the tile count (one per sequence)
-        err = tt_launch_pdl(kernel, dim3(exact_tiles, kv_heads, splits), dim3(DECODE_WARPS * 32), shared, stream,
-            (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, table, table_width, pool_blocks, cu,
-            len_before, sequences, heads, kv_heads, scale * 1.4426950408889634f, window, splits, tokens_per_tile,
-            (__nv_bfloat16*)out, part_acc, part_ml, status);
+        err = tt_launch_pdl(kernel, dim3(sequences, kv_heads, splits), dim3(D::WARPS * 32), shared, stream,
+            (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, table, table_width, pool_blocks,
+            len_before, heads, kv_heads, scale_log2, window, splits, (__nv_bfloat16*)out, part_acc, part_ml, status);
     } else {
-        err = tt_launch_pdl(attention_mma_kernel<HD, 1>, dim3((tiles + MMA_WARPS - 1) / MMA_WARPS, kv_heads, splits), dim3(MMA_WARPS * 32), 0, stream,
+        const int tokens_per_tile = 16 / group;
+        const int tiles = (n_tokens + tokens_per_tile - 1) / tokens_per_tile + sequences;   // upper bound; spare warps leave at once
+        err = tt_launch_pdl(attention_mma_kernel<HD>, dim3((tiles + MMA_WARPS - 1) / MMA_WARPS, kv_heads, splits), dim3(MMA_WARPS * 32), 0, stream,
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, table, table_width, pool_blocks, cu,
-            len_before, sequences, heads, kv_heads, scale * 1.4426950408889634f, window, splits, tokens_per_tile,
+            len_before, sequences, heads, kv_heads, scale_log2, window, splits, tokens_per_tile,
             (__nv_bfloat16*)out, part_acc, part_ml, status);
     }
     if (err != cudaSuccess) return (int)err;
@@ -338,8 +454,8 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* tab
 
 }  // namespace
 
-// shared_tiles: 0 = every warp has a tile of its own (prompts); otherwise the number of
-// tiles (sequences, when each brings one token) and the warps of a CTA share a tile.
+// one_token_each: 0 = packed prompts (any number of tokens per sequence); 1 = every
+// sequence brings exactly one token (n_tokens == sequences) and the decode kernel runs.
 // 1 if this kernel takes the sizes, 0 if the exact kernel has to serve them.
 extern "C" int tt_attention_mma_supports(int heads, int kv_heads, int head_dim) {
     if (kv_heads <= 0 || heads % kv_heads || heads / kv_heads > 16) return 0;
@@ -349,13 +465,13 @@ extern "C" int tt_attention_mma_supports(int heads, int kv_heads, int head_dim) 
 extern "C" int tt_attention_mma(const void* q, const void* k_pool, const void* v_pool, const int* table, int table_width,
                                 int pool_blocks, const int* cu, const int* len_before, int sequences, int n_tokens,
                                 int heads, int kv_heads, int head_dim, float scale, int window, int splits,
-                                int shared_tiles, void* out, float* part_acc, float* part_ml, unsigned* status,
+                                int one_token_each, void* out, float* part_acc, float* part_ml, unsigned* status,
                                 cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (!tt_attention_mma_supports(heads, kv_heads, head_dim) || splits < 1 || splits > 65535 || kv_heads > 65535)
         return (int)cudaErrorInvalidValue;
     if (splits > 1 && (!part_acc || !part_ml)) return (int)cudaErrorInvalidValue;
-#define TT_LAUNCH(HD) return launch<HD>(q, k_pool, v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, scale, window, splits, shared_tiles, out, part_acc, part_ml, status, stream)
+#define TT_LAUNCH(HD) return launch<HD>(q, k_pool, v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, scale, window, splits, one_token_each, out, part_acc, part_ml, status, stream)
     switch (head_dim) {
         case 32: TT_LAUNCH(32);
         case 64: TT_LAUNCH(64);

@@ -95,8 +95,9 @@ class CausalAttention(Mixer):
         groups up to 16), the exact kernel otherwise."""
         tensor_cores = api.attention_mma_supports(q.dtype, self.heads, self.kv_heads, self.head_dim)
         if tensor_cores:
-            # decoding: one CTA of eight warps per (sequence, kv head, slice); about one CTA per SM
-            splits = kv_splits(ctx, ctx.sequences * self.kv_heads, 512, 128)
+            # decoding: one CTA per (sequence, kv head, slice), each streaming with a deep copy pipeline;
+            # measured on a B200, slicing pays only while there are fewer than about 32 such CTAs
+            splits = kv_splits(ctx, ctx.sequences * self.kv_heads, 512, 32)
         else:
             splits = kv_splits(ctx, ctx.n_tokens * self.heads, 256, 8 * 148)
         part_acc = part_ml = None
