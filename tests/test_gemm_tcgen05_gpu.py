@@ -45,6 +45,13 @@ def test_tokens_on_m(tokens, features, k, splits):
     run(tokens, features, k, splits, with_bias=(features % 2 == 1))
 
 
+@pytest.mark.parametrize("tokens,features,k", [(2048, 3072, 2048), (1500, 2000, 1000), (3000, 1000, 136), (12345, 311, 72), (2048, 2048, 8192)])
+def test_tokens_on_m_persistent(tokens, features, k):
+    """Enough 128 x 256 tiles for the persistent kernel: tiles that hang over every edge,
+    several tiles per CTA (two accumulators in turn), bias."""
+    run(tokens, features, k, 1, with_bias=(k % 3 == 0), seed=7)
+
+
 def test_split_policy_and_refusals():
     from thintensor_b200.kernels import api
 
@@ -58,7 +65,7 @@ def test_split_policy_and_refusals():
         api.gemm_tcgen05(x, w, None, torch.empty(1, 4, 32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV))
 
 
-@pytest.mark.parametrize("tokens,inter,k", [(129, 128, 64), (300, 200, 72), (2048, 1024, 512), (257, 8192, 2048)])
+@pytest.mark.parametrize("tokens,inter,k", [(129, 128, 64), (300, 200, 72), (2048, 1024, 512), (257, 8192, 2048), (5000, 1100, 200), (2048, 8192, 2048)])
 def test_fused_swiglu(tokens, inter, k):
     from thintensor_b200.kernels import api
 

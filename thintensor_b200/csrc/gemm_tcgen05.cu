@@ -23,6 +23,11 @@
 //                          `splits` slices (grid.z) so that few output tiles still fill
 //                          148 SMs; consumers sum the slices.
 //
+// Prompts with enough tiles to fill the GPU run the persistent kernel further down: one
+// CTA per SM walks over 128 x 256 tiles (or 128 x 128 gate + 128 x 128 up), with two
+// accumulators in tensor memory so that the epilogue of one tile runs under the products
+// of the next.
+//
 // Every wait is bounded: when one runs out the kernel raises TT_STATUS_WAIT_EXPIRED,
 // drains its outstanding copies, frees its tensor memory and returns.
 //
@@ -95,6 +100,24 @@ __device__ __forceinline__ void tmem_load16(uint32_t addr, float* v) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ void tmem_load32(uint32_t addr, float* v) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(addr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
 // Shared-memory matrix descriptor of a k-major bfloat16 tile whose rows are 128 bytes
@@ -310,6 +333,179 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 1) tmem_dealloc(tmem_base, S::tmem_cols);
 }
 
+
+// ------------------------------------------------------------------ persistent kernel
+// Tokens on M, for prompts.  One CTA per SM takes tiles blockIdx.x, blockIdx.x + gridDim.x,
+// ...; tile id -> (token tile = id % tiles_m, feature tile = id / tiles_m), so the CTAs that
+// run together share weight tiles in L2.  A tile is 128 tokens x 256 features (plain) or
+// 128 x 128 gate and 128 x 128 up (SwiGLU): 256 accumulator columns, and tensor memory holds
+// two such accumulators.  The producer and the issuing thread run ahead over tile
+// boundaries; the epilogue warps drain accumulator (j & 1) of the CTA's j-th tile while the
+// products of tile j + 1 fill the other one.
+constexpr int P_STAGES = 4;
+constexpr int P_STAGE_BYTES = BM * BK * 2 + 256 * BK * 2;       // A tile + 256 rows of B
+
+template <int FORM>
+__global__ void __launch_bounds__(THREADS)
+gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Args args,
+                               int tiles_m, int tiles_total) {
+    constexpr bool dual = FORM == TOKENS_ON_M_SWIGLU;
+    constexpr int TILE_N = dual ? 128 : 256;                    // output features per tile
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ uint64_t full_bar[P_STAGES], empty_bar[P_STAGES], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_base_shared;
+
+    tt_pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_kb = (args.k + BK - 1) / BK;
+    const int my_tiles = (int)blockIdx.x < tiles_total ? (tiles_total - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < P_STAGES; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(smem_u32(&acc_full[b]), 1); mbar_init(smem_u32(&acc_empty[b]), 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(&tmem_base_shared), 512);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_shared;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            tt_pdl_wait();
+            long long it = 0;                                  // k-blocks issued so far, over all tiles
+            bool ok = true;
+            for (int j = 0; j < my_tiles && ok; ++j) {
+                const int tile = (int)blockIdx.x + j * (int)gridDim.x;
+                const int a_row = (tile % tiles_m) * BM, b_row = (tile / tiles_m) * TILE_N;
+                for (int i = 0; i < n_kb; ++i, ++it) {
+                    const int s = (int)(it % P_STAGES);
+                    if (!mbar_wait(smem_u32(&empty_bar[s]), (uint32_t)(((it / P_STAGES) & 1) ^ 1))) {
+                        atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; break;
+                    }
+                    const uint32_t bar = smem_u32(&full_bar[s]);
+                    mbar_expect_tx(bar, P_STAGE_BYTES);
+                    uint8_t* stage = smem + (size_t)s * P_STAGE_BYTES;
+                    const int kx = i * BK;
+                    tma_load_2d(smem_u32(stage), &map_a, kx, a_row, bar);
+                    if (dual) {
+                        tma_load_2d(smem_u32(stage + BM * BK * 2), &map_b, kx, b_row, bar);
+                        tma_load_2d(smem_u32(stage + BM * BK * 2 + 128 * BK * 2), &map_b, kx, args.up_row_offset + b_row, bar);
+                    } else {
+                        tma_load_2d(smem_u32(stage + BM * BK * 2), &map_b, kx, b_row, bar);       // one box of 256 rows
+                    }
+                }
+            }
+            // drain: every copy issued must have landed before shared memory is given up
+            for (long long i = it > P_STAGES ? it - P_STAGES : 0; i < it; ++i)
+                if (!mbar_wait(smem_u32(&full_bar[i % P_STAGES]), (uint32_t)((i / P_STAGES) & 1))) { atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); break; }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(BM, TILE_N);
+            long long it = 0;
+            bool ok = true;
+            for (int j = 0; j < my_tiles && ok; ++j) {
+                const int buf = j & 1;
+                // the epilogue must have drained this accumulator (tiles j - 2, j - 4, ...)
+                if (j >= 2 && !mbar_wait(smem_u32(&acc_empty[buf]), (uint32_t)(((j >> 1) & 1) ^ 1))) {
+                    atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t acc_addr = tmem_base + buf * 256;
+                for (int i = 0; i < n_kb; ++i, ++it) {
+                    const int s = (int)(it % P_STAGES);
+                    if (!mbar_wait(smem_u32(&full_bar[s]), (uint32_t)((it / P_STAGES) & 1))) {
+                        atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = smem_u32(smem + (size_t)s * P_STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + BM * BK * 2;
+#pragma unroll
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                        const uint32_t accumulate = (i > 0 || kk > 0) ? 1u : 0u;
+                        const uint64_t da = smem_desc(a_addr + kk * UMMA_K * 2);
+                        umma_bf16(acc_addr, da, smem_desc(b_addr + kk * UMMA_K * 2), idesc, accumulate);
+                        if (dual) umma_bf16(acc_addr + 128, da, smem_desc(b_addr + 128 * BK * 2 + kk * UMMA_K * 2), idesc, accumulate);
+                    }
+                    umma_commit(smem_u32(&empty_bar[s]));
+                }
+                if (ok) umma_commit(smem_u32(&acc_full[buf]));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue
+        tt_pdl_wait();
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        for (int j = 0; j < my_tiles; ++j) {
+            const int buf = j & 1;
+            const int tile = (int)blockIdx.x + j * (int)gridDim.x;
+            const int token = (tile % tiles_m) * BM + row, f_base = (tile / tiles_m) * TILE_N;
+            if (!mbar_wait(smem_u32(&acc_full[buf]), (uint32_t)((j >> 1) & 1))) {
+                if (lane == 0) atomicOr(args.status, TT_STATUS_WAIT_EXPIRED);
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256;
+            if (dual) {
+                __nv_bfloat16* out = (__nv_bfloat16*)args.out + (size_t)token * args.ld_out;
+                for (int c = 0; c < 128; c += 32) {
+                    float gate[32], up[32];
+                    tmem_load32(lane_addr + c, gate);
+                    tmem_load32(lane_addr + 128 + c, up);
+                    if (token < args.tokens) {
+#pragma unroll
+                        for (int e = 0; e < 32; e += 2) {
+                            const int f = f_base + c + e;
+                            const float y0 = gate[e] / (1.0f + __expf(-gate[e])) * up[e];
+                            const float y1 = gate[e + 1] / (1.0f + __expf(-gate[e + 1])) * up[e + 1];
+                            if (f + 1 < args.features && (args.ld_out & 1) == 0) {
+                                *reinterpret_cast<__nv_bfloat162*>(out + f) = __floats2bfloat162_rn(y0, y1);
+                            } else {
+                                if (f < args.features) out[f] = __float2bfloat16_rn(y0);
+                                if (f + 1 < args.features) out[f + 1] = __float2bfloat16_rn(y1);
+                            }
+                        }
+                    }
+                }
+            } else {
+                float* out = (float*)args.out + (size_t)token * args.ld_out;
+                const bool vec = (args.ld_out & 3) == 0 && (((uintptr_t)args.out) & 15) == 0;
+                for (int c = 0; c < 256; c += 32) {
+                    float v[32];
+                    tmem_load32(lane_addr + c, v);
+                    if (token < args.tokens) {
+                        const int f0 = f_base + c;
+                        if (args.bias) {
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) if (f0 + e < args.features) v[e] += args.bias[f0 + e];
+                        }
+                        if (vec && f0 + 32 <= args.features) {
+#pragma unroll
+                            for (int e = 0; e < 32; e += 4) *reinterpret_cast<float4*>(out + f0 + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) if (f0 + e < args.features) out[f0 + e] = v[e];
+                        }
+                    }
+                }
+            }
+            // this warp is done with the accumulator: tell the issuer
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
 // ------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -354,6 +550,26 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const Args& args,
     return (int)cudaGetLastError();
 }
 
+template <int FORM>
+int launch_persistent(const CUtensorMap& map_a, const CUtensorMap& map_b, const Args& args, int tiles_m, int tiles_total,
+                      cudaStream_t stream) {
+    constexpr int shared = P_STAGE_BYTES * P_STAGES + 1024;
+    static bool configured = false;
+    static int sm_count = 0;
+    auto kernel = gemm_tcgen05_persistent_kernel<FORM>;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
+        if (err != cudaSuccess) return (int)err;
+        int device = 0;
+        if ((err = cudaGetDevice(&device)) != cudaSuccess) return (int)err;
+        if ((err = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device)) != cudaSuccess) return (int)err;
+        configured = true;
+    }
+    const int ctas = tiles_total < sm_count ? tiles_total : sm_count;
+    tt_launch_pdl(kernel, dim3(ctas), dim3(THREADS), shared, stream, map_a, map_b, args, tiles_m, tiles_total);
+    return (int)cudaGetLastError();
+}
+
 }  // namespace
 
 // How many tokens the features-on-m form takes at most.
@@ -378,11 +594,19 @@ extern "C" int tt_gemm_tcgen05(const void* x, long long ldx, const void* w, long
     args.k_blocks_per_split = (k_blocks + splits - 1) / splits;
     args.up_row_offset = features; args.status = status;
     CUtensorMap map_a, map_b;
+    const int tiles_m = (tokens + BM - 1) / BM;
     if (form == 1) {
         if (splits != 1 || bias) return (int)cudaErrorInvalidValue;
         if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, 2LL * features, k, ldw, 128)) return -1;
-        const dim3 grid((features + 127) / 128, (tokens + BM - 1) / BM, 1);
+        const int tiles = tiles_m * ((features + 127) / 128);
+        if (tiles >= 96) return launch_persistent<TOKENS_ON_M_SWIGLU>(map_a, map_b, args, tiles_m, tiles, stream);
+        const dim3 grid((features + 127) / 128, tiles_m, 1);
         return launch<TOKENS_ON_M_SWIGLU, 128, 4>(map_a, map_b, args, grid, stream);
+    }
+    if (tokens > 128 && splits == 1 && tiles_m * ((features + 255) / 256) >= 96) {
+        // enough 128 x 256 tiles for (most of) a wave of one CTA per SM
+        if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, features, k, ldw, 256)) return -1;
+        return launch_persistent<TOKENS_ON_M>(map_a, map_b, args, tiles_m, tiles_m * ((features + 255) / 256), stream);
     }
     if (tokens > 128) {
         if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, features, k, ldw, 128)) return -1;
