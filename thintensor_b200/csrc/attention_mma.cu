@@ -156,28 +156,51 @@ __device__ __forceinline__ void load_queries(TileState<HD>& st, const __nv_bfloa
 }
 
 // ------------------------------------------------------------------------------ prompts
+// Four warps = 64 query rows (16 rows each) of one sequence and one key/value head share
+// every block of keys: the block's K and V tiles are copied once per CTA into shared
+// memory with cp.async, two or three blocks ahead, and every warp reads its fragments
+// from there with 16-byte loads.  A tile row of 128 bytes or a multiple covers all 32
+// banks, so the two rows that a quarter-warp touches together would collide; the 16-byte
+// chunk index is therefore XOR-ed with 4 on odd rows when it is written and when it is read.
+// Heavy tiles (late tokens, many keys) are scheduled first.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* src) {
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int HD> struct PromptShape {
+    static constexpr int K_ROW = HD * 2;                       // bytes of one key row
+    static constexpr bool K_SWIZZLE = (K_ROW % 128) == 0;      // rows that start on the same bank
+    static constexpr int TILE_BYTES = 64 * HD * 2;             // one K tile = one V tile
+    static constexpr int STAGES = HD <= 64 ? 3 : 2;
+};
+
 template <int HD>
 __global__ void __launch_bounds__(MMA_WARPS * 32)
 attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                      const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ table, int table_width,
                      int pool_blocks, const int* __restrict__ cu, const int* __restrict__ len_before, int sequences,
-                     int heads, int kv_heads, float scale_log2, int window, int splits, int tokens_per_tile,
-                     __nv_bfloat16* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml,
-                     unsigned* status) {
+                     int heads, int kv_heads, float scale_log2, int window, int tokens_per_tile, int cta_tiles,
+                     __nv_bfloat16* __restrict__ out, unsigned* status) {
+    using P = PromptShape<HD>;
+    constexpr int NT = HD / 8, STAGES = P::STAGES;
+    extern __shared__ uint4 stage_mem[];                       // [STAGES][K tile, V tile]
     tt_pdl_launch_dependents();
     tt_pdl_wait();
-    constexpr int NT = HD / 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const int kh = blockIdx.y, split = blockIdx.z;
+    const int kh = blockIdx.y;
     const int group = heads / kv_heads;
+    const int tokens_per_cta = tokens_per_tile * MMA_WARPS;
 
-    // which sequence and which of its tiles this warp has: lanes look at 32 sequences at a
-    // time, a warp scan of their tile counts finds the owner
-    int tile = (int)blockIdx.x * MMA_WARPS + warp;
+    // which sequence and which of its CTA tiles: lanes look at 32 sequences at a time, a warp
+    // scan of their tile counts finds the owner.  Late tiles of a sequence come first.
+    int tile = cta_tiles - 1 - (int)blockIdx.x;
     int b = -1;
     for (int base = 0; base < sequences && b < 0; base += 32) {
         const int mine = base + lane;
-        const int count = mine < sequences ? (cu[mine + 1] - cu[mine] + tokens_per_tile - 1) / tokens_per_tile : 0;
+        const int count = mine < sequences ? (cu[mine + 1] - cu[mine] + tokens_per_cta - 1) / tokens_per_cta : 0;
         int prefix = count;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -193,10 +216,12 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
             tile -= __shfl_sync(0xffffffffu, prefix, 31);
         }
     }
-    if (b < 0) return;                 // a spare warp
+    if (b < 0) return;                 // a spare CTA (the grid is an upper bound): all its warps leave together
     const int seq_begin = cu[b], seq_new = cu[b + 1] - seq_begin, before = len_before[b];
-    const int tok0 = tile * tokens_per_tile;
-    const int tile_tokens = min(tokens_per_tile, seq_new - tok0);
+    const int cta_tok0 = tile * tokens_per_cta;
+    const int cta_tokens = min(tokens_per_cta, seq_new - cta_tok0);
+    const int tok0 = cta_tok0 + warp * tokens_per_tile;                          // this warp's first token
+    const int tile_tokens = max(0, min(tokens_per_tile, seq_new - tok0));       // 0: the warp only helps copying
 
     TileState<HD> st;
     size_t row_q[2];
@@ -211,30 +236,71 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
         st.row_pos[i] = row_ok[i] ? before + tok0 + local : -1;
         st.row_first[i] = (window > 0 && st.row_pos[i] - window + 1 > 0) ? st.row_pos[i] - window + 1 : 0;
     }
-
-    // the blocks of keys this tile needs, and this slice's share of them
-    const int lo_pos = before + tok0, hi_pos = before + tok0 + tile_tokens - 1;
-    const int lo_key = (window > 0 && lo_pos - window + 1 > 0) ? lo_pos - window + 1 : 0;
-    const int block0 = lo_key / TT_BLOCK_TOKENS, block1 = hi_pos / TT_BLOCK_TOKENS;
-    const int per = (block1 - block0 + 1 + splits - 1) / splits;
-    const int my_begin = block0 + split * per, my_end = min(block1 + 1, my_begin + per);
-
     load_queries<HD>(st, q, row_q, row_ok, t);
+
+    // blocks of keys: the CTA walks from the first block any of its rows sees to the last; a warp
+    // skips the arithmetic of blocks beyond its own last position
+    const int cta_lo = before + cta_tok0, cta_hi = before + cta_tok0 + cta_tokens - 1;
+    const int lo_key = (window > 0 && cta_lo - window + 1 > 0) ? cta_lo - window + 1 : 0;
+    const int block0 = lo_key / TT_BLOCK_TOKENS, block1 = cta_hi / TT_BLOCK_TOKENS;
+    const int n_blocks = block1 - block0 + 1;
+    const int my_hi = tile_tokens > 0 ? before + tok0 + tile_tokens - 1 : -1;
+    const int my_lo = before + tok0;
+    const int my_lo_key = (window > 0 && my_lo - window + 1 > 0) ? my_lo - window + 1 : 0;
     const int* table_row = table + (size_t)b * table_width;
-    int next_block = my_begin < my_end ? table_row[my_begin] : -1;
-    for (int kb = my_begin; kb < my_end; ++kb) {
-        const int block = next_block;
-        if (kb + 1 < my_end) next_block = table_row[kb + 1];      // the next entry travels while this block is worked on
-        if (block < 0 || block >= pool_blocks) {
-            if (lane == 0) atomicOr(status, TT_STATUS_BAD_BLOCK);
-            continue;
+    uint8_t* stages = reinterpret_cast<uint8_t*>(stage_mem);
+    unsigned bad = 0;                                            // bit i % 32: block i has no usable data
+
+    auto issue = [&](int i) {                                    // all threads: copy block block0 + i into its stage
+        if (i < n_blocks) {
+            const int block = table_row[block0 + i];
+            if (block >= 0 && block < pool_blocks) {
+                const uint8_t* ksrc = reinterpret_cast<const uint8_t*>(k_pool + ((size_t)block * kv_heads + kh) * TT_BLOCK_TOKENS * HD);
+                const uint8_t* vsrc = reinterpret_cast<const uint8_t*>(v_pool + ((size_t)block * kv_heads + kh) * HD * TT_BLOCK_TOKENS);
+                uint8_t* kdst = stages + (size_t)(i % STAGES) * 2 * P::TILE_BYTES;
+                uint8_t* vdst = kdst + P::TILE_BYTES;
+                constexpr int K_CHUNKS = P::K_ROW / 16;          // 16-byte chunks per key row
+                for (int c = threadIdx.x; c < P::TILE_BYTES / 16; c += MMA_WARPS * 32) {
+                    const int row = c / K_CHUNKS, ch = c - row * K_CHUNKS;
+                    const int to = P::K_SWIZZLE ? (ch ^ ((row & 1) << 2)) : ch;
+                    cp_async16(kdst + row * P::K_ROW + to * 16, ksrc + (size_t)c * 16);
+                }
+                for (int c = threadIdx.x; c < P::TILE_BYTES / 16; c += MMA_WARPS * 32) {
+                    const int row = c >> 3, ch = c & 7;          // a value row is 64 tokens = 8 chunks
+                    cp_async16(vdst + row * 128 + ((ch ^ ((row & 1) << 2)) * 16), vsrc + (size_t)c * 16);
+                }
+                bad &= ~(1u << (i & 31));
+            } else {
+                bad |= 1u << (i & 31);
+                if (threadIdx.x == 0) atomicOr(status, TT_STATUS_BAD_BLOCK);
+            }
         }
-        const __nv_bfloat16* kbase = k_pool + ((size_t)block * kv_heads + kh) * TT_BLOCK_TOKENS * HD + 8 * t;
-        const __nv_bfloat16* vbase = v_pool + ((size_t)block * kv_heads + kh) * HD * TT_BLOCK_TOKENS + (size_t)g * TT_BLOCK_TOKENS + 8 * t;
+        cp_async_commit();
+    };
+
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; ++i) issue(i);
+    for (int i = 0; i < n_blocks; ++i) {
+        cp_async_wait<STAGES - 2>();          // this thread's copies of block i are done ...
+        __syncthreads();                      // ... and so are everybody's; the stage of block i - 1 is free again
+        issue(i + STAGES - 1);
+        const int kb = block0 + i;
+        if ((bad >> (i & 31)) & 1u) continue;
+        if (kb * TT_BLOCK_TOKENS > my_hi || (kb + 1) * TT_BLOCK_TOKENS <= my_lo_key) continue;   // nothing for this warp here
+        const uint8_t* ktile = stages + (size_t)(i % STAGES) * 2 * P::TILE_BYTES;
+        const uint8_t* vtile = ktile + P::TILE_BYTES;
         block_math<HD>(st, kb * TT_BLOCK_TOKENS, t, scale_log2,
-                       [&](int j, int c) { return load16(kbase + (size_t)key_of(j, g) * HD + 32 * c); },
-                       [&](int n, int half) { return load16(vbase + (size_t)(8 * n) * TT_BLOCK_TOKENS + 32 * half); });
+                       [&](int j, int c) {
+                           const int row = key_of(j, g), ch = 4 * c + t;
+                           const int at = P::K_SWIZZLE ? (ch ^ ((row & 1) << 2)) : ch;
+                           return *reinterpret_cast<const uint4*>(ktile + row * P::K_ROW + at * 16);
+                       },
+                       [&](int n, int half) {
+                           const int row = 8 * n + g, ch = 4 * half + t;
+                           return *reinterpret_cast<const uint4*>(vtile + row * 128 + ((ch ^ ((row & 1) << 2)) * 16));
+                       });
     }
+    cp_async_wait<0>();
 
     // row sums live spread over the four threads of a quad
 #pragma unroll
@@ -245,33 +311,15 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         if (!row_ok[i]) continue;
-        if (splits == 1) {
-            const float inv = st.l_run[i] > 0.0f ? 1.0f / st.l_run[i] : 0.0f;
-            __nv_bfloat16* dst = out + row_q[i] + 2 * t;
+        const float inv = st.l_run[i] > 0.0f ? 1.0f / st.l_run[i] : 0.0f;
+        __nv_bfloat16* dst = out + row_q[i] + 2 * t;
 #pragma unroll
-            for (int n = 0; n < NT; ++n)
-                *reinterpret_cast<uint32_t*>(dst + 8 * n) = pack_bf16(st.o[n][2 * i] * inv, st.o[n][2 * i + 1] * inv);
-        } else {
-            const size_t slot = (row_q[i] / HD) * splits + split;          // (token * heads + head) * splits + split
-            float* dst = part_acc + slot * HD + 2 * t;
-#pragma unroll
-            for (int n = 0; n < NT; ++n)
-                *reinterpret_cast<float2*>(dst + 8 * n) = make_float2(st.o[n][2 * i], st.o[n][2 * i + 1]);
-            if (t == 0) {
-                part_ml[slot * 2] = st.m_run[i] * 0.6931471805599453f;       // the merge works with natural exponents
-                part_ml[slot * 2 + 1] = st.l_run[i];
-            }
-        }
+        for (int n = 0; n < NT; ++n)
+            *reinterpret_cast<uint32_t*>(dst + 8 * n) = pack_bf16(st.o[n][2 * i] * inv, st.o[n][2 * i + 1] * inv);
     }
 }
 
 // ----------------------------------------------------------------------------- decoding
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* src) {
-    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // How many warps share a tile and how many blocks each keeps in flight, so that the
 // slots fit one CTA per SM: warps * stages * (HD * 256 bytes) <= 192 KB.
@@ -436,12 +484,23 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* tab
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, table, table_width, pool_blocks,
             len_before, heads, kv_heads, scale_log2, window, splits, (__nv_bfloat16*)out, part_acc, part_ml, status);
     } else {
+        // packed prompts: keys are not sliced (a prompt has tiles enough); a CTA is 64 query rows
+        if (splits != 1) return (int)cudaErrorInvalidValue;
+        using P = PromptShape<HD>;
+        constexpr int shared = P::STAGES * 2 * P::TILE_BYTES;
+        static bool configured = false;
+        auto kernel = attention_mma_kernel<HD>;
+        if (!configured) {
+            err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
+            if (err != cudaSuccess) return (int)err;
+            configured = true;
+        }
         const int tokens_per_tile = 16 / group;
-        const int tiles = (n_tokens + tokens_per_tile - 1) / tokens_per_tile + sequences;   // upper bound; spare warps leave at once
-        err = tt_launch_pdl(attention_mma_kernel<HD>, dim3((tiles + MMA_WARPS - 1) / MMA_WARPS, kv_heads, splits), dim3(MMA_WARPS * 32), 0, stream,
+        const int tokens_per_cta = tokens_per_tile * MMA_WARPS;
+        const int cta_tiles = (n_tokens + tokens_per_cta - 1) / tokens_per_cta + sequences;   // upper bound; spare CTAs leave at once
+        err = tt_launch_pdl(kernel, dim3(cta_tiles, kv_heads, 1), dim3(MMA_WARPS * 32), shared, stream,
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, table, table_width, pool_blocks, cu,
-            len_before, sequences, heads, kv_heads, scale_log2, window, splits, tokens_per_tile,
-            (__nv_bfloat16*)out, part_acc, part_ml, status);
+            len_before, sequences, heads, kv_heads, scale_log2, window, tokens_per_tile, cta_tiles, (__nv_bfloat16*)out, status);
     }
     if (err != cudaSuccess) return (int)err;
     if (splits > 1) {
