@@ -257,7 +257,7 @@ def test_attention_refuses_bad_sizes():
 
 # ----------------------------------------------------------------------------------- rope
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads,kv_heads,head_dim,rotary_dim", [(4, 2, 16, 16), (3, 1, 32, 32), (6, 3, 48, 24), (2, 2, 128, 128)])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,rotary_dim", [(4, 2, 16, 16), (3, 1, 32, 32), (6, 3, 48, 24), (2, 2, 128, 128), (2, 1, 16, 12), (5, 5, 80, 40)])
 def test_rope_append(dtype, heads, kv_heads, head_dim, rotary_dim):
     from thintensor_b200.kernels import api
 

@@ -55,6 +55,14 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 __device__ __forceinline__ uint4 load16(const __nv_bfloat16* p) { return *reinterpret_cast<const uint4*>(p); }
 
+// 2^x on the special-function unit; exact enough for probabilities that are rounded to bfloat16
+// (relative error about 2^-22), and 2^-inf = 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // Which key of a 64-key block score column n of score tile j stands for (see the header).
 __device__ __forceinline__ int key_of(int j, int n) { return 32 * (j >> 2) + 8 * (n >> 1) + 2 * (j & 3) + (n & 1); }
 
@@ -85,31 +93,46 @@ __device__ __forceinline__ void block_math(TileState<HD>& st, int key_base, int 
             mma_bf16(s[j], st.qa[c][2], st.qb[c][2], st.qa[c][3], st.qb[c][3], kr.z, kr.w);
         }
     }
+    // a block whose every key is visible to both rows needs no mask
+    const int lo = min(st.row_pos[0], st.row_pos[1]), first = max(st.row_first[0], st.row_first[1]);
+    const bool all_visible = key_base + TT_BLOCK_TOKENS - 1 <= lo && key_base >= first;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         float mx = -INFINITY;
+        if (all_visible) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < 8; ++j) {
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int key = key_base + key_of(j, 2 * t + e);
-                const bool seen = key <= st.row_pos[i] && key >= st.row_first[i];
-                const float v = seen ? s[j][2 * i + e] * scale_log2 : -INFINITY;
-                s[j][2 * i + e] = v;
-                mx = fmaxf(mx, v);
+                for (int e = 0; e < 2; ++e) {
+                    const float v = s[j][2 * i + e] * scale_log2;
+                    s[j][2 * i + e] = v;
+                    mx = fmaxf(mx, v);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int key = key_base + key_of(j, 2 * t + e);
+                    const bool seen = key <= st.row_pos[i] && key >= st.row_first[i];
+                    const float v = seen ? s[j][2 * i + e] * scale_log2 : -INFINITY;
+                    s[j][2 * i + e] = v;
+                    mx = fmaxf(mx, v);
+                }
             }
         }
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
         const float m_new = fmaxf(st.m_run[i], mx);
-        const float corr = (m_new == -INFINITY) ? 1.0f : exp2f(st.m_run[i] - m_new);
+        const float corr = (m_new == -INFINITY) ? 1.0f : fast_exp2(st.m_run[i] - m_new);
         const float base = (m_new == -INFINITY) ? 0.0f : m_new;
         float sum = 0.0f;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                const float p = exp2f(s[j][2 * i + e] - base);
+                const float p = fast_exp2(s[j][2 * i + e] - base);
                 s[j][2 * i + e] = p;
                 sum += p;
             }

@@ -88,6 +88,18 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __
     }
 }
 
+// four consecutive outputs as one store (the row start is 16-byte aligned and j counts groups of four)
+__device__ __forceinline__ void tt_store4(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void tt_store4(__nv_bfloat16* p, float a, float b, float c, float d) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 v;
+    v.x = *reinterpret_cast<const uint32_t*>(&lo);
+    v.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = v;
+}
+
 // The same for hidden sizes that are multiples of 4 up to 16384: every thread keeps its
 // (up to four) float4 pieces of the row in registers, all loads of the k-slices are
 // independent, and the order of additions is the one of the kernel above.
@@ -142,10 +154,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const float* __restrict__ d
             const float4 w = __ldg(w4 + j);
             const float y0 = x[v].x * rstd * (w.x + weight_offset), y1 = x[v].y * rstd * (w.y + weight_offset);
             const float y2 = x[v].z * rstd * (w.z + weight_offset), y3 = x[v].w * rstd * (w.w + weight_offset);
-            o[4 * j] = tt_from_float<TOut>(y0);
-            o[4 * j + 1] = tt_from_float<TOut>(y1);
-            o[4 * j + 2] = tt_from_float<TOut>(y2);
-            o[4 * j + 3] = tt_from_float<TOut>(y3);
+            tt_store4(o + 4 * j, y0, y1, y2, y3);
         }
     }
 }
@@ -156,7 +165,7 @@ extern "C" int tt_add_rmsnorm(float* residual, const float* delta, int splits, l
     if (n_rows <= 0) return 0;
     if (!delta) splits = 0;
     if (hidden % 4 == 0 && hidden <= 4096 * NORM_VEC_MAX && split_stride % 4 == 0 && ((uintptr_t)residual & 15) == 0 &&
-        ((uintptr_t)delta & 15) == 0 && ((uintptr_t)weight & 15) == 0) {
+        ((uintptr_t)delta & 15) == 0 && ((uintptr_t)weight & 15) == 0 && ((uintptr_t)out & 15) == 0) {
         int threads = ((hidden / 4 + 31) / 32) * 32;
         if (threads > 1024) threads = 1024;
         if (out_dtype == TT_F32)
@@ -268,6 +277,95 @@ __global__ void rope_append_kernel(const float* __restrict__ qkv, int splits, si
     }
 }
 
+// The same with four neighbouring items per thread (float4 loads, 8-byte stores of q and k): used
+// when the rotary part and the rest of a head are multiples of 8 and 4 numbers.
+__device__ __forceinline__ float4 sum_slices4(const float* __restrict__ p, int splits, size_t split_stride) {
+    float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int s = 0; s < splits; ++s) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(p + (size_t)s * split_stride));
+        total.x += v.x; total.y += v.y; total.z += v.z; total.w += v.w;
+    }
+    return total;
+}
+
+template <typename TAct>
+__global__ void rope_append_vec_kernel(const float* __restrict__ qkv, int splits, size_t split_stride,
+                                       const float* __restrict__ inv_freq, int rotary_dim, float attention_scaling,
+                                       TAct* __restrict__ q_out, TAct* __restrict__ k_pool, TAct* __restrict__ v_pool,
+                                       const int* __restrict__ table, int table_width, int pool_blocks,
+                                       const int* __restrict__ cu, const int* __restrict__ len_before, int sequences,
+                                       int heads, int kv_heads, int head_dim, int write_cache, unsigned* status) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
+    const int t = blockIdx.x;
+    const int b = tt_find_sequence(cu, sequences, t);
+    const int pos = len_before[b] + (t - cu[b]);
+    const int half = rotary_dim >> 1, half4 = half >> 2;
+    const int q_cols = heads * head_dim;
+    const int kv_cols = write_cache ? kv_heads * head_dim : 0;
+    const int cols = q_cols + 2 * kv_cols;
+    const float* row = qkv + (size_t)t * cols;
+    const int* table_row = table + (size_t)b * table_width;
+    const int rot_heads = heads + (write_cache ? kv_heads : 0);
+    const int pass4 = (head_dim - rotary_dim) >> 2;
+    const int n_rot = rot_heads * half4, n_pass = rot_heads * pass4;
+    int w = blockIdx.y * blockDim.x + threadIdx.x;
+    if (w < n_rot) {
+        const int head = w / half4, i = (w - head * half4) * 4;
+        const int col = head * head_dim + i;
+        const float4 a = sum_slices4(row + col, splits, split_stride);
+        const float4 c = sum_slices4(row + col + half, splits, split_stride);
+        const float4 f = __ldg(reinterpret_cast<const float4*>(inv_freq + i));
+        float s0, c0, s1, c1, s2, c2, s3, c3;
+        sincosf(f.x * (float)pos, &s0, &c0);
+        sincosf(f.y * (float)pos, &s1, &c1);
+        sincosf(f.z * (float)pos, &s2, &c2);
+        sincosf(f.w * (float)pos, &s3, &c3);
+        const float k = attention_scaling;
+        const float ra0 = (a.x * c0 - c.x * s0) * k, rb0 = (c.x * c0 + a.x * s0) * k;
+        const float ra1 = (a.y * c1 - c.y * s1) * k, rb1 = (c.y * c1 + a.y * s1) * k;
+        const float ra2 = (a.z * c2 - c.z * s2) * k, rb2 = (c.z * c2 + a.z * s2) * k;
+        const float ra3 = (a.w * c3 - c.w * s3) * k, rb3 = (c.w * c3 + a.w * s3) * k;
+        TAct* dst;
+        if (head < heads) {
+            dst = q_out + (size_t)t * q_cols + col;
+        } else {
+            const long long off = tt_cache_offset(table_row, pos, head - heads, kv_heads, head_dim, pool_blocks, status);
+            if (off < 0) return;
+            dst = k_pool + off + i;
+        }
+        tt_store4(dst, ra0, ra1, ra2, ra3);
+        tt_store4(dst + half, rb0, rb1, rb2, rb3);
+        return;
+    }
+    w -= n_rot;
+    if (w < n_pass) {
+        const int head = w / pass4, i = rotary_dim + (w - head * pass4) * 4;
+        const int col = head * head_dim + i;
+        const float4 a = sum_slices4(row + col, splits, split_stride);
+        if (head < heads) {
+            tt_store4(q_out + (size_t)t * q_cols + col, a.x, a.y, a.z, a.w);
+        } else {
+            const long long off = tt_cache_offset(table_row, pos, head - heads, kv_heads, head_dim, pool_blocks, status);
+            if (off >= 0) tt_store4(k_pool + off + i, a.x, a.y, a.z, a.w);
+        }
+        return;
+    }
+    w -= n_pass;
+    if (w < (kv_cols >> 2)) {
+        const int e = w * 4, kh = e / head_dim, i = e - kh * head_dim;
+        const float4 a = sum_slices4(row + q_cols + kv_cols + e, splits, split_stride);
+        const long long off = tt_value_offset(table_row, pos, kh, kv_heads, head_dim, pool_blocks, status);
+        if (off >= 0) {
+            TAct* dst = v_pool + off + (long long)i * TT_BLOCK_TOKENS;      // values lie transposed: one number per 64-token row
+            dst[0] = tt_from_float<TAct>(a.x);
+            dst[TT_BLOCK_TOKENS] = tt_from_float<TAct>(a.y);
+            dst[2 * TT_BLOCK_TOKENS] = tt_from_float<TAct>(a.z);
+            dst[3 * TT_BLOCK_TOKENS] = tt_from_float<TAct>(a.w);
+        }
+    }
+}
+
 extern "C" int tt_rope_append(const float* qkv, int splits, long long split_stride,
                               const float* inv_freq, int rotary_dim, float attention_scaling, void* q_out,
                               void* k_pool, void* v_pool, int act_dtype, const int* table, int table_width,
@@ -277,6 +375,19 @@ extern "C" int tt_rope_append(const float* qkv, int splits, long long split_stri
     if (n_tokens <= 0) return 0;
     if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return (int)cudaErrorInvalidValue;
     const int rot_heads = heads + (write_cache ? kv_heads : 0);
+    if (rotary_dim % 8 == 0 && (head_dim - rotary_dim) % 4 == 0 && split_stride % 4 == 0 && ((uintptr_t)qkv & 15) == 0 &&
+        ((uintptr_t)inv_freq & 15) == 0 && ((uintptr_t)q_out & 15) == 0 && ((uintptr_t)k_pool & 15) == 0) {
+        const int items4 = rot_heads * (rotary_dim / 8) + rot_heads * ((head_dim - rotary_dim) / 4) + (write_cache ? kv_heads * head_dim / 4 : 0);
+        const int threads4 = 128;
+        const dim3 grid4(n_tokens, (items4 + threads4 - 1) / threads4);
+        if (grid4.y <= 65535) {
+            if (act_dtype == TT_F32)
+                tt_launch_pdl(rope_append_vec_kernel<float>, grid4, dim3(threads4), 0, stream, qkv, splits, (size_t)split_stride, inv_freq, rotary_dim, attention_scaling, (float*)q_out, (float*)k_pool, (float*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, heads, kv_heads, head_dim, write_cache, status);
+            else
+                tt_launch_pdl(rope_append_vec_kernel<__nv_bfloat16>, grid4, dim3(threads4), 0, stream, qkv, splits, (size_t)split_stride, inv_freq, rotary_dim, attention_scaling, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, heads, kv_heads, head_dim, write_cache, status);
+            TT_LAUNCH_CHECK();
+        }
+    }
     const int items = rot_heads * (rotary_dim / 2) + rot_heads * (head_dim - rotary_dim) + (write_cache ? kv_heads * head_dim : 0);
     const int threads = 128;
     const dim3 grid(n_tokens, (items + threads - 1) / threads);
