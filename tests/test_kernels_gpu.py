@@ -207,6 +207,42 @@ def test_attention_mma_prompts_with_cached_prefix(heads, kv_heads, head_dim):
     assert int(st.item()) == 0
 
 
+@pytest.mark.parametrize("window", [0, 90])
+@pytest.mark.parametrize("heads,kv_heads,head_dim", [(8, 2, 64), (32, 8, 64), (4, 4, 64), (24, 8, 128), (32, 8, 128), (5, 1, 64), (16, 1, 128)])
+def test_attention_tcgen05_prompts(heads, kv_heads, head_dim, window):
+    """The tcgen05 prompt kernel: packed prompts of unequal length with cached prefixes, tiles
+    that end inside a sequence, groups that do not divide 128, many blocks per tile (both S
+    accumulators and all stages in turn), a window, and a far key that dominates one row."""
+    from thintensor_b200.kernels import api
+
+    dtype = torch.bfloat16
+    totals, news = [700, 5, 200, 64, 130, 333], [700, 2, 9, 1, 130, 300]
+    k_pool, v_pool, table, keys, values = make_cache(totals, kv_heads, head_dim, dtype, seed=14)
+    tokens = sum(news)
+    q = randn(tokens, heads, head_dim, dtype=dtype, seed=15)
+    # the last token of the first sequence, head 0: one far key dominates (inside the window when there is one)
+    far = 5 if not window else totals[0] - window
+    q_last = q[news[0] - 1, 0].float()
+    spike = (q_last * (24.0 * head_dim ** 0.5 / float(q_last.norm()) ** 2)).to(dtype)
+    block, offset = int(table[0, far // 64]), far % 64
+    k_pool[block, 0, offset] = spike
+    keys[0][far, 0] = spike.float().cpu()
+    cu = torch.tensor([0] + list(torch.tensor(news).cumsum(0)), dtype=torch.int32, device=DEV)
+    before = torch.tensor([t - n for t, n in zip(totals, news)], dtype=torch.int32, device=DEV)
+    out = torch.full((tokens, heads * head_dim), float("nan"), dtype=dtype, device=DEV)
+    st = status()
+    scale = head_dim ** -0.5
+    api.attention_tcgen05(q.view(tokens, -1), k_pool, v_pool, table, cu, before, len(totals), tokens, heads, kv_heads, head_dim, scale,
+                          window, out, st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    want = attention_reference(q.float().cpu(), keys, values, news, heads, kv_heads, scale, window)
+    got = out.double().cpu().view(tokens, heads, head_dim)
+    assert torch.isfinite(got).all()
+    torch.testing.assert_close(got, want, **tol(dtype))
+    assert torch.allclose(want[news[0] - 1, 0], values[0][far, 0].double(), atol=0.35)
+
+
 @pytest.mark.parametrize("shared_tile", [False, True])
 @pytest.mark.parametrize("splits", [1, 2, 5, 16])
 @pytest.mark.parametrize("window", [0, 100])

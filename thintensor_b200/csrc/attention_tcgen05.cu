@@ -1,0 +1,478 @@
+// Causal grouped-query attention for prompts on the 5th-generation tensor cores: both
+// products of every block of 64 keys (S = Q K^T and O += P V) are tcgen05.mma with their
+// accumulators in tensor memory, operands arrive by TMA, and the softmax between them runs
+// in registers with one thread per query row.  bfloat16, head size 64 or 128.
+//
+// A CTA owns 128 query rows of one sequence and one key/value head: 128 / group tokens by
+// `group` heads, fetched as one 3-D TMA box from q [token][head][dim].  Per block of keys:
+//   warp 0 (one thread)  looks the block up in the table and issues TMA loads of the K tile
+//                        [64 keys][dim] and of the V tile, which the cache stores transposed
+//                        ([dim][64 keys], see common.cuh): both are "k contiguous" B operands
+//                        exactly as they lie in the cache;
+//   warp 1 (one thread)  issues S_i = Q K_i^T (M 128, N 64) into one of two S accumulators as
+//                        soon as K_i has landed, and O += P_i V_i (M 128, N dim) once the
+//                        softmax warps have written P_i, so S_{i+1} is computed while
+//                        softmax_i runs and P_i V_i while softmax_{i+1} runs;
+//   warps 2-5            read a row of S per thread (tcgen05.ld, no shuffles needed for the
+//                        row maximum and sum), scale, mask the diagonal blocks, exponentiate,
+//                        write P as a swizzled bfloat16 A operand into shared memory.  O stays
+//                        in tensor memory; it is rescaled only when a row's maximum has grown
+//                        by more than 2^8 since the scale in use (then the warp reads, scales
+//                        and writes back its 32 rows of O), otherwise the old scale stays.
+// At the end every thread divides its row of O by the row sum and stores it.
+// Every wait is bounded as in gemm_tcgen05.cu.
+//
+// The reference has no counterpart: it feeds prompts token by token through its
+// single-token attention (thinruntime/cli.py:2802-2807, thinruntime/triton_kernels.py:14-109).
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int ROWS = 128;            // query rows of a CTA
+constexpr int KEYS = TT_BLOCK_TOKENS;
+constexpr int THREADS = 192;
+constexpr int KV_STAGES = 3;
+constexpr uint32_t SPIN_LIMIT = 1u << 24;
+constexpr float RESCALE_THRESHOLD = 8.0f;     // in log2 units
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_load32(uint32_t addr, float* v) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(addr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_store32(uint32_t addr, const float* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(addr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+          "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+          "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+          "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+          "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// k-major bfloat16 tile, rows 128 bytes apart, 128-byte swizzle in groups of eight rows
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(1024u >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <int HD> struct Layout {
+    static constexpr int CHUNKS = HD / 64;                      // 64-wide slices of the head dimension
+    static constexpr int Q_BYTES = ROWS * HD * 2;
+    static constexpr int K_BYTES = KEYS * HD * 2;               // = V tile
+    static constexpr int P_BYTES = ROWS * KEYS * 2;
+    static constexpr int STAGE_BYTES = 2 * K_BYTES;
+    static constexpr int SMEM = Q_BYTES + KV_STAGES * STAGE_BYTES + 2 * P_BYTES + 1024;
+    static constexpr int TMEM_COLS = 256;                       // S: 2 x 64, O: HD (64 or 128)
+    static constexpr int O_COL = 128;
+};
+
+struct Args {
+    const int* table;
+    int table_width, pool_blocks;
+    const int* cu;
+    const int* len_before;
+    int sequences, heads, kv_heads, group, tokens_per_tile, cta_tiles;
+    float scale_log2;
+    int window;
+    __nv_bfloat16* out;
+    unsigned* status;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS)
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                         const __grid_constant__ CUtensorMap map_v, const Args args) {
+    using L = Layout<HD>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* q_smem = smem;
+    uint8_t* kv_smem = q_smem + L::Q_BYTES;
+    uint8_t* p_smem = kv_smem + KV_STAGES * L::STAGE_BYTES;
+    __shared__ uint64_t q_full, kv_full[KV_STAGES], kv_empty[KV_STAGES], s_full[2], p_ready[2], pv_done[2];
+    __shared__ uint32_t tmem_base_shared;
+    __shared__ int tile_info[2];                                  // sequence, tile within the sequence
+
+    tt_pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kh = blockIdx.y;
+
+    if (warp == 0) {
+        // which sequence and which of its tiles (late tiles, which see most keys, first)
+        int tile = args.cta_tiles - 1 - (int)blockIdx.x;
+        int b = -1;
+        for (int base = 0; base < args.sequences && b < 0; base += 32) {
+            const int mine = base + lane;
+            const int count = mine < args.sequences ? (args.cu[mine + 1] - args.cu[mine] + args.tokens_per_tile - 1) / args.tokens_per_tile : 0;
+            int prefix = count;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, prefix, o);
+                if (lane >= o) prefix += up;
+            }
+            const unsigned owner = __ballot_sync(0xffffffffu, tile < prefix);
+            if (owner) {
+                const int first = __ffs(owner) - 1;
+                b = base + first;
+                tile -= __shfl_sync(0xffffffffu, prefix - count, first);
+            } else {
+                tile -= __shfl_sync(0xffffffffu, prefix, 31);
+            }
+        }
+        if (lane == 0) { tile_info[0] = b; tile_info[1] = tile; }
+    }
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&q_full), 1);
+        for (int s = 0; s < KV_STAGES; ++s) { mbar_init(smem_u32(&kv_full[s]), 1); mbar_init(smem_u32(&kv_empty[s]), 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&s_full[i]), 1); mbar_init(smem_u32(&p_ready[i]), 4); mbar_init(smem_u32(&pv_done[i]), 1); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const int b = tile_info[0], tile = tile_info[1];
+    if (b < 0) return;                                            // a spare CTA: everybody leaves before tensor memory is touched
+    if (warp == 1) tmem_alloc(smem_u32(&tmem_base_shared), L::TMEM_COLS);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_shared;
+
+    tt_pdl_wait();                                                // queries and this step's keys come from the previous kernel
+    const int seq_begin = args.cu[b], seq_new = args.cu[b + 1] - seq_begin, before = args.len_before[b];
+    const int tok0 = tile * args.tokens_per_tile;
+    const int tile_tokens = min(args.tokens_per_tile, seq_new - tok0);
+    const int lo_pos = before + tok0, hi_pos = before + tok0 + tile_tokens - 1;
+    const int lo_key = (args.window > 0 && lo_pos - args.window + 1 > 0) ? lo_pos - args.window + 1 : 0;
+    const int block0 = lo_key / KEYS, block1 = hi_pos / KEYS;
+    const int n_blocks = block1 - block0 + 1;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            const uint32_t qbar = smem_u32(&q_full);
+            // the box holds group * tokens_per_tile rows (128, or a few less when the group does not divide 128)
+            mbar_expect_tx(qbar, (uint32_t)(L::CHUNKS * args.group * args.tokens_per_tile * 128));
+#pragma unroll
+            for (int c = 0; c < L::CHUNKS; ++c)
+                tma_load_3d(smem_u32(q_smem + c * ROWS * 128), &map_q, c * 64, kh * args.group, seq_begin + tok0, qbar);
+            const int* table_row = args.table + (size_t)b * args.table_width;
+            int issued = 0;
+            for (int i = 0; i < n_blocks; ++i) {
+                const int s = i % KV_STAGES;
+                if (i >= KV_STAGES && !mbar_wait(smem_u32(&kv_empty[s]), (uint32_t)(((i / KV_STAGES) & 1) ^ 1))) {
+                    atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); break;
+                }
+                int block = table_row[block0 + i];
+                if (block < 0 || block >= args.pool_blocks) { atomicOr(args.status, TT_STATUS_BAD_BLOCK); block = 0; }
+                const uint32_t bar = smem_u32(&kv_full[s]);
+                mbar_expect_tx(bar, L::STAGE_BYTES);
+                uint8_t* stage = kv_smem + (size_t)s * L::STAGE_BYTES;
+                const int k_row = (block * args.kv_heads + kh) * KEYS, v_row = (block * args.kv_heads + kh) * HD;
+#pragma unroll
+                for (int c = 0; c < L::CHUNKS; ++c) tma_load_2d(smem_u32(stage + c * KEYS * 128), &map_k, c * 64, k_row, bar);
+                tma_load_2d(smem_u32(stage + L::K_BYTES), &map_v, 0, v_row, bar);
+                ++issued;
+            }
+            for (int i = max(0, issued - KV_STAGES); i < issued; ++i)       // drain before shared memory is given up
+                if (!mbar_wait(smem_u32(&kv_full[i % KV_STAGES]), (uint32_t)((i / KV_STAGES) & 1))) { atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); break; }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = instr_desc(ROWS, KEYS), idesc_o = instr_desc(ROWS, HD);
+            bool ok = mbar_wait(smem_u32(&q_full), 0);
+            if (!ok) atomicOr(args.status, TT_STATUS_WAIT_EXPIRED);
+            auto issue_s = [&](int i) {                           // S_i = Q K_i^T into S accumulator i & 1
+                const int s = i % KV_STAGES;
+                if (!mbar_wait(smem_u32(&kv_full[s]), (uint32_t)((i / KV_STAGES) & 1))) { atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; return; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t q_addr = smem_u32(q_smem), k_addr = smem_u32(kv_smem + (size_t)s * L::STAGE_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint32_t off_q = (kk / 4) * ROWS * 128 + (kk % 4) * 32, off_k = (kk / 4) * KEYS * 128 + (kk % 4) * 32;
+                    umma_bf16(tmem_base + (i & 1) * 64, smem_desc(q_addr + off_q), smem_desc(k_addr + off_k), idesc_s, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(smem_u32(&s_full[i & 1]));
+            };
+            if (ok) issue_s(0);
+            if (ok && n_blocks > 1) issue_s(1);
+            for (int i = 0; i < n_blocks && ok; ++i) {
+                // O += P_i V_i once the softmax warps have written P_i
+                if (!mbar_wait(smem_u32(&p_ready[i & 1]), (uint32_t)((i >> 1) & 1))) { atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const int s = i % KV_STAGES;
+                const uint32_t p_addr = smem_u32(p_smem + (i & 1) * L::P_BYTES);
+                const uint32_t v_addr = smem_u32(kv_smem + (size_t)s * L::STAGE_BYTES + L::K_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < KEYS / 16; ++kk)
+                    umma_bf16(tmem_base + L::O_COL, smem_desc(p_addr + kk * 32), smem_desc(v_addr + kk * 32), idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(smem_u32(&kv_empty[s]));              // K_i and V_i are free once these products are done
+                umma_commit(smem_u32(&pv_done[i & 1]));
+                if (i + 2 < n_blocks) issue_s(i + 2);             // its S accumulator was read before P_i was announced
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ softmax: one thread per query row
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const int local = r / args.group;
+        const bool row_ok = local < tile_tokens;
+        const int pos = row_ok ? before + tok0 + local : -1;
+        const int first = (args.window > 0 && pos - args.window + 1 > 0) ? pos - args.window + 1 : 0;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        float m_used = -INFINITY, l = 0.0f;                       // the scale in use (log2 units) and the running sum
+        bool ok = true;
+        for (int i = 0; i < n_blocks && ok; ++i) {
+            if (!mbar_wait(smem_u32(&s_full[i & 1]), (uint32_t)((i >> 1) & 1))) { if (lane == 0) atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float s[KEYS];
+            tmem_load32(lane_base + (i & 1) * 64, s);
+            tmem_load32(lane_base + (i & 1) * 64 + 32, s + 32);
+            const int key_base = (block0 + i) * KEYS;
+            const bool all_visible = __all_sync(0xffffffffu, key_base + KEYS - 1 <= pos && key_base >= first);
+            float mx = -INFINITY;
+            if (all_visible) {
+#pragma unroll
+                for (int j = 0; j < KEYS; ++j) { s[j] *= args.scale_log2; mx = fmaxf(mx, s[j]); }
+            } else {
+#pragma unroll
+                for (int j = 0; j < KEYS; ++j) {
+                    const int key = key_base + j;
+                    s[j] = (key <= pos && key >= first) ? s[j] * args.scale_log2 : -INFINITY;
+                    mx = fmaxf(mx, s[j]);
+                }
+            }
+            // keep the old scale unless the maximum has grown a lot; a warp rescales its rows of O together
+            const bool grow = mx > m_used + RESCALE_THRESHOLD || (m_used == -INFINITY && mx != -INFINITY);
+            if (__any_sync(0xffffffffu, grow)) {
+                const float m_new = grow ? mx : m_used;
+                const float corr = (m_used == -INFINITY) ? 0.0f : fast_exp2(m_used - m_new);
+                if (i > 0) {
+                    // O must be at rest: the products of block i - 1 have to be finished
+                    if (!mbar_wait(smem_u32(&pv_done[(i - 1) & 1]), (uint32_t)(((i - 1) >> 1) & 1))) { if (lane == 0) atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                    for (int c = 0; c < HD; c += 32) {
+                        float o[32];
+                        tmem_load32(lane_base + L::O_COL + c, o);
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) o[e] *= corr;
+                        tmem_store32(lane_base + L::O_COL + c, o);
+                    }
+                }
+                l *= corr;
+                m_used = m_new;
+            }
+            const float base = (m_used == -INFINITY) ? 0.0f : m_used;
+            float sum = 0.0f;
+            uint32_t packed[KEYS / 2];
+#pragma unroll
+            for (int j = 0; j < KEYS; j += 2) {
+                const float p0 = fast_exp2(s[j] - base), p1 = fast_exp2(s[j + 1] - base);
+                sum += p0 + p1;
+                const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                packed[j / 2] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            l += sum;
+            // P_i goes to buffer i & 1, which the products of block i - 2 must have finished reading
+            if (i >= 2 && !mbar_wait(smem_u32(&pv_done[i & 1]), (uint32_t)(((i - 2) >> 1) & 1))) { if (lane == 0) atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; break; }
+            uint8_t* p_row = p_smem + (i & 1) * L::P_BYTES + r * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)                            // 16-byte chunk c of the row sits at position c ^ (row % 8)
+                *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) * 16)) = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // make the stores visible to the tensor core's reads
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&p_ready[i & 1]));
+        }
+        if (ok) {
+            const int last = n_blocks - 1;
+            if (!mbar_wait(smem_u32(&pv_done[last & 1]), (uint32_t)((last >> 1) & 1))) { if (lane == 0) atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; }
+        }
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            const int token = seq_begin + tok0 + local, head = kh * args.group + (r - local * args.group);
+            __nv_bfloat16* dst = args.out + ((size_t)token * args.heads + head) * HD;
+#pragma unroll
+            for (int c = 0; c < HD; c += 32) {
+                float o[32];
+                tmem_load32(lane_base + L::O_COL + c, o);          // warp-collective: every lane takes part, valid row or not
+                if (row_ok) {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 8) {
+                        uint4 v;
+                        __nv_bfloat162 h0 = __floats2bfloat162_rn(o[e] * inv, o[e + 1] * inv), h1 = __floats2bfloat162_rn(o[e + 2] * inv, o[e + 3] * inv);
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(o[e + 4] * inv, o[e + 5] * inv), h3 = __floats2bfloat162_rn(o[e + 6] * inv, o[e + 7] * inv);
+                        v.x = *reinterpret_cast<uint32_t*>(&h0); v.y = *reinterpret_cast<uint32_t*>(&h1);
+                        v.z = *reinterpret_cast<uint32_t*>(&h2); v.w = *reinterpret_cast<uint32_t*>(&h3);
+                        *reinterpret_cast<uint4*>(dst + c + e) = v;
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, L::TMEM_COLS);
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    }
+    return fn;
+}
+
+bool make_map(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box) {
+    EncodeTiled fn = encode_fn();
+    if (!fn) return false;
+    const cuuint32_t elem[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int HD>
+int launch(const void* q, const void* k_pool, const void* v_pool, const Args& args, int n_tokens, cudaStream_t stream) {
+    using L = Layout<HD>;
+    CUtensorMap map_q, map_k, map_v;
+    {   // q [token][head][dim]: a box of 64 dims x group heads x tokens_per_tile tokens = up to 128 rows of 128 bytes
+        const cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)args.heads, (cuuint64_t)n_tokens};
+        const cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)args.heads * HD * 2};
+        const cuuint32_t box[3] = {64, (cuuint32_t)args.group, (cuuint32_t)args.tokens_per_tile};
+        if (!make_map(&map_q, q, 3, dims, strides, box)) return -1;
+    }
+    {   // keys [block * kv_head * 64 tokens][dim]
+        const cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)args.pool_blocks * args.kv_heads * KEYS};
+        const cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+        const cuuint32_t box[2] = {64, KEYS};
+        if (!make_map(&map_k, k_pool, 2, dims, strides, box)) return -1;
+    }
+    {   // values [block * kv_head * dim][64 tokens]
+        const cuuint64_t dims[2] = {(cuuint64_t)KEYS, (cuuint64_t)args.pool_blocks * args.kv_heads * HD};
+        const cuuint64_t strides[1] = {(cuuint64_t)KEYS * 2};
+        const cuuint32_t box[2] = {KEYS, (cuuint32_t)HD};
+        if (!make_map(&map_v, v_pool, 2, dims, strides, box)) return -1;
+    }
+    static bool configured = false;
+    auto kernel = attention_tcgen05_kernel<HD>;
+    if (!configured) {
+        const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM);
+        if (err != cudaSuccess) return (int)err;
+        configured = true;
+    }
+    tt_launch_pdl(kernel, dim3(args.cta_tiles, args.kv_heads), dim3(THREADS), (size_t)L::SMEM, stream, map_q, map_k, map_v, args);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" int tt_attention_tcgen05_supports(int heads, int kv_heads, int head_dim) {
+    if (kv_heads <= 0 || heads % kv_heads || heads / kv_heads > 16) return 0;
+    return head_dim == 64 || head_dim == 128;
+}
+
+// Packed prompts (any number of tokens per sequence) attending over the block cache; the
+// new tokens' keys and values are already in the cache.  Returns a cudaError_t value, or -1
+// if the tensor maps could not be made.
+extern "C" int tt_attention_tcgen05(const void* q, const void* k_pool, const void* v_pool, const int* table, int table_width,
+                                    int pool_blocks, const int* cu, const int* len_before, int sequences, int n_tokens,
+                                    int heads, int kv_heads, int head_dim, float scale, int window, void* out,
+                                    unsigned* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (!tt_attention_tcgen05_supports(heads, kv_heads, head_dim) || ((uintptr_t)q & 15) || ((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15))
+        return (int)cudaErrorInvalidValue;
+    Args args;
+    args.table = table; args.table_width = table_width; args.pool_blocks = pool_blocks; args.cu = cu; args.len_before = len_before;
+    args.sequences = sequences; args.heads = heads; args.kv_heads = kv_heads; args.group = heads / kv_heads;
+    args.tokens_per_tile = ROWS / args.group;
+    args.cta_tiles = (n_tokens + args.tokens_per_tile - 1) / args.tokens_per_tile + sequences;   // upper bound; spare CTAs leave at once
+    args.scale_log2 = scale * 1.4426950408889634f; args.window = window; args.out = (__nv_bfloat16*)out; args.status = status;
+    if (head_dim == 64) return launch<64>(q, k_pool, v_pool, args, n_tokens, stream);
+    return launch<128>(q, k_pool, v_pool, args, n_tokens, stream);
+}

@@ -203,6 +203,27 @@ def attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, t
               _stream()), "attention_mma", 2 if splits > 1 else 1)
 
 
+def attention_tcgen05_supports(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int) -> bool:
+    """Whether the tcgen05 prompt attention takes these sizes (bfloat16, head size 64 or 128,
+    at most 16 query heads per key/value head)."""
+    return dtype == torch.bfloat16 and head_dim in (64, 128) and heads % kv_heads == 0 and heads // kv_heads <= 16
+
+
+def attention_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor, cu: torch.Tensor,
+                      len_before: torch.Tensor, sequences: int, n_tokens: int, heads: int, kv_heads: int, head_dim: int,
+                      scale: float, window: int, out: torch.Tensor, status: torch.Tensor) -> None:
+    """Causal attention of packed bfloat16 prompts over the block cache with both products on
+    the tcgen05 tensor cores."""
+    if not attention_tcgen05_supports(q.dtype, heads, kv_heads, head_dim):
+        raise KernelError(f"the tcgen05 attention kernel does not take {q.dtype}, {heads}/{kv_heads} heads of size {head_dim}")
+    if not (k_pool.dtype == v_pool.dtype == out.dtype == torch.bfloat16) or not q.is_contiguous():
+        raise KernelError("queries, cache and output must all be contiguous bfloat16")
+    fn = _fn("attention_tcgen05", "tt_attention_tcgen05", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
+                                                           c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(table), table.shape[1], k_pool.shape[0], _ptr(cu), _ptr(len_before), sequences,
+              n_tokens, heads, kv_heads, head_dim, scale, window, _ptr(out), _ptr(status), _stream()), "attention_tcgen05")
+
+
 # -------------------------------------------------------------------------------- gemm
 def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor) -> None:
     """out[s] = x @ w[:, k-slice s].T in float32 FMA; ``out`` is float32

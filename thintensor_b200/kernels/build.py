@@ -34,6 +34,7 @@ SOURCES: dict[str, list[str]] = {
     "attention_static_scratch": [],
     "gemm_tcgen05": [],
     "attention_mma": [],
+    "attention_tcgen05": [],
 }
 
 

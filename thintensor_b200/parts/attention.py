@@ -91,8 +91,13 @@ class CausalAttention(Mixer):
         return Delta(self.out(ctx, mixed, "attention.out"))
 
     def attend(self, ctx, q, cache, table, mixed) -> None:
-        """Tensor cores where the kernel takes the sizes (bfloat16, head size 32/64/96/128,
-        groups up to 16), the exact kernel otherwise."""
+        """Prompts in bfloat16 with head size 64 or 128: the tcgen05 kernel.  Other bfloat16
+        sizes up to 128 and all decoding: the mma.sync kernels.  Everything else (float32,
+        head sizes 48, 80, 144 ...): the exact kernel."""
+        if not ctx.decode and api.attention_tcgen05_supports(q.dtype, self.heads, self.kv_heads, self.head_dim):
+            api.attention_tcgen05(q, cache.k_pool, cache.v_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads,
+                                  self.kv_heads, self.head_dim, self.scale, self.window or 0, mixed, ctx.status)
+            return
         tensor_cores = api.attention_mma_supports(q.dtype, self.heads, self.kv_heads, self.head_dim)
         if tensor_cores:
             # decoding: one CTA per (sequence, kv head, slice), each streaming with a deep copy pipeline;
