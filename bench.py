@@ -169,7 +169,7 @@ def main() -> int:
     # token equals keeps the loop on the path that looks at every token)
     e2e_steps = min(args.steps, 128)
     stats = GenerationStats()
-    runtime.generate(prompts[:BATCH], max_new_tokens=4, stop_ids=(-1,), batch_size=BATCH, context=CONTEXT)  # warm-up
+    runtime.generate(prompts[:BATCH], max_new_tokens=e2e_steps + 1, stop_ids=(-1,), batch_size=BATCH, context=CONTEXT)  # warm-up, same shape
     runtime.generate(prompts[:BATCH], max_new_tokens=e2e_steps + 1, stop_ids=(-1,), batch_size=BATCH, context=CONTEXT, stats=stats)
     e2e_value = stats.decoded_tokens / stats.decode_seconds if stats.decode_seconds > 0 else None
 
