@@ -306,18 +306,21 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             tmem_load32(lane_base + (i & 1) * 64 + 32, s + 32);
             const int key_base = (block0 + i) * KEYS;
             const bool all_visible = __all_sync(0xffffffffu, key_base + KEYS - 1 <= pos && key_base >= first);
+            // the maximum is taken over the raw scores (the scale is positive), the scale is folded
+            // into the exponent's multiply-add below
             float mx = -INFINITY;
             if (all_visible) {
 #pragma unroll
-                for (int j = 0; j < KEYS; ++j) { s[j] *= args.scale_log2; mx = fmaxf(mx, s[j]); }
+                for (int j = 0; j < KEYS; ++j) mx = fmaxf(mx, s[j]);
             } else {
 #pragma unroll
                 for (int j = 0; j < KEYS; ++j) {
                     const int key = key_base + j;
-                    s[j] = (key <= pos && key >= first) ? s[j] * args.scale_log2 : -INFINITY;
+                    s[j] = (key <= pos && key >= first) ? s[j] : -INFINITY;
                     mx = fmaxf(mx, s[j]);
                 }
             }
+            mx *= args.scale_log2;
             // keep the old scale unless the maximum has grown a lot; a warp rescales its rows of O together
             const bool grow = mx > m_used + RESCALE_THRESHOLD || (m_used == -INFINITY && mx != -INFINITY);
             if (__any_sync(0xffffffffu, grow)) {
@@ -344,7 +347,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             uint32_t packed[KEYS / 2];
 #pragma unroll
             for (int j = 0; j < KEYS; j += 2) {
-                const float p0 = fast_exp2(s[j] - base), p1 = fast_exp2(s[j + 1] - base);
+                const float p0 = fast_exp2(fmaf(s[j], args.scale_log2, -base)), p1 = fast_exp2(fmaf(s[j + 1], args.scale_log2, -base));
                 sum += p0 + p1;
                 const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                 packed[j / 2] = *reinterpret_cast<const uint32_t*>(&h);
