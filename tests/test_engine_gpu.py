@@ -177,3 +177,28 @@ def test_step_cut_into_pieces(model_folders, dtype):
     for i, p in enumerate(prompts):
         want = oracle_logits(folder, p)
         assert_close(logits[2 * i: 2 * i + 2], want[[0, len(p) - 1]], dtype, f"pieces request {i}")
+
+
+def test_bfloat16_engine_keeps_float32_tensors(model_folders):
+    """A checkpoint stored in float32 run by the bfloat16 engine: the tensors stay in 32 bits
+    (the exact product kernel takes bfloat16 activations with float32 weights), activations and
+    cache are bfloat16, and the logits follow the oracle on the float32 weights."""
+    import thintensor_b200
+    from thintensor_b200.engine.engine import Entry
+
+    name = "c"
+    folder = model_folders(name, "float32")
+    runtime = thintensor_b200.load_model(folder, dtype="bf16")
+    mixer = runtime.model.layers[0].parts["mixer"]
+    assert mixer.qkv.weight.dtype == torch.float32 and runtime.model.embedding.part.table.dtype == torch.float32
+    engine = runtime.new_engine(max_tokens=256, max_sequences=2)
+    assert engine.cache.kv_groups[0].storage.dtype == torch.bfloat16
+    tokens = token_ids(TINY[name]["vocab_size"], 90, 700)
+    want = oracle_logits(folder, tokens)
+    slot = engine.open()
+    got = [engine.step([Entry(slot, tokens[:70], list(range(70)))])]
+    for t in range(70, 90):
+        got.append(engine.step([Entry(slot, [tokens[t]], [0])]))
+    engine.close(slot)
+    engine.check_status()
+    assert_close(torch.cat(got), want, "bfloat16", "float32 checkpoint in the bfloat16 engine")
