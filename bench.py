@@ -34,6 +34,15 @@ LLAMA_1B = {
                      "original_max_position_embeddings": 8192},
     "max_position_embeddings": 131072, "tie_word_embeddings": True,
 }
+# the other two shapes of the family, for `--only` measurements (the headline stays the 1B shape)
+SHAPES = {
+    "1b": {},
+    "3b": {"num_hidden_layers": 28, "hidden_size": 3072, "num_attention_heads": 24, "head_dim": 128},
+    "8b": {"num_hidden_layers": 32, "hidden_size": 4096, "num_attention_heads": 32, "head_dim": 128, "intermediate_size": 14336,
+           "tie_word_embeddings": False,
+           "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                            "original_max_position_embeddings": 8192}},
+}
 FULL_LAYERS = 16
 CONTEXT = 4096
 PROMPT = 2048
@@ -125,6 +134,7 @@ def main() -> int:
     parser.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64")
     parser.add_argument("--only", choices=["decode", "prefill"], help="run one phase only and print its numbers (for profiling)")
     parser.add_argument("--batch", type=int, default=BATCH, help="with --only decode: sequences decoded together")
+    parser.add_argument("--shape", choices=sorted(SHAPES), default="1b", help="with --only: layer sizes of another model of the family")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm(min(args.steps, 128), args.warmup)
@@ -143,6 +153,8 @@ def main() -> int:
     pk = peaks()
     raw = dict(LLAMA_1B)
     raw["num_hidden_layers"] = args.layers
+    if args.only and args.shape != "1b":
+        raw.update(SHAPES[args.shape])
     runtime = thintensor_b200.random_model(raw, seed=0, dtype="bf16", device="cuda:0")
     vocab = raw["vocab_size"]
     g = torch.Generator().manual_seed(1)
