@@ -24,113 +24,22 @@
 //
 // The reference has no counterpart: it feeds prompts token by token through its
 // single-token attention (thinruntime/cli.py:2802-2807, thinruntime/triton_kernels.py:14-109).
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace {
+
+using namespace tc;
 
 constexpr int ROWS = 128;            // query rows of a CTA
 constexpr int KEYS = TT_BLOCK_TOKENS;
 constexpr int THREADS = 192;
 constexpr int KV_STAGES = 3;
-constexpr uint32_t SPIN_LIMIT = 1u << 24;
 constexpr float RESCALE_THRESHOLD = 8.0f;     // in log2 units
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_load32(uint32_t addr, float* v) {
-    uint32_t r[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(addr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void tmem_store32(uint32_t addr, const float* v) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-        ::"r"(addr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
-          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
-          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
-          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
-          "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
-          "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
-          "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
-          "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
-        : "memory");
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
-}
-
-// k-major bfloat16 tile, rows 128 bytes apart, 128-byte swizzle in groups of eight rows
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)(1024u >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
-__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 template <int HD> struct Layout {
@@ -202,15 +111,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         mbar_init(smem_u32(&q_full), 1);
         for (int s = 0; s < KV_STAGES; ++s) { mbar_init(smem_u32(&kv_full[s]), 1); mbar_init(smem_u32(&kv_empty[s]), 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&s_full[i]), 1); mbar_init(smem_u32(&p_ready[i]), 4); mbar_init(smem_u32(&pv_done[i]), 1); }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_barrier_init();
     }
     __syncthreads();
     const int b = tile_info[0], tile = tile_info[1];
     if (b < 0) return;                                            // a spare CTA: everybody leaves before tensor memory is touched
     if (warp == 1) tmem_alloc(smem_u32(&tmem_base_shared), L::TMEM_COLS);
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    fence_before_sync();
     __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    fence_after_sync();
     const uint32_t tmem_base = tmem_base_shared;
 
     tt_pdl_wait();                                                // queries and this step's keys come from the previous kernel
@@ -261,7 +170,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             auto issue_s = [&](int i) {                           // S_i = Q K_i^T into S accumulator i & 1
                 const int s = i % KV_STAGES;
                 if (!mbar_wait(smem_u32(&kv_full[s]), (uint32_t)((i / KV_STAGES) & 1))) { atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; return; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                fence_after_sync();
                 const uint32_t q_addr = smem_u32(q_smem), k_addr = smem_u32(kv_smem + (size_t)s * L::STAGE_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk) {
@@ -275,7 +184,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             for (int i = 0; i < n_blocks && ok; ++i) {
                 // O += P_i V_i once the softmax warps have written P_i
                 if (!mbar_wait(smem_u32(&p_ready[i & 1]), (uint32_t)((i >> 1) & 1))) { atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                fence_after_sync();
                 const int s = i % KV_STAGES;
                 const uint32_t p_addr = smem_u32(p_smem + (i & 1) * L::P_BYTES);
                 const uint32_t v_addr = smem_u32(kv_smem + (size_t)s * L::STAGE_BYTES + L::K_BYTES);
@@ -300,7 +209,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         bool ok = true;
         for (int i = 0; i < n_blocks && ok; ++i) {
             if (!mbar_wait(smem_u32(&s_full[i & 1]), (uint32_t)((i >> 1) & 1))) { if (lane == 0) atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            fence_after_sync();
             float s[KEYS];
             tmem_load32(lane_base + (i & 1) * 64, s);
             tmem_load32(lane_base + (i & 1) * 64 + 32, s + 32);
@@ -329,7 +238,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 if (i > 0) {
                     // O must be at rest: the products of block i - 1 have to be finished
                     if (!mbar_wait(smem_u32(&pv_done[(i - 1) & 1]), (uint32_t)(((i - 1) >> 1) & 1))) { if (lane == 0) atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; break; }
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    fence_after_sync();
 #pragma unroll
                     for (int c = 0; c < HD; c += 32) {
                         float o[32];
@@ -359,8 +268,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #pragma unroll
             for (int c = 0; c < 8; ++c)                            // 16-byte chunk c of the row sits at position c ^ (row % 8)
                 *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) * 16)) = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // make the stores visible to the tensor core's reads
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            fence_async_shared();
+            fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&p_ready[i & 1]));
         }
@@ -369,7 +278,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             if (!mbar_wait(smem_u32(&pv_done[last & 1]), (uint32_t)((last >> 1) & 1))) { if (lane == 0) atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; }
         }
         if (ok) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            fence_after_sync();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             const int token = seq_begin + tok0 + local, head = kh * args.group + (r - local * args.group);
             __nv_bfloat16* dst = args.out + ((size_t)token * args.heads + head) * HD;
@@ -391,33 +300,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
         }
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    fence_before_sync();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, L::TMEM_COLS);
-}
-
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_fn() {
-    static EncodeTiled fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult result;
-        if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault, &result) == cudaSuccess &&
-            result == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiled)p;
-    }
-    return fn;
-}
-
-bool make_map(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box) {
-    EncodeTiled fn = encode_fn();
-    if (!fn) return false;
-    const cuuint32_t elem[3] = {1, 1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 template <int HD>
@@ -428,19 +313,19 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const Args& ar
         const cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)args.heads, (cuuint64_t)n_tokens};
         const cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)args.heads * HD * 2};
         const cuuint32_t box[3] = {64, (cuuint32_t)args.group, (cuuint32_t)args.tokens_per_tile};
-        if (!make_map(&map_q, q, 3, dims, strides, box)) return -1;
+        if (!tc::make_map(&map_q, q, 3, dims, strides, box)) return -1;
     }
     {   // keys [block * kv_head * 64 tokens][dim]
         const cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)args.pool_blocks * args.kv_heads * KEYS};
         const cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
         const cuuint32_t box[2] = {64, KEYS};
-        if (!make_map(&map_k, k_pool, 2, dims, strides, box)) return -1;
+        if (!tc::make_map(&map_k, k_pool, 2, dims, strides, box)) return -1;
     }
     {   // values [block * kv_head * dim][64 tokens]
         const cuuint64_t dims[2] = {(cuuint64_t)KEYS, (cuuint64_t)args.pool_blocks * args.kv_heads * HD};
         const cuuint64_t strides[1] = {(cuuint64_t)KEYS * 2};
         const cuuint32_t box[2] = {KEYS, (cuuint32_t)HD};
-        if (!make_map(&map_v, v_pool, 2, dims, strides, box)) return -1;
+        if (!tc::make_map(&map_v, v_pool, 2, dims, strides, box)) return -1;
     }
     static bool configured = false;
     auto kernel = attention_tcgen05_kernel<HD>;

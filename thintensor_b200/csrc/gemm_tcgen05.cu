@@ -34,9 +34,7 @@
 // Counterparts in random-unknown-username/Thintensor: the Triton matvec kernels
 // thinruntime/triton_kernels.py:484-535, 2074-2185 (multi_matvec), 3022-3083 (split-k)
 // and _fused_gate_up_silu_kernel :3155-3239; all SIMT, one token.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace {
 
@@ -44,99 +42,10 @@ constexpr int BM = 128;          // accumulator rows (UMMA M)
 constexpr int BK = 64;           // k elements per stage: 128 bytes, one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
-constexpr uint32_t SPIN_LIMIT = 1u << 24;
 
 enum Form { TOKENS_ON_M = 0, TOKENS_ON_M_SWIGLU = 1, FEATURES_ON_M = 2 };
 
-// ---------------------------------------------------------------- small PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_load16(uint32_t addr, float* v) {
-    uint32_t r[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(addr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-__device__ __forceinline__ void tmem_load32(uint32_t addr, float* v) {
-    uint32_t r[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(addr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-
-// Shared-memory matrix descriptor of a k-major bfloat16 tile whose rows are 128 bytes
-// apart and swizzled in 1024-byte groups of eight rows (what TMA writes with
-// CU_TENSOR_MAP_SWIZZLE_128B): start address, stride between eight-row groups = 1024
-// bytes, descriptor version 1, layout type 2 (128-byte swizzle).
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)(1024u >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
-
-// Instruction descriptor: float32 accumulator, bfloat16 a and b, both k-major, M x N.
-__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
+using namespace tc;
 
 template <int FORM, int BN> struct Shape {
     static constexpr bool dual = FORM == TOKENS_ON_M_SWIGLU;
@@ -166,7 +75,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle groups need 1024-byte alignment
     __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
     __shared__ uint32_t tmem_base_shared;
-    __shared__ int aborted;
 
     tt_pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -179,13 +87,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
         mbar_init(smem_u32(&acc_bar), 1);
-        aborted = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_barrier_init();
     }
     if (warp == 1) tmem_alloc(smem_u32(&tmem_base_shared), S::tmem_cols);
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    fence_before_sync();
     __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    fence_after_sync();
     const uint32_t tmem_base = tmem_base_shared;
 
     // rows of the two operands this tile reads
@@ -225,7 +132,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             for (int i = first; i < n_kb; ++i) {
                 const int s = i % STAGES;
                 const uint32_t parity = ((i / STAGES) & 1) ^ 1;
-                if (!mbar_wait(smem_u32(&empty_bar[s]), parity)) { atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); aborted = 1; break; }
+                if (!mbar_wait(smem_u32(&empty_bar[s]), parity)) { atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); break; }
                 const uint32_t bar = smem_u32(&full_bar[s]);
                 mbar_expect_tx(bar, S::stage_bytes);
                 uint8_t* stage = smem + (size_t)s * S::stage_bytes;
@@ -246,8 +153,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             bool ok = true;
             for (int i = 0; i < n_kb && ok; ++i) {
                 const int s = i % STAGES;
-                if (!mbar_wait(smem_u32(&full_bar[s]), (i / STAGES) & 1)) { atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); aborted = 1; ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (!mbar_wait(smem_u32(&full_bar[s]), (i / STAGES) & 1)) { atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; break; }
+                fence_after_sync();
                 const uint32_t a_addr = smem_u32(smem + (size_t)s * S::stage_bytes);
                 const uint32_t b_addr = a_addr + S::a_bytes;
 #pragma unroll
@@ -267,8 +174,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int quarter = warp & 3;                      // the 32 tensor-memory lanes this warp may read
         const int row = quarter * 32 + lane;               // accumulator row owned by this thread
         bool ok = n_kb == 0 ? true : mbar_wait(smem_u32(&acc_bar), 0);
-        if (!ok && lane == 0) { atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); aborted = 1; }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (!ok && lane == 0) { atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); }
+        fence_after_sync();
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
         if (ok) {
             if (FORM == TOKENS_ON_M) {
@@ -328,7 +235,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
         }
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    fence_before_sync();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, S::tmem_cols);
 }
@@ -364,12 +271,12 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
     if (threadIdx.x == 0) {
         for (int s = 0; s < P_STAGES; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(smem_u32(&acc_full[b]), 1); mbar_init(smem_u32(&acc_empty[b]), 4); }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_barrier_init();
     }
     if (warp == 1) tmem_alloc(smem_u32(&tmem_base_shared), 512);
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    fence_before_sync();
     __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    fence_after_sync();
     const uint32_t tmem_base = tmem_base_shared;
 
     if (warp == 0) {
@@ -415,14 +322,14 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                 if (j >= 2 && !mbar_wait(smem_u32(&acc_empty[buf]), (uint32_t)(((j >> 1) & 1) ^ 1))) {
                     atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; break;
                 }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                fence_after_sync();
                 const uint32_t acc_addr = tmem_base + buf * 256;
                 for (int i = 0; i < n_kb; ++i, ++it) {
                     const int s = (int)(it % P_STAGES);
                     if (!mbar_wait(smem_u32(&full_bar[s]), (uint32_t)((it / P_STAGES) & 1))) {
                         atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; break;
                     }
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    fence_after_sync();
                     const uint32_t a_addr = smem_u32(smem + (size_t)s * P_STAGE_BYTES);
                     const uint32_t b_addr = a_addr + BM * BK * 2;
 #pragma unroll
@@ -450,7 +357,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                 if (lane == 0) atomicOr(args.status, TT_STATUS_WAIT_EXPIRED);
                 break;
             }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            fence_after_sync();
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256;
             if (dual) {
                 __nv_bfloat16* out = (__nv_bfloat16*)args.out + (size_t)token * args.ld_out;
@@ -496,44 +403,23 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                 }
             }
             // this warp is done with the accumulator: tell the issuer
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));
         }
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    fence_before_sync();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
 // ------------------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_fn() {
-    static EncodeTiled fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult result;
-        if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault, &result) == cudaSuccess &&
-            result == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiled)p;
-    }
-    return fn;
-}
-
 // A [rows, k] bfloat16 matrix with `ld` elements between rows, read in boxes of box_rows x 64.
 bool make_map(CUtensorMap* map, const void* base, long long rows, long long k, long long ld, int box_rows) {
-    EncodeTiled fn = encode_fn();
-    if (!fn) return false;
     const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
     const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return tc::make_map(map, base, 2, dims, strides, box);
 }
 
 template <int FORM, int BN, int STAGES>

@@ -280,11 +280,6 @@ SM_COUNT = 148              # B200
 SKINNY_TOKENS = 128         # up to this many tokens the weights go on the 128-row side of the tile
 
 
-def tcgen05_ready() -> bool:
-    """Whether the tcgen05 matrix product is part of this build."""
-    return "gemm_tcgen05" in build.SOURCES
-
-
 def gemm_tcgen05_usable(x: torch.Tensor, w: torch.Tensor) -> bool:
     """TMA needs 16-byte aligned bases and row strides, i.e. k and both leading
     dimensions must be multiples of 8 bfloat16 numbers."""

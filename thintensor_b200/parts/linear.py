@@ -34,7 +34,7 @@ class Linear:
         tokens = x.shape[0]
         if x.shape[1] != self.in_features:
             raise ValueError(f"{name}: input has {x.shape[1]} features, the weight takes {self.in_features}")
-        if api.tcgen05_ready() and api.gemm_tcgen05_usable(x, self.weight):
+        if api.gemm_tcgen05_usable(x, self.weight):
             splits = api.gemm_tcgen05_splits(tokens, self.out_features, self.in_features)
             out = ctx.scratch(name, (splits, tokens, self.out_features), torch.float32)
             api.gemm_tcgen05(x, self.weight, self.bias, out, ctx.status)
@@ -60,7 +60,7 @@ class GatedLinear:
         tokens = x.shape[0]
         act = ctx.scratch(name + ".act", (tokens, self.inter))
         w = self.fused
-        if tokens > api.SKINNY_TOKENS and w.bias is None and api.tcgen05_ready() and api.gemm_tcgen05_usable(x, w.weight):
+        if tokens > api.SKINNY_TOKENS and w.bias is None and api.gemm_tcgen05_usable(x, w.weight):
             api.gemm_tcgen05_swiglu(x, w.weight, act, ctx.status)       # prompts: the float32 gate/up never reach global memory
             return act
         api.swiglu(w(ctx, x, name), act)
