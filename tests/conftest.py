@@ -52,8 +52,23 @@ TINY = {
                          "original_max_position_embeddings": 128},
         "max_position_embeddings": 1024, "tie_word_embeddings": True,
     },
+    # head sizes 64 and 128, the sizes the tcgen05 prompt attention and the pipelined decode attention take
+    "d": {
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+        "num_hidden_layers": 2, "hidden_size": 128, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64,
+        "intermediate_size": 192, "vocab_size": 300, "rope_theta": 500000.0, "rms_norm_eps": 1e-5,
+        "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                         "original_max_position_embeddings": 8192},
+        "max_position_embeddings": 4096, "tie_word_embeddings": True,
+    },
+    "e": {
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+        "num_hidden_layers": 2, "hidden_size": 96, "num_attention_heads": 3, "num_key_value_heads": 1, "head_dim": 128,
+        "intermediate_size": 160, "vocab_size": 257, "rope_theta": 10000.0, "rms_norm_eps": 1e-6,
+        "max_position_embeddings": 4096, "tie_word_embeddings": False,
+    },
 }
-SEEDS = {"a": 0, "b": 2, "c": 5}
+SEEDS = {"a": 0, "b": 2, "c": 5, "d": 7, "e": 8}
 
 
 def write_tiny_model(folder: Path, name: str, stored: str = "float32", sharpen: float = 8.0) -> Path:
