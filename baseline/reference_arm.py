@@ -16,7 +16,7 @@ scripts/thin_runtime.py:1115-1117) and feeds a prompt token by token
 (thinruntime/cli.py:2802-2807).  A batch of 8 is therefore served the only way it can
 be: one sequence after the other, each with its 2,048-token prompt; the reported value is
 all decoded tokens divided by all decode time.  If that would take longer than the time
-budget, fewer of the 8 sequences are run and the line says how many.
+limit, fewer of the 8 sequences are run and the line says how many.
 """
 from __future__ import annotations
 
@@ -94,7 +94,7 @@ def write_thin(path: Path, shape: dict, seed: int) -> None:
             out.write(value.to(torch.bfloat16).view(torch.int16).numpy().tobytes())
 
 
-def run(shape: dict, metric: str, batch: int, prompt_len: int, context: int, steps: int, warmup: int, budget_s: float = 150.0) -> dict:
+def run(shape: dict, metric: str, batch: int, prompt_len: int, context: int, steps: int, warmup: int, limit_s: float = 150.0) -> dict:
     if not (REF / "thinruntime").is_dir():
         return {"impl": "reference", "unavailable": f"the reference is not installed under {REF} (pip install --target baseline/_ref was not run here)"}
     sys.path.insert(0, str(REF))
@@ -113,7 +113,7 @@ def run(shape: dict, metric: str, batch: int, prompt_len: int, context: int, ste
         decoded, decode_ms, prefill_s, sequences_run = 0, 0.0, 0.0, 0
         started = time.perf_counter()
         for prompt in prompts:
-            if sequences_run and (time.perf_counter() - started) * (sequences_run + 1) / sequences_run > budget_s:
+            if sequences_run and (time.perf_counter() - started) * (sequences_run + 1) / sequences_run > limit_s:
                 break
             cache.reset(reuse_pages=True)
             clock = time.perf_counter()

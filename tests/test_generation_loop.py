@@ -1,5 +1,5 @@
 """The generation loop's decisions with a scripted backend: batches, stop tokens,
-sequences that end earlier, budgets, and that every sequence is finished exactly once."""
+sequences that end earlier, token limits, and that every sequence is finished exactly once."""
 from __future__ import annotations
 
 import pytest
@@ -68,7 +68,7 @@ def test_stop_tokens_and_early_finish():
     assert stats.decoded_tokens == 15 - 5
 
 
-def test_without_stop_ids_runs_to_the_budget_without_reading_tokens():
+def test_without_stop_ids_runs_to_the_limit_without_reading_tokens():
     script = {r: list(range(10)) for r in range(3)}
     backend = ScriptedBackend(script)
     out = run_generation(backend, [[1, 2], [3], [4, 5, 6]], max_new_tokens=6, stop_ids=(), batch_size=8)

@@ -9,7 +9,7 @@
 // host program that links this library through its C interface alone and has already
 // divided the GPU's memory between weights and cache at start-up, so that any later
 // cudaMalloc could fail or fragment what it planned; a step that runs under a latency
-// budget and may not pay for cudaMalloc's implicit device synchronisation; code that
+// bound and may not pay for cudaMalloc's implicit device synchronisation; code that
 // runs where only pre-registered buffers may be touched.  For them this entry point does
 // the same computation with the scratch in an array that is part of the library's own
 // image: nothing is allocated at any time, by any route.

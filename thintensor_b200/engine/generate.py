@@ -2,7 +2,7 @@
 
 ``run_generation`` holds every decision of the loop and touches no device: which
 requests form the next batch, when a sequence ends (a stop token, which is kept in the
-output, or its token budget), that a sequence that ended leaves the batch and gives its
+output, or its token limit), that a sequence that ended leaves the batch and gives its
 slot back at once, and that batches follow one another until no request is left.  It
 drives a *backend* with four calls; :class:`EngineBackend` is the one that runs on the
 GPU, tests use a scripted one.
@@ -125,7 +125,7 @@ def run_generation(backend: Backend, prompts: Sequence[Sequence[int]], max_new_t
         produced = 1
         while live:
             if not stop:
-                # nothing can end early: run to the budget without reading tokens back
+                # nothing can end early: run to the limit without reading tokens back
                 steps = max_new_tokens - produced
                 for tokens in backend.decode_run(live, steps):
                     for position, token in zip(live, tokens):
