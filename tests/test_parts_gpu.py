@@ -270,3 +270,155 @@ def test_toy_mixer_with_state_of_its_own():
         engine.close(slot)
     finally:
         MIXERS.unregister("toy_running_mean")
+
+
+def test_toy_feed_forward_with_routing():
+    """A feed-forward that routes every token to one of three experts (router logits in
+    float32, the expert with the largest logit), defined and registered here and used for
+    layer 1 while layer 0 keeps the dense SwiGLU: the loader finds its tensors by name, the
+    engine steps it in batches of unequal length, and padding-free packing means a token's
+    expert does not depend on its neighbours."""
+    from dataclasses import replace
+
+    from thintensor_b200.engine.engine import Entry
+    from thintensor_b200.parts import FEED_FORWARDS
+    from thintensor_b200.parts.base import Delta, FeedForward, WeightDecl
+    from thintensor_b200.parts.spec import PartSpec
+
+    experts, hidden, inter = 3, 64, 40
+
+    @FEED_FORWARDS.register("toy_routed")
+    class Routed(FeedForward):
+        def __init__(self, hidden, inter, experts):
+            self.hidden, self.inter, self.experts = hidden, inter, experts
+
+        def weights(self):
+            out = {"router.weight": WeightDecl((self.experts, self.hidden))}
+            for e in range(self.experts):
+                out[f"experts.{e}.up.weight"] = WeightDecl((self.inter, self.hidden))
+                out[f"experts.{e}.down.weight"] = WeightDecl((self.hidden, self.inter))
+            return out
+
+        def bind(self, tensors, dtype, device):
+            self.router = tensors["router.weight"].float()
+            self.up = torch.stack([tensors[f"experts.{e}.up.weight"].float() for e in range(self.experts)])
+            self.down = torch.stack([tensors[f"experts.{e}.down.weight"].float() for e in range(self.experts)])
+
+        def forward(self, ctx, x):
+            xf = x.float()
+            choice = (xf @ self.router.T).argmax(dim=-1)
+            hidden_act = torch.relu(torch.einsum("tih,th->ti", self.up[choice], xf))
+            return Delta(torch.einsum("thi,ti->th", self.down[choice], hidden_act).unsqueeze(0).contiguous())
+
+    try:
+        spec = llama_spec("a")
+        layers = list(spec.layers)
+        layers[1] = replace(layers[1], parts={**layers[1].parts, "ffn": PartSpec("toy_routed", {"hidden": hidden, "inter": inter, "experts": experts}, "model.layers.1.moe.")})
+        spec = replace(spec, layers=tuple(layers))
+        engine, host = make_engine(spec, torch.float32, seed=13, scale={**SHARP, "router.weight": 30.0})
+        assert "model.layers.1.moe.experts.2.down.weight" in host and "model.layers.1.mlp.gate_proj.weight" not in host
+        cfg = plain_llama.normalise_config(TINY["a"])
+        w = {k: v.double() for k, v in host.items()}
+
+        def plain(tokens):
+            positions = torch.arange(len(tokens))
+            inv_freq = plain_llama.rope_inv_freq(cfg["head_dim"], cfg["theta"], cfg["scaling"])
+            h = plain_llama.embed(w["model.embed_tokens.weight"], tokens)
+            h = plain_llama.decoder_layer(h, w, 0, cfg, positions, inv_freq)
+            p = "model.layers.1."
+            h = h + plain_llama.attention_block(plain_llama.rms_norm(h, w[p + "input_layernorm.weight"], cfg["eps"]), w, p + "self_attn.", cfg, positions, inv_freq)
+            x = plain_llama.rms_norm(h, w[p + "post_attention_layernorm.weight"], cfg["eps"])
+            choice = (x @ w[p + "moe.router.weight"].T).argmax(dim=-1)
+            rows = []
+            for t in range(len(tokens)):
+                e = int(choice[t])
+                rows.append(w[p + f"moe.experts.{e}.down.weight"] @ torch.relu(w[p + f"moe.experts.{e}.up.weight"] @ x[t]))
+            h = h + torch.stack(rows)
+            return plain_llama.head(plain_llama.rms_norm(h, w["model.norm.weight"], cfg["eps"]), w), choice
+
+        prompts = [token_ids(256, n, 130 + n) for n in (40, 3, 66)]
+        assert len({int(c) for p in prompts for c in plain(p)[1]}) == experts, "the prompts should reach every expert"
+        slots = [engine.open() for _ in prompts]
+        heads = [30, 3, 50]
+        logits = engine.step([Entry(s, p[:h], list(range(h))) for s, p, h in zip(slots, prompts, heads)])
+        at = 0
+        for i, h in enumerate(heads):
+            want = plain(prompts[i])[0]
+            assert float((logits[at: at + h].double().cpu() - want[:h]).abs().max()) <= 2e-4 * float(want.abs().max())
+            at += h
+        for t in range(10):
+            logits = engine.step([Entry(slots[0], [prompts[0][30 + t]], [0]), Entry(slots[2], [prompts[2][50 + t]], [0])])
+            for row, (i, place) in enumerate([(0, 30 + t), (2, 50 + t)]):
+                want = plain(prompts[i])[0]
+                assert float((logits[row].double().cpu() - want[place]).abs().max()) <= 2e-4 * float(want.abs().max())
+        for s in slots:
+            engine.close(s)
+    finally:
+        FEED_FORWARDS.unregister("toy_routed")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_toy_position_encoding(dtype):
+    """Another position encoding, defined and registered here: positions divided by a factor
+    (linear interpolation) with a rotary part of half the head.  Attention takes it through
+    its `position` parameter; nothing in the library changes."""
+    from dataclasses import replace
+
+    from thintensor_b200.engine.engine import Entry
+    from thintensor_b200.parts import POSITION_ENCODINGS
+    from thintensor_b200.parts.base import PositionEncoding
+    from thintensor_b200.parts.spec import PartSpec
+
+    @POSITION_ENCODINGS.register("toy_interpolated")
+    class Interpolated(PositionEncoding):
+        def __init__(self, head_dim, theta, factor):
+            self.head_dim, self.rotary_dim, self.attention_scaling = head_dim, head_dim // 2, 1.0
+            index = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32)
+            self.table = theta ** (-index / self.rotary_dim) / factor
+
+        def bind(self, tensors, dtype, device):
+            self.inv_freq = self.table.to(device)
+
+    try:
+        name = "d"
+        spec = llama_spec(name)
+        layers = []
+        for layer in spec.layers:
+            mixer = layer.parts["mixer"]
+            position = PartSpec("toy_interpolated", {"head_dim": 64, "theta": 1000.0, "factor": 4.0})
+            layers.append(replace(layer, parts={**layer.parts, "mixer": PartSpec(mixer.kind, {**mixer.params, "position": position}, mixer.prefix)}))
+        spec = replace(spec, layers=tuple(layers))
+        engine, host = make_engine(spec, dtype, seed=17, scale=SHARP)
+        cfg = plain_llama.normalise_config(TINY[name])
+        w = {k: (v.to(dtype).double() if v.is_floating_point() else v) for k, v in host.items()}
+        inv_freq = (1000.0 ** (-torch.arange(0, 32, 2, dtype=torch.float32) / 32) / 4.0)
+
+        def plain(tokens):
+            T = len(tokens)
+            positions = torch.arange(T)
+            cos, sin = plain_llama.rope_cos_sin(inv_freq, positions, torch.float64)
+            h = plain_llama.embed(w["model.embed_tokens.weight"], tokens)
+            for layer in range(cfg["layers"]):
+                p = f"model.layers.{layer}."
+                x = plain_llama.rms_norm(h, w[p + "input_layernorm.weight"], cfg["eps"])
+                q = (x @ w[p + "self_attn.q_proj.weight"].T).reshape(T, cfg["heads"], 64)
+                k = (x @ w[p + "self_attn.k_proj.weight"].T).reshape(T, cfg["kv_heads"], 64)
+                v = (x @ w[p + "self_attn.v_proj.weight"].T).reshape(T, cfg["kv_heads"], 64)
+                q = torch.cat((plain_llama.apply_rope(q[..., :32], cos, sin), q[..., 32:]), dim=-1)
+                k = torch.cat((plain_llama.apply_rope(k[..., :32], cos, sin), k[..., 32:]), dim=-1)
+                h = h + plain_llama.output_projection(plain_llama.causal_attention(q, k, v), w, p + "self_attn.")
+                h = h + plain_llama.swiglu(plain_llama.rms_norm(h, w[p + "post_attention_layernorm.weight"], cfg["eps"]), w, p + "mlp.")
+            return plain_llama.head(plain_llama.rms_norm(h, w["model.norm.weight"], cfg["eps"]), w)
+
+        tokens = token_ids(cfg["vocab"], 150, 171)
+        want = plain(tokens)
+        slot = engine.open()
+        got = [engine.step([Entry(slot, tokens[:140], list(range(140)))])]
+        for t in range(140, 150):
+            got.append(engine.step([Entry(slot, [tokens[t]], [0])]))
+        engine.close(slot)
+        engine.check_status()
+        from conftest import assert_close
+        assert_close(torch.cat(got), want, "float32" if dtype == torch.float32 else "bfloat16", "toy position encoding")
+    finally:
+        POSITION_ENCODINGS.unregister("toy_interpolated")
