@@ -65,7 +65,10 @@ def test_split_policy_and_refusals():
         api.gemm_tcgen05(x, w, None, torch.empty(1, 4, 32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV))
 
 
-@pytest.mark.parametrize("tokens,inter,k", [(129, 128, 64), (300, 200, 72), (2048, 1024, 512), (257, 8192, 2048), (5000, 1100, 200), (2048, 8192, 2048)])
+@pytest.mark.parametrize("tokens,inter,k", [(129, 128, 64), (300, 200, 72), (2048, 1024, 512), (257, 8192, 2048), (5000, 1100, 200), (2048, 8192, 2048),
+                                            # few tokens: features on the 128-row side, gate rows paired with up rows in one tile
+                                            (1, 64, 64), (8, 8192, 2048), (3, 100, 72), (16, 1000, 520), (17, 328, 200), (40, 72, 2048),
+                                            (64, 14336, 4096), (65, 130, 136), (128, 1100, 512)])
 def test_fused_swiglu(tokens, inter, k):
     from thintensor_b200.kernels import api
 

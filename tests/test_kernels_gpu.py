@@ -280,6 +280,66 @@ def test_attention_mma_decode_splits_and_window(splits, window, heads, kv_heads,
     assert int(st.item()) == 0
 
 
+@pytest.mark.parametrize("write_cache", [True, False])
+@pytest.mark.parametrize("splits", [1, 3, 16])
+@pytest.mark.parametrize("window", [0, 100])
+@pytest.mark.parametrize("heads,kv_heads,head_dim", [(8, 2, 64), (3, 1, 128), (32, 8, 64), (10, 5, 128)])
+def test_attention_decode_with_rotation_and_cache_write(splits, window, heads, kv_heads, head_dim, write_cache):
+    """Decoding straight from the slices of the qkv product: the kernel rotates q and k, writes
+    k and v at each sequence's position (first slot of a block, last slot, the middle) and
+    attends.  The cache holds garbage at those positions beforehand, and the new key of one
+    sequence is made to dominate, so a key that is written late or not at all shows."""
+    from thintensor_b200.kernels import api
+
+    dtype = torch.bfloat16
+    totals = [700, 1, 65, 300, 128]
+    n = len(totals)
+    k_pool, v_pool, table, keys, values = make_cache(totals, kv_heads, head_dim, dtype, seed=40)
+    cols = (heads + (2 * kv_heads if write_cache else 0)) * head_dim
+    slices = 3
+    qkv = randn(slices, n, cols, seed=41, scale=3 ** -0.5)
+    inv_freq = plain_llama.rope_inv_freq(head_dim, 10000.0, None).to(DEV)
+    x = qkv.double().sum(0).cpu()
+    positions = torch.tensor([t - 1 for t in totals])
+    cos, sin = plain_llama.rope_cos_sin(inv_freq.cpu(), positions, torch.float64)
+    scaling = 1.25
+    q = plain_llama.apply_rope(x[:, : heads * head_dim].view(n, heads, head_dim), cos, sin) * scaling
+    if write_cache:
+        group = heads // kv_heads
+        # sequence 3: the new key is the direction of head 0's query, long enough to take all the weight
+        q3 = x[3, :head_dim]
+        boost = (q3 * (30.0 * head_dim ** 0.5 / float(q3.norm()) ** 2 / scaling ** 2)).float().to(DEV)
+        qkv[:, 3, heads * head_dim: heads * head_dim + head_dim] = boost / slices
+        x = qkv.double().sum(0).cpu()
+        k_new = plain_llama.apply_rope(x[:, heads * head_dim: (heads + kv_heads) * head_dim].view(n, kv_heads, head_dim), cos, sin) * scaling
+        v_new = x[:, (heads + kv_heads) * head_dim:].view(n, kv_heads, head_dim)
+        table_cpu = table.cpu()
+        for b, total in enumerate(totals):
+            keys[b][total - 1] = k_new[b].to(dtype).float()
+            values[b][total - 1] = v_new[b].to(dtype).float()
+            block, off = int(table_cpu[b, (total - 1) // 64]), (total - 1) % 64
+            k_pool[block, :, off] = 77.0
+            v_pool[block, :, :, off] = -55.0
+    before = torch.tensor([t - 1 for t in totals], dtype=torch.int32, device=DEV)
+    out = torch.full((n, heads * head_dim), float("nan"), dtype=dtype, device=DEV)
+    rows = n * heads
+    part_acc = torch.full((rows * splits * head_dim,), float("nan"), dtype=torch.float32, device=DEV)
+    part_ml = torch.full((rows * splits * 2,), float("nan"), dtype=torch.float32, device=DEV)
+    st = status()
+    scale = head_dim ** -0.5
+    api.attention_decode_rope(qkv, inv_freq, head_dim, scaling, write_cache, k_pool, v_pool, table, before, n, heads, kv_heads, head_dim,
+                              scale, window, splits, out, part_acc, part_ml, st)
+    assert int(st.item()) == 0
+    want = attention_reference(q.to(dtype).float(), keys, values, [1] * n, heads, kv_heads, scale, window)
+    torch.testing.assert_close(out.double().cpu().view(n, heads, head_dim), want, **tol(dtype))
+    if write_cache:
+        assert torch.allclose(want[3, 0], values[3][totals[3] - 1, 0].double(), atol=0.35)
+        for b, total in enumerate(totals):
+            block, off = int(table_cpu[b, (total - 1) // 64]), (total - 1) % 64
+            torch.testing.assert_close(k_pool[block, :, off].float().cpu(), keys[b][total - 1], rtol=0, atol=2 ** -7 * float(keys[b][total - 1].abs().max()))
+            torch.testing.assert_close(v_pool[block, :, :, off].float().cpu(), values[b][total - 1], rtol=0, atol=2 ** -7 * float(values[b][total - 1].abs().max()))
+
+
 def test_attention_refuses_bad_sizes():
     from thintensor_b200.kernels import api
 

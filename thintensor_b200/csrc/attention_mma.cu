@@ -352,81 +352,162 @@ template <> struct DecodeShape<64> { static constexpr int WARPS = 4, STAGES = 3;
 template <> struct DecodeShape<96> { static constexpr int WARPS = 4, STAGES = 2; };
 template <> struct DecodeShape<128> { static constexpr int WARPS = 3, STAGES = 2; };
 
-template <int HD>
+// What the fused form of the decode kernel does before attention: the step's q, k and v
+// come as float32 slices of the qkv product ([splits][sequences][(heads + 2 kv_heads) * HD]);
+// q and k are rotated (all HD numbers of a head, pairs d and d + HD / 2), and the CTA that
+// holds a sequence's last block writes k and v into the cache before it reads that block.
+struct DecodeRope {
+    const float* qkv;
+    int splits;
+    size_t split_stride;
+    const float* inv_freq;
+    float attention_scaling;
+    int write_cache;
+};
+
+template <int HD, bool ROPE>
 __global__ void __launch_bounds__(DecodeShape<HD>::WARPS * 32)
-attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
-                        const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ table, int table_width,
+attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __nv_bfloat16* __restrict__ k_pool,
+                        __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ table, int table_width,
                         int pool_blocks, const int* __restrict__ len_before, int heads, int kv_heads, float scale_log2,
                         int window, int splits, __nv_bfloat16* __restrict__ out, float* __restrict__ part_acc,
                         float* __restrict__ part_ml, unsigned* status) {
     constexpr int WARPS = DecodeShape<HD>::WARPS, STAGES = DecodeShape<HD>::STAGES;
     constexpr int KC = HD / 32, NT = HD / 8;
     constexpr int K_LOADS = 8 * KC, V_LOADS = NT * 2, LOADS = K_LOADS + V_LOADS;    // 16-byte pieces per thread and block
+    static_assert(STAGES <= 3, "the wait below knows three depths");
     extern __shared__ uint4 slots[];                  // [WARPS][STAGES][LOADS][32 lanes]
     tt_pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int b = blockIdx.x, kh = blockIdx.y, split = blockIdx.z;
     const int group = heads / kv_heads;
-    // Lengths and tables were written before the previous kernel started (by the step before
-    // this one, or by the host), so they may be read ahead of the wait.
+    // Lengths and tables were written before this step's first kernel started (by the step
+    // before, or by the host), so they may be read ahead of the wait; so may every block but
+    // the one that this step's token goes into.
     const int pos = len_before[b];                    // position of this step's token = keys 0 .. pos
     const int lo_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int block0 = lo_key / TT_BLOCK_TOKENS, block1 = pos / TT_BLOCK_TOKENS;
     const int per = (block1 - block0 + 1 + splits - 1) / splits;
     const int my_begin = block0 + split * per, my_end = min(block1 + 1, my_begin + per);
     const int n_mine = my_begin + warp < my_end ? (my_end - my_begin - warp + WARPS - 1) / WARPS : 0;   // blocks of this warp
+    // block1, if it is this warp's, is its last; it is copied only after the wait
+    const int n_early = (n_mine > 0 && my_begin + warp + (n_mine - 1) * WARPS == block1) ? n_mine - 1 : n_mine;
     const int* table_row = table + (size_t)b * table_width;
     uint4* my_slots = slots + (size_t)warp * STAGES * LOADS * 32 + lane;
-    bool waited = false;
     unsigned valid = 0;                                // bit i % 32: block i of this warp has usable data
+    int issued = 0;                                    // blocks of this warp whose copies have started, one group each
 
-    auto issue = [&](int i) {                          // start the copies of this warp's i-th block (or an empty group)
-        if (i < n_mine) {
-            const int kb = my_begin + warp + i * WARPS;
-            if (kb == block1 && !waited) { tt_pdl_wait(); waited = true; }     // the block this step's token was written into
-            const int block = table_row[kb];
-            if (block >= 0 && block < pool_blocks) {
-                const __nv_bfloat16* kbase = k_pool + ((size_t)block * kv_heads + kh) * TT_BLOCK_TOKENS * HD + 8 * t;
-                const __nv_bfloat16* vbase = v_pool + ((size_t)block * kv_heads + kh) * HD * TT_BLOCK_TOKENS + (size_t)g * TT_BLOCK_TOKENS + 8 * t;
-                uint4* dst = my_slots + (size_t)(i % STAGES) * LOADS * 32;
+    auto issue_next = [&]() {
+        const int i = issued++;
+        const int kb = my_begin + warp + i * WARPS;
+        const int block = table_row[kb];
+        if (block >= 0 && block < pool_blocks) {
+            const __nv_bfloat16* kbase = k_pool + ((size_t)block * kv_heads + kh) * TT_BLOCK_TOKENS * HD + 8 * t;
+            const __nv_bfloat16* vbase = v_pool + ((size_t)block * kv_heads + kh) * HD * TT_BLOCK_TOKENS + (size_t)g * TT_BLOCK_TOKENS + 8 * t;
+            uint4* dst = my_slots + (size_t)(i % STAGES) * LOADS * 32;
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
+            for (int j = 0; j < 8; ++j)
 #pragma unroll
-                    for (int c = 0; c < KC; ++c) cp_async16(dst + (j * KC + c) * 32, kbase + (size_t)key_of(j, g) * HD + 32 * c);
+                for (int c = 0; c < KC; ++c) cp_async16(dst + (j * KC + c) * 32, kbase + (size_t)key_of(j, g) * HD + 32 * c);
 #pragma unroll
-                for (int n = 0; n < NT; ++n)
+            for (int n = 0; n < NT; ++n)
 #pragma unroll
-                    for (int half = 0; half < 2; ++half)
-                        cp_async16(dst + (K_LOADS + n * 2 + half) * 32, vbase + (size_t)(8 * n) * TT_BLOCK_TOKENS + 32 * half);
-                valid |= 1u << (i & 31);
-            } else {
-                valid &= ~(1u << (i & 31));
-                if (lane == 0) atomicOr(status, TT_STATUS_BAD_BLOCK);
-            }
+                for (int half = 0; half < 2; ++half)
+                    cp_async16(dst + (K_LOADS + n * 2 + half) * 32, vbase + (size_t)(8 * n) * TT_BLOCK_TOKENS + 32 * half);
+            valid |= 1u << (i & 31);
+        } else {
+            valid &= ~(1u << (i & 31));
+            if (lane == 0) atomicOr(status, TT_STATUS_BAD_BLOCK);
         }
         cp_async_commit();
     };
 
-#pragma unroll
-    for (int i = 0; i < STAGES - 1; ++i) issue(i);
-    if (!waited) { tt_pdl_wait(); waited = true; }     // the queries come from the previous kernel
+    while (issued < min(STAGES - 1, n_early)) issue_next();
+    tt_pdl_wait();                                     // the queries (or the qkv product) come from the previous kernel
 
     TileState<HD> st;
-    size_t row_q[2];
-    bool row_ok[2];
+    if constexpr (ROPE) {
+        // All threads share the work: one item is a rotated pair (d, d + HD / 2) of a query head
+        // or of the new key, or one number of the new value.  Queries go to shared memory, from
+        // where every warp takes its fragments; key and value go to the cache.
+        constexpr int HALF = HD / 2, PITCH_Q = HD + 8;
+        __shared__ __align__(16) __nv_bfloat16 q_sh[16 * PITCH_Q];
+        const int q_cols = heads * HD, kv_cols = rope.write_cache ? kv_heads * HD : 0;
+        const float* row = rope.qkv + (size_t)b * (q_cols + 2 * kv_cols);
+        const bool append = rope.write_cache && my_begin <= block1 && block1 < my_end;   // this CTA reads the new key
+        const int pair_rows = group + (append ? 1 : 0);
+        const int items = pair_rows * HALF + (append ? HD : 0);
+        auto sum_slices = [&](const float* p) {
+            float total = 0.0f;
+#pragma unroll 8
+            for (int s = 0; s < rope.splits; ++s) total += __ldg(p + (size_t)s * rope.split_stride);
+            return total;
+        };
+        long long k_off = -1, v_off = -1;
+        if (append) {
+            k_off = tt_cache_offset(table_row, pos, kh, kv_heads, HD, pool_blocks, status);
+            v_off = tt_value_offset(table_row, pos, kh, kv_heads, HD, pool_blocks, status);
+        }
+        for (int item = threadIdx.x; item < items; item += WARPS * 32) {
+            if (item < pair_rows * HALF) {
+                const int r = item / HALF, i = item - r * HALF;
+                const float* p = r < group ? row + (size_t)(kh * group + r) * HD + i : row + q_cols + (size_t)kh * HD + i;
+                const float a = sum_slices(p), bb = sum_slices(p + HALF);
+                float si, co;
+                sincosf(rope.inv_freq[i] * (float)pos, &si, &co);
+                co *= rope.attention_scaling;
+                si *= rope.attention_scaling;
+                const __nv_bfloat16 lo = __float2bfloat16_rn(a * co - bb * si), hi = __float2bfloat16_rn(bb * co + a * si);
+                if (r < group) {
+                    q_sh[r * PITCH_Q + i] = lo;
+                    q_sh[r * PITCH_Q + i + HALF] = hi;
+                } else if (k_off >= 0) {
+                    k_pool[k_off + i] = lo;
+                    k_pool[k_off + i + HALF] = hi;
+                }
+            } else {
+                const int d = item - pair_rows * HALF;
+                const float a = sum_slices(row + q_cols + kv_cols + (size_t)kh * HD + d);
+                if (v_off >= 0) v_pool[v_off + (long long)d * TT_BLOCK_TOKENS] = __float2bfloat16_rn(a);
+            }
+        }
+        if (append) __threadfence();                   // key and value are in memory before their block is copied
+        __syncthreads();
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const int r = g + 8 * i;
-        row_ok[i] = r < group;                         // one token: the tile's rows are the heads of the group
-        row_q[i] = ((size_t)b * heads + kh * group + r) * HD;
-        st.row_pos[i] = row_ok[i] ? pos : -1;
-        st.row_first[i] = lo_key;
+        for (int i = 0; i < 2; ++i) {
+            const int r = g + 8 * i;
+            const bool ok = r < group;
+            st.row_pos[i] = ok ? pos : -1;
+            st.row_first[i] = lo_key;
+            uint32_t (*frag)[4] = i == 0 ? st.qa : st.qb;
+#pragma unroll
+            for (int c = 0; c < KC; ++c) {
+                const uint4 v = ok ? *reinterpret_cast<const uint4*>(q_sh + r * PITCH_Q + 32 * c + 8 * t) : make_uint4(0, 0, 0, 0);
+                frag[c][0] = v.x; frag[c][1] = v.y; frag[c][2] = v.z; frag[c][3] = v.w;
+            }
+        }
+#pragma unroll
+        for (int n = 0; n < NT; ++n) { st.o[n][0] = st.o[n][1] = st.o[n][2] = st.o[n][3] = 0.0f; }
+        st.m_run[0] = st.m_run[1] = -INFINITY;
+        st.l_run[0] = st.l_run[1] = 0.0f;
+    } else {
+        size_t row_q[2];
+        bool row_ok[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int r = g + 8 * i;
+            row_ok[i] = r < group;                     // one token: the tile's rows are the heads of the group
+            row_q[i] = ((size_t)b * heads + kh * group + r) * HD;
+            st.row_pos[i] = row_ok[i] ? pos : -1;
+            st.row_first[i] = lo_key;
+        }
+        load_queries<HD>(st, q, row_q, row_ok, t);
     }
-    load_queries<HD>(st, q, row_q, row_ok, t);
 
     for (int i = 0; i < n_mine; ++i) {
-        issue(i + STAGES - 1);
-        cp_async_wait<STAGES - 1>();                   // all but the newest STAGES - 1 groups are done: block i has landed
+        while (issued < min(n_mine, i + STAGES)) issue_next();     // block i and up to STAGES - 1 beyond it
+        const int newer = issued - i - 1;              // groups that may stay in flight while block i is used
+        if (newer >= 2) cp_async_wait<2>(); else if (newer == 1) cp_async_wait<1>(); else cp_async_wait<0>();
         if (!((valid >> (i & 31)) & 1u)) continue;
         const uint4* src = my_slots + (size_t)(i % STAGES) * LOADS * 32;
         const int kb = my_begin + warp + i * WARPS;
@@ -484,6 +565,38 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     }
 }
 
+// The decode kernel, plain (ROPE = false: rotated queries in q, the cache already holds the
+// step's keys and values) or fused with the rotation and the cache write.
+template <int HD, bool ROPE>
+cudaError_t launch_decode(const void* q, const DecodeRope& rope, void* k_pool, void* v_pool, const int* table, int table_width,
+                          int pool_blocks, const int* len_before, int sequences, int heads, int kv_heads, float scale_log2,
+                          int window, int splits, void* out, float* part_acc, float* part_ml, unsigned* status,
+                          cudaStream_t stream) {
+    using D = DecodeShape<HD>;
+    constexpr int shared = D::WARPS * D::STAGES * (8 * (HD / 32) + (HD / 8) * 2) * 32 * 16;
+    static_assert(shared >= D::WARPS * 16 * (HD + 6) * 4, "the slots must also hold the warps' partial results");
+    static bool configured = false;
+    auto kernel = attention_decode_kernel<HD, ROPE>;
+    if (!configured) {
+        const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
+        if (err != cudaSuccess) return err;
+        configured = true;
+    }
+    return tt_launch_pdl(kernel, dim3(sequences, kv_heads, splits), dim3(D::WARPS * 32), shared, stream,
+        (const __nv_bfloat16*)q, rope, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks,
+        len_before, heads, kv_heads, scale_log2, window, splits, (__nv_bfloat16*)out, part_acc, part_ml, status);
+}
+
+template <int HD>
+int merge_slices(int n_rows_tokens, int heads, int splits, void* out, float* part_acc, float* part_ml, cudaStream_t stream) {
+    if (splits > 1) {
+        const long long rows = (long long)n_rows_tokens * heads;
+        tt_launch_pdl(attention_merge_kernel<__nv_bfloat16>, dim3((unsigned)((rows + ATTN_WARPS - 1) / ATTN_WARPS)), dim3(ATTN_WARPS * 32), 0, stream,
+            part_acc, part_ml, splits, HD, rows, (__nv_bfloat16*)out);
+    }
+    return (int)cudaGetLastError();
+}
+
 template <int HD>
 int launch(const void* q, const void* k_pool, const void* v_pool, const int* table, int table_width, int pool_blocks,
            const int* cu, const int* len_before, int sequences, int n_tokens, int heads, int kv_heads, float scale,
@@ -493,19 +606,9 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* tab
     const float scale_log2 = scale * 1.4426950408889634f;
     cudaError_t err;
     if (one_token_each) {
-        using D = DecodeShape<HD>;
-        constexpr int shared = D::WARPS * D::STAGES * (8 * (HD / 32) + (HD / 8) * 2) * 32 * 16;
-        static_assert(shared >= D::WARPS * 16 * (HD + 6) * 4, "the slots must also hold the warps' partial results");
-        static bool configured = false;
-        auto kernel = attention_decode_kernel<HD>;
-        if (!configured) {
-            err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
-            if (err != cudaSuccess) return (int)err;
-            configured = true;
-        }
-        err = tt_launch_pdl(kernel, dim3(sequences, kv_heads, splits), dim3(D::WARPS * 32), shared, stream,
-            (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, table, table_width, pool_blocks,
-            len_before, heads, kv_heads, scale_log2, window, splits, (__nv_bfloat16*)out, part_acc, part_ml, status);
+        err = launch_decode<HD, false>(q, DecodeRope{}, const_cast<void*>(k_pool), const_cast<void*>(v_pool), table, table_width,
+                                       pool_blocks, len_before, sequences, heads, kv_heads, scale_log2, window, splits, out,
+                                       part_acc, part_ml, status, stream);
     } else {
         // packed prompts: keys are not sliced (a prompt has tiles enough); a CTA is 64 query rows
         if (splits != 1) return (int)cudaErrorInvalidValue;
@@ -526,12 +629,7 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* tab
             len_before, sequences, heads, kv_heads, scale_log2, window, tokens_per_tile, cta_tiles, (__nv_bfloat16*)out, status);
     }
     if (err != cudaSuccess) return (int)err;
-    if (splits > 1) {
-        const long long rows = (long long)n_tokens * heads;
-        tt_launch_pdl(attention_merge_kernel<__nv_bfloat16>, dim3((unsigned)((rows + ATTN_WARPS - 1) / ATTN_WARPS)), dim3(ATTN_WARPS * 32), 0, stream,
-            part_acc, part_ml, splits, HD, rows, (__nv_bfloat16*)out);
-    }
-    return (int)cudaGetLastError();
+    return merge_slices<HD>(n_tokens, heads, splits, out, part_acc, part_ml, stream);
 }
 
 }  // namespace
@@ -561,4 +659,40 @@ extern "C" int tt_attention_mma(const void* q, const void* k_pool, const void* v
         default: TT_LAUNCH(128);
     }
 #undef TT_LAUNCH
+}
+
+// Decoding with the rotation and the cache write inside the attention kernel: takes the
+// float32 slices of the qkv product instead of rotated queries.  For bfloat16 caches, head
+// size 64 or 128 rotated whole (rotary_dim == head_dim), one token per sequence.
+// write_cache = 0: the product holds queries only and the cache is read as it is.
+// 1 if the sizes are taken, 0 if rope_append and the plain kernel have to serve them.
+extern "C" int tt_attention_decode_rope_supports(int heads, int kv_heads, int head_dim, int rotary_dim) {
+    if (!tt_attention_mma_supports(heads, kv_heads, head_dim)) return 0;
+    return (head_dim == 64 || head_dim == 128) && rotary_dim == head_dim;
+}
+
+extern "C" int tt_attention_decode_rope(const float* qkv, int qkv_splits, long long split_stride, const float* inv_freq,
+                                        int rotary_dim, float attention_scaling, int write_cache, void* k_pool, void* v_pool,
+                                        const int* table, int table_width, int pool_blocks, const int* len_before,
+                                        int sequences, int heads, int kv_heads, int head_dim, float scale, int window,
+                                        int splits, void* out, float* part_acc, float* part_ml, unsigned* status,
+                                        cudaStream_t stream) {
+    if (sequences <= 0) return 0;
+    if (!tt_attention_decode_rope_supports(heads, kv_heads, head_dim, rotary_dim) || splits < 1 || splits > 65535 || kv_heads > 65535 ||
+        qkv_splits < 1 || split_stride % 4 != 0 || ((uintptr_t)qkv & 15) != 0)
+        return (int)cudaErrorInvalidValue;
+    if (splits > 1 && (!part_acc || !part_ml)) return (int)cudaErrorInvalidValue;
+    const DecodeRope rope{qkv, qkv_splits, (size_t)split_stride, inv_freq, attention_scaling, write_cache};
+    const float scale_log2 = scale * 1.4426950408889634f;
+    cudaError_t err;
+    if (head_dim == 64) {
+        err = launch_decode<64, true>(nullptr, rope, k_pool, v_pool, table, table_width, pool_blocks, len_before, sequences, heads,
+                                      kv_heads, scale_log2, window, splits, out, part_acc, part_ml, status, stream);
+        if (err != cudaSuccess) return (int)err;
+        return merge_slices<64>(sequences, heads, splits, out, part_acc, part_ml, stream);
+    }
+    err = launch_decode<128, true>(nullptr, rope, k_pool, v_pool, table, table_width, pool_blocks, len_before, sequences, heads,
+                                   kv_heads, scale_log2, window, splits, out, part_acc, part_ml, status, stream);
+    if (err != cudaSuccess) return (int)err;
+    return merge_slices<128>(sequences, heads, splits, out, part_acc, part_ml, stream);
 }

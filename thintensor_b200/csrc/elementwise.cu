@@ -16,8 +16,12 @@ template <typename TW>
 __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
                                     float* __restrict__ residual, int hidden, int vocab, float scale,
                                     unsigned* status) {
-    tt_pdl_launch_dependents();
+    // The first kernel of every step waits before it lets its dependents start: whatever a
+    // later kernel of this step reads ahead of its own wait (lengths, tables, cache blocks of
+    // earlier steps) is then complete, because no kernel of this step starts before the
+    // previous step's last kernel has finished.
     tt_pdl_wait();
+    tt_pdl_launch_dependents();
     const int t = blockIdx.x;
     int id = tokens[t];
     if (id < 0 || id >= vocab) {

@@ -10,7 +10,7 @@
 // accumulator with tcgen05.ld and store.  Warp 0 loads, warp 1 owns tensor memory and
 // issues, warps 2-5 are the epilogue (each reads the 32 lanes its warp index allows).
 //
-// Three forms:
+// Four forms:
 //   TOKENS_ON_M            tile = 128 tokens x BN features; float32 partial sums
 //                          out[split][token][feature] (+ bias in split 0).  Prompts.
 //   TOKENS_ON_M + SWIGLU   the weight holds gate rows then up rows; each k-block issues
@@ -22,6 +22,10 @@
 //                          once; the output is written transposed.  k may be cut into
 //                          `splits` slices (grid.z) so that few output tiles still fill
 //                          148 SMs; consumers sum the slices.
+//   FEATURES_ON_M + SWIGLU the 128 rows of a tile are 64 gate rows over the 64 up rows of the
+//                          same features (two TMA boxes per stage); the up half of the
+//                          accumulator crosses to the gate half's threads through shared
+//                          memory and silu(gate) * up is stored in bfloat16.  k is not cut.
 //
 // Prompts with enough tiles to fill the GPU run the persistent kernel further down: one
 // CTA per SM walks over 128 x 256 tiles (or 128 x 128 gate + 128 x 128 up), with two
@@ -43,7 +47,7 @@ constexpr int BK = 64;           // k elements per stage: 128 bytes, one swizzle
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 
-enum Form { TOKENS_ON_M = 0, TOKENS_ON_M_SWIGLU = 1, FEATURES_ON_M = 2 };
+enum Form { TOKENS_ON_M = 0, TOKENS_ON_M_SWIGLU = 1, FEATURES_ON_M = 2, FEATURES_ON_M_SWIGLU = 3 };
 
 using namespace tc;
 
@@ -96,8 +100,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint32_t tmem_base = tmem_base_shared;
 
     // rows of the two operands this tile reads
-    const int a_row = tile_m * BM;                      // tokens (TOKENS_ON_M*) or features (FEATURES_ON_M)
+    constexpr bool weights_are_a = FORM == FEATURES_ON_M || FORM == FEATURES_ON_M_SWIGLU;
+    constexpr bool paired_rows = FORM == FEATURES_ON_M_SWIGLU;     // 64 gate rows over the 64 up rows of the same features
+    const int a_row = tile_m * (paired_rows ? BM / 2 : BM);       // tokens (TOKENS_ON_M*) or features (FEATURES_ON_M*)
     const int b_row = tile_n * BN;
+    auto load_a = [&](uint8_t* stage, int kx, uint32_t bar) {
+        if (paired_rows) {
+            tma_load_2d(smem_u32(stage), &map_a, kx, a_row, bar);
+            tma_load_2d(smem_u32(stage + S::a_bytes / 2), &map_a, kx, args.up_row_offset + a_row, bar);
+        } else {
+            tma_load_2d(smem_u32(stage), &map_a, kx, a_row, bar);
+        }
+    };
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -106,7 +120,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // activations; under programmatic dependent launch that fetch overlaps the
         // tail of the previous kernel.
         if (lane == 0) {
-            constexpr bool weights_are_a = FORM == FEATURES_ON_M;
             const int first = min(n_kb, STAGES);
             for (int i = 0; i < first; ++i) {               // stages are empty: nothing to wait for
                 const uint32_t bar = smem_u32(&full_bar[i]);
@@ -114,7 +127,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 uint8_t* stage = smem + (size_t)i * S::stage_bytes;
                 const int kx = (kb_begin + i) * BK;
                 if (weights_are_a) {
-                    tma_load_2d(smem_u32(stage), &map_a, kx, a_row, bar);
+                    load_a(stage, kx, bar);
                 } else {
                     tma_load_2d(smem_u32(stage + S::a_bytes), &map_b, kx, b_row, bar);
                     if (S::dual) tma_load_2d(smem_u32(stage + S::a_bytes + BN * BK * 2), &map_b, kx, args.up_row_offset + b_row, bar);
@@ -126,7 +139,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 uint8_t* stage = smem + (size_t)i * S::stage_bytes;
                 const int kx = (kb_begin + i) * BK;
                 if (weights_are_a) tma_load_2d(smem_u32(stage + S::a_bytes), &map_b, kx, b_row, bar);
-                else tma_load_2d(smem_u32(stage), &map_a, kx, a_row, bar);
+                else load_a(stage, kx, bar);
             }
             int issued = first;
             for (int i = first; i < n_kb; ++i) {
@@ -137,7 +150,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 mbar_expect_tx(bar, S::stage_bytes);
                 uint8_t* stage = smem + (size_t)s * S::stage_bytes;
                 const int kx = (kb_begin + i) * BK;
-                tma_load_2d(smem_u32(stage), &map_a, kx, a_row, bar);
+                load_a(stage, kx, bar);
                 tma_load_2d(smem_u32(stage + S::a_bytes), &map_b, kx, b_row, bar);
                 if (S::dual) tma_load_2d(smem_u32(stage + S::a_bytes + BN * BK * 2), &map_b, kx, args.up_row_offset + b_row, bar);
                 ++issued;
@@ -177,7 +190,41 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (!ok && lane == 0) { atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); }
         fence_after_sync();
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        if (ok) {
+        if (FORM == FEATURES_ON_M_SWIGLU) {
+            // Accumulator rows 0..63 are the gate, rows 64..127 the up projection of features
+            // a_row .. a_row + 63.  The up half goes through shared memory to the threads of the
+            // gate half (the ring is free: every product has read it), which store
+            // silu(gate) * up in bfloat16.  Both halves meet at named barrier 1.
+            constexpr int PITCH = BN + 1;
+            float* exchange = reinterpret_cast<float*>(smem);
+            const bool is_up = quarter >= 2;
+            const int r = row & 63;
+            if (ok && is_up) {
+                for (int c = 0; c < BN; c += 16) {
+                    float v[16];
+                    tmem_load16(lane_addr + c, v);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) exchange[r * PITCH + c + j] = v[j];
+                }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int feature = a_row + r;
+            if (ok && !is_up) {
+                __nv_bfloat16* out = (__nv_bfloat16*)args.out;
+                for (int c = 0; c < BN; c += 16) {
+                    float g[16];
+                    tmem_load16(lane_addr + c, g);
+                    if (feature < args.features) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int token = b_row + c + j;
+                            if (token < args.tokens)
+                                out[(size_t)token * args.ld_out + feature] = __float2bfloat16_rn(g[j] / (1.0f + __expf(-g[j])) * exchange[r * PITCH + c + j]);
+                        }
+                    }
+                }
+            }
+        } else if (ok) {
             if (FORM == TOKENS_ON_M) {
                 const int token = a_row + row;
                 float* out = (float*)args.out + (size_t)split * args.split_stride + (size_t)token * args.ld_out;
@@ -484,6 +531,18 @@ extern "C" int tt_gemm_tcgen05(const void* x, long long ldx, const void* w, long
     if (form == 1) {
         if (splits != 1 || bias) return (int)cudaErrorInvalidValue;
         if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, 2LL * features, k, ldw, 128)) return -1;
+        if (tokens <= 128) {
+            // few tokens: features on the 128-row side, 64 gate rows paired with their 64 up rows
+            const int bn = tokens <= 16 ? 16 : tokens <= 32 ? 32 : tokens <= 64 ? 64 : 128;
+            if (!make_map(&map_a, w, 2LL * features, k, ldw, BM / 2) || !make_map(&map_b, x, tokens, k, ldx, bn)) return -1;
+            const dim3 grid(1, (features + BM / 2 - 1) / (BM / 2), 1);
+            switch (bn) {
+                case 16: return launch<FEATURES_ON_M_SWIGLU, 16, 6>(map_a, map_b, args, grid, stream);
+                case 32: return launch<FEATURES_ON_M_SWIGLU, 32, 5>(map_a, map_b, args, grid, stream);
+                case 64: return launch<FEATURES_ON_M_SWIGLU, 64, 4>(map_a, map_b, args, grid, stream);
+                default: return launch<FEATURES_ON_M_SWIGLU, 128, 3>(map_a, map_b, args, grid, stream);
+            }
+        }
         const int tiles = tiles_m * ((features + 127) / 128);
         if (tiles >= 96) return launch_persistent<TOKENS_ON_M_SWIGLU>(map_a, map_b, args, tiles_m, tiles, stream);
         const dim3 grid((features + 127) / 128, tiles_m, 1);

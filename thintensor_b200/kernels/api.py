@@ -203,6 +203,38 @@ def attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, t
               _stream()), "attention_mma", 2 if splits > 1 else 1)
 
 
+def attention_decode_rope_supports(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int, rotary_dim: int) -> bool:
+    """Whether decoding may rotate q and k and write the cache inside the attention kernel
+    (bfloat16, head size 64 or 128 rotated whole, at most 16 query heads per key/value head)."""
+    return attention_mma_supports(dtype, heads, kv_heads, head_dim) and head_dim in (64, 128) and rotary_dim == head_dim
+
+
+def attention_decode_rope(qkv: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, attention_scaling: float, write_cache: bool,
+                          k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor, len_before: torch.Tensor,
+                          sequences: int, heads: int, kv_heads: int, head_dim: int, scale: float, window: int, splits: int,
+                          out: torch.Tensor, part_acc: torch.Tensor | None, part_ml: torch.Tensor | None,
+                          status: torch.Tensor) -> None:
+    """One decode step of attention straight from the float32 partial sums ``qkv``
+    [slices, sequences, cols] of the qkv product: q and k are rotated, k and v are written to
+    the cache (``write_cache``; else ``qkv`` holds queries only), then every sequence's token
+    attends over its cache.  One launch instead of rope_append and attention_mma."""
+    _need(qkv, torch.float32, "qkv")
+    _need(inv_freq, torch.float32, "inv_freq")
+    if not attention_decode_rope_supports(out.dtype, heads, kv_heads, head_dim, rotary_dim):
+        raise KernelError(f"the fused decode attention does not take {out.dtype}, {heads}/{kv_heads} heads of size {head_dim}, rotary part {rotary_dim}")
+    if not (k_pool.dtype == v_pool.dtype == torch.bfloat16):
+        raise KernelError("cache and output must be bfloat16")
+    cols = heads * head_dim + (2 * kv_heads * head_dim if write_cache else 0)
+    if qkv.shape[-1] != cols or qkv.shape[1] != sequences:
+        raise KernelError(f"qkv is {tuple(qkv.shape)}, expected [slices, {sequences}, {cols}]")
+    fn = _fn("attention_mma", "tt_attention_decode_rope", [c_void_p, c_int, c_longlong, c_void_p, c_int, c_float, c_int, c_void_p, c_void_p,
+                                                           c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                                                           c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(qkv), qkv.shape[0], qkv.stride(0), _ptr(inv_freq), rotary_dim, attention_scaling, 1 if write_cache else 0, _ptr(k_pool),
+              _ptr(v_pool), _ptr(table), table.shape[1], k_pool.shape[0], _ptr(len_before), sequences, heads, kv_heads, head_dim, scale,
+              window, splits, _ptr(out), _ptr(part_acc), _ptr(part_ml), _ptr(status), _stream()), "attention_decode_rope", 2 if splits > 1 else 1)
+
+
 def attention_tcgen05_supports(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int) -> bool:
     """Whether the tcgen05 prompt attention takes these sizes (bfloat16, head size 64 or 128,
     at most 16 query heads per key/value head)."""

@@ -60,8 +60,12 @@ class GatedLinear:
         tokens = x.shape[0]
         act = ctx.scratch(name + ".act", (tokens, self.inter))
         w = self.fused
-        if tokens > api.SKINNY_TOKENS and w.bias is None and api.gemm_tcgen05_usable(x, w.weight):
-            api.gemm_tcgen05_swiglu(x, w.weight, act, ctx.status)       # prompts: the float32 gate/up never reach global memory
+        if w.bias is None and api.gemm_tcgen05_usable(x, w.weight) and (
+                tokens > api.SKINNY_TOKENS or api.gemm_tcgen05_splits(tokens, 2 * self.inter, x.shape[1]) == 1):
+            # the float32 gate/up never reach global memory.  With few tokens this form cannot cut k
+            # into slices, so it is taken only where the plain product would not slice either
+            # (measured on a B200: 3 % faster for 14336 x 4096 at 8 tokens, 2 % slower for 8192 x 2048).
+            api.gemm_tcgen05_swiglu(x, w.weight, act, ctx.status)
             return act
         api.swiglu(w(ctx, x, name), act)
         return act
