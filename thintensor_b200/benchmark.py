@@ -112,7 +112,7 @@ def measure_decode(runtime, prompts: list[list[int]], context: int, warmup: int,
         state.step(params, use_graph)
     torch.cuda.synchronize()
     launches_before = api.launch_count()
-    if use_graph and state.graph is None:
+    if use_graph and not state.graphs:
         state.step(params, use_graph)
     lengths_before = [engine.cache.length(s) for s in state.slots]
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

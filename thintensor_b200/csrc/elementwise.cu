@@ -453,3 +453,22 @@ extern "C" int tt_advance_lengths(int* len, const int* cu, int sequences, cudaSt
     tt_launch_pdl(advance_lengths_kernel, dim3((sequences + 127) / 128), dim3(128), 0, stream, len, cu, sequences);
     TT_LAUNCH_CHECK();
 }
+
+// ------------------------------------------------------------------------------------
+// A few int32 numbers between device memory and pinned host memory that the device can
+// address (token ids in, sampled ids out): as a kernel in the chain of a step this costs
+// a fraction of a copy node in a CUDA graph.  Host memory is read and written uncached.
+// ------------------------------------------------------------------------------------
+__global__ void copy_int32_kernel(int* __restrict__ dst, const int* __restrict__ src, int n) {
+    tt_pdl_wait();
+    tt_pdl_launch_dependents();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) __stcg(dst + i, __ldcv(src + i));
+}
+
+extern "C" int tt_copy_int32(int* dst, const int* src, int n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    tt_launch_pdl(copy_int32_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, dst, src, n);
+    TT_LAUNCH_CHECK();
+}
+

@@ -80,6 +80,7 @@ class Engine:
         self._staging = _Staging()
         self.vocab_size = model.spec.vocab_size
         self.launch_count = 0
+        self.decode_states: dict = {}        # the generation loop's captured decode steps, by shape
 
     # ------------------------------------------------------------- sequences
     def open(self) -> int:

@@ -31,6 +31,9 @@ class GenerationError(ValueError):
     pass
 
 
+MAX_DECODE_STATES = 16      # decode shapes whose captured steps an engine keeps
+
+
 class Backend(Protocol):
     def fits(self, totals: Sequence[int]) -> bool:
         """Whether sequences that grow to these lengths can be live together."""
@@ -161,30 +164,22 @@ def run_generation(backend: Backend, prompts: Sequence[Sequence[int]], max_new_t
 class _DecodeState:
     """Device-resident description of a decode batch, so that a step needs nothing from
     the host: tokens (each step's samples are written where the next step reads them),
-    lengths (advanced by a kernel), block tables, request ids and step counters."""
+    lengths (advanced by a kernel), block tables, request ids and step counters.
 
-    def __init__(self, engine: Engine, slots: list[int], requests: list[int], last_tokens: list[int], steps_done: list[int],
-                 totals: list[int]):
+    A state is made for a shape (number of sequences, width of the block tables) and filled
+    for a batch; the graphs it captured serve every later batch of that shape, so only the
+    first batch of a shape pays for the capture."""
+
+    def __init__(self, engine: Engine, sequences: int, width: int):
         cache = engine.cache
         self.engine = engine
-        self.slots = list(slots)
-        self.sequences = b = len(slots)
-        self.width = max(1, max(-(-t // cache.block_tokens) for t in totals))
+        self.sequences = b = sequences
+        self.width = width
+        self.max_total = width * cache.block_tokens          # bound of any length the tables can describe
+        self.slots: list[int] = []
         groups = len(cache.kv_groups)
-        for slot, total in zip(slots, totals):
-            cache.reserve(slot, total)          # tables stay as they are for the whole run
-        flat: list[int] = []
-        flat.extend(last_tokens)                # tokens
-        flat.extend(range(b + 1))               # cu
-        flat.extend(cache.length(s) for s in slots)
-        flat.extend(slots)
-        for g in range(groups):
-            for row in cache.table_rows(g, slots, self.width):
-                flat.extend(row)
-        flat.extend(range(b))                   # rows: every token's logits
-        flat.extend(requests)
-        flat.extend(steps_done)
-        self.meta = torch.tensor(flat, dtype=torch.int32).to(engine.device)
+        self.groups = groups
+        self.meta = torch.zeros(b + (b + 1) + b + b + groups * b * width + 3 * b, dtype=torch.int32, device=engine.device)
         p = 0
 
         def cut(n):
@@ -196,10 +191,35 @@ class _DecodeState:
         self.tokens, self.cu, self.lengths, self.d_slots = cut(b), cut(b + 1), cut(b), cut(b)
         self.tables = [cut(b * self.width).view(b, self.width) for _ in range(groups)]
         self.rows, self.requests, self.steps = cut(b), cut(b), cut(b)
-        self.max_total = max(totals)
-        self.graph: torch.cuda.CUDAGraph | None = None
+        self.graphs: dict[bool, tuple[torch.cuda.CUDAGraph, int]] = {}   # by whether the step copies tokens from and to the host
+        pinned = torch.empty((2, b), dtype=torch.int32, pin_memory=True)
+        self.host_in, self.host_out = pinned[0], pinned[1]    # tokens fed by the host, tokens sampled
+        self.feed = self.host_in.numpy()                      # the same memory, written without a tensor in between
         self.warm = False
         self.launches_per_step = 0              # kernels of this library in one decode step
+
+    def fill(self, slots: list[int], requests: list[int], last_tokens: list[int], steps_done: list[int], totals: list[int]) -> None:
+        """Describe a batch: its slots, the token each sequence is fed next, its length, the
+        blocks it may grow into (reserved here, so the tables stay as they are for the run)."""
+        cache = self.engine.cache
+        b = self.sequences
+        if len(slots) != b or max(-(-t // cache.block_tokens) for t in totals) > self.width:
+            raise GenerationError("the batch does not have the shape this decode state was made for")
+        self.slots = list(slots)
+        for slot, total in zip(slots, totals):
+            cache.reserve(slot, total)
+        flat: list[int] = []
+        flat.extend(last_tokens)                # tokens
+        flat.extend(range(b + 1))               # cu
+        flat.extend(cache.length(s) for s in slots)
+        flat.extend(slots)
+        for g in range(self.groups):
+            for row in cache.table_rows(g, slots, self.width):
+                flat.extend(row)
+        flat.extend(range(b))                   # rows: every token's logits
+        flat.extend(requests)
+        flat.extend(steps_done)
+        self.meta.copy_(torch.tensor(flat, dtype=torch.int32))
 
     def context(self) -> StepContext:
         e = self.engine
@@ -218,24 +238,34 @@ class _DecodeState:
         api.advance_lengths(self.lengths, self.cu, self.sequences)
         self.steps.add_(1)
 
-    def step(self, params: SamplingParams, use_graph: bool) -> None:
+    def body_with_host(self, params: SamplingParams) -> None:
+        """The step with the host as the authority on tokens: ``host_in`` goes up before it,
+        the samples come down into ``host_out`` after it, both by small kernels that address
+        the pinned host memory (a copy node in a graph costs several times as much)."""
+        api.copy_int32(self.tokens, self.host_in)
+        self.body(params)
+        api.copy_int32(self.host_out, self.tokens)
+
+    def step(self, params: SamplingParams, use_graph: bool, host_io: bool = False) -> None:
         e = self.engine
+        body = self.body_with_host if host_io else self.body
         if not use_graph or not self.warm:
             before = api.launch_count()
-            self.body(params)                   # the first run also allocates scratch and compiles
+            body(params)                        # the first run also allocates scratch and compiles
             self.launches_per_step = api.launch_count() - before
             self.warm = True
         else:
-            if self.graph is None:
+            graph, generation = self.graphs.get(host_io, (None, -1))
+            if graph is None or generation != e.workspace.generation:     # a graph holds the addresses of scratch memory
                 generation = e.workspace.generation
                 graph = torch.cuda.CUDAGraph()
                 # capture replays nothing; the captured step runs at the first replay
                 with torch.cuda.graph(graph):
-                    self.body(params)
+                    body(params)
                 if e.workspace.generation != generation:
                     raise RuntimeError("scratch memory moved while a decode step was being captured")
-                self.graph = graph
-            self.graph.replay()
+                self.graphs[host_io] = (graph, generation)
+            graph.replay()
         for slot in self.slots:
             e.cache.advance(slot, 1)
 
@@ -254,7 +284,6 @@ class EngineBackend:
         self._steps: list[int] = []
         self._state: _DecodeState | None = None
         self._state_live: tuple[int, ...] = ()
-        self._pinned: torch.Tensor | None = None
 
     def fits(self, totals: Sequence[int]) -> bool:
         cache = self.engine.cache
@@ -281,24 +310,30 @@ class EngineBackend:
     def _state_for(self, live: Sequence[int]) -> _DecodeState:
         key = tuple(live)
         if self._state is None or self._state_live != key:
-            self._state = _DecodeState(
-                self.engine, [self._slots[p] for p in live], [self._requests[p] for p in live], [self._last[p] for p in live],
-                [self._steps[p] for p in live], [self._totals[p] for p in live],
-            )
-            self._state_live = key
+            e = self.engine
+            totals = [self._totals[p] for p in live]
+            width = max(1, max(-(-t // e.cache.block_tokens) for t in totals))
+            # states and their graphs are kept with the engine, by everything a captured step holds as a constant
+            shape = (len(live), width, self.params)
+            state = e.decode_states.pop(shape, None)
+            if state is None:
+                state = _DecodeState(e, len(live), width)
+                while len(e.decode_states) >= MAX_DECODE_STATES:
+                    e.decode_states.pop(next(iter(e.decode_states)))       # the one used longest ago
+            e.decode_states[shape] = state                                  # most recently used last
+            state.fill([self._slots[p] for p in live], [self._requests[p] for p in live], [self._last[p] for p in live],
+                       [self._steps[p] for p in live], totals)
+            self._state, self._state_live = state, key
         return self._state
 
     def decode_step(self, live) -> list[int]:
         """The host is the authority on what each sequence is fed: the last tokens go up
         from pinned memory, the new ones come back, every step."""
         state = self._state_for(live)
-        if self._pinned is None or self._pinned.numel() < len(live):
-            self._pinned = torch.empty(max(64, len(live)), dtype=torch.int32, pin_memory=True)
-        feed = self._pinned[: len(live)]
-        feed.copy_(torch.tensor([self._last[p] for p in live], dtype=torch.int32))
-        state.tokens.copy_(feed, non_blocking=True)
-        state.step(self.params, self.use_graph)
-        tokens = state.tokens.tolist()
+        state.feed[:] = [self._last[p] for p in live]
+        state.step(self.params, self.use_graph, host_io=True)
+        torch.cuda.current_stream(self.engine.device).synchronize()
+        tokens = state.host_out.tolist()
         for position, token in zip(live, tokens):
             self._last[position] = token
             self._steps[position] += 1

@@ -149,6 +149,17 @@ def swiglu(gate_up: torch.Tensor, act: torch.Tensor) -> None:
     _check(fn(_ptr(gate_up), gate_up.shape[0], gate_up.stride(0), _ptr(act), dtype_code(act.dtype), gate_up.shape[1], inter, _stream()), "swiglu")
 
 
+def copy_int32(dst: torch.Tensor, src: torch.Tensor) -> None:
+    """dst[:] = src for small int32 vectors; either side may be pinned host memory."""
+    for t, name in ((dst, "dst"), (src, "src")):
+        if t.dtype != torch.int32 or not t.is_contiguous() or not (t.is_cuda or t.is_pinned()):
+            raise KernelError(f"copy_int32: {name} must be contiguous int32 on the device or in pinned host memory")
+    if dst.numel() != src.numel():
+        raise KernelError("copy_int32: sizes differ")
+    fn = _fn("elementwise", "tt_copy_int32", [c_void_p, c_void_p, c_int, c_void_p])
+    _check(fn(c_void_p(dst.data_ptr()), c_void_p(src.data_ptr()), dst.numel(), _stream()), "copy_int32")
+
+
 def advance_lengths(lengths: torch.Tensor, cu: torch.Tensor, sequences: int) -> None:
     fn = _fn("elementwise", "tt_advance_lengths", [c_void_p, c_void_p, c_int, c_void_p])
     _check(fn(_ptr(lengths), _ptr(cu), sequences, _stream()), "advance_lengths")
