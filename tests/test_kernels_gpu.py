@@ -280,6 +280,33 @@ def test_attention_mma_decode_splits_and_window(splits, window, heads, kv_heads,
     assert int(st.item()) == 0
 
 
+@pytest.mark.parametrize("splits", [1, 3])
+def test_attention_mma_decode_many_sequences(splits):
+    """More CTAs than SMs: head size 64 then runs the variant with half the warps and two CTAs per SM."""
+    from thintensor_b200.kernels import api
+
+    dtype, heads, kv_heads, head_dim = torch.bfloat16, 8, 4, 64
+    g = torch.Generator().manual_seed(50)
+    totals = [int(v) for v in torch.randint(1, 400, (50,), generator=g)]
+    totals[7], totals[8], totals[9] = 64, 65, 128
+    n = len(totals)
+    k_pool, v_pool, table, keys, values = make_cache(totals, kv_heads, head_dim, dtype, seed=51)
+    q = randn(n, heads, head_dim, dtype=dtype, seed=52)
+    cu = torch.arange(n + 1, dtype=torch.int32, device=DEV)
+    before = torch.tensor([t - 1 for t in totals], dtype=torch.int32, device=DEV)
+    out = torch.full((n, heads * head_dim), float("nan"), dtype=dtype, device=DEV)
+    part_acc = torch.full((n * heads * splits * head_dim,), float("nan"), dtype=torch.float32, device=DEV)
+    part_ml = torch.full((n * heads * splits * 2,), float("nan"), dtype=torch.float32, device=DEV)
+    st = status()
+    scale = head_dim ** -0.5
+    assert n * kv_heads * splits > api.SM_COUNT
+    api.attention_mma(q.view(n, -1), k_pool, v_pool, table, cu, before, n, n, heads, kv_heads, head_dim, scale, 0, splits, out,
+                      part_acc, part_ml, st, one_token_each=True)
+    want = attention_reference(q.float().cpu(), keys, values, [1] * n, heads, kv_heads, scale, 0)
+    torch.testing.assert_close(out.double().cpu().view(n, heads, head_dim), want, **tol(dtype))
+    assert int(st.item()) == 0
+
+
 @pytest.mark.parametrize("write_cache", [True, False])
 @pytest.mark.parametrize("splits", [1, 3, 16])
 @pytest.mark.parametrize("window", [0, 100])

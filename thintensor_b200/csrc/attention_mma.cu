@@ -345,12 +345,17 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
 // ----------------------------------------------------------------------------- decoding
 
 // How many warps share a tile and how many blocks each keeps in flight, so that the
-// slots fit one CTA per SM: warps * stages * (HD * 256 bytes) <= 192 KB.
-template <int HD> struct DecodeShape;
-template <> struct DecodeShape<32> { static constexpr int WARPS = 8, STAGES = 3; };
-template <> struct DecodeShape<64> { static constexpr int WARPS = 4, STAGES = 3; };
-template <> struct DecodeShape<96> { static constexpr int WARPS = 4, STAGES = 2; };
-template <> struct DecodeShape<128> { static constexpr int WARPS = 3, STAGES = 2; };
+// slots fit one CTA per SM: warps * stages * (HD * 256 bytes) <= 192 KB.  Measured on a
+// B200 for head size 64: 6 warps with 2 blocks each beat 4 warps with 3 (more warps hide
+// more of the arithmetic's latency; 7 warps gain nothing further).  SMALL: half the warps
+// and half the shared memory, so that two CTAs share an SM and one's start and end run
+// under the other's streaming; faster when the grid has several waves, slower when not.
+template <int HD, bool SMALL> struct DecodeShape;
+template <> struct DecodeShape<32, false> { static constexpr int WARPS = 8, STAGES = 3; };
+template <> struct DecodeShape<64, false> { static constexpr int WARPS = 6, STAGES = 2; };
+template <> struct DecodeShape<64, true> { static constexpr int WARPS = 3, STAGES = 2; };
+template <> struct DecodeShape<96, false> { static constexpr int WARPS = 4, STAGES = 2; };
+template <> struct DecodeShape<128, false> { static constexpr int WARPS = 3, STAGES = 2; };
 
 // What the fused form of the decode kernel does before attention: the step's q, k and v
 // come as float32 slices of the qkv product ([splits][sequences][(heads + 2 kv_heads) * HD]);
@@ -365,14 +370,14 @@ struct DecodeRope {
     int write_cache;
 };
 
-template <int HD, bool ROPE>
-__global__ void __launch_bounds__(DecodeShape<HD>::WARPS * 32)
+template <int HD, bool ROPE, bool SMALL>
+__global__ void __launch_bounds__(DecodeShape<HD, SMALL>::WARPS * 32)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __nv_bfloat16* __restrict__ k_pool,
                         __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ table, int table_width,
                         int pool_blocks, const int* __restrict__ len_before, int heads, int kv_heads, float scale_log2,
                         int window, int splits, __nv_bfloat16* __restrict__ out, float* __restrict__ part_acc,
                         float* __restrict__ part_ml, unsigned* status) {
-    constexpr int WARPS = DecodeShape<HD>::WARPS, STAGES = DecodeShape<HD>::STAGES;
+    constexpr int WARPS = DecodeShape<HD, SMALL>::WARPS, STAGES = DecodeShape<HD, SMALL>::STAGES;
     constexpr int KC = HD / 32, NT = HD / 8;
     constexpr int K_LOADS = 8 * KC, V_LOADS = NT * 2, LOADS = K_LOADS + V_LOADS;    // 16-byte pieces per thread and block
     static_assert(STAGES <= 3, "the wait below knows three depths");
@@ -567,16 +572,16 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
 
 // The decode kernel, plain (ROPE = false: rotated queries in q, the cache already holds the
 // step's keys and values) or fused with the rotation and the cache write.
-template <int HD, bool ROPE>
+template <int HD, bool ROPE, bool SMALL = false>
 cudaError_t launch_decode(const void* q, const DecodeRope& rope, void* k_pool, void* v_pool, const int* table, int table_width,
                           int pool_blocks, const int* len_before, int sequences, int heads, int kv_heads, float scale_log2,
                           int window, int splits, void* out, float* part_acc, float* part_ml, unsigned* status,
                           cudaStream_t stream) {
-    using D = DecodeShape<HD>;
+    using D = DecodeShape<HD, SMALL>;
     constexpr int shared = D::WARPS * D::STAGES * (8 * (HD / 32) + (HD / 8) * 2) * 32 * 16;
     static_assert(shared >= D::WARPS * 16 * (HD + 6) * 4, "the slots must also hold the warps' partial results");
     static bool configured = false;
-    auto kernel = attention_decode_kernel<HD, ROPE>;
+    auto kernel = attention_decode_kernel<HD, ROPE, SMALL>;
     if (!configured) {
         const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
         if (err != cudaSuccess) return err;
@@ -606,9 +611,20 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* tab
     const float scale_log2 = scale * 1.4426950408889634f;
     cudaError_t err;
     if (one_token_each) {
-        err = launch_decode<HD, false>(q, DecodeRope{}, const_cast<void*>(k_pool), const_cast<void*>(v_pool), table, table_width,
-                                       pool_blocks, len_before, sequences, heads, kv_heads, scale_log2, window, splits, out,
-                                       part_acc, part_ml, status, stream);
+        static int sm_count = 0;
+        if (sm_count == 0) {
+            int device = 0;
+            if ((err = cudaGetDevice(&device)) != cudaSuccess) return (int)err;
+            if ((err = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device)) != cudaSuccess) return (int)err;
+        }
+        if (HD == 64 && (long long)sequences * kv_heads * splits > sm_count)     // several waves: two smaller CTAs per SM
+            err = launch_decode<HD, false, HD == 64>(q, DecodeRope{}, const_cast<void*>(k_pool), const_cast<void*>(v_pool), table,
+                                                     table_width, pool_blocks, len_before, sequences, heads, kv_heads, scale_log2,
+                                                     window, splits, out, part_acc, part_ml, status, stream);
+        else
+            err = launch_decode<HD, false>(q, DecodeRope{}, const_cast<void*>(k_pool), const_cast<void*>(v_pool), table, table_width,
+                                           pool_blocks, len_before, sequences, heads, kv_heads, scale_log2, window, splits, out,
+                                           part_acc, part_ml, status, stream);
     } else {
         // packed prompts: keys are not sliced (a prompt has tiles enough); a CTA is 64 query rows
         if (splits != 1) return (int)cudaErrorInvalidValue;

@@ -16,6 +16,7 @@ when there are no stop tokens.
 from __future__ import annotations
 
 import time
+import weakref
 from dataclasses import dataclass, field
 from typing import Protocol, Sequence
 
@@ -172,7 +173,10 @@ class _DecodeState:
 
     def __init__(self, engine: Engine, sequences: int, width: int):
         cache = engine.cache
-        self.engine = engine
+        # The engine keeps its states, so a state must not keep the engine alive: a cycle would leave
+        # the graphs to the garbage collector, and a graph destroyed while another is being captured
+        # invalidates that capture.
+        self._engine = weakref.ref(engine)
         self.sequences = b = sequences
         self.width = width
         self.max_total = width * cache.block_tokens          # bound of any length the tables can describe
@@ -197,6 +201,13 @@ class _DecodeState:
         self.feed = self.host_in.numpy()                      # the same memory, written without a tensor in between
         self.warm = False
         self.launches_per_step = 0              # kernels of this library in one decode step
+
+    @property
+    def engine(self) -> Engine:
+        engine = self._engine()
+        if engine is None:
+            raise GenerationError("the engine of this decode state is gone")
+        return engine
 
     def fill(self, slots: list[int], requests: list[int], last_tokens: list[int], steps_done: list[int], totals: list[int]) -> None:
         """Describe a batch: its slots, the token each sequence is fed next, its length, the

@@ -24,8 +24,8 @@ def kv_splits(ctx, parallel_units: int, keys_per_slice: int, target_units: int) 
     shape and the length bound, never on the lengths on the device."""
     if not ctx.decode:
         return 1
-    want = -(-target_units // max(parallel_units, 1))
-    most = max(1, ctx.max_total // keys_per_slice)
+    want = target_units // max(parallel_units, 1)
+    most = ctx.max_total // keys_per_slice
     return max(1, min(want, most, 64))
 
 
@@ -84,7 +84,10 @@ class CausalAttention(Mixer):
         projection = (self.qkv if cache.writes else self.q_only)(ctx, x, "attention.qkv")
         mixed = ctx.scratch("attention.mixed", (ctx.n_tokens, q_cols))
         position = self.position
-        splits = kv_splits(ctx, ctx.sequences * self.kv_heads, 512, 32)
+        # decoding: one CTA per (sequence, kv head, slice).  Measured on a B200 from 1 to 64 sequences and
+        # 2,048 to 32,768 keys: the step is fastest when the slices just fill one wave of one CTA per SM
+        # and keep at least 8 blocks each; a second wave gains nothing.
+        splits = kv_splits(ctx, ctx.sequences * self.kv_heads, 512, api.SM_COUNT)
         if (ctx.decode and ctx.sequences * self.kv_heads * splits <= api.SM_COUNT
                 and api.attention_decode_rope_supports(mixed.dtype, self.heads, self.kv_heads, self.head_dim, position.rotary_dim)):
             # decoding: rotation, cache write and attention in one kernel.  Every CTA pays the
@@ -119,9 +122,7 @@ class CausalAttention(Mixer):
             return
         tensor_cores = api.attention_mma_supports(q.dtype, self.heads, self.kv_heads, self.head_dim)
         if tensor_cores:
-            # decoding: one CTA per (sequence, kv head, slice), each streaming with a deep copy pipeline;
-            # measured on a B200, slicing pays only while there are fewer than about 32 such CTAs
-            splits = kv_splits(ctx, ctx.sequences * self.kv_heads, 512, 32)
+            splits = kv_splits(ctx, ctx.sequences * self.kv_heads, 512, api.SM_COUNT)
         else:
             splits = kv_splits(ctx, ctx.n_tokens * self.heads, 256, 8 * 148)
         part_acc, part_ml = self.slice_scratch(ctx, splits)
