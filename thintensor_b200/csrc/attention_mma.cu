@@ -37,6 +37,9 @@
 // head, SIMT); prompts are fed token by token there.
 #include "attention_kernels.cuh"
 
+#include <cooperative_groups.h>
+namespace cg = cooperative_groups;
+
 namespace {
 
 constexpr int MMA_WARPS = 4;          // warps of a CTA of the prompt kernel
@@ -375,8 +378,8 @@ __global__ void __launch_bounds__(DecodeShape<HD, SMALL>::WARPS * 32)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __nv_bfloat16* __restrict__ k_pool,
                         __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ table, int table_width,
                         int pool_blocks, const int* __restrict__ len_before, int heads, int kv_heads, float scale_log2,
-                        int window, int splits, __nv_bfloat16* __restrict__ out, float* __restrict__ part_acc,
-                        float* __restrict__ part_ml, unsigned* status) {
+                        int window, int splits, int cluster_merge, __nv_bfloat16* __restrict__ out,
+                        float* __restrict__ part_acc, float* __restrict__ part_ml, unsigned* status) {
     constexpr int WARPS = DecodeShape<HD, SMALL>::WARPS, STAGES = DecodeShape<HD, SMALL>::STAGES;
     constexpr int KC = HD / 32, NT = HD / 8;
     constexpr int K_LOADS = 8 * KC, V_LOADS = NT * 2, LOADS = K_LOADS + V_LOADS;    // 16-byte pieces per thread and block
@@ -542,6 +545,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
         if (t == 0) { sh_m[warp * 16 + r] = st.m_run[i]; sh_l[warp * 16 + r] = st.l_run[i]; }
     }
     __syncthreads();
+    // cluster_merge: the slices of a (sequence, kv head) form a thread-block cluster; each leaves its
+    // result in its own shared memory and the first CTA combines them over distributed shared memory
+    float* cta_acc = sh_l + WARPS * 16;                // [16][HD]
+    float* cta_ml = cta_acc + 16 * HD;                 // [16][2]
     for (int idx = threadIdx.x; idx < group * HD; idx += WARPS * 32) {
         const int r = idx / HD, d = idx - r * HD;
         float m = -INFINITY;
@@ -559,6 +566,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
         const size_t row_index = (size_t)b * heads + kh * group + r;
         if (splits == 1) {
             out[row_index * HD + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+        } else if (cluster_merge) {
+            cta_acc[r * HD + d] = acc;
+            if (d == 0) { cta_ml[2 * r] = m; cta_ml[2 * r + 1] = l; }
         } else {
             const size_t slot = row_index * splits + split;
             part_acc[slot * HD + d] = acc;
@@ -568,7 +578,33 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
             }
         }
     }
+    if (splits > 1 && cluster_merge) {
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();                                // every slice's result is in its shared memory
+        if (cluster.block_rank() == 0) {
+            for (int idx = threadIdx.x; idx < group * HD; idx += WARPS * 32) {
+                const int r = idx / HD, d = idx - r * HD;
+                float m = -INFINITY;
+                for (int s = 0; s < splits; ++s) m = fmaxf(m, cluster.map_shared_rank(cta_ml, s)[2 * r]);
+                float l = 0.0f, acc = 0.0f;
+                if (m != -INFINITY) {
+                    for (int s = 0; s < splits; ++s) {
+                        const float* ml = cluster.map_shared_rank(cta_ml, s);
+                        const float weight = exp2f(ml[2 * r] - m);     // 0 for a slice that saw no key
+                        l = fmaf(ml[2 * r + 1], weight, l);
+                        acc = fmaf(cluster.map_shared_rank(cta_acc, s)[r * HD + d], weight, acc);
+                    }
+                }
+                out[((size_t)b * heads + kh * group + r) * HD + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+            }
+        }
+        cluster.sync();                                // no slice leaves while its shared memory is being read
+    }
 }
+
+// Up to 8 slices (the portable cluster size) are combined inside the decode kernel by a
+// thread-block cluster; more go through scratch memory and the merge kernel.
+inline bool slices_form_cluster(int splits) { return splits > 1 && splits <= 8; }
 
 // The decode kernel, plain (ROPE = false: rotated queries in q, the cache already holds the
 // step's keys and values) or fused with the rotation and the cache write.
@@ -579,7 +615,7 @@ cudaError_t launch_decode(const void* q, const DecodeRope& rope, void* k_pool, v
                           cudaStream_t stream) {
     using D = DecodeShape<HD, SMALL>;
     constexpr int shared = D::WARPS * D::STAGES * (8 * (HD / 32) + (HD / 8) * 2) * 32 * 16;
-    static_assert(shared >= D::WARPS * 16 * (HD + 6) * 4, "the slots must also hold the warps' partial results");
+    static_assert(shared >= D::WARPS * 16 * (HD + 6) * 4 + 16 * (HD + 2) * 4, "the slots must also hold the warps' and the CTA's partial results");
     static bool configured = false;
     auto kernel = attention_decode_kernel<HD, ROPE, SMALL>;
     if (!configured) {
@@ -587,14 +623,19 @@ cudaError_t launch_decode(const void* q, const DecodeRope& rope, void* k_pool, v
         if (err != cudaSuccess) return err;
         configured = true;
     }
+    if (slices_form_cluster(splits))
+        return tt_launch_pdl_cluster(kernel, dim3(sequences, kv_heads, splits), dim3(D::WARPS * 32), shared, stream, (unsigned)splits,
+            (const __nv_bfloat16*)q, rope, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks,
+            len_before, heads, kv_heads, scale_log2, window, splits, 1, (__nv_bfloat16*)out, part_acc, part_ml, status);
     return tt_launch_pdl(kernel, dim3(sequences, kv_heads, splits), dim3(D::WARPS * 32), shared, stream,
         (const __nv_bfloat16*)q, rope, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks,
-        len_before, heads, kv_heads, scale_log2, window, splits, (__nv_bfloat16*)out, part_acc, part_ml, status);
+        len_before, heads, kv_heads, scale_log2, window, splits, 0, (__nv_bfloat16*)out, part_acc, part_ml, status);
 }
 
 template <int HD>
-int merge_slices(int n_rows_tokens, int heads, int splits, void* out, float* part_acc, float* part_ml, cudaStream_t stream) {
-    if (splits > 1) {
+int merge_slices(int n_rows_tokens, int heads, int splits, void* out, float* part_acc, float* part_ml, cudaStream_t stream,
+                 bool inside_kernel = false) {
+    if (splits > 1 && !inside_kernel) {
         const long long rows = (long long)n_rows_tokens * heads;
         tt_launch_pdl(attention_merge_kernel<__nv_bfloat16>, dim3((unsigned)((rows + ATTN_WARPS - 1) / ATTN_WARPS)), dim3(ATTN_WARPS * 32), 0, stream,
             part_acc, part_ml, splits, HD, rows, (__nv_bfloat16*)out);
@@ -645,7 +686,7 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* tab
             len_before, sequences, heads, kv_heads, scale_log2, window, tokens_per_tile, cta_tiles, (__nv_bfloat16*)out, status);
     }
     if (err != cudaSuccess) return (int)err;
-    return merge_slices<HD>(n_tokens, heads, splits, out, part_acc, part_ml, stream);
+    return merge_slices<HD>(n_tokens, heads, splits, out, part_acc, part_ml, stream, one_token_each && slices_form_cluster(splits));
 }
 
 }  // namespace
@@ -705,10 +746,10 @@ extern "C" int tt_attention_decode_rope(const float* qkv, int qkv_splits, long l
         err = launch_decode<64, true>(nullptr, rope, k_pool, v_pool, table, table_width, pool_blocks, len_before, sequences, heads,
                                       kv_heads, scale_log2, window, splits, out, part_acc, part_ml, status, stream);
         if (err != cudaSuccess) return (int)err;
-        return merge_slices<64>(sequences, heads, splits, out, part_acc, part_ml, stream);
+        return merge_slices<64>(sequences, heads, splits, out, part_acc, part_ml, stream, slices_form_cluster(splits));
     }
     err = launch_decode<128, true>(nullptr, rope, k_pool, v_pool, table, table_width, pool_blocks, len_before, sequences, heads,
                                    kv_heads, scale_log2, window, splits, out, part_acc, part_ml, status, stream);
     if (err != cudaSuccess) return (int)err;
-    return merge_slices<128>(sequences, heads, splits, out, part_acc, part_ml, stream);
+    return merge_slices<128>(sequences, heads, splits, out, part_acc, part_ml, stream, slices_form_cluster(splits));
 }

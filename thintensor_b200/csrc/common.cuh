@@ -48,6 +48,27 @@ static inline cudaError_t tt_launch_pdl(Kernel kernel, dim3 grid, dim3 block, si
     return cudaLaunchKernelEx(&config, kernel, args...);
 }
 
+// The same with the grid's z dimension grouped into thread-block clusters of cluster_z CTAs.
+template <typename Kernel, typename... Args>
+static inline cudaError_t tt_launch_pdl_cluster(Kernel kernel, dim3 grid, dim3 block, size_t shared, cudaStream_t stream,
+                                                unsigned cluster_z, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = shared;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[2];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    attribute[1].id = cudaLaunchAttributeClusterDimension;
+    attribute[1].val.clusterDim.x = 1;
+    attribute[1].val.clusterDim.y = 1;
+    attribute[1].val.clusterDim.z = cluster_z;
+    config.attrs = attribute;
+    config.numAttrs = 2;
+    return cudaLaunchKernelEx(&config, kernel, args...);
+}
+
 template <typename T> __device__ __forceinline__ float tt_to_float(T v);
 template <> __device__ __forceinline__ float tt_to_float<float>(float v) { return v; }
 template <> __device__ __forceinline__ float tt_to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
