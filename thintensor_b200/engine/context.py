@@ -21,9 +21,14 @@ class Workspace:
     def __init__(self, device: torch.device):
         self.device = device
         self._buffers: dict[str, torch.Tensor] = {}
+        self._views: dict[tuple, torch.Tensor] = {}   # (name, shape, dtype) -> the view handed out last time
         self.generation = 0  # bumped whenever a buffer moves
 
     def get(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        key = (name, shape, dtype)
+        view = self._views.get(key)
+        if view is not None:
+            return view
         count = 1
         for s in shape:
             count *= int(s)
@@ -34,7 +39,11 @@ class Workspace:
             buffer = torch.empty(grow, dtype=torch.uint8, device=self.device)
             self._buffers[name] = buffer
             self.generation += 1
-        return buffer[:nbytes].view(dtype).view(*shape)
+            self._views = {k: v for k, v in self._views.items() if k[0] != name}   # views of the old buffer
+        view = buffer[:nbytes].view(dtype).view(*shape)
+        if len(self._views) < 4096:
+            self._views[key] = view
+        return view
 
     def bytes(self) -> int:
         return sum(b.numel() for b in self._buffers.values())
