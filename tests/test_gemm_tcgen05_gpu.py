@@ -59,6 +59,8 @@ def test_split_policy_and_refusals():
     assert api.gemm_tcgen05_splits(8, 2048, 8192) == 16
     assert api.gemm_tcgen05_splits(8, 128256, 2048) == 1
     assert api.gemm_tcgen05_splits(2048, 3072, 2048) == 1
+    assert api.gemm_tcgen05_splits(300, 2048, 8192) == 1        # 3 x 8 tiles of 128 x 256: the persistent kernel
+    assert api.gemm_tcgen05_splits(300, 200, 4096) > 1          # too few tiles for it
     x, w = randn(4, 70, seed=1), randn(32, 70, seed=2)             # k = 70 is no multiple of 8
     assert not api.gemm_tcgen05_usable(x, w)
     with pytest.raises(api.KernelError):

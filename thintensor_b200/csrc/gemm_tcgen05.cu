@@ -544,12 +544,12 @@ extern "C" int tt_gemm_tcgen05(const void* x, long long ldx, const void* w, long
             }
         }
         const int tiles = tiles_m * ((features + 127) / 128);
-        if (tiles >= 96) return launch_persistent<TOKENS_ON_M_SWIGLU>(map_a, map_b, args, tiles_m, tiles, stream);
+        if (tiles >= 8) return launch_persistent<TOKENS_ON_M_SWIGLU>(map_a, map_b, args, tiles_m, tiles, stream);
         const dim3 grid((features + 127) / 128, tiles_m, 1);
         return launch<TOKENS_ON_M_SWIGLU, 128, 4>(map_a, map_b, args, grid, stream);
     }
-    if (tokens > 128 && splits == 1 && tiles_m * ((features + 255) / 256) >= 96) {
-        // enough 128 x 256 tiles for (most of) a wave of one CTA per SM
+    if (tokens > 128 && splits == 1 && tiles_m * ((features + 255) / 256) >= 8) {
+        // from 8 tiles of 128 x 256 on the persistent kernel wins even with idle SMs (measured)
         if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, features, k, ldw, 256)) return -1;
         return launch_persistent<TOKENS_ON_M>(map_a, map_b, args, tiles_m, tiles_m * ((features + 255) / 256), stream);
     }
