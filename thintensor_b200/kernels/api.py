@@ -190,6 +190,12 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table
               _ptr(part_acc), _ptr(part_ml), _ptr(status), _stream()), "attention", 2 if splits > 1 else 1)
 
 
+def _attention_launches(splits: int, decode: bool) -> int:
+    """Kernels one call launches: the decode kernel combines up to 8 slices itself (a thread-block
+    cluster), more slices need the merge kernel."""
+    return 1 if splits == 1 or (decode and splits <= 8) else 2
+
+
 def attention_mma_supports(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int) -> bool:
     """Whether the tensor-core attention kernel takes these sizes (bfloat16, head size 32,
     64, 96 or 128, at most 16 query heads per key/value head)."""
@@ -213,7 +219,7 @@ def attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, t
     _check(fn(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(table), table.shape[1], k_pool.shape[0], _ptr(cu), _ptr(len_before), sequences,
               n_tokens, heads, kv_heads, head_dim, scale, window, splits, sequences if one_token_each else 0, _ptr(out), _ptr(part_acc),
               _ptr(part_ml), _ptr(status),
-              _stream()), "attention_mma", 2 if splits > 1 else 1)
+              _stream()), "attention_mma", _attention_launches(splits, one_token_each))
 
 
 def attention_decode_rope_supports(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int, rotary_dim: int) -> bool:
@@ -245,7 +251,8 @@ def attention_decode_rope(qkv: torch.Tensor, inv_freq: torch.Tensor, rotary_dim:
                                                            c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
     _check(fn(_ptr(qkv), qkv.shape[0], qkv.stride(0), _ptr(inv_freq), rotary_dim, attention_scaling, 1 if write_cache else 0, _ptr(k_pool),
               _ptr(v_pool), _ptr(table), table.shape[1], k_pool.shape[0], _ptr(len_before), sequences, heads, kv_heads, head_dim, scale,
-              window, splits, _ptr(out), _ptr(part_acc), _ptr(part_ml), _ptr(status), _stream()), "attention_decode_rope", 2 if splits > 1 else 1)
+              window, splits, _ptr(out), _ptr(part_acc), _ptr(part_ml), _ptr(status), _stream()), "attention_decode_rope",
+           _attention_launches(splits, True))
 
 
 def attention_tcgen05_supports(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int) -> bool:
