@@ -310,7 +310,7 @@ def test_attention_mma_decode_many_sequences(splits):
 @pytest.mark.parametrize("write_cache", [True, False])
 @pytest.mark.parametrize("splits", [1, 3, 16])
 @pytest.mark.parametrize("window", [0, 100])
-@pytest.mark.parametrize("heads,kv_heads,head_dim", [(8, 2, 64), (3, 1, 128), (32, 8, 64), (10, 5, 128)])
+@pytest.mark.parametrize("heads,kv_heads,head_dim", [(8, 2, 64), (3, 1, 64), (32, 8, 64), (10, 5, 64), (16, 1, 64)])
 def test_attention_decode_with_rotation_and_cache_write(splits, window, heads, kv_heads, head_dim, write_cache):
     """Decoding straight from the slices of the qkv product: the kernel rotates q and k, writes
     k and v at each sequence's position (first slot of a block, last slot, the middle) and

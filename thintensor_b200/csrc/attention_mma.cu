@@ -720,12 +720,14 @@ extern "C" int tt_attention_mma(const void* q, const void* k_pool, const void* v
 
 // Decoding with the rotation and the cache write inside the attention kernel: takes the
 // float32 slices of the qkv product instead of rotated queries.  For bfloat16 caches, head
-// size 64 or 128 rotated whole (rotary_dim == head_dim), one token per sequence.
+// size 64 rotated whole (rotary_dim == head_dim), one token per sequence.  (Head size 128 was
+// measured slower this way than with the separate kernel: its CTAs have 96 threads for the
+// rotation, and the copies in flight leave no room for more.)
 // write_cache = 0: the product holds queries only and the cache is read as it is.
 // 1 if the sizes are taken, 0 if rope_append and the plain kernel have to serve them.
 extern "C" int tt_attention_decode_rope_supports(int heads, int kv_heads, int head_dim, int rotary_dim) {
     if (!tt_attention_mma_supports(heads, kv_heads, head_dim)) return 0;
-    return (head_dim == 64 || head_dim == 128) && rotary_dim == head_dim;
+    return head_dim == 64 && rotary_dim == head_dim;
 }
 
 extern "C" int tt_attention_decode_rope(const float* qkv, int qkv_splits, long long split_stride, const float* inv_freq,
@@ -741,15 +743,8 @@ extern "C" int tt_attention_decode_rope(const float* qkv, int qkv_splits, long l
     if (splits > 1 && (!part_acc || !part_ml)) return (int)cudaErrorInvalidValue;
     const DecodeRope rope{qkv, qkv_splits, (size_t)split_stride, inv_freq, attention_scaling, write_cache};
     const float scale_log2 = scale * 1.4426950408889634f;
-    cudaError_t err;
-    if (head_dim == 64) {
-        err = launch_decode<64, true>(nullptr, rope, k_pool, v_pool, table, table_width, pool_blocks, len_before, sequences, heads,
-                                      kv_heads, scale_log2, window, splits, out, part_acc, part_ml, status, stream);
-        if (err != cudaSuccess) return (int)err;
-        return merge_slices<64>(sequences, heads, splits, out, part_acc, part_ml, stream, slices_form_cluster(splits));
-    }
-    err = launch_decode<128, true>(nullptr, rope, k_pool, v_pool, table, table_width, pool_blocks, len_before, sequences, heads,
-                                   kv_heads, scale_log2, window, splits, out, part_acc, part_ml, status, stream);
+    const cudaError_t err = launch_decode<64, true>(nullptr, rope, k_pool, v_pool, table, table_width, pool_blocks, len_before, sequences,
+                                                    heads, kv_heads, scale_log2, window, splits, out, part_acc, part_ml, status, stream);
     if (err != cudaSuccess) return (int)err;
-    return merge_slices<128>(sequences, heads, splits, out, part_acc, part_ml, stream, slices_form_cluster(splits));
+    return merge_slices<64>(sequences, heads, splits, out, part_acc, part_ml, stream, slices_form_cluster(splits));
 }

@@ -224,8 +224,8 @@ def attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, t
 
 def attention_decode_rope_supports(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int, rotary_dim: int) -> bool:
     """Whether decoding may rotate q and k and write the cache inside the attention kernel
-    (bfloat16, head size 64 or 128 rotated whole, at most 16 query heads per key/value head)."""
-    return attention_mma_supports(dtype, heads, kv_heads, head_dim) and head_dim in (64, 128) and rotary_dim == head_dim
+    (bfloat16, head size 64 rotated whole, at most 16 query heads per key/value head)."""
+    return attention_mma_supports(dtype, heads, kv_heads, head_dim) and head_dim == 64 and rotary_dim == head_dim
 
 
 def attention_decode_rope(qkv: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, attention_scaling: float, write_cache: bool,
