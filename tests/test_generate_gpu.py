@@ -103,3 +103,43 @@ def test_bfloat16_greedy_follows_float32(model_folders):
     clear = (top2[:, 0] - top2[:, 1]) > 0.25
     assert int(clear.sum()) > 5
     assert bool((outs[0].argmax(-1) == outs[1].argmax(-1))[clear].all())
+
+
+@pytest.mark.parametrize("name,dtype", [("b", "fp32"), ("d", "bf16")])
+def test_captured_decode_steps_serve_later_batches(model_folders, name, dtype):
+    """The engine keeps the captured decode step of a batch shape.  Later batches of that shape
+    (other prompts, other slots and blocks, other lengths inside the same number of blocks) must
+    replay it with their own data; a step whose scratch memory has moved since the capture (a
+    longer prompt in between) must be captured again; and other sampling parameters must not
+    reuse a graph that has the old ones baked in."""
+    import thintensor_b200
+
+    folder = model_folders(name, "float32" if dtype == "fp32" else "bfloat16")
+    runtime = thintensor_b200.load_model(folder, dtype=dtype)
+    fresh = thintensor_b200.load_model(folder, dtype=dtype)
+    vocab = TINY[name]["vocab_size"]
+
+    def both(prompts, steps, **kw):
+        got = runtime.generate(prompts, max_new_tokens=steps, stop_ids=(-1,), batch_size=len(prompts), context=512, **kw)
+        new_engine = fresh.new_engine(max_tokens=512 * len(prompts), max_sequences=len(prompts))
+        from thintensor_b200.engine.generate import EngineBackend, run_generation
+        from thintensor_b200.sampling.sampler import SamplingParams
+        params = SamplingParams(kw.get("temperature", 0.0), kw.get("top_k", 0), kw.get("top_p", 1.0), kw.get("seed", 0))
+        want = run_generation(EngineBackend(new_engine, params, use_graph=False), prompts, steps, (-1,), len(prompts), 512, None)
+        assert got == want
+        return got
+
+    first = [token_ids(vocab, n, 40 + n) for n in (20, 33, 7)]
+    both(first, 100)                                                      # 133 tokens at most: three blocks per sequence
+    engine = runtime._engine
+    states = dict(engine.decode_states)
+    assert len(states) == 1
+    second = [token_ids(vocab, n, 90 + n) for n in (9, 30, 25)]          # same shape: 3 sequences, three blocks each
+    both(second, 100)
+    assert runtime._engine is engine and dict(engine.decode_states) == states, "the same shape should reuse the captured step"
+    generation = engine.workspace.generation
+    both([token_ids(vocab, 180, 5)], 6)                                   # a long prompt on the same engine: scratch memory grows
+    assert runtime._engine is engine and engine.workspace.generation > generation
+    both(first, 100)                                                      # the old graph holds stale addresses and is replaced
+    both(second, 100, temperature=0.9, seed=3)                            # other sampling parameters: another state
+    assert len(engine.decode_states) == 3

@@ -35,6 +35,16 @@ class GenerationError(ValueError):
 MAX_DECODE_STATES = 16      # decode shapes whose captured steps an engine keeps
 
 
+def table_width(blocks: int) -> int:
+    """The width of a decode state's block tables for sequences of up to ``blocks`` blocks: the
+    next power of two up to 16, then the next multiple of 16, so that batches whose lengths differ
+    a little share a shape (and its captured step); entries beyond a sequence's blocks stay -1."""
+    blocks = max(1, blocks)
+    if blocks <= 16:
+        return 1 << (blocks - 1).bit_length()
+    return -(-blocks // 16) * 16
+
+
 class Backend(Protocol):
     def fits(self, totals: Sequence[int]) -> bool:
         """Whether sequences that grow to these lengths can be live together."""
@@ -323,7 +333,7 @@ class EngineBackend:
         if self._state is None or self._state_live != key:
             e = self.engine
             totals = [self._totals[p] for p in live]
-            width = max(1, max(-(-t // e.cache.block_tokens) for t in totals))
+            width = table_width(max(-(-t // e.cache.block_tokens) for t in totals))
             # states and their graphs are kept with the engine, by everything a captured step holds as a constant
             shape = (len(live), width, self.params)
             state = e.decode_states.pop(shape, None)

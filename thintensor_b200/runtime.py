@@ -84,10 +84,14 @@ class Runtime:
         return Engine(self.model, cache, max_step_tokens)
 
     def engine_for(self, max_tokens: int, max_sequences: int) -> Engine:
-        key = (max_tokens, max_sequences)
-        if self._engine is None or self._engine_key != key:
-            self._engine = None
-            self._engine = self.new_engine(max_tokens, max_sequences)
+        """The runtime's own engine, kept from call to call (with its cache, its scratch memory and
+        the decode steps it has captured) as long as it is large enough; a call that needs more
+        replaces it with a larger one."""
+        have = self._engine_key
+        if self._engine is None or have[0] < max_tokens or have[1] < max_sequences:
+            key = (max(max_tokens, have[0] if have else 0), max(max_sequences, have[1] if have else 0))
+            self._engine = None                                    # the old cache goes before the new one comes
+            self._engine = self.new_engine(*key)
             self._engine_key = key
         return self._engine
 
