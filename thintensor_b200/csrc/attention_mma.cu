@@ -1,6 +1,7 @@
-// Causal grouped-query attention over the block cache on tensor cores, bfloat16, for head
-// sizes 32, 64, 96 and 128 and up to 16 query heads per key/value head.  One kernel for
-// prompts and for decoding.
+// Causal grouped-query attention over the block cache on tensor cores (mma.sync), bfloat16,
+// for head sizes 32, 64, 96 and 128 and up to 16 query heads per key/value head: the decode
+// kernel of every such model, and the prompt kernel for the head sizes the tcgen05 kernel
+// does not take.
 //
 // A warp owns a tile of 16 query rows that share one sequence and one key/value head:
 // rows are (token, head of the group) pairs, 16 / group tokens by `group` heads, so a
@@ -9,28 +10,32 @@
 // its slice of the keys; per block S = Q K^T and O += P V run as m16n8k16 mma.sync with a
 // running softmax in float32.
 //
-// No shared memory and no transposes: both products read their B operand straight from
-// global memory with 16-byte loads.  That works because (1) a dot product does not care in
-// which order its terms are added, so the k index of each product is permuted such that a
-// thread's four fragment registers are 16 contiguous bytes of a cache row (for Q K^T the
-// head dimension is permuted identically in Q and K; for P V the key index is permuted
-// identically in P's columns and V's rows, by choosing which key each score column
-// stands for), and (2) values are stored transposed inside a cache block
-// ([head_dim][64 tokens], see common.cuh), which is the "k contiguous" order P V needs.
-// The four warps of a CTA take neighbouring tiles, so their loads of the same keys meet in L1.
+// No ldmatrix and no transposes: both products take their B operand as 16-byte pieces of
+// cache rows.  That works because (1) a dot product does not care in which order its terms
+// are added, so the k index of each product is permuted such that a thread's four fragment
+// registers are 16 contiguous bytes of a cache row (for Q K^T the head dimension is
+// permuted identically in Q and K; for P V the key index is permuted identically in P's
+// columns and V's rows, by choosing which key each score column stands for), and (2)
+// values are stored transposed inside a cache block ([head_dim][64 tokens], see
+// common.cuh), which is the "k contiguous" order P V needs.
 //
-// Two kernels share the per-block arithmetic.  Prompts (attention_mma_kernel): every warp has
-// a tile of its own and loads fragments with plain 16-byte loads; the four warps of a CTA
-// take neighbouring tiles, so their loads of the same keys meet in L1.  Decoding
-// (attention_decode_kernel): one token per sequence, a tile is one CTA; its warps split
-// the tile's blocks of keys among themselves (warp w takes blocks w, w + WARPS, ...).  The
-// step is bound by reading the cache once, so every thread streams exactly the 16-byte
-// pieces it will later use as fragments into private shared-memory slots with cp.async,
-// several blocks ahead of the arithmetic (no registers held, no synchronisation needed: a
-// thread reads only what it copied itself); copies of blocks that the step does not
-// write start before the wait for the previous kernel.  The warps' (max, sum,
-// accumulator) meet in shared memory at the end.  grid.z may cut the keys into slices as
-// well; then partial results go to scratch and attention_merge_kernel combines them.
+// Two kernels share the per-block arithmetic (block_math).
+// Prompts (attention_mma_kernel): the four warps of a CTA hold 64 query rows of one
+// sequence and one key/value head; each block's K and V tiles are copied once per CTA into
+// shared memory with cp.async, two or three blocks ahead, and every warp takes its
+// fragments from there.
+// Decoding (attention_decode_kernel): one token per sequence, a tile is one CTA; its warps
+// split the tile's blocks of keys among themselves (warp w takes blocks w, w + WARPS, ...).
+// The step is bound by reading the cache once, so every thread streams exactly the 16-byte
+// pieces it will later use as fragments into private shared-memory slots with cp.async, a
+// block ahead of the arithmetic (no registers held, no synchronisation needed: a thread
+// reads only what it copied itself); copies of blocks that the step does not write start
+// before the wait for the previous kernel.  The warps' (max, sum, accumulator) meet in
+// shared memory at the end.  grid.z may cut the keys into slices as well: up to 8 slices
+// form a thread-block cluster and are combined by its first CTA over distributed shared
+// memory, more leave partial results in scratch for attention_merge_kernel.  For head size
+// 64 the kernel can also do what comes before attention in a step: rotate q and k and
+// write the new key and value into the cache (DecodeRope).
 //
 // Counterparts in random-unknown-username/Thintensor: _single_token_gqa_attention_kernel and
 // the split pair, thinruntime/triton_kernels.py:14-245 (one token, one program per query

@@ -236,7 +236,7 @@ def attention_decode_rope(qkv: torch.Tensor, inv_freq: torch.Tensor, rotary_dim:
     """One decode step of attention straight from the float32 partial sums ``qkv``
     [slices, sequences, cols] of the qkv product: q and k are rotated, k and v are written to
     the cache (``write_cache``; else ``qkv`` holds queries only), then every sequence's token
-    attends over its cache.  One launch instead of rope_append and attention_mma."""
+    attends over its cache: one launch where rope_append and attention_mma would be two."""
     _need(qkv, torch.float32, "qkv")
     _need(inv_freq, torch.float32, "inv_freq")
     if not attention_decode_rope_supports(out.dtype, heads, kv_heads, head_dim, rotary_dim):
