@@ -114,11 +114,19 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const float* __restrict__ d
                        const float* __restrict__ weight, float weight_offset, float eps, TOut* __restrict__ out,
                        const int* __restrict__ rows, int hidden) {
     tt_pdl_launch_dependents();
-    tt_pdl_wait();
     __shared__ float reduce[32];
     const int i = blockIdx.x;
-    const int r = rows ? rows[i] : i;
     const int quads = hidden >> 2;
+    // the norm's weight is written by no kernel: it is fetched while the previous kernel still runs
+    const float4* w4 = reinterpret_cast<const float4*>(weight);
+    float4 w[NORM_VEC_MAX];
+#pragma unroll
+    for (int v = 0; v < NORM_VEC_MAX; ++v) {
+        const int j = threadIdx.x + v * blockDim.x;
+        if (j < quads) w[v] = __ldg(w4 + j);
+    }
+    tt_pdl_wait();
+    const int r = rows ? rows[i] : i;
     float4* res = reinterpret_cast<float4*>(residual + (size_t)r * hidden);
     const float4* del = delta ? reinterpret_cast<const float4*>(delta + (size_t)r * hidden) : nullptr;
     const size_t stride4 = split_stride >> 2;
@@ -150,14 +158,12 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const float* __restrict__ d
     const float total = tt_block_sum(sumsq, reduce);
     const float rstd = rsqrtf(total / (float)hidden + eps);
     TOut* o = out + (size_t)i * hidden;
-    const float4* w4 = reinterpret_cast<const float4*>(weight);
 #pragma unroll
     for (int v = 0; v < NORM_VEC_MAX; ++v) {
         const int j = threadIdx.x + v * blockDim.x;
         if (j < quads) {
-            const float4 w = __ldg(w4 + j);
-            const float y0 = x[v].x * rstd * (w.x + weight_offset), y1 = x[v].y * rstd * (w.y + weight_offset);
-            const float y2 = x[v].z * rstd * (w.z + weight_offset), y3 = x[v].w * rstd * (w.w + weight_offset);
+            const float y0 = x[v].x * rstd * (w[v].x + weight_offset), y1 = x[v].y * rstd * (w[v].y + weight_offset);
+            const float y2 = x[v].z * rstd * (w[v].z + weight_offset), y3 = x[v].w * rstd * (w[v].w + weight_offset);
             tt_store4(o + 4 * j, y0, y1, y2, y3);
         }
     }
