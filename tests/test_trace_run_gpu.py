@@ -32,8 +32,9 @@ def read_step(out: Path, step: int, vocab: int) -> torch.Tensor:
     return torch.from_numpy(np.fromfile(out / f"{step}.f32", dtype="<f4").reshape(-1, vocab).copy())
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["a", "b"])
+# a, b: every replay mode in both precisions; d, e (head sizes 64 and 128): the tensor-core attention kernels
+@pytest.mark.parametrize("name,dtype", [("a", "float32"), ("a", "bfloat16"), ("b", "float32"), ("b", "bfloat16"),
+                                        ("d", "bfloat16"), ("e", "bfloat16")])
 def test_replay_modes_agree_with_plain(model_folders, tmp_path, name, dtype):
     folder = model_folders(name, "float32" if dtype == "float32" else "bfloat16")
     vocab = TINY[name]["vocab_size"]
