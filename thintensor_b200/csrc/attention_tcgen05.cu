@@ -10,12 +10,14 @@
 //                        ([dim][64 keys], see common.cuh): both are "k contiguous" B operands
 //                        exactly as they lie in the cache;
 //   warp 1 (one thread)  issues S_i = Q K_i^T (M 128, N 64) into one of two S accumulators as
-//                        soon as K_i has landed, and O += P_i V_i (M 128, N dim) once the
-//                        softmax warps have written P_i, so S_{i+1} is computed while
-//                        softmax_i runs and P_i V_i while softmax_{i+1} runs;
+//                        soon as K_i has landed, and O += P_i V_i (M 128, N dim, A operand in
+//                        tensor memory) once the softmax warps have written P_i, so S_{i+1} is
+//                        computed while softmax_i runs and P_i V_i while softmax_{i+1} runs;
 //   warps 2-5            read a row of S per thread (tcgen05.ld, no shuffles needed for the
 //                        row maximum and sum), scale, mask the diagonal blocks, exponentiate,
-//                        write P as a swizzled bfloat16 A operand into shared memory.  O stays
+//                        and write P back to tensor memory as bfloat16 pairs (tcgen05.st), one
+//                        of two buffers: P never passes through shared memory, which took a
+//                        third of a block's time when it did (stores, proxy fence).  O stays
 //                        in tensor memory; it is rescaled only when a row's maximum has grown
 //                        by more than 2^8 since the scale in use (then the warp reads, scales
 //                        and writes back its 32 rows of O), otherwise the old scale stays.
@@ -46,11 +48,11 @@ template <int HD> struct Layout {
     static constexpr int CHUNKS = HD / 64;                      // 64-wide slices of the head dimension
     static constexpr int Q_BYTES = ROWS * HD * 2;
     static constexpr int K_BYTES = KEYS * HD * 2;               // = V tile
-    static constexpr int P_BYTES = ROWS * KEYS * 2;
     static constexpr int STAGE_BYTES = 2 * K_BYTES;
-    static constexpr int SMEM = Q_BYTES + KV_STAGES * STAGE_BYTES + 2 * P_BYTES + 1024;
-    static constexpr int TMEM_COLS = 256;                       // S: 2 x 64, O: HD (64 or 128)
-    static constexpr int O_COL = 128;
+    static constexpr int SMEM = Q_BYTES + KV_STAGES * STAGE_BYTES + 1024;
+    static constexpr int O_COL = 128;                           // S: 2 x 64 columns, then O: HD, then P: 2 x 32 (bfloat16 pairs)
+    static constexpr int P_COL = O_COL + HD;
+    static constexpr int TMEM_COLS = HD == 64 ? 256 : 512;
 };
 
 struct Args {
@@ -74,7 +76,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_smem = smem;
     uint8_t* kv_smem = q_smem + L::Q_BYTES;
-    uint8_t* p_smem = kv_smem + KV_STAGES * L::STAGE_BYTES;
     __shared__ uint64_t q_full, kv_full[KV_STAGES], kv_empty[KV_STAGES], s_full[2], p_ready[2], pv_done[2];
     __shared__ uint32_t tmem_base_shared;
     __shared__ int tile_info[2];                                  // sequence, tile within the sequence
@@ -186,11 +187,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 if (!mbar_wait(smem_u32(&p_ready[i & 1]), (uint32_t)((i >> 1) & 1))) { atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; break; }
                 fence_after_sync();
                 const int s = i % KV_STAGES;
-                const uint32_t p_addr = smem_u32(p_smem + (i & 1) * L::P_BYTES);
+                const uint32_t p_tmem = tmem_base + L::P_COL + (i & 1) * 32;
                 const uint32_t v_addr = smem_u32(kv_smem + (size_t)s * L::STAGE_BYTES + L::K_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < KEYS / 16; ++kk)
-                    umma_bf16(tmem_base + L::O_COL, smem_desc(p_addr + kk * 32), smem_desc(v_addr + kk * 32), idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+                    umma_bf16_a_in_tmem(tmem_base + L::O_COL, p_tmem + kk * 8, smem_desc(v_addr + kk * 32), idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(smem_u32(&kv_empty[s]));              // K_i and V_i are free once these products are done
                 umma_commit(smem_u32(&pv_done[i & 1]));
                 if (i + 2 < n_blocks) issue_s(i + 2);             // its S accumulator was read before P_i was announced
@@ -217,19 +218,20 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             const bool all_visible = __all_sync(0xffffffffu, key_base + KEYS - 1 <= pos && key_base >= first);
             // the maximum is taken over the raw scores (the scale is positive), the scale is folded
             // into the exponent's multiply-add below
-            float mx = -INFINITY;
-            if (all_visible) {
-#pragma unroll
-                for (int j = 0; j < KEYS; ++j) mx = fmaxf(mx, s[j]);
-            } else {
+            if (!all_visible) {
 #pragma unroll
                 for (int j = 0; j < KEYS; ++j) {
                     const int key = key_base + j;
                     s[j] = (key <= pos && key >= first) ? s[j] : -INFINITY;
-                    mx = fmaxf(mx, s[j]);
                 }
             }
-            mx *= args.scale_log2;
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};     // four chains instead of one of 64 links
+#pragma unroll
+            for (int j = 0; j < KEYS; j += 4) {
+                mx4[0] = fmaxf(mx4[0], s[j]); mx4[1] = fmaxf(mx4[1], s[j + 1]);
+                mx4[2] = fmaxf(mx4[2], s[j + 2]); mx4[3] = fmaxf(mx4[3], s[j + 3]);
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * args.scale_log2;
             // keep the old scale unless the maximum has grown a lot; a warp rescales its rows of O together
             const bool grow = mx > m_used + RESCALE_THRESHOLD || (m_used == -INFINITY && mx != -INFINITY);
             if (__any_sync(0xffffffffu, grow)) {
@@ -252,23 +254,19 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 m_used = m_new;
             }
             const float base = (m_used == -INFINITY) ? 0.0f : m_used;
-            float sum = 0.0f;
+            float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             uint32_t packed[KEYS / 2];
 #pragma unroll
             for (int j = 0; j < KEYS; j += 2) {
                 const float p0 = fast_exp2(fmaf(s[j], args.scale_log2, -base)), p1 = fast_exp2(fmaf(s[j + 1], args.scale_log2, -base));
-                sum += p0 + p1;
+                sum4[(j >> 1) & 3] += p0 + p1;
                 const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                 packed[j / 2] = *reinterpret_cast<const uint32_t*>(&h);
             }
-            l += sum;
+            l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             // P_i goes to buffer i & 1, which the products of block i - 2 must have finished reading
             if (i >= 2 && !mbar_wait(smem_u32(&pv_done[i & 1]), (uint32_t)(((i - 2) >> 1) & 1))) { if (lane == 0) atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; break; }
-            uint8_t* p_row = p_smem + (i & 1) * L::P_BYTES + r * 128;
-#pragma unroll
-            for (int c = 0; c < 8; ++c)                            // 16-byte chunk c of the row sits at position c ^ (row % 8)
-                *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) * 16)) = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-            fence_async_shared();
+            tmem_store32(lane_base + L::P_COL + (i & 1) * 32, reinterpret_cast<const float*>(packed));   // this row's 64 probabilities, two to a column
             fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&p_ready[i & 1]));
