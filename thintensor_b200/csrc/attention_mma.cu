@@ -358,6 +358,7 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
 // more of the arithmetic's latency; 7 warps gain nothing further).  SMALL: half the warps
 // and half the shared memory, so that two CTAs share an SM and one's start and end run
 // under the other's streaming; faster when the grid has several waves, slower when not.
+constexpr int DECODE_TABLE_CACHE = 1024;     // table entries (64 K tokens) a decode CTA keeps in shared memory
 template <int HD, bool SMALL> struct DecodeShape;
 template <> struct DecodeShape<32, false> { static constexpr int WARPS = 8, STAGES = 3; };
 template <> struct DecodeShape<64, false> { static constexpr int WARPS = 6, STAGES = 2; };
@@ -396,8 +397,13 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
     const int group = heads / kv_heads;
     // Lengths and tables were written before this step's first kernel started (by the step
     // before, or by the host), so they may be read ahead of the wait; so may every block but
-    // the one that this step's token goes into.
+    // the one that this step's token goes into.  The sequence's table row goes to shared memory
+    // while the length is still on its way, so that no copy has to wait for a table entry.
+    __shared__ int table_sh[DECODE_TABLE_CACHE];
+    const int* table_row = table + (size_t)b * table_width;
+    for (int i = threadIdx.x; i < min(table_width, DECODE_TABLE_CACHE); i += WARPS * 32) table_sh[i] = table_row[i];
     const int pos = len_before[b];                    // position of this step's token = keys 0 .. pos
+    __syncthreads();
     const int lo_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int block0 = lo_key / TT_BLOCK_TOKENS, block1 = pos / TT_BLOCK_TOKENS;
     const int per = (block1 - block0 + 1 + splits - 1) / splits;
@@ -405,7 +411,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
     const int n_mine = my_begin + warp < my_end ? (my_end - my_begin - warp + WARPS - 1) / WARPS : 0;   // blocks of this warp
     // block1, if it is this warp's, is its last; it is copied only after the wait
     const int n_early = (n_mine > 0 && my_begin + warp + (n_mine - 1) * WARPS == block1) ? n_mine - 1 : n_mine;
-    const int* table_row = table + (size_t)b * table_width;
     uint4* my_slots = slots + (size_t)warp * STAGES * LOADS * 32 + lane;
     unsigned valid = 0;                                // bit i % 32: block i of this warp has usable data
     int issued = 0;                                    // blocks of this warp whose copies have started, one group each
@@ -413,7 +418,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
     auto issue_next = [&]() {
         const int i = issued++;
         const int kb = my_begin + warp + i * WARPS;
-        const int block = table_row[kb];
+        const int block = kb < DECODE_TABLE_CACHE ? table_sh[kb] : table_row[kb];
         if (block >= 0 && block < pool_blocks) {
             const __nv_bfloat16* kbase = k_pool + ((size_t)block * kv_heads + kh) * TT_BLOCK_TOKENS * HD + 8 * t;
             const __nv_bfloat16* vbase = v_pool + ((size_t)block * kv_heads + kh) * HD * TT_BLOCK_TOKENS + (size_t)g * TT_BLOCK_TOKENS + 8 * t;
@@ -449,7 +454,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
         const float* row = rope.qkv + (size_t)b * (q_cols + 2 * kv_cols);
         const bool append = rope.write_cache && my_begin <= block1 && block1 < my_end;   // this CTA reads the new key
         const int pair_rows = group + (append ? 1 : 0);
-        const int items = pair_rows * HALF + (append ? HD : 0);
+        const int items = pair_rows * HALF + (append ? HALF : 0);      // the value's numbers go two to an item, like the pairs
         auto sum_slices = [&](const float* p) {
             float total = 0.0f;
 #pragma unroll 8
@@ -480,8 +485,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
                 }
             } else {
                 const int d = item - pair_rows * HALF;
-                const float a = sum_slices(row + q_cols + kv_cols + (size_t)kh * HD + d);
-                if (v_off >= 0) v_pool[v_off + (long long)d * TT_BLOCK_TOKENS] = __float2bfloat16_rn(a);
+                const float* p = row + q_cols + kv_cols + (size_t)kh * HD + d;
+                const float a = sum_slices(p), bb = sum_slices(p + HALF);
+                if (v_off >= 0) {
+                    v_pool[v_off + (long long)d * TT_BLOCK_TOKENS] = __float2bfloat16_rn(a);
+                    v_pool[v_off + (long long)(d + HALF) * TT_BLOCK_TOKENS] = __float2bfloat16_rn(bb);
+                }
             }
         }
         if (append) __threadfence();                   // key and value are in memory before their block is copied
@@ -551,32 +560,36 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
     }
     __syncthreads();
     // cluster_merge: the slices of a (sequence, kv head) form a thread-block cluster; each leaves its
-    // result in its own shared memory and the first CTA combines them over distributed shared memory
+    // result in its own shared memory and the CTAs combine them over distributed shared memory
     float* cta_acc = sh_l + WARPS * 16;                // [16][HD]
     float* cta_ml = cta_acc + 16 * HD;                 // [16][2]
-    for (int idx = threadIdx.x; idx < group * HD; idx += WARPS * 32) {
-        const int r = idx / HD, d = idx - r * HD;
+    // one item = two neighbouring numbers of one row
+    for (int idx = threadIdx.x; idx < group * (HD / 2); idx += WARPS * 32) {
+        const int r = idx / (HD / 2), d = 2 * (idx - r * (HD / 2));
         float m = -INFINITY;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) m = fmaxf(m, sh_m[w * 16 + r]);
-        float l = 0.0f, acc = 0.0f;
+        float l = 0.0f, acc0 = 0.0f, acc1 = 0.0f;
         if (m != -INFINITY) {
 #pragma unroll
             for (int w = 0; w < WARPS; ++w) {
                 const float weight = exp2f(sh_m[w * 16 + r] - m);       // 0 for a warp that saw no key
+                const float2 o = *reinterpret_cast<const float2*>(sh_o + ((size_t)w * 16 + r) * PITCH + d);
                 l = fmaf(sh_l[w * 16 + r], weight, l);
-                acc = fmaf(sh_o[((size_t)w * 16 + r) * PITCH + d], weight, acc);
+                acc0 = fmaf(o.x, weight, acc0);
+                acc1 = fmaf(o.y, weight, acc1);
             }
         }
         const size_t row_index = (size_t)b * heads + kh * group + r;
         if (splits == 1) {
-            out[row_index * HD + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            *reinterpret_cast<__nv_bfloat162*>(out + row_index * HD + d) = __floats2bfloat162_rn(acc0 * inv, acc1 * inv);
         } else if (cluster_merge) {
-            cta_acc[r * HD + d] = acc;
+            *reinterpret_cast<float2*>(cta_acc + r * HD + d) = make_float2(acc0, acc1);
             if (d == 0) { cta_ml[2 * r] = m; cta_ml[2 * r + 1] = l; }
         } else {
             const size_t slot = row_index * splits + split;
-            part_acc[slot * HD + d] = acc;
+            *reinterpret_cast<float2*>(part_acc + slot * HD + d) = make_float2(acc0, acc1);
             if (d == 0) {
                 part_ml[slot * 2] = m * 0.6931471805599453f;            // the merge works with natural exponents
                 part_ml[slot * 2 + 1] = l;
@@ -586,22 +599,26 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
     if (splits > 1 && cluster_merge) {
         cg::cluster_group cluster = cg::this_cluster();
         cluster.sync();                                // every slice's result is in its shared memory
-        if (cluster.block_rank() == 0) {
-            for (int idx = threadIdx.x; idx < group * HD; idx += WARPS * 32) {
-                const int r = idx / HD, d = idx - r * HD;
-                float m = -INFINITY;
-                for (int s = 0; s < splits; ++s) m = fmaxf(m, cluster.map_shared_rank(cta_ml, s)[2 * r]);
-                float l = 0.0f, acc = 0.0f;
-                if (m != -INFINITY) {
-                    for (int s = 0; s < splits; ++s) {
-                        const float* ml = cluster.map_shared_rank(cta_ml, s);
-                        const float weight = exp2f(ml[2 * r] - m);     // 0 for a slice that saw no key
-                        l = fmaf(ml[2 * r + 1], weight, l);
-                        acc = fmaf(cluster.map_shared_rank(cta_acc, s)[r * HD + d], weight, acc);
-                    }
+        // every CTA of the cluster combines the rows rank, rank + splits, ... and stores them
+        const int rank = (int)cluster.block_rank();
+        const int my_rows = rank < group ? (group - rank + splits - 1) / splits : 0;
+        for (int idx = threadIdx.x; idx < my_rows * (HD / 2); idx += WARPS * 32) {
+            const int r = rank + (idx / (HD / 2)) * splits, d = 2 * (idx % (HD / 2));
+            float m = -INFINITY;
+            for (int s = 0; s < splits; ++s) m = fmaxf(m, cluster.map_shared_rank(cta_ml, s)[2 * r]);
+            float l = 0.0f, acc0 = 0.0f, acc1 = 0.0f;
+            if (m != -INFINITY) {
+                for (int s = 0; s < splits; ++s) {
+                    const float* ml = cluster.map_shared_rank(cta_ml, s);
+                    const float weight = exp2f(ml[2 * r] - m);         // 0 for a slice that saw no key
+                    const float2 o = *reinterpret_cast<const float2*>(cluster.map_shared_rank(cta_acc, s) + r * HD + d);
+                    l = fmaf(ml[2 * r + 1], weight, l);
+                    acc0 = fmaf(o.x, weight, acc0);
+                    acc1 = fmaf(o.y, weight, acc1);
                 }
-                out[((size_t)b * heads + kh * group + r) * HD + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
             }
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            *reinterpret_cast<__nv_bfloat162*>(out + ((size_t)b * heads + kh * group + r) * HD + d) = __floats2bfloat162_rn(acc0 * inv, acc1 * inv);
         }
         cluster.sync();                                // no slice leaves while its shared memory is being read
     }
