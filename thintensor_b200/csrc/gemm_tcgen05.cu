@@ -162,7 +162,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = instr_desc(BM, BN);
+            constexpr uint32_t idesc = instr_desc(BM, S::dual ? 2 * BN : BN);   // gate and up tiles lie like one tile of 2 BN rows
             bool ok = true;
             for (int i = 0; i < n_kb && ok; ++i) {
                 const int s = i % STAGES;
@@ -175,7 +175,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
                     const uint64_t da = smem_desc(a_addr + kk * UMMA_K * 2);
                     umma_bf16(tmem_base, da, smem_desc(b_addr + kk * UMMA_K * 2), idesc, acc);
-                    if (S::dual) umma_bf16(tmem_base + BN, da, smem_desc(b_addr + BN * BK * 2 + kk * UMMA_K * 2), idesc, acc);
                 }
                 umma_commit(smem_u32(&empty_bar[s]));     // the stage is free once these products have read it
             }
@@ -360,7 +359,11 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = instr_desc(BM, TILE_N);
+            // The gate rows and the up rows of a SwiGLU stage lie next to each other in shared memory
+            // exactly like one box of 256 rows, so both forms issue one product of N = 256 per k step
+            // (gate in accumulator columns 0..127, up in 128..255); two of N = 128 would cost twice the
+            // issue time, which is what bounds this kernel.
+            constexpr uint32_t idesc = instr_desc(BM, 256);
             long long it = 0;
             bool ok = true;
             for (int j = 0; j < my_tiles && ok; ++j) {
@@ -384,7 +387,6 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                         const uint32_t accumulate = (i > 0 || kk > 0) ? 1u : 0u;
                         const uint64_t da = smem_desc(a_addr + kk * UMMA_K * 2);
                         umma_bf16(acc_addr, da, smem_desc(b_addr + kk * UMMA_K * 2), idesc, accumulate);
-                        if (dual) umma_bf16(acc_addr + 128, da, smem_desc(b_addr + 128 * BK * 2 + kk * UMMA_K * 2), idesc, accumulate);
                     }
                     umma_commit(smem_u32(&empty_bar[s]));
                 }
