@@ -140,6 +140,44 @@ __device__ __forceinline__ void tmem_store32(uint32_t addr, const float* v) {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+// ---- CTA pairs (cta_group::2): two CTAs of a cluster, on neighbouring SMs, share one product of
+// M = 256.  Each holds its own 128 rows of A, half of B's rows and its 128 rows of the accumulator;
+// the even CTA of the pair issues, and the barriers that count both CTAs' copies live in its shared
+// memory.  A shared-memory address of either CTA and-ed with PEER_MASK is the even CTA's copy.
+constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;
+
+// issued by the warp with the same index in both CTAs
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+// D (+)= A B^T over both CTAs: descriptors are the even CTA's, the odd CTA's operands lie at the same offsets.
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    const uint32_t zero = 0;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(zero) : "memory");
+}
+// One arrival on the barrier at this offset in each CTA of `cta_mask` when every product issued so far is done.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(cta_mask) : "memory");
+}
+// A tiled copy into this CTA's shared memory whose bytes are counted by the even CTA's barrier.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar & PEER_MASK) : "memory");
+}
+// An arrival on the even CTA's barrier from either CTA.
+__device__ __forceinline__ void mbar_arrive_even_cta(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar & PEER_MASK) : "memory");
+}
+
 // Shared-memory matrix descriptor of a k-major bfloat16 tile whose rows are 128 bytes
 // apart and swizzled in 1024-byte groups of eight rows (what TMA writes with
 // CU_TENSOR_MAP_SWIZZLE_128B): start address, stride between eight-row groups = 1024
