@@ -298,6 +298,8 @@ __device__ __forceinline__ float4 sum_slices4(const float* __restrict__ p, int s
     return total;
 }
 
+constexpr int ROPE_MAX_HALF = 128;          // half of the largest rotary part (head sizes go up to 256)
+
 template <typename TAct>
 __global__ void rope_append_vec_kernel(const float* __restrict__ qkv, int splits, size_t split_stride,
                                        const float* __restrict__ inv_freq, int rotary_dim, float attention_scaling,
@@ -319,50 +321,52 @@ __global__ void rope_append_vec_kernel(const float* __restrict__ qkv, int splits
     const int rot_heads = heads + (write_cache ? kv_heads : 0);
     const int pass4 = (head_dim - rotary_dim) >> 2;
     const int n_rot = rot_heads * half4, n_pass = rot_heads * pass4;
-    int w = blockIdx.y * blockDim.x + threadIdx.x;
-    if (w < n_rot) {
-        const int head = w / half4, i = (w - head * half4) * 4;
-        const int col = head * head_dim + i;
-        const float4 a = sum_slices4(row + col, splits, split_stride);
-        const float4 c = sum_slices4(row + col + half, splits, split_stride);
-        const float4 f = __ldg(reinterpret_cast<const float4*>(inv_freq + i));
-        float s0, c0, s1, c1, s2, c2, s3, c3;
-        sincosf(f.x * (float)pos, &s0, &c0);
-        sincosf(f.y * (float)pos, &s1, &c1);
-        sincosf(f.z * (float)pos, &s2, &c2);
-        sincosf(f.w * (float)pos, &s3, &c3);
-        const float k = attention_scaling;
-        const float ra0 = (a.x * c0 - c.x * s0) * k, rb0 = (c.x * c0 + a.x * s0) * k;
-        const float ra1 = (a.y * c1 - c.y * s1) * k, rb1 = (c.y * c1 + a.y * s1) * k;
-        const float ra2 = (a.z * c2 - c.z * s2) * k, rb2 = (c.z * c2 + a.z * s2) * k;
-        const float ra3 = (a.w * c3 - c.w * s3) * k, rb3 = (c.w * c3 + a.w * s3) * k;
-        TAct* dst;
-        if (head < heads) {
-            dst = q_out + (size_t)t * q_cols + col;
-        } else {
-            const long long off = tt_cache_offset(table_row, pos, head - heads, kv_heads, head_dim, pool_blocks, status);
-            if (off < 0) return;
-            dst = k_pool + off + i;
+    // the angles depend on the position only: one table per block instead of one sincosf per head and pair
+    __shared__ float cos_sh[ROPE_MAX_HALF], sin_sh[ROPE_MAX_HALF];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(__ldg(inv_freq + i) * (float)pos, &sin_sh[i], &cos_sh[i]);
+    __syncthreads();
+    const int n_val = kv_cols >> 2;
+    // one block per token walks over all of the token's items
+    for (int item = threadIdx.x; item < n_rot + n_pass + n_val; item += blockDim.x) {
+        int w = item;
+        if (w < n_rot) {
+            const int head = w / half4, i = (w - head * half4) * 4;
+            const int col = head * head_dim + i;
+            const float4 a = sum_slices4(row + col, splits, split_stride);
+            const float4 c = sum_slices4(row + col + half, splits, split_stride);
+            const float s0 = sin_sh[i], c0 = cos_sh[i], s1 = sin_sh[i + 1], c1 = cos_sh[i + 1];
+            const float s2 = sin_sh[i + 2], c2 = cos_sh[i + 2], s3 = sin_sh[i + 3], c3 = cos_sh[i + 3];
+            const float k = attention_scaling;
+            const float ra0 = (a.x * c0 - c.x * s0) * k, rb0 = (c.x * c0 + a.x * s0) * k;
+            const float ra1 = (a.y * c1 - c.y * s1) * k, rb1 = (c.y * c1 + a.y * s1) * k;
+            const float ra2 = (a.z * c2 - c.z * s2) * k, rb2 = (c.z * c2 + a.z * s2) * k;
+            const float ra3 = (a.w * c3 - c.w * s3) * k, rb3 = (c.w * c3 + a.w * s3) * k;
+            TAct* dst;
+            if (head < heads) {
+                dst = q_out + (size_t)t * q_cols + col;
+            } else {
+                const long long off = tt_cache_offset(table_row, pos, head - heads, kv_heads, head_dim, pool_blocks, status);
+                if (off < 0) continue;
+                dst = k_pool + off + i;
+            }
+            tt_store4(dst, ra0, ra1, ra2, ra3);
+            tt_store4(dst + half, rb0, rb1, rb2, rb3);
+            continue;
         }
-        tt_store4(dst, ra0, ra1, ra2, ra3);
-        tt_store4(dst + half, rb0, rb1, rb2, rb3);
-        return;
-    }
-    w -= n_rot;
-    if (w < n_pass) {
-        const int head = w / pass4, i = rotary_dim + (w - head * pass4) * 4;
-        const int col = head * head_dim + i;
-        const float4 a = sum_slices4(row + col, splits, split_stride);
-        if (head < heads) {
-            tt_store4(q_out + (size_t)t * q_cols + col, a.x, a.y, a.z, a.w);
-        } else {
-            const long long off = tt_cache_offset(table_row, pos, head - heads, kv_heads, head_dim, pool_blocks, status);
-            if (off >= 0) tt_store4(k_pool + off + i, a.x, a.y, a.z, a.w);
+        w -= n_rot;
+        if (w < n_pass) {
+            const int head = w / pass4, i = rotary_dim + (w - head * pass4) * 4;
+            const int col = head * head_dim + i;
+            const float4 a = sum_slices4(row + col, splits, split_stride);
+            if (head < heads) {
+                tt_store4(q_out + (size_t)t * q_cols + col, a.x, a.y, a.z, a.w);
+            } else {
+                const long long off = tt_cache_offset(table_row, pos, head - heads, kv_heads, head_dim, pool_blocks, status);
+                if (off >= 0) tt_store4(k_pool + off + i, a.x, a.y, a.z, a.w);
+            }
+            continue;
         }
-        return;
-    }
-    w -= n_pass;
-    if (w < (kv_cols >> 2)) {
+        w -= n_pass;
         const int e = w * 4, kh = e / head_dim, i = e - kh * head_dim;
         const float4 a = sum_slices4(row + q_cols + kv_cols + e, splits, split_stride);
         const long long off = tt_value_offset(table_row, pos, kh, kv_heads, head_dim, pool_blocks, status);
@@ -385,18 +389,16 @@ extern "C" int tt_rope_append(const float* qkv, int splits, long long split_stri
     if (n_tokens <= 0) return 0;
     if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return (int)cudaErrorInvalidValue;
     const int rot_heads = heads + (write_cache ? kv_heads : 0);
-    if (rotary_dim % 8 == 0 && (head_dim - rotary_dim) % 4 == 0 && split_stride % 4 == 0 && ((uintptr_t)qkv & 15) == 0 &&
+    if (rotary_dim % 8 == 0 && rotary_dim / 2 <= ROPE_MAX_HALF && (head_dim - rotary_dim) % 4 == 0 && split_stride % 4 == 0 && ((uintptr_t)qkv & 15) == 0 &&
         ((uintptr_t)inv_freq & 15) == 0 && ((uintptr_t)q_out & 15) == 0 && ((uintptr_t)k_pool & 15) == 0) {
         const int items4 = rot_heads * (rotary_dim / 8) + rot_heads * ((head_dim - rotary_dim) / 4) + (write_cache ? kv_heads * head_dim / 4 : 0);
-        const int threads4 = 128;
-        const dim3 grid4(n_tokens, (items4 + threads4 - 1) / threads4);
-        if (grid4.y <= 65535) {
-            if (act_dtype == TT_F32)
-                tt_launch_pdl(rope_append_vec_kernel<float>, grid4, dim3(threads4), 0, stream, qkv, splits, (size_t)split_stride, inv_freq, rotary_dim, attention_scaling, (float*)q_out, (float*)k_pool, (float*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, heads, kv_heads, head_dim, write_cache, status);
-            else
-                tt_launch_pdl(rope_append_vec_kernel<__nv_bfloat16>, grid4, dim3(threads4), 0, stream, qkv, splits, (size_t)split_stride, inv_freq, rotary_dim, attention_scaling, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, heads, kv_heads, head_dim, write_cache, status);
-            TT_LAUNCH_CHECK();
-        }
+        const int threads4 = items4 >= 256 ? 256 : (items4 >= 128 ? 128 : 64);
+        const dim3 grid4(n_tokens);
+        if (act_dtype == TT_F32)
+            tt_launch_pdl(rope_append_vec_kernel<float>, grid4, dim3(threads4), 0, stream, qkv, splits, (size_t)split_stride, inv_freq, rotary_dim, attention_scaling, (float*)q_out, (float*)k_pool, (float*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, heads, kv_heads, head_dim, write_cache, status);
+        else
+            tt_launch_pdl(rope_append_vec_kernel<__nv_bfloat16>, grid4, dim3(threads4), 0, stream, qkv, splits, (size_t)split_stride, inv_freq, rotary_dim, attention_scaling, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, heads, kv_heads, head_dim, write_cache, status);
+        TT_LAUNCH_CHECK();
     }
     const int items = rot_heads * (rotary_dim / 2) + rot_heads * (head_dim - rotary_dim) + (write_cache ? kv_heads * head_dim : 0);
     const int threads = 128;
