@@ -103,12 +103,12 @@ class Engine:
             self.cache.length(entry.slot)  # raises if the slot is not live
             if not entry.tokens:
                 raise StepError(f"slot {entry.slot} brings no tokens")
-            for token in entry.tokens:
-                if not 0 <= token < self.vocab_size:
-                    raise StepError(f"token id {token} is outside the vocabulary of {self.vocab_size}")
-            for place in entry.want:
-                if not 0 <= place < len(entry.tokens):
-                    raise StepError(f"wanted place {place} is outside the {len(entry.tokens)} tokens slot {entry.slot} brings")
+            if min(entry.tokens) < 0 or max(entry.tokens) >= self.vocab_size:
+                token = next(t for t in entry.tokens if not 0 <= t < self.vocab_size)
+                raise StepError(f"token id {token} is outside the vocabulary of {self.vocab_size}")
+            if entry.want and (min(entry.want) < 0 or max(entry.want) >= len(entry.tokens)):
+                place = next(p for p in entry.want if not 0 <= p < len(entry.tokens))
+                raise StepError(f"wanted place {place} is outside the {len(entry.tokens)} tokens slot {entry.slot} brings")
 
     def step(self, entries: list[Entry]) -> torch.Tensor:
         """Run the entries' tokens and return float32 logits ``[wanted, vocab]`` on the
