@@ -120,3 +120,32 @@ def test_no_cpu_path():
         thintensor_b200.load_model(".", dtype="bf16", device="cuda")
     with pytest.raises(RuntimeError, match="no CPU path"):
         thintensor_b200.load_model(".", dtype="bf16", device="cpu")
+
+
+def test_table_widths_fall_into_few_shapes():
+    """Decode states are keyed by the width of their block tables: powers of two up to 16
+    blocks, then multiples of 16, never less than what the sequences need."""
+    from thintensor_b200.engine.generate import table_width
+
+    assert [table_width(b) for b in (0, 1, 2, 3, 4, 5, 8, 9, 16)] == [1, 1, 2, 4, 4, 8, 8, 16, 16]
+    assert [table_width(b) for b in (17, 32, 33, 64, 65, 512, 513)] == [32, 32, 48, 64, 80, 512, 528]
+    assert all(table_width(b) >= b for b in range(1, 3000))
+    assert len({table_width(b) for b in range(1, 1025)}) <= 5 + 63
+
+
+def test_key_slices_fill_one_wave():
+    """How many slices a decode step cuts its keys into: enough to fill one wave of CTAs, at
+    least 512 keys each, one for prompts."""
+    from types import SimpleNamespace
+
+    from thintensor_b200.parts.attention import kv_splits
+
+    def step(sequences, total, decode=True):
+        return SimpleNamespace(decode=decode, max_total=total, sequences=sequences)
+
+    assert kv_splits(step(8, 4096), 8 * 8, 512, 148) == 2           # 64 CTAs -> 128
+    assert kv_splits(step(1, 2048), 8, 512, 148) == 4               # limited by 512 keys a slice
+    assert kv_splits(step(1, 32768), 8, 512, 148) == 18             # 144 CTAs
+    assert kv_splits(step(64, 2048), 64 * 8, 512, 148) == 1         # already several waves
+    assert kv_splits(step(8, 4096, decode=False), 64, 512, 148) == 1
+    assert kv_splits(step(1, 100), 8, 512, 148) == 1
