@@ -326,8 +326,8 @@ __global__ void rope_append_vec_kernel(const float* __restrict__ qkv, int splits
     for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(__ldg(inv_freq + i) * (float)pos, &sin_sh[i], &cos_sh[i]);
     __syncthreads();
     const int n_val = kv_cols >> 2;
-    // one block per token walks over all of the token's items
-    for (int item = threadIdx.x; item < n_rot + n_pass + n_val; item += blockDim.x) {
+    // the token's blocks (one when there are many tokens, several when there are few) walk over its items
+    for (int item = blockIdx.y * blockDim.x + threadIdx.x; item < n_rot + n_pass + n_val; item += gridDim.y * blockDim.x) {
         int w = item;
         if (w < n_rot) {
             const int head = w / half4, i = (w - head * half4) * 4;
@@ -392,8 +392,9 @@ extern "C" int tt_rope_append(const float* qkv, int splits, long long split_stri
     if (rotary_dim % 8 == 0 && rotary_dim / 2 <= ROPE_MAX_HALF && (head_dim - rotary_dim) % 4 == 0 && split_stride % 4 == 0 && ((uintptr_t)qkv & 15) == 0 &&
         ((uintptr_t)inv_freq & 15) == 0 && ((uintptr_t)q_out & 15) == 0 && ((uintptr_t)k_pool & 15) == 0) {
         const int items4 = rot_heads * (rotary_dim / 8) + rot_heads * ((head_dim - rotary_dim) / 4) + (write_cache ? kv_heads * head_dim / 4 : 0);
-        const int threads4 = items4 >= 256 ? 256 : (items4 >= 128 ? 128 : 64);
-        const dim3 grid4(n_tokens);
+        // prompts: one block per token (fewer blocks, each with more loads in flight); few tokens: a block per 128 items
+        const int threads4 = n_tokens >= 1024 ? (items4 >= 256 ? 256 : (items4 >= 128 ? 128 : 64)) : 128;
+        const dim3 grid4(n_tokens, n_tokens >= 1024 ? 1 : (items4 + threads4 - 1) / threads4);
         if (act_dtype == TT_F32)
             tt_launch_pdl(rope_append_vec_kernel<float>, grid4, dim3(threads4), 0, stream, qkv, splits, (size_t)split_stride, inv_freq, rotary_dim, attention_scaling, (float*)q_out, (float*)k_pool, (float*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, heads, kv_heads, head_dim, write_cache, status);
         else
