@@ -13,8 +13,9 @@
 //                        soon as K_i has landed, and O += P_i V_i (M 128, N dim, A operand in
 //                        tensor memory) once the softmax warps have written P_i, so S_{i+1} is
 //                        computed while softmax_i runs and P_i V_i while softmax_{i+1} runs;
-//   warps 2-5            read a row of S per thread (tcgen05.ld, no shuffles needed for the
-//                        row maximum and sum), scale, mask the diagonal blocks, exponentiate,
+//   warps 2-5 (2-9)      read a row of S per thread (tcgen05.ld, no shuffles needed for the
+//                        row maximum and sum; head size 128: two threads per row, 32 scores each,
+//                        which exchange their maxima), scale, mask the diagonal blocks, exponentiate,
 //                        and write P back to tensor memory as bfloat16 pairs (tcgen05.st), one
 //                        of two buffers: P never passes through shared memory, which took a
 //                        third of a block's time when it did (stores, proxy fence).  O stays
@@ -34,7 +35,6 @@ using namespace tc;
 
 constexpr int ROWS = 128;            // query rows of a CTA
 constexpr int KEYS = TT_BLOCK_TOKENS;
-constexpr int THREADS = 192;
 constexpr int KV_STAGES = 3;
 constexpr float RESCALE_THRESHOLD = 8.0f;     // in log2 units
 
@@ -45,6 +45,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 template <int HD> struct Layout {
+    // Threads per query row in the softmax.  Head size 128 leaves room for one CTA per SM only, and
+    // four softmax warps cannot hide their own latencies: two threads per row (8 warps) are 10 %
+    // faster there.  Head size 64 runs two CTAs per SM and is bound elsewhere: one thread per row.
+    static constexpr int SPLIT = HD == 128 ? 2 : 1;
+    static constexpr int THREADS = 64 + SPLIT * ROWS;
     static constexpr int CHUNKS = HD / 64;                      // 64-wide slices of the head dimension
     static constexpr int Q_BYTES = ROWS * HD * 2;
     static constexpr int K_BYTES = KEYS * HD * 2;               // = V tile
@@ -68,7 +73,7 @@ struct Args {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(Layout<HD>::THREADS, HD == 64 ? 2 : 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const Args args) {
     using L = Layout<HD>;
@@ -79,6 +84,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     __shared__ uint64_t q_full, kv_full[KV_STAGES], kv_empty[KV_STAGES], s_full[2], p_ready[2], pv_done[2];
     __shared__ uint32_t tmem_base_shared;
     __shared__ int tile_info[2];                                  // sequence, tile within the sequence
+    __shared__ float pair_max[2][2][ROWS];
 
     tt_pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -111,7 +117,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&q_full), 1);
         for (int s = 0; s < KV_STAGES; ++s) { mbar_init(smem_u32(&kv_full[s]), 1); mbar_init(smem_u32(&kv_empty[s]), 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&s_full[i]), 1); mbar_init(smem_u32(&p_ready[i]), 4); mbar_init(smem_u32(&pv_done[i]), 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&s_full[i]), 1); mbar_init(smem_u32(&p_ready[i]), 4 * L::SPLIT); mbar_init(smem_u32(&pv_done[i]), 1); }
         fence_barrier_init();
     }
     __syncthreads();
@@ -198,56 +204,67 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
         }
     } else {
-        // ------------------------------------------------------------ softmax: one thread per query row
+        // ------------------------------------------------------------ softmax: SPLIT threads per query row
+        // With two: warps 2-5 take keys 0..31 of a block, warps 6-9 keys 32..63; the two threads of a row
+        // sit in warps with the same index modulo 4 (the tensor-memory lanes a warp may read), exchange
+        // their maxima through shared memory at a named barrier of their own, keep separate sums, and
+        // share the columns of O between them.  After a failed wait a thread keeps walking through the
+        // barriers (without waiting for anything else), so its partner is never left alone at one.
         const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int r = quarter * 32 + lane;
         const int local = r / args.group;
         const bool row_ok = local < tile_tokens;
         const int pos = row_ok ? before + tok0 + local : -1;
         const int first = (args.window > 0 && pos - args.window + 1 > 0) ? pos - args.window + 1 : 0;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        float m_used = -INFINITY, l = 0.0f;                       // the scale in use (log2 units) and the running sum
+        constexpr int SPLIT = L::SPLIT, HALF_KEYS = KEYS / SPLIT, O_COLS = HD / SPLIT;   // what one thread of a row handles
+        float m_used = -INFINITY, l = 0.0f;                       // the scale in use (log2 units) and this thread's part of the sum
         bool ok = true;
-        for (int i = 0; i < n_blocks && ok; ++i) {
-            if (!mbar_wait(smem_u32(&s_full[i & 1]), (uint32_t)((i >> 1) & 1))) { if (lane == 0) atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; break; }
+        auto pair_barrier = [&]() { if (SPLIT == 2) asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory"); };
+        auto expired = [&]() { if (lane == 0) atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; };
+        for (int i = 0; i < n_blocks; ++i) {
+            if (ok && !mbar_wait(smem_u32(&s_full[i & 1]), (uint32_t)((i >> 1) & 1))) expired();
             fence_after_sync();
-            float s[KEYS];
-            tmem_load32(lane_base + (i & 1) * 64, s);
-            tmem_load32(lane_base + (i & 1) * 64 + 32, s + 32);
-            const int key_base = (block0 + i) * KEYS;
-            const bool all_visible = __all_sync(0xffffffffu, key_base + KEYS - 1 <= pos && key_base >= first);
-            // the maximum is taken over the raw scores (the scale is positive), the scale is folded
-            // into the exponent's multiply-add below
+            float s[HALF_KEYS];
+#pragma unroll
+            for (int c = 0; c < HALF_KEYS; c += 32) tmem_load32(lane_base + (i & 1) * 64 + half * HALF_KEYS + c, s + c);
+            const int key_base = (block0 + i) * KEYS + half * HALF_KEYS;
+            const bool all_visible = __all_sync(0xffffffffu, key_base + HALF_KEYS - 1 <= pos && key_base >= first);
             if (!all_visible) {
 #pragma unroll
-                for (int j = 0; j < KEYS; ++j) {
+                for (int j = 0; j < HALF_KEYS; ++j) {
                     const int key = key_base + j;
                     s[j] = (key <= pos && key >= first) ? s[j] : -INFINITY;
                 }
             }
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};     // four chains instead of one of 64 links
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int j = 0; j < KEYS; j += 4) {
+            for (int j = 0; j < HALF_KEYS; j += 4) {
                 mx4[0] = fmaxf(mx4[0], s[j]); mx4[1] = fmaxf(mx4[1], s[j + 1]);
                 mx4[2] = fmaxf(mx4[2], s[j + 2]); mx4[3] = fmaxf(mx4[3], s[j + 3]);
             }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * args.scale_log2;
-            // keep the old scale unless the maximum has grown a lot; a warp rescales its rows of O together
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            if (SPLIT == 2) {
+                pair_max[i & 1][half][r] = mx;
+                pair_barrier();
+                mx = fmaxf(mx, pair_max[i & 1][half ^ 1][r]);
+            }
+            mx *= args.scale_log2;
             const bool grow = mx > m_used + RESCALE_THRESHOLD || (m_used == -INFINITY && mx != -INFINITY);
             if (__any_sync(0xffffffffu, grow)) {
                 const float m_new = grow ? mx : m_used;
                 const float corr = (m_used == -INFINITY) ? 0.0f : fast_exp2(m_used - m_new);
                 if (i > 0) {
-                    // O must be at rest: the products of block i - 1 have to be finished
-                    if (!mbar_wait(smem_u32(&pv_done[(i - 1) & 1]), (uint32_t)(((i - 1) >> 1) & 1))) { if (lane == 0) atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; break; }
+                    if (ok && !mbar_wait(smem_u32(&pv_done[(i - 1) & 1]), (uint32_t)(((i - 1) >> 1) & 1))) expired();
                     fence_after_sync();
 #pragma unroll
-                    for (int c = 0; c < HD; c += 32) {
+                    for (int c = 0; c < O_COLS; c += 32) {
                         float o[32];
-                        tmem_load32(lane_base + L::O_COL + c, o);
+                        tmem_load32(lane_base + L::O_COL + half * O_COLS + c, o);
 #pragma unroll
                         for (int e = 0; e < 32; ++e) o[e] *= corr;
-                        tmem_store32(lane_base + L::O_COL + c, o);
+                        tmem_store32(lane_base + L::O_COL + half * O_COLS + c, o);
                     }
                 }
                 l *= corr;
@@ -255,9 +272,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
             const float base = (m_used == -INFINITY) ? 0.0f : m_used;
             float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            uint32_t packed[KEYS / 2];
+            uint32_t packed[HALF_KEYS / 2];
 #pragma unroll
-            for (int j = 0; j < KEYS; j += 2) {
+            for (int j = 0; j < HALF_KEYS; j += 2) {
                 const float p0 = fast_exp2(fmaf(s[j], args.scale_log2, -base)), p1 = fast_exp2(fmaf(s[j + 1], args.scale_log2, -base));
                 sum4[(j >> 1) & 3] += p0 + p1;
                 const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
@@ -265,25 +282,31 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
             l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             // P_i goes to buffer i & 1, which the products of block i - 2 must have finished reading
-            if (i >= 2 && !mbar_wait(smem_u32(&pv_done[i & 1]), (uint32_t)(((i - 2) >> 1) & 1))) { if (lane == 0) atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; break; }
-            tmem_store32(lane_base + L::P_COL + (i & 1) * 32, reinterpret_cast<const float*>(packed));   // this row's 64 probabilities, two to a column
+            if (ok && i >= 2 && !mbar_wait(smem_u32(&pv_done[i & 1]), (uint32_t)(((i - 2) >> 1) & 1))) expired();
+            if (SPLIT == 2) tmem_store16(lane_base + L::P_COL + (i & 1) * 32 + half * 16, packed);
+            else tmem_store32(lane_base + L::P_COL + (i & 1) * 32, reinterpret_cast<const float*>(packed));
             fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&p_ready[i & 1]));
+            if (lane == 0 && ok) mbar_arrive(smem_u32(&p_ready[i & 1]));
         }
         if (ok) {
             const int last = n_blocks - 1;
-            if (!mbar_wait(smem_u32(&pv_done[last & 1]), (uint32_t)((last >> 1) & 1))) { if (lane == 0) atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; }
+            if (!mbar_wait(smem_u32(&pv_done[last & 1]), (uint32_t)((last >> 1) & 1))) expired();
+        }
+        if (SPLIT == 2) {               // the row sum is the two threads' sums together (both rescaled to the same maximum)
+            pair_max[n_blocks & 1][half][r] = l;
+            pair_barrier();
+            l += pair_max[n_blocks & 1][half ^ 1][r];
         }
         if (ok) {
             fence_after_sync();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             const int token = seq_begin + tok0 + local, head = kh * args.group + (r - local * args.group);
-            __nv_bfloat16* dst = args.out + ((size_t)token * args.heads + head) * HD;
+            __nv_bfloat16* dst = args.out + ((size_t)token * args.heads + head) * HD + half * O_COLS;
 #pragma unroll
-            for (int c = 0; c < HD; c += 32) {
+            for (int c = 0; c < O_COLS; c += 32) {
                 float o[32];
-                tmem_load32(lane_base + L::O_COL + c, o);          // warp-collective: every lane takes part, valid row or not
+                tmem_load32(lane_base + L::O_COL + half * O_COLS + c, o);
                 if (row_ok) {
 #pragma unroll
                     for (int e = 0; e < 32; e += 8) {
@@ -332,7 +355,7 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const Args& ar
         if (err != cudaSuccess) return (int)err;
         configured = true;
     }
-    tt_launch_pdl(kernel, dim3(args.cta_tiles, args.kv_heads), dim3(THREADS), (size_t)L::SMEM, stream, map_q, map_k, map_v, args);
+    tt_launch_pdl(kernel, dim3(args.cta_tiles, args.kv_heads), dim3(L::THREADS), (size_t)L::SMEM, stream, map_q, map_k, map_v, args);
     return (int)cudaGetLastError();
 }
 
