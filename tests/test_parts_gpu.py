@@ -37,7 +37,7 @@ def context_for(engine, slots, news):
     entries = [Entry(s, [0] * n, []) for s, n in zip(slots, news)]
     for e in entries:
         engine.cache.reserve(e.slot, engine.cache.length(e.slot) + len(e.tokens))
-    ctx, _, _ = engine._prepare(entries, [(i, 0, n) for i, n in enumerate(news)], [0] * len(news))
+    ctx, _, _ = engine._prepare(entries, engine.validate(entries), [(i, 0, n) for i, n in enumerate(news)], [0] * len(news))
     return ctx
 
 

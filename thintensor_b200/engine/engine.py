@@ -17,6 +17,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+import numpy as np
 import torch
 
 from ..cache.cache import SequenceCache
@@ -92,7 +93,10 @@ class Engine:
         self.cache.free_slot(slot)
 
     # ------------------------------------------------------------------ step
-    def validate(self, entries: list[Entry]) -> None:
+    def validate(self, entries: list[Entry]) -> list[np.ndarray]:
+        """Check a step on the host and return every entry's tokens as an int32 array (made once
+        here, so that the range check and the copy to the device need no second pass over the list)."""
+        arrays: list[np.ndarray] = []
         if not entries:
             raise StepError("a step needs at least one sequence")
         seen: set[int] = set()
@@ -103,17 +107,23 @@ class Engine:
             self.cache.length(entry.slot)  # raises if the slot is not live
             if not entry.tokens:
                 raise StepError(f"slot {entry.slot} brings no tokens")
-            if min(entry.tokens) < 0 or max(entry.tokens) >= self.vocab_size:
+            try:
+                tokens = np.fromiter(entry.tokens, dtype=np.int64, count=len(entry.tokens))
+            except (OverflowError, TypeError, ValueError) as exc:
+                raise StepError(f"slot {entry.slot}: token ids must be integers ({exc})") from None
+            if tokens.min() < 0 or tokens.max() >= self.vocab_size:
                 token = next(t for t in entry.tokens if not 0 <= t < self.vocab_size)
                 raise StepError(f"token id {token} is outside the vocabulary of {self.vocab_size}")
+            arrays.append(tokens.astype(np.int32))
             if entry.want and (min(entry.want) < 0 or max(entry.want) >= len(entry.tokens)):
                 place = next(p for p in entry.want if not 0 <= p < len(entry.tokens))
                 raise StepError(f"wanted place {place} is outside the {len(entry.tokens)} tokens slot {entry.slot} brings")
+        return arrays
 
     def step(self, entries: list[Entry]) -> torch.Tensor:
         """Run the entries' tokens and return float32 logits ``[wanted, vocab]`` on the
         device, ordered by entry and then by ``want``."""
-        self.validate(entries)
+        arrays = self.validate(entries)
         for entry in entries:
             self.cache.reserve(entry.slot, self.cache.length(entry.slot) + len(entry.tokens))
         total_wanted = sum(len(e.want) for e in entries)
@@ -125,7 +135,7 @@ class Engine:
             running += len(entry.want)
 
         for piece in self._pieces(entries):
-            ctx, rows, targets = self._prepare(entries, piece, out_base)
+            ctx, rows, targets = self._prepare(entries, arrays, piece, out_base)
             if rows is not None:
                 logits = self.model.forward(ctx, self.cache, rows)
                 out.index_copy_(0, targets, logits)
@@ -170,19 +180,17 @@ class Engine:
                 room -= count
         return pieces
 
-    def _prepare(self, entries, piece, out_base):
+    def _prepare(self, entries, arrays, piece, out_base):
         slots = [entries[i].slot for i, _, _ in piece]
         before = [self.cache.length(s) for s in slots]
         new = [count for _, _, count in piece]
         n_tokens = sum(new)
         sequences = len(piece)
-        tokens: list[int] = []
         rows: list[int] = []
         targets: list[int] = []
         offset = 0
         for (index, start, count) in piece:
             entry = entries[index]
-            tokens.extend(entry.tokens[start : start + count])
             for k, place in enumerate(entry.want):
                 if start <= place < start + count:
                     rows.append(offset + place - start)
@@ -197,8 +205,12 @@ class Engine:
         n_ints = n_tokens + (sequences + 1) + 2 * sequences + groups * sequences * width + 2 * len(rows)
         host, staging_index = self._staging.take(n_ints)
         device = self.workspace.get("step.meta", (n_ints,), torch.int32)
+        staged = host.numpy()
+        at = 0
+        for (index, start, count) in piece:                      # the tokens: array to pinned memory, no Python loop
+            staged[at : at + count] = arrays[index][start : start + count]
+            at += count
         flat: list[int] = []
-        flat.extend(tokens)
         flat.extend(cu)
         flat.extend(before)
         flat.extend(slots)
@@ -207,7 +219,7 @@ class Engine:
                 flat.extend(row)
         flat.extend(rows)
         flat.extend(targets)
-        host[:n_ints] = torch.tensor(flat, dtype=torch.int32)
+        staged[n_tokens:n_ints] = flat
         device.copy_(host[:n_ints], non_blocking=True)
         self._staging.sent(staging_index)
 
