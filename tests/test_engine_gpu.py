@@ -159,6 +159,56 @@ def test_long_decoding(model_folders, dtype):
     assert_close(torch.cat(got), want[2:], dtype, "long decoding")
 
 
+@pytest.mark.parametrize("name", ["d", "e"])
+def test_long_context_and_many_sequences_on_the_tensor_core_kernels(model_folders, name):
+    """bfloat16 with head sizes 64 and 128.  A prompt of 4,700 tokens (the prompt attention's
+    long loop), then decoding over it: the keys are cut into more than 8 slices (scratch and merge
+    kernel).  Then 80 short sequences decoded together: more CTAs than SMs, which for head size 64
+    is the variant with half the warps; and slices combined by a thread-block cluster in between
+    (a 1,300-token context).  A peaked attention makes a lost slice or block show."""
+    from thintensor_b200.engine.engine import Entry
+
+    dtype = "bfloat16"
+    folder = folder_for(model_folders, name, dtype)
+    runtime = load(folder, dtype)
+    vocab = TINY[name]["vocab_size"]
+    engine = runtime.new_engine(max_tokens=4800 + 80 * 64, max_sequences=81)
+
+    tokens = token_ids(vocab, 4712, 41)
+    want = oracle_logits(folder, tokens)
+    slot = engine.open()
+    head = 4700
+    got = [engine.step([Entry(slot, tokens[:head], [0, 1300, head - 1])])]
+    for t in range(head, len(tokens)):
+        got.append(engine.step([Entry(slot, [tokens[t]], [0])]))
+    engine.close(slot)
+    engine.check_status()
+    assert_close(torch.cat(got), want[[0, 1300] + list(range(head - 1, len(tokens)))], dtype, "long context")
+
+    middle = token_ids(vocab, 1312, 42)
+    want = oracle_logits(folder, middle)
+    slot = engine.open()
+    got = [engine.step([Entry(slot, middle[:1300], [1299])])]
+    for t in range(1300, len(middle)):
+        got.append(engine.step([Entry(slot, [middle[t]], [0])]))
+    engine.close(slot)
+    assert_close(torch.cat(got), want[1299:], dtype, "slices combined in a cluster")
+
+    prompts = [token_ids(vocab, 6 + (i * 7) % 50, 900 + i) for i in range(80)]
+    slots = [engine.open() for _ in prompts]
+    heads = [len(p) - 4 for p in prompts]
+    engine.step([Entry(s, p[:h], []) for s, p, h in zip(slots, prompts, heads)])
+    check = [0, 17, 42, 79]
+    oracle = {i: oracle_logits(folder, prompts[i]) for i in check}
+    for t in range(4):
+        logits = engine.step([Entry(s, [p[h + t]], [0]) for s, p, h in zip(slots, prompts, heads)])
+        for i in check:
+            assert_close(logits[i : i + 1], oracle[i][heads[i] + t : heads[i] + t + 1], dtype, f"many sequences, request {i} step {t}")
+    for s in slots:
+        engine.close(s)
+    engine.check_status()
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_step_cut_into_pieces(model_folders, dtype):
     """A step with more tokens than max_step_tokens runs in pieces with the same result."""
