@@ -48,11 +48,12 @@ def test_embed_gather(dtype):
 
 # ----------------------------------------------------------------------------------- norm
 @pytest.mark.parametrize("out_dtype", DTYPES)
-@pytest.mark.parametrize("hidden,splits", [(72, 0), (1000, 1), (1002, 5), (2048, 3), (2048, 16), (12000, 2), (20000, 1)])
-def test_add_rmsnorm(out_dtype, hidden, splits):
+@pytest.mark.parametrize("hidden,splits,rows", [(72, 0, 7), (1000, 1, 7), (1002, 5, 7), (2048, 3, 7), (2048, 16, 7), (12000, 2, 7), (20000, 1, 7),
+                                                # many rows: the launch with several pieces of a row per thread
+                                                (2048, 1, 1100), (4096, 2, 1030), (1000, 1, 1500), (8192, 1, 1024)])
+def test_add_rmsnorm(out_dtype, hidden, splits, rows):
     from thintensor_b200.kernels import api
 
-    rows = 7
     residual = randn(rows, hidden, seed=2)
     delta = randn(max(splits, 1), rows, hidden, seed=3) if splits else None
     weight = 1.0 + 0.1 * randn(hidden, seed=4)

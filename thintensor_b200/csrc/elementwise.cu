@@ -178,6 +178,13 @@ extern "C" int tt_add_rmsnorm(float* residual, const float* delta, int splits, l
         ((uintptr_t)delta & 15) == 0 && ((uintptr_t)weight & 15) == 0 && ((uintptr_t)out & 15) == 0) {
         int threads = ((hidden / 4 + 31) / 32) * 32;
         if (threads > 1024) threads = 1024;
+        if (n_rows >= 1024) {
+            // prompts: up to four pieces of the row per thread (fewer, fatter blocks: measured 5.33 -> 5.20 ms for a
+            // 2,048-token prefill of the 1B shape)
+            const int fewest = (((hidden / 4 + NORM_VEC_MAX - 1) / NORM_VEC_MAX + 31) / 32) * 32;
+            threads = fewest < 128 ? 128 : fewest;
+            if (threads > 1024) threads = 1024;
+        }
         if (out_dtype == TT_F32)
             tt_launch_pdl(add_rmsnorm_vec_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, residual, delta, splits, (size_t)split_stride, weight, weight_offset, eps, (float*)out, rows, hidden);
         else
