@@ -135,6 +135,7 @@ def main() -> int:
     parser.add_argument("--only", choices=["decode", "prefill"], help="run one phase only and print its numbers (for profiling)")
     parser.add_argument("--batch", type=int, default=BATCH, help="with --only decode: sequences decoded together")
     parser.add_argument("--shape", choices=sorted(SHAPES), default="1b", help="with --only: layer sizes of another model of the family")
+    parser.add_argument("--prompt-len", type=int, default=PROMPT, help="with --only: tokens per prompt (the context is this plus room for the steps)")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm(min(args.steps, 128), args.warmup)
@@ -155,13 +156,17 @@ def main() -> int:
     raw["num_hidden_layers"] = args.layers
     if args.only and args.shape != "1b":
         raw.update(SHAPES[args.shape])
+    prompt_len = args.prompt_len if args.only else PROMPT
+    if prompt_len != PROMPT:
+        raw["max_position_embeddings"] = max(raw.get("max_position_embeddings", 0), 2 * prompt_len)
     runtime = thintensor_b200.random_model(raw, seed=0, dtype="bf16", device="cuda:0")
     vocab = raw["vocab_size"]
     g = torch.Generator().manual_seed(1)
-    prompts = [torch.randint(0, vocab, (PROMPT,), generator=g).tolist() for _ in range(64)]
+    prompts = [torch.randint(0, vocab, (prompt_len,), generator=g).tolist() for _ in range(max(64, args.batch) if args.only == "decode" else 64)]
 
     if args.only == "decode":
-        print(json.dumps(measure_decode(runtime, prompts[:args.batch], CONTEXT, args.warmup, args.steps)))
+        context = CONTEXT if prompt_len == PROMPT else prompt_len + args.warmup + args.steps + 64
+        print(json.dumps(measure_decode(runtime, prompts[:args.batch], context, args.warmup, args.steps)))
         return 0
     if args.only == "prefill":
         print(json.dumps(measure_prefill(runtime, prompts[0], repeats=max(1, args.steps), warmup=args.warmup)))
