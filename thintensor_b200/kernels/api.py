@@ -73,16 +73,17 @@ def _need(t: torch.Tensor, dtype: torch.dtype, name: str) -> None:
         raise KernelError(f"{name} must be contiguous")
 
 
-_prototyped: set[tuple[str, str]] = set()
+_functions: dict[str, object] = {}
 
 
 def _fn(lib: str, name: str, argtypes: list):
-    handle = build.load(lib)
-    fn = getattr(handle, name)
-    if (lib, name) not in _prototyped:
+    """The C entry point ``name`` of library ``lib`` (built and loaded at first use), with its prototype set."""
+    fn = _functions.get(name)
+    if fn is None:
+        fn = getattr(build.load(lib), name)
         fn.argtypes = argtypes
         fn.restype = c_int
-        _prototyped.add((lib, name))
+        _functions[name] = fn
     return fn
 
 
@@ -355,13 +356,15 @@ def gemm_tcgen05_splits(tokens: int, features: int, k: int) -> int:
     return max(1, min(2 * SM_COUNT // tiles, k_blocks // 4, 16))
 
 
-def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor, status: torch.Tensor) -> None:
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor, status: torch.Tensor,
+                 operands_checked: bool = False) -> None:
     """out[s] = x @ w[:, k-slice s].T on the tensor cores; bfloat16 operands, float32
-    ``out`` [splits, tokens, features]; bias (float32) goes into slice 0."""
+    ``out`` [splits, tokens, features]; bias (float32) goes into slice 0.  ``operands_checked``: the
+    caller has already called :func:`gemm_tcgen05_usable` on these operands."""
     _need(out, torch.float32, "gemm output")
     tokens, k = x.shape
     features = w.shape[0]
-    if not gemm_tcgen05_usable(x, w) or w.shape[1] != k or tuple(out.shape[1:]) != (tokens, features):
+    if not (operands_checked or gemm_tcgen05_usable(x, w)) or w.shape[1] != k or tuple(out.shape[1:]) != (tokens, features):
         raise KernelError(f"tcgen05 gemm cannot take x {tuple(x.shape)} / w {tuple(w.shape)} / out {tuple(out.shape)} (k and strides must be multiples of 8)")
     if out.shape[0] > -(-k // 64):
         raise KernelError(f"{out.shape[0]} k-slices for k = {k}: a slice needs at least one block of 64")

@@ -37,7 +37,7 @@ class Linear:
         if api.gemm_tcgen05_usable(x, self.weight):
             splits = api.gemm_tcgen05_splits(tokens, self.out_features, self.in_features)
             out = ctx.scratch(name, (splits, tokens, self.out_features), torch.float32)
-            api.gemm_tcgen05(x, self.weight, self.bias, out, ctx.status)
+            api.gemm_tcgen05(x, self.weight, self.bias, out, ctx.status, operands_checked=True)
             return out
         out = ctx.scratch(name, (1, tokens, self.out_features), torch.float32)
         api.gemm_simt(x, self.weight, self.bias, out)
