@@ -84,10 +84,7 @@ class CausalAttention(Mixer):
         projection = (self.qkv if cache.writes else self.q_only)(ctx, x, "attention.qkv")
         mixed = ctx.scratch("attention.mixed", (ctx.n_tokens, q_cols))
         position = self.position
-        # decoding: one CTA per (sequence, kv head, slice).  Measured on a B200 from 1 to 64 sequences and
-        # 2,048 to 32,768 keys: the step is fastest when the slices just fill one wave of one CTA per SM
-        # and keep at least 8 blocks each; a second wave gains nothing.
-        splits = kv_splits(ctx, ctx.sequences * self.kv_heads, 512, api.SM_COUNT)
+        splits = self.decode_slices(ctx)
         if (ctx.decode and ctx.sequences * self.kv_heads * splits <= api.SM_COUNT
                 and api.attention_decode_rope_supports(mixed.dtype, self.heads, self.kv_heads, self.head_dim, position.rotary_dim)):
             # decoding: rotation, cache write and attention in one kernel.  Every CTA pays the
@@ -104,6 +101,13 @@ class CausalAttention(Mixer):
                         ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads, self.kv_heads, self.head_dim, ctx.status)
         self.attend(ctx, q, cache, table, mixed)
         return Delta(self.out(ctx, mixed, "attention.out"))
+
+    def decode_slices(self, ctx) -> int:
+        """Slices of the keys for the tensor-core decode kernel, which runs one CTA per (sequence, kv
+        head, slice).  Measured on a B200 from 1 to 64 sequences and 2,048 to 32,768 keys: a step is
+        fastest when the slices just fill one wave of one CTA per SM and keep at least 8 blocks each; a
+        second wave gains nothing."""
+        return kv_splits(ctx, ctx.sequences * self.kv_heads, 512, api.SM_COUNT)
 
     def slice_scratch(self, ctx, splits: int):
         """Where the slices of the keys leave their partial results (nothing for one slice)."""
@@ -122,9 +126,9 @@ class CausalAttention(Mixer):
             return
         tensor_cores = api.attention_mma_supports(q.dtype, self.heads, self.kv_heads, self.head_dim)
         if tensor_cores:
-            splits = kv_splits(ctx, ctx.sequences * self.kv_heads, 512, api.SM_COUNT)
+            splits = self.decode_slices(ctx)
         else:
-            splits = kv_splits(ctx, ctx.n_tokens * self.heads, 256, 8 * 148)
+            splits = kv_splits(ctx, ctx.n_tokens * self.heads, 256, 8 * api.SM_COUNT)
         part_acc, part_ml = self.slice_scratch(ctx, splits)
         if tensor_cores:
             api.attention_mma(q, cache.k_pool, cache.v_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads,
