@@ -52,6 +52,20 @@ def test_tokens_on_m_persistent(tokens, features, k):
     run(tokens, features, k, 1, with_bias=(k % 3 == 0), seed=7)
 
 
+@pytest.mark.parametrize("tokens,features,k,splits", [
+    (512, 2048, 2048, 4),        # 32 tiles x 4 slices of 8 k-blocks
+    (512, 2048, 8192, 4),
+    (1000, 2048, 4096, 4),       # 64 tiles x 4 = 256 work items: two per CTA, both accumulators
+    (300, 2000, 2120, 4),        # 34 k-blocks in slices of 9, 9, 9, 7; the last block half empty; ragged edges
+    (640, 520, 1096, 3),         # 18 k-blocks in slices of 6
+    (200, 2048, 2368, 9),        # 37 k-blocks in 9 slices would leave the last one empty: the generic kernel writes its zeros
+])
+def test_tokens_on_m_persistent_sliced(tokens, features, k, splits):
+    """The persistent kernel with k cut into slices: every slice in its own plane of the output,
+    the bias in the first only."""
+    run(tokens, features, k, splits, with_bias=(k % 3 != 0), seed=11)
+
+
 def test_split_policy_and_refusals():
     from thintensor_b200.kernels import api
 
@@ -59,7 +73,10 @@ def test_split_policy_and_refusals():
     assert api.gemm_tcgen05_splits(8, 2048, 8192) == 16
     assert api.gemm_tcgen05_splits(8, 128256, 2048) == 1
     assert api.gemm_tcgen05_splits(2048, 3072, 2048) == 1
-    assert api.gemm_tcgen05_splits(300, 2048, 8192) == 1        # 3 x 8 tiles of 128 x 256: the persistent kernel
+    assert api.gemm_tcgen05_splits(300, 2048, 8192) == 6        # 3 x 8 tiles of 128 x 256: the persistent kernel, 144 work items
+    assert api.gemm_tcgen05_splits(512, 2048, 2048) == 4        # 32 tiles, 32 k-blocks
+    assert api.gemm_tcgen05_splits(1024, 3072, 2048) == 1       # 96 tiles: one round of the SMs already
+    assert api.gemm_tcgen05_splits(4096, 256, 8192) == 1        # CTA pairs do not slice
     assert api.gemm_tcgen05_splits(300, 200, 4096) > 1          # too few tiles for it
     x, w = randn(4, 70, seed=1), randn(32, 70, seed=2)             # k = 70 is no multiple of 8
     assert not api.gemm_tcgen05_usable(x, w)

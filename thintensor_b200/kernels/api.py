@@ -341,18 +341,26 @@ def gemm_tcgen05_usable(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 PERSISTENT_TILES = 8        # from this many 128 x 256 output tiles on, prompts run the persistent kernel
+PAIR_TOKENS = 2048          # from this many tokens on, CTA pairs run them, which do not slice k
+PERSISTENT_SLICE_BLOCKS = 8  # a k-slice of the persistent kernel has at least this many 64-wide k-blocks
 
 
 def gemm_tcgen05_splits(tokens: int, features: int, k: int) -> int:
-    """Into how many slices k is cut so that few output tiles still fill the GPU: about
-    two CTAs per SM, at least four 64-wide k-blocks per slice, at most 16 slices.  Prompts
-    (more than 128 tokens) with at least 8 tiles of 128 x 256 are not sliced: the persistent
-    kernel with its larger tiles is faster even when it leaves SMs idle (measured from 160 to
-    2,048 tokens)."""
-    if tokens > SKINNY_TOKENS and -(-tokens // 128) * -(-features // 256) >= PERSISTENT_TILES:
-        return 1
-    tiles = -(-features // 128) * (1 if tokens <= SKINNY_TOKENS else -(-tokens // 128))
+    """Into how many slices k is cut so that few output tiles still fill the GPU.  Few tokens:
+    about two CTAs per SM, at least four 64-wide k-blocks per slice, at most 16 slices.
+    Prompts (more than 128 tokens) with at least 8 tiles of 128 x 256 run the persistent kernel,
+    one CTA per SM: as many slices as keep its work items within one round of the SMs (a
+    512-token prompt has 32 tiles in the 1B shape's output projection), none of them empty."""
     k_blocks = -(-k // 64)
+    if tokens > SKINNY_TOKENS and -(-tokens // 128) * -(-features // 256) >= PERSISTENT_TILES:
+        if tokens >= PAIR_TOKENS:
+            return 1
+        tiles = -(-tokens // 128) * -(-features // 256)
+        splits = max(1, min(SM_COUNT // tiles, k_blocks // PERSISTENT_SLICE_BLOCKS, 16))
+        while splits > 1 and (splits - 1) * -(-k_blocks // splits) >= k_blocks:
+            splits -= 1
+        return splits
+    tiles = -(-features // 128) * (1 if tokens <= SKINNY_TOKENS else -(-tokens // 128))
     return max(1, min(2 * SM_COUNT // tiles, k_blocks // 4, 16))
 
 
