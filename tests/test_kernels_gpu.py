@@ -281,9 +281,10 @@ def test_attention_mma_decode_splits_and_window(splits, window, heads, kv_heads,
     assert int(st.item()) == 0
 
 
-@pytest.mark.parametrize("splits", [1, 3])
+@pytest.mark.parametrize("splits", [1, 2, 3])
 def test_attention_mma_decode_many_sequences(splits):
-    """More CTAs than SMs: head size 64 then runs the variant with half the warps and two CTAs per SM."""
+    """More CTAs than SMs: head size 64 then runs the variants with fewer warps and two CTAs per SM
+    (200 and 600 CTAs) or three (400 CTAs)."""
     from thintensor_b200.kernels import api
 
     dtype, heads, kv_heads, head_dim = torch.bfloat16, 8, 4, 64

@@ -352,19 +352,28 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
 
 // ----------------------------------------------------------------------------- decoding
 
-// How many warps share a tile and how many blocks each keeps in flight, so that the
-// slots fit one CTA per SM: warps * stages * (HD * 256 bytes) <= 192 KB.  Measured on a
-// B200 for head size 64: 6 warps with 2 blocks each beat 4 warps with 3 (more warps hide
-// more of the arithmetic's latency; 7 warps gain nothing further).  SMALL: half the warps
-// and half the shared memory, so that two CTAs share an SM and one's start and end run
-// under the other's streaming; faster when the grid has several waves, slower when not.
+// How many warps share a tile and how many blocks each keeps in flight.  ONE_PER_SM: the slots
+// fill an SM, warps * stages * (HD * 256 bytes) <= 192 KB; for grids of at most one CTA per SM.
+// Measured on a B200 for head size 64: 6 warps with 2 blocks each beat 4 warps with 3 (more warps
+// hide more of the arithmetic's latency; 7 warps gain nothing further).  TWO_PER_SM: half the
+// warps and half the shared memory, so that one CTA's start and end run under the other's
+// streaming; faster when the grid has several waves, slower when not.  THREE_PER_SM: for grids of
+// more than two and at most three CTAs per SM, which then run as one wave instead of two (384
+// CTAs of 32 blocks: 1780 -> 1558 us per decode step of the 1B shape).  Other shapes measured for
+// the grids of several waves, us per step with 3 x 2 / 2 x 3 / 2 x 2 / 1 x 3 warps x stages: 512
+// CTAs 1841 / 1796 / 1865 / 1804; 1,024 CTAs 2913 / 2870 / 2795 / 2855; 256 CTAs of 128 blocks
+// 2281 / 2175 / 2658 / 3661 (none better throughout).  Head size 128 with
+// one warp per CTA (2 or 3 CTAs per SM) was 18 to 30 % slower per step than one CTA per SM.
 constexpr int DECODE_TABLE_CACHE = 1024;     // table entries (64 K tokens) a decode CTA keeps in shared memory
-template <int HD, bool SMALL> struct DecodeShape;
-template <> struct DecodeShape<32, false> { static constexpr int WARPS = 8, STAGES = 3; };
-template <> struct DecodeShape<64, false> { static constexpr int WARPS = 6, STAGES = 2; };
-template <> struct DecodeShape<64, true> { static constexpr int WARPS = 3, STAGES = 2; };
-template <> struct DecodeShape<96, false> { static constexpr int WARPS = 4, STAGES = 2; };
-template <> struct DecodeShape<128, false> { static constexpr int WARPS = 3, STAGES = 2; };
+constexpr int ONE_PER_SM = 0, TWO_PER_SM = 1, THREE_PER_SM = 2;
+template <int HD, int SHAPE> struct DecodeShape;
+template <> struct DecodeShape<32, ONE_PER_SM> { static constexpr int WARPS = 8, STAGES = 3; };
+template <> struct DecodeShape<64, ONE_PER_SM> { static constexpr int WARPS = 6, STAGES = 2; };
+template <> struct DecodeShape<64, TWO_PER_SM> { static constexpr int WARPS = 3, STAGES = 2; };
+template <> struct DecodeShape<64, THREE_PER_SM> { static constexpr int WARPS = 2, STAGES = 2; };
+template <> struct DecodeShape<96, ONE_PER_SM> { static constexpr int WARPS = 4, STAGES = 2; };
+template <> struct DecodeShape<128, ONE_PER_SM> { static constexpr int WARPS = 3, STAGES = 2; };
+template <int HD> constexpr bool decode_has_small_shapes = HD == 64;
 
 // What the fused form of the decode kernel does before attention: the step's q, k and v
 // come as float32 slices of the qkv product ([splits][sequences][(heads + 2 kv_heads) * HD]);
@@ -379,14 +388,14 @@ struct DecodeRope {
     int write_cache;
 };
 
-template <int HD, bool ROPE, bool SMALL>
-__global__ void __launch_bounds__(DecodeShape<HD, SMALL>::WARPS * 32)
+template <int HD, bool ROPE, int SHAPE>
+__global__ void __launch_bounds__(DecodeShape<HD, SHAPE>::WARPS * 32)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __nv_bfloat16* __restrict__ k_pool,
                         __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ table, int table_width,
                         int pool_blocks, const int* __restrict__ len_before, int heads, int kv_heads, float scale_log2,
                         int window, int splits, int cluster_merge, __nv_bfloat16* __restrict__ out,
                         float* __restrict__ part_acc, float* __restrict__ part_ml, unsigned* status) {
-    constexpr int WARPS = DecodeShape<HD, SMALL>::WARPS, STAGES = DecodeShape<HD, SMALL>::STAGES;
+    constexpr int WARPS = DecodeShape<HD, SHAPE>::WARPS, STAGES = DecodeShape<HD, SHAPE>::STAGES;
     constexpr int KC = HD / 32, NT = HD / 8;
     constexpr int K_LOADS = 8 * KC, V_LOADS = NT * 2, LOADS = K_LOADS + V_LOADS;    // 16-byte pieces per thread and block
     static_assert(STAGES <= 3, "the wait below knows three depths");
@@ -630,16 +639,16 @@ inline bool slices_form_cluster(int splits) { return splits > 1 && splits <= 8; 
 
 // The decode kernel, plain (ROPE = false: rotated queries in q, the cache already holds the
 // step's keys and values) or fused with the rotation and the cache write.
-template <int HD, bool ROPE, bool SMALL = false>
+template <int HD, bool ROPE, int SHAPE = ONE_PER_SM>
 cudaError_t launch_decode(const void* q, const DecodeRope& rope, void* k_pool, void* v_pool, const int* table, int table_width,
                           int pool_blocks, const int* len_before, int sequences, int heads, int kv_heads, float scale_log2,
                           int window, int splits, void* out, float* part_acc, float* part_ml, unsigned* status,
                           cudaStream_t stream) {
-    using D = DecodeShape<HD, SMALL>;
+    using D = DecodeShape<HD, SHAPE>;
     constexpr int shared = D::WARPS * D::STAGES * (8 * (HD / 32) + (HD / 8) * 2) * 32 * 16;
     static_assert(shared >= D::WARPS * 16 * (HD + 6) * 4 + 16 * (HD + 2) * 4, "the slots must also hold the warps' and the CTA's partial results");
     static bool configured = false;
-    auto kernel = attention_decode_kernel<HD, ROPE, SMALL>;
+    auto kernel = attention_decode_kernel<HD, ROPE, SHAPE>;
     if (!configured) {
         const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
         if (err != cudaSuccess) return err;
@@ -680,11 +689,22 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* tab
             if ((err = cudaGetDevice(&device)) != cudaSuccess) return (int)err;
             if ((err = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device)) != cudaSuccess) return (int)err;
         }
-        if (HD == 64 && (long long)sequences * kv_heads * splits > sm_count)     // several waves: two smaller CTAs per SM
-            err = launch_decode<HD, false, HD == 64>(q, DecodeRope{}, const_cast<void*>(k_pool), const_cast<void*>(v_pool), table,
-                                                     table_width, pool_blocks, len_before, sequences, heads, kv_heads, scale_log2,
-                                                     window, splits, out, part_acc, part_ml, status, stream);
-        else
+        const long long ctas = (long long)sequences * kv_heads * splits;
+        bool done = false;
+        if constexpr (decode_has_small_shapes<HD>) {
+            if (ctas > 2 * sm_count && ctas <= 3 * sm_count) {          // one wave of three CTAs per SM
+                err = launch_decode<HD, false, THREE_PER_SM>(q, DecodeRope{}, const_cast<void*>(k_pool), const_cast<void*>(v_pool), table,
+                                                             table_width, pool_blocks, len_before, sequences, heads, kv_heads, scale_log2,
+                                                             window, splits, out, part_acc, part_ml, status, stream);
+                done = true;
+            } else if (ctas > sm_count) {                               // several waves
+                err = launch_decode<HD, false, TWO_PER_SM>(q, DecodeRope{}, const_cast<void*>(k_pool), const_cast<void*>(v_pool), table,
+                                                           table_width, pool_blocks, len_before, sequences, heads, kv_heads, scale_log2,
+                                                           window, splits, out, part_acc, part_ml, status, stream);
+                done = true;
+            }
+        }
+        if (!done)
             err = launch_decode<HD, false>(q, DecodeRope{}, const_cast<void*>(k_pool), const_cast<void*>(v_pool), table, table_width,
                                            pool_blocks, len_before, sequences, heads, kv_heads, scale_log2, window, splits, out,
                                            part_acc, part_ml, status, stream);
