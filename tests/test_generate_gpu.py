@@ -58,6 +58,24 @@ def test_stop_tokens_end_sequences_early(model_folders):
     assert engine.cache.slots.free_count == engine.cache.max_slots
 
 
+def test_an_error_in_a_batch_leaves_the_cache_whole(model_folders):
+    """A request that the step refuses (a token outside the vocabulary) ends the call with an
+    error; the slots and blocks of its batch are given back, so the next call has the whole cache."""
+    import thintensor_b200
+    from thintensor_b200.engine.engine import StepError
+
+    folder = model_folders("a", "float32")
+    runtime = thintensor_b200.load_model(folder, dtype="fp32")
+    vocab = TINY["a"]["vocab_size"]
+    prompts = [token_ids(vocab, n, 900 + n) for n in (4, 7, 3)]
+    want = runtime.generate(prompts, max_new_tokens=6, stop_ids=(), batch_size=3)
+    with pytest.raises(StepError, match="outside the vocabulary"):
+        runtime.generate([prompts[0], prompts[1] + [vocab], prompts[2]], max_new_tokens=6, stop_ids=(), batch_size=3)
+    cache = runtime._engine.cache
+    assert cache.free_blocks == cache.num_blocks and cache.slots.free_count == cache.max_slots
+    assert runtime.generate(prompts, max_new_tokens=6, stop_ids=(), batch_size=3) == want
+
+
 @pytest.mark.parametrize("sampling", [
     {"temperature": 0.8, "seed": 4},
     {"temperature": 1.3, "top_k": 5, "seed": 9},

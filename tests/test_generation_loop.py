@@ -53,6 +53,10 @@ class ScriptedBackend:
         self.live_now.remove(position)
         self.finished.append(self.batch[position])
 
+    def abandon(self):
+        self.calls.append(("abandon", tuple(sorted(self.live_now))))
+        self.live_now.clear()
+
 
 def test_stop_tokens_and_early_finish():
     script = {0: [5, 6, 99, 1, 1, 1], 1: [99, 2, 2, 2, 2, 2], 2: [7, 7, 7, 7, 7, 7], 3: [8, 99, 0, 0, 0, 0], 4: [4, 4, 4, 99, 0, 0]}
@@ -88,6 +92,25 @@ def test_batches_follow_the_cache_capacity():
     assert [c[1] for c in backend.calls if c[0] == "start"] == [(0, 1), (2,), (3, 4)]
     with pytest.raises(GenerationError, match="more than the cache can hold"):
         run_generation(ScriptedBackend(script, capacity_tokens=20), prompts, max_new_tokens=4)
+
+
+def test_a_failing_step_gives_back_what_the_batch_holds():
+    """A backend call that raises in the middle of a batch: the loop frees the batch's unfinished
+    sequences before the error goes on, and runs no further batch."""
+    script = {0: [5, 99, 0, 0], 1: [6, 6, 6, 6], 2: [7, 7, 7, 7], 3: [8, 8, 8, 8]}
+
+    class Failing(ScriptedBackend):
+        def decode_step(self, live):
+            if sum(1 for c in self.calls if c[0] == "step") == 2:
+                raise RuntimeError("device status 0x4")
+            return super().decode_step(live)
+
+    backend = Failing(script)
+    with pytest.raises(RuntimeError, match="device status"):
+        run_generation(backend, [[1]] * 4, max_new_tokens=4, stop_ids=[99], batch_size=3)
+    assert backend.finished == [0]                                  # request 0 had ended on its stop token
+    assert backend.calls[-1] == ("abandon", (1, 2)) and not backend.live_now
+    assert [c[1] for c in backend.calls if c[0] == "start"] == [(0, 1, 2)]
 
 
 def test_argument_errors():

@@ -65,6 +65,10 @@ class Backend(Protocol):
     def finish(self, position: int) -> None:
         """The sequence at ``position`` of the batch has ended: free what it holds."""
 
+    def abandon(self) -> None:
+        """A call of the current batch raised: free what its unfinished sequences still hold,
+        so that the error leaves the cache as it was before the batch."""
+
 
 @dataclass
 class GenerationStats:
@@ -121,50 +125,60 @@ def run_generation(backend: Backend, prompts: Sequence[Sequence[int]], max_new_t
     while pending:
         batch = plan_batch(pending, totals, batch_size, backend)
         pending = pending[len(batch):]
-        stats.batches += 1
-        stats.batch_sizes.append(len(batch))
-        stats.prefill_steps += 1
-        stats.prompt_tokens += sum(len(prompts[i]) for i in batch)
-        clock = time.perf_counter()
-        first = backend.start_batch(batch, [prompts[i] for i in batch], [totals[i] for i in batch])
-        stats.prefill_seconds += time.perf_counter() - clock
-        clock = time.perf_counter()
-        live: list[int] = []                      # positions in the batch still running
-        for position, (index, token) in enumerate(zip(batch, first)):
-            results[index].append(int(token))
-            if int(token) in stop or max_new_tokens == 1:
-                backend.finish(position)
-            else:
-                live.append(position)
-        produced = 1
-        while live:
-            if not stop:
-                # nothing can end early: run to the limit without reading tokens back
-                steps = max_new_tokens - produced
-                for tokens in backend.decode_run(live, steps):
-                    for position, token in zip(live, tokens):
-                        results[batch[position]].append(int(token))
-                stats.decode_steps += steps
-                stats.decoded_tokens += steps * len(live)
-                for position in live:
-                    backend.finish(position)
-                live = []
-                break
-            tokens = backend.decode_step(live)
-            stats.decode_steps += 1
-            stats.decoded_tokens += len(live)
-            produced += 1
-            still: list[int] = []
-            for position, token in zip(live, tokens):
-                results[batch[position]].append(int(token))
-                if int(token) in stop or produced == max_new_tokens:
-                    backend.finish(position)
-                else:
-                    still.append(position)
-            live = still
-        stats.decode_seconds += time.perf_counter() - clock
+        try:
+            _run_batch(backend, batch, prompts, totals, max_new_tokens, stop, results, stats)
+        except BaseException:
+            backend.abandon()
+            raise
     stats.new_tokens = sum(len(r) for r in results)
     return results
+
+
+def _run_batch(backend: Backend, batch: list[int], prompts, totals: list[int], max_new_tokens: int, stop: frozenset,
+               results: list[list[int]], stats: GenerationStats) -> None:
+    """One batch from its prompts to the end of its last sequence."""
+    stats.batches += 1
+    stats.batch_sizes.append(len(batch))
+    stats.prefill_steps += 1
+    stats.prompt_tokens += sum(len(prompts[i]) for i in batch)
+    clock = time.perf_counter()
+    first = backend.start_batch(batch, [prompts[i] for i in batch], [totals[i] for i in batch])
+    stats.prefill_seconds += time.perf_counter() - clock
+    clock = time.perf_counter()
+    live: list[int] = []                      # positions in the batch still running
+    for position, (index, token) in enumerate(zip(batch, first)):
+        results[index].append(int(token))
+        if int(token) in stop or max_new_tokens == 1:
+            backend.finish(position)
+        else:
+            live.append(position)
+    produced = 1
+    while live:
+        if not stop:
+            # nothing can end early: run to the limit without reading tokens back
+            steps = max_new_tokens - produced
+            for tokens in backend.decode_run(live, steps):
+                for position, token in zip(live, tokens):
+                    results[batch[position]].append(int(token))
+            stats.decode_steps += steps
+            stats.decoded_tokens += steps * len(live)
+            for position in live:
+                backend.finish(position)
+            live = []
+            break
+        tokens = backend.decode_step(live)
+        stats.decode_steps += 1
+        stats.decoded_tokens += len(live)
+        produced += 1
+        still: list[int] = []
+        for position, token in zip(live, tokens):
+            results[batch[position]].append(int(token))
+            if int(token) in stop or produced == max_new_tokens:
+                backend.finish(position)
+            else:
+                still.append(position)
+        live = still
+    stats.decode_seconds += time.perf_counter() - clock
 
 
 # --------------------------------------------------------------------------------------
@@ -313,7 +327,9 @@ class EngineBackend:
 
     def start_batch(self, requests, prompts, totals) -> list[int]:
         e = self.engine
-        self._slots = [e.open() for _ in prompts]
+        self._slots = []
+        for _ in prompts:                       # one by one: if the cache runs out of slots, abandon() finds the earlier ones
+            self._slots.append(e.open())
         self._requests, self._totals = list(requests), list(totals)
         self._steps = [1] * len(prompts)
         self._state = None
@@ -381,4 +397,11 @@ class EngineBackend:
             raise GenerationError(f"the sequence at position {position} was finished twice")
         self.engine.close(slot)
         self._slots[position] = None
+        self._state = None
+
+    def abandon(self) -> None:
+        for position, slot in enumerate(self._slots):
+            if slot is not None:
+                self.engine.close(slot)
+                self._slots[position] = None
         self._state = None
