@@ -25,25 +25,10 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-# the Llama-3.2-1B shape: every size comes from here, as a config.json would give it
-LLAMA_1B = {
-    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
-    "num_hidden_layers": 16, "hidden_size": 2048, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64,
-    "intermediate_size": 8192, "vocab_size": 128256, "rope_theta": 500000.0, "rms_norm_eps": 1e-5,
-    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
-                     "original_max_position_embeddings": 8192},
-    "max_position_embeddings": 131072, "tie_word_embeddings": True,
-}
-# the other two shapes of the family, for `--only` measurements (the headline stays the 1B shape)
-SHAPES = {
-    "1b": {},
-    "3b": {"num_hidden_layers": 28, "hidden_size": 3072, "num_attention_heads": 24, "head_dim": 128},
-    "8b": {"num_hidden_layers": 32, "hidden_size": 4096, "num_attention_heads": 32, "head_dim": 128, "intermediate_size": 14336,
-           "tie_word_embeddings": False,
-           "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
-                            "original_max_position_embeddings": 8192}},
-}
-FULL_LAYERS = 16
+# Every size comes from the package's table of named shapes (whole config.json dicts, kept as
+# data).  --shape picks another one for `--only` measurements; the headline stays the 1B shape.
+SHAPES = json.loads((ROOT / "thintensor_b200" / "config" / "shapes.json").read_text(encoding="utf-8"))
+SHAPE_NAMES = {"1b": "llama-3.2-1b", "3b": "llama-3.2-3b", "8b": "llama-3.1-8b"}
 CONTEXT = 4096
 PROMPT = 2048
 BATCH = 8
@@ -111,13 +96,13 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def reference_arm(steps: int, warmup: int) -> int:
+def reference_arm(config: dict, steps: int, warmup: int) -> int:
     """The unmodified reference from baseline/_ref on the same shape and workload."""
     sys.path.insert(0, str(ROOT / "baseline"))
     try:
         import reference_arm as arm
 
-        line = arm.run(LLAMA_1B, METRIC, BATCH, PROMPT, CONTEXT, steps, max(warmup, 3))
+        line = arm.run(config, METRIC, BATCH, PROMPT, CONTEXT, steps, max(warmup, 3))
     except Exception as exc:  # noqa: BLE001 - the arm must always print a line and exit 0
         line = {"impl": "reference", "unavailable": f"the reference failed to run: {type(exc).__name__}: {str(exc)[:300]}"}
     print(json.dumps(line))
@@ -130,15 +115,15 @@ def main() -> int:
     parser.add_argument("--steps", type=int, default=256)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    parser.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration has (both numbers are reported)")
+    parser.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (both numbers are reported)")
     parser.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64")
     parser.add_argument("--only", choices=["decode", "prefill"], help="run one phase only and print its numbers (for profiling)")
     parser.add_argument("--batch", type=int, default=BATCH, help="with --only decode: sequences decoded together")
-    parser.add_argument("--shape", choices=sorted(SHAPES), default="1b", help="with --only: layer sizes of another model of the family")
+    parser.add_argument("--shape", choices=sorted(SHAPE_NAMES), default="1b", help="with --only: layer sizes of another model of the family")
     parser.add_argument("--prompt-len", type=int, default=PROMPT, help="with --only: tokens per prompt (the context is this plus room for the steps)")
     args = parser.parse_args()
     if args.impl == "reference":
-        return reference_arm(min(args.steps, 128), args.warmup)
+        return reference_arm(dict(SHAPES[SHAPE_NAMES["1b"]]), min(args.steps, 128), args.warmup)
     if args.gpus != 1:
         print("bench.py measures one GPU only: this library does not run on several GPUs")
         return 2
@@ -152,10 +137,10 @@ def main() -> int:
     from thintensor_b200.engine.generate import GenerationStats
 
     pk = peaks()
-    raw = dict(LLAMA_1B)
-    raw["num_hidden_layers"] = args.layers
-    if args.only and args.shape != "1b":
-        raw.update(SHAPES[args.shape])
+    raw = dict(SHAPES[SHAPE_NAMES[args.shape if args.only else "1b"]])
+    full_layers = raw["num_hidden_layers"]
+    if args.layers is not None:
+        raw["num_hidden_layers"] = args.layers
     prompt_len = args.prompt_len if args.only else PROMPT
     if prompt_len != PROMPT:
         raw["max_position_embeddings"] = max(raw.get("max_position_embeddings", 0), 2 * prompt_len)
@@ -206,7 +191,7 @@ def main() -> int:
         "data": "synthetic: random weights N(0, 0.02) from a seed, token ids uniform in [0, vocab)",
         "impl": "ours",
         "config": {
-            "model": "Llama-3.2-1B shape", "layers": args.layers, "layers_of_configuration": FULL_LAYERS,
+            "model": "Llama-3.2-1B shape", "layers": raw["num_hidden_layers"], "layers_of_configuration": full_layers,
             "hidden_size": raw["hidden_size"], "heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"],
             "head_dim": raw["head_dim"], "intermediate_size": raw["intermediate_size"], "vocab_size": vocab,
             "tied_embeddings": True, "rope": "llama3 factor 32", "global_batch": BATCH, "prompt_len": PROMPT,

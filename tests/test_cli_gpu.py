@@ -34,5 +34,8 @@ def test_random_run_validate_bench(tmp_path):
     assert report["tier"] in ("exact_pass", "ranking_pass") and set(report["modes"]) == {"whole", "tail_by_one", "unequal_batch"}
     bench = json.loads(cli("bench", str(folder), "--steps", "8", "--warmup", "3", "--prompt-len", "20", "--batch", "2", "--json"))
     assert bench["tokens_per_s"] > 0 and bench["prefill_tokens_per_s"] > 0 and bench["batch_size"] == 2
+    shaped = json.loads(cli("bench", "--shape", "tiny-a", "--steps", "6", "--warmup", "3", "--prompt-len", "9", "--batch", "1,3", "--json"))
+    assert [b["batch_size"] for b in shaped["batches"]] == [1, 3] and all(b["tokens_per_s"] > 0 for b in shaped["batches"])
+    cli("bench", expect=1)                                  # neither a folder nor a shape
     # the context limit is checked before anything runs, as the reference does
     cli("run", str(folder), "--prompt-token-ids", "1,2,3", "--max-new-tokens", "10", "--context", "8", expect=2)

@@ -95,3 +95,20 @@ def test_description_is_data():
     assert mixer.params["position"].params["scaling"]["factor"] == 8.0
     assert spec.layers[0].parts["ffn"].params == {"hidden": 96, "inter": 320, "bias": False}
     assert spec.final_norm.params["eps"] == 1e-6 and spec.head.params["tied"] is False
+
+
+def test_named_shapes_are_whole_configurations():
+    """The named benchmark shapes are config.json dicts kept as data; the command line offers
+    exactly those names and each of them gives a valid typed configuration."""
+    from pathlib import Path
+
+    from thintensor_b200.cli import SHAPE_NAMES
+
+    file = Path(__file__).resolve().parent.parent / "thintensor_b200" / "config" / "shapes.json"
+    shapes = json.loads(file.read_text())
+    assert tuple(shapes) == SHAPE_NAMES
+    for name, raw in shapes.items():
+        arch, config = load_config(raw)
+        assert arch.name == "LlamaForCausalLM" and config.hidden_size == raw["hidden_size"], name
+    one_b = load_config(shapes["llama-3.2-1b"])[1]
+    assert (one_b.num_hidden_layers, one_b.num_attention_heads, one_b.num_key_value_heads, one_b.head_dim) == (16, 32, 8, 64)

@@ -7,12 +7,20 @@ holds), so consecutive timed steps cannot serve each other from cache.
 """
 from __future__ import annotations
 
+import json
+from pathlib import Path
+
 import torch
 
 from .engine.engine import Entry
 from .engine.generate import EngineBackend, _DecodeState
 from .kernels import api
 from .sampling.sampler import SamplingParams
+
+# Named shapes for benchmarks with random weights, each a whole config.json: the three Llama 3
+# models the reference's reports measure and two tiny ones that differ in every size and option.
+# They are data (config/shapes.json), read here and by bench.py.
+SHAPES: dict[str, dict] = json.loads((Path(__file__).resolve().parent / "config" / "shapes.json").read_text(encoding="utf-8"))
 
 
 def weight_bytes_per_step(model) -> int:

@@ -5,9 +5,10 @@ Option names and meanings follow the reference's ``thintensor`` command
 ``validate``): ``--prompt``, ``--context`` (most prompt + new tokens), ``--max-new-tokens``
 / ``--steps``, ``--temperature``, ``--top-p``, ``--top-k``, ``--seed``, ``--device``,
 ``--dtype``, ``--tokenizer``, ``--json``; ``bench`` has ``--steps``, ``--warmup``,
-``--prompt-token-ids``, ``--out``; ``validate`` has ``--require-tier``.  What the
-reference's flags select among engines, profiles, quantisation and residency has no
-counterpart here.  Unlike the reference, which refuses anything but greedy decoding
+``--prompt-token-ids``, ``--out``; ``validate`` has ``--require-tier``.  ``bench`` and
+``validate`` also take ``--shape NAME`` in place of a model folder: random weights of a
+named size.  What the reference's flags select among engines, profiles, quantisation and
+residency has no counterpart here.  Unlike the reference, which refuses anything but greedy decoding
 (thinruntime/cli.py:1940-1945), sampling options are honoured.
 """
 from __future__ import annotations
@@ -17,6 +18,9 @@ import json
 import sys
 import time
 from pathlib import Path
+
+
+SHAPE_NAMES = ("llama-3.2-1b", "llama-3.2-3b", "llama-3.1-8b", "tiny-a", "tiny-b")     # keys of config/shapes.json
 
 
 def build_parser() -> argparse.ArgumentParser:
@@ -42,12 +46,14 @@ def build_parser() -> argparse.ArgumentParser:
     run.add_argument("--json", action="store_true", help="JSON output")
 
     bench = sub.add_parser("bench", help="Benchmark prefill and decode", formatter_class=argparse.ArgumentDefaultsHelpFormatter)
-    bench.add_argument("model", help="model folder")
-    bench.add_argument("--steps", type=int, default=200, help="Timed decode steps")
+    bench.add_argument("model", nargs="?", help="model folder (or --shape)")
+    bench.add_argument("--shape", choices=SHAPE_NAMES, help="Random weights of a named shape instead of a model folder")
+    bench.add_argument("--steps", "--decode-steps", dest="steps", type=int, default=200, help="Timed decode steps")
     bench.add_argument("--warmup", type=int, default=10, help="Warmup decode steps")
     bench.add_argument("--prompt-token-ids", help="Comma-separated explicit prompt token ids used by every sequence")
     bench.add_argument("--prompt-len", type=int, default=128, help="Length of the synthetic prompt when no ids are given")
-    bench.add_argument("--batch", type=int, default=1, help="Sequences decoded together")
+    bench.add_argument("--batch", default="1", help="Sequences decoded together; a comma-separated list measures each")
+    bench.add_argument("--context", type=int, help="Context length of a sequence (default: prompt + warm-up + steps)")
     bench.add_argument("--seed", type=int, default=0)
     bench.add_argument("--device", choices=["cuda"], default="cuda")
     bench.add_argument("--dtype", choices=["bf16", "fp32"], default="bf16")
@@ -56,7 +62,8 @@ def build_parser() -> argparse.ArgumentParser:
 
     validate = sub.add_parser("validate", help="Compare the engine's ways of running with its 32-bit path",
                               formatter_class=argparse.ArgumentDefaultsHelpFormatter)
-    validate.add_argument("model", help="model folder")
+    validate.add_argument("model", nargs="?", help="model folder (or --shape)")
+    validate.add_argument("--shape", choices=SHAPE_NAMES, help="Random weights of a named shape, written to a temporary folder")
     validate.add_argument("--require-tier", choices=["ranking", "exact"], default="ranking", help="Minimum accepted correctness tier")
     validate.add_argument("--prompt-token-ids", help="Comma-separated token ids; default is a seeded synthetic sequence")
     validate.add_argument("--length", type=int, default=96, help="Length of the synthetic sequence")
@@ -132,24 +139,36 @@ def cmd_bench(args) -> int:
     import torch
 
     import thintensor_b200
-    from thintensor_b200.benchmark import measure_decode, measure_prefill
+    from thintensor_b200.benchmark import SHAPES, measure_decode, measure_prefill
 
-    runtime = thintensor_b200.load_model(args.model, dtype=args.dtype, device=args.device)
+    if (args.model is None) == (args.shape is None):
+        raise SystemExit("bench needs a model folder or --shape, not both")
+    if args.shape:
+        runtime = thintensor_b200.random_model(SHAPES[args.shape], seed=args.seed, dtype=args.dtype, device=args.device)
+    else:
+        runtime = thintensor_b200.load_model(args.model, dtype=args.dtype, device=args.device)
+    batches = parse_ids(args.batch)
+    if not batches or min(batches) <= 0:
+        raise SystemExit("--batch must name positive numbers of sequences")
     vocab = runtime.model.spec.vocab_size
     if args.prompt_token_ids:
         prompt = parse_ids(args.prompt_token_ids)
     else:
         g = torch.Generator().manual_seed(args.seed)
         prompt = torch.randint(0, vocab, (args.prompt_len,), generator=g).tolist()
-    context = len(prompt) + args.warmup + args.steps + 1
+    context = args.context or len(prompt) + max(args.warmup, 2) + args.steps + 1
     prefill = measure_prefill(runtime, prompt, repeats=3)
-    decode = measure_decode(runtime, [prompt] * args.batch, context, args.warmup, args.steps)
+    runs = [measure_decode(runtime, [prompt] * batch, context, args.warmup, args.steps) for batch in batches]
+    decode = runs[0]
     result = {
-        "model": str(args.model), "dtype": args.dtype, "batch_size": args.batch, "prompt_tokens": len(prompt),
-        "steps": args.steps, "warmup_steps": args.warmup,
+        "model": str(args.model or args.shape), "dtype": args.dtype, "batch_size": batches[0], "prompt_tokens": len(prompt),
+        "steps": args.steps, "warmup_steps": args.warmup, "context": context,
         "tokens_per_s": decode["tokens_per_s"], "ms_per_token": decode["ms_per_step"],
         "prefill_tokens_per_s": prefill["tokens_per_s"], "prefill_ms": prefill["ms"],
     }
+    if len(runs) > 1:
+        result["batches"] = [{"batch_size": r["batch"], "tokens_per_s": r["tokens_per_s"], "ms_per_step": r["ms_per_step"],
+                              "bytes_per_step": r["bytes_per_step"]} for r in runs]
     text = json.dumps(result, indent=None if args.json else 2)
     if args.out:
         Path(args.out).write_text(text + "\n")
@@ -161,7 +180,19 @@ def cmd_validate(args) -> int:
     from thintensor_b200.validate import validate_model
 
     ids = parse_ids(args.prompt_token_ids) if args.prompt_token_ids else None
-    report = validate_model(args.model, dtype=args.dtype, tokens=ids, length=args.length, seed=args.seed)
+    if (args.model is None) == (args.shape is None):
+        raise SystemExit("validate needs a model folder or --shape, not both")
+    if args.shape:
+        import tempfile
+
+        import thintensor_b200
+        from thintensor_b200.benchmark import SHAPES
+
+        with tempfile.TemporaryDirectory() as folder:      # both dtypes are read from the same file
+            thintensor_b200.save_random_model(folder, SHAPES[args.shape], seed=args.seed, dtype="bfloat16")
+            report = validate_model(folder, dtype=args.dtype, tokens=ids, length=args.length, seed=args.seed)
+    else:
+        report = validate_model(args.model, dtype=args.dtype, tokens=ids, length=args.length, seed=args.seed)
     print(json.dumps(report) if args.json else json.dumps(report, indent=2))
     order = {"fail": 0, "ranking_pass": 1, "exact_pass": 2}
     needed = {"ranking": 1, "exact": 2}[args.require_tier]
