@@ -501,3 +501,23 @@ def test_sampling_follows_plain(vocab, params):
     counts = torch.bincount(out.long().cpu(), minlength=vocab).double() / draws
     assert float(counts[p == 0].sum()) == 0.0, "a token outside the kept set was drawn"
     assert float(0.5 * (counts - p).abs().sum()) < 0.12 + 0.5 * math.sqrt(float((p > 0).sum()) / draws)
+
+
+# ------------------------------------------------------------------------ step bookkeeping
+@pytest.mark.parametrize("sequences", [1, 7, 300])
+def test_advance_lengths_and_step_counters(sequences):
+    """After a step every sequence's length grows by the tokens it brought; the step counters,
+    where the caller keeps some, go up by one; without counters only the lengths change."""
+    from thintensor_b200.kernels import api
+
+    g = torch.Generator().manual_seed(sequences)
+    new = torch.randint(1, 9, (sequences,), generator=g)
+    cu = torch.cat([torch.zeros(1, dtype=torch.int64), new.cumsum(0)]).to(torch.int32).to(DEV)
+    before = torch.randint(0, 5000, (sequences,), generator=g).to(torch.int32)
+    lengths, counters = before.to(DEV), torch.arange(sequences, dtype=torch.int32, device=DEV)
+    api.advance_lengths(lengths, cu, sequences, counters)
+    assert torch.equal(lengths.cpu(), before + new.to(torch.int32))
+    assert torch.equal(counters.cpu(), torch.arange(sequences, dtype=torch.int32) + 1)
+    api.advance_lengths(lengths, cu, sequences)
+    assert torch.equal(lengths.cpu(), before + 2 * new.to(torch.int32))
+    assert torch.equal(counters.cpu(), torch.arange(sequences, dtype=torch.int32) + 1)

@@ -455,18 +455,22 @@ extern "C" int tt_swiglu(const float* gate_up, int splits, long long split_strid
 }
 
 // ------------------------------------------------------------------------------------
-// after a step: len[b] += cu[b + 1] - cu[b]
+// after a step: len[b] += cu[b + 1] - cu[b]; counters[b] += 1 where the caller keeps a count of
+// the steps each sequence has taken (the sampler's random numbers are indexed by it)
 // ------------------------------------------------------------------------------------
-__global__ void advance_lengths_kernel(int* __restrict__ len, const int* __restrict__ cu, int sequences) {
+__global__ void advance_lengths_kernel(int* __restrict__ len, const int* __restrict__ cu, int* __restrict__ counters, int sequences) {
     tt_pdl_launch_dependents();
     tt_pdl_wait();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
-    if (b < sequences) len[b] += cu[b + 1] - cu[b];
+    if (b < sequences) {
+        len[b] += cu[b + 1] - cu[b];
+        if (counters) counters[b] += 1;
+    }
 }
 
-extern "C" int tt_advance_lengths(int* len, const int* cu, int sequences, cudaStream_t stream) {
+extern "C" int tt_advance_lengths(int* len, const int* cu, int* counters, int sequences, cudaStream_t stream) {
     if (sequences <= 0) return 0;
-    tt_launch_pdl(advance_lengths_kernel, dim3((sequences + 127) / 128), dim3(128), 0, stream, len, cu, sequences);
+    tt_launch_pdl(advance_lengths_kernel, dim3((sequences + 127) / 128), dim3(128), 0, stream, len, cu, counters, sequences);
     TT_LAUNCH_CHECK();
 }
 

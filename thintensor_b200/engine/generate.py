@@ -270,8 +270,7 @@ class _DecodeState:
         e = self.engine
         logits = e.model.forward(self.context(), e.cache, self.rows)
         sample(logits, params, self.requests, self.steps, self.tokens)
-        api.advance_lengths(self.lengths, self.cu, self.sequences)
-        self.steps.add_(1)
+        api.advance_lengths(self.lengths, self.cu, self.sequences, self.steps)
 
     def body_with_host(self, params: SamplingParams) -> None:
         """The step with the host as the authority on tokens: ``host_in`` goes up before it,

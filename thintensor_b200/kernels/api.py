@@ -163,9 +163,12 @@ def copy_int32(dst: torch.Tensor, src: torch.Tensor) -> None:
     _check(fn(c_void_p(dst.data_ptr()), c_void_p(src.data_ptr()), dst.numel(), _stream()), "copy_int32")
 
 
-def advance_lengths(lengths: torch.Tensor, cu: torch.Tensor, sequences: int) -> None:
-    fn = _fn("elementwise", "tt_advance_lengths", [c_void_p, c_void_p, c_int, c_void_p])
-    _check(fn(_ptr(lengths), _ptr(cu), sequences, _stream()), "advance_lengths")
+def advance_lengths(lengths: torch.Tensor, cu: torch.Tensor, sequences: int, counters: torch.Tensor | None = None) -> None:
+    """lengths[b] += cu[b + 1] - cu[b] after a step; ``counters`` (int32, one per sequence), if given, go up by one."""
+    if counters is not None:
+        _need(counters, torch.int32, "step counters")
+    fn = _fn("elementwise", "tt_advance_lengths", [c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+    _check(fn(_ptr(lengths), _ptr(cu), _ptr(counters), sequences, _stream()), "advance_lengths")
 
 
 # --------------------------------------------------------------------------- attention
