@@ -134,11 +134,15 @@ class Engine:
             out_base.append(running)
             running += len(entry.want)
 
-        for piece in self._pieces(entries):
+        pieces = self._pieces(entries)
+        for piece in pieces:
             ctx, rows, targets = self._prepare(entries, arrays, piece, out_base)
             if rows is not None:
+                if len(pieces) == 1:
+                    ctx.logits_out = out            # one piece: its wanted rows are the result's rows, in order
                 logits = self.model.forward(ctx, self.cache, rows)
-                out.index_copy_(0, targets, logits)
+                if logits.data_ptr() != out.data_ptr() or logits.shape != out.shape:
+                    out.index_copy_(0, targets.to(torch.int64), logits)
             else:
                 self._forward_without_logits(ctx)
             for index, start, count in piece:
@@ -232,7 +236,7 @@ class Engine:
         d_tokens, d_cu, d_before, d_slots = cut(n_tokens), cut(sequences + 1), cut(sequences), cut(sequences)
         d_tables = [cut(sequences * width).view(sequences, width) for _ in range(groups)]
         d_rows = cut(len(rows)) if rows else None
-        d_targets = cut(len(rows)).to(torch.int64) if rows else None
+        d_targets = cut(len(rows)) if rows else None
         ctx = StepContext(
             n_tokens=n_tokens, sequences=sequences, decode=all(c == 1 for c in new), max_new=max(new),
             max_total=max(b + c for b, c in zip(before, new)), tokens=d_tokens, cu=d_cu, len_before=d_before, slots=d_slots,

@@ -382,7 +382,7 @@ class EngineBackend:
         history = torch.empty((steps, len(live)), dtype=torch.int32, device=self.engine.device)
         for i in range(steps):
             state.step(self.params, self.use_graph)
-            history[i].copy_(state.tokens)
+            api.copy_int32(history[i], state.tokens)
         out = history.tolist()
         for position, token in zip(live, out[-1]):
             self._last[position] = token

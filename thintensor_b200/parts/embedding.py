@@ -50,7 +50,10 @@ class LinearHead(Head):
         self.linear = Linear(tensors["weight"], tensors.get("bias"))
 
     def forward(self, ctx, x) -> torch.Tensor:
-        logits = self.linear(ctx, x, "head.logits")
+        """Float32 logits ``[rows, vocab]``: in ``ctx.logits_out`` where the step gave one and the
+        product could write there, else in scratch memory."""
+        into = ctx.logits_out if ctx.logits_out is not None and ctx.logits_out.shape[0] == x.shape[0] else None
+        logits = self.linear(ctx, x, "head.logits", into)
         if logits.shape[0] == 1:
             return logits[0]
         return logits.sum(dim=0)

@@ -30,16 +30,24 @@ class Linear:
         """The projection onto output features begin..end-1 (shares storage)."""
         return Linear(self.weight[begin:end], None if self.bias is None else self.bias[begin:end])
 
-    def __call__(self, ctx, x: torch.Tensor, name: str) -> torch.Tensor:
+    def __call__(self, ctx, x: torch.Tensor, name: str, into: torch.Tensor | None = None) -> torch.Tensor:
+        """``into``: a float32 ``[tokens, out_features]`` tensor of the caller's that receives the
+        product itself where k is not cut into slices (the result is then a view of it);
+        otherwise the result lies in scratch memory that the next step reuses."""
         tokens = x.shape[0]
         if x.shape[1] != self.in_features:
             raise ValueError(f"{name}: input has {x.shape[1]} features, the weight takes {self.in_features}")
+        if into is not None and (into.dtype != torch.float32 or tuple(into.shape) != (tokens, self.out_features) or not into.is_contiguous()):
+            raise ValueError(f"{name}: the given output must be contiguous float32 [{tokens}, {self.out_features}]")
         if api.gemm_tcgen05_usable(x, self.weight):
             splits = api.gemm_tcgen05_splits(tokens, self.out_features, self.in_features)
-            out = ctx.scratch(name, (splits, tokens, self.out_features), torch.float32)
+            if splits == 1 and into is not None:
+                out = into.unsqueeze(0)
+            else:
+                out = ctx.scratch(name, (splits, tokens, self.out_features), torch.float32)
             api.gemm_tcgen05(x, self.weight, self.bias, out, ctx.status, operands_checked=True)
             return out
-        out = ctx.scratch(name, (1, tokens, self.out_features), torch.float32)
+        out = into.unsqueeze(0) if into is not None else ctx.scratch(name, (1, tokens, self.out_features), torch.float32)
         api.gemm_simt(x, self.weight, self.bias, out)
         return out
 
