@@ -132,3 +132,42 @@ def test_random_model_folder(tmp_path, name):
     assert (folder / "model.safetensors").read_bytes() != (third / "model.safetensors").read_bytes()
     cfg, weights = plain_llama.read_model(third)
     assert plain_llama.forward(cfg, weights, [1, 2, 3]).shape == (3, config.vocab_size)
+
+
+def test_wrapper_checkpoints_are_read_without_their_prefix(tmp_path):
+    """A multimodal wrapper's folder: the decoder's numbers under ``text_config``, its tensors
+    under ``language_model.`` or ``model.language_model.``, other towers beside them.  The decoder
+    is found under its plain names, the other towers are left alone, a missing tensor is still named."""
+    from thintensor_b200.weights import load_checkpoint
+    from thintensor_b200.weights.loader import decoder_names
+
+    config, declared = declared_for("b")
+    tensors = random_tensors(declared, 5, torch.float32)
+    stored = {}
+    for name, tensor in tensors.items():
+        if name == "lm_head.weight":
+            stored["language_model.lm_head.weight"] = tensor
+        elif name.startswith("model.layers.1."):
+            stored["model.language_model." + name[len("model."):]] = tensor      # the form without the inner "model."
+        else:
+            stored["language_model." + name] = tensor
+    stored["vision_tower.patch_embedding.weight"] = torch.zeros(4, 4)
+    stored["multi_modal_projector.linear.weight"] = torch.zeros(2, 2)
+    names = decoder_names(list(stored))
+    assert set(names) == set(tensors) and names["model.layers.1.mlp.up_proj.weight"] == "model.language_model.layers.1.mlp.up_proj.weight"
+    folder = tmp_path / "wrapper"
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps({"model_type": "llama", "text_config": TINY["b"]}))
+    write_safetensors(folder / "model.safetensors", stored)
+    arch, again = load_config(folder)
+    assert again.hidden_size == config.hidden_size
+    loaded = load_checkpoint(folder, declared, torch.float32, "cpu", wrapped=True)
+    assert set(loaded) == set(tensors) and all(torch.equal(loaded[k], tensors[k]) for k in tensors)
+    with pytest.raises(WeightError, match="unexpected tensors"):                 # read as a plain folder nothing fits
+        load_checkpoint(folder, declared, torch.float32, "cpu")
+    del stored["language_model.model.norm.weight"]
+    write_safetensors(folder / "model.safetensors", stored)
+    with pytest.raises(WeightError, match=r"missing tensors \(1\): model.norm.weight"):
+        load_checkpoint(folder, declared, torch.float32, "cpu", wrapped=True)
+    with pytest.raises(WeightError, match="both stand for"):
+        decoder_names(["language_model.model.norm.weight", "model.language_model.norm.weight"])

@@ -19,6 +19,7 @@ from typing import Sequence
 import torch
 
 from .cache.cache import BLOCK_TOKENS
+from .config.base import read_config_json
 from .config.registry import load_config
 from .engine.engine import Engine
 from .engine.generate import EngineBackend, GenerationStats, run_generation
@@ -118,7 +119,8 @@ def load_model(path: str | Path, dtype="bf16", device="cuda") -> Runtime:
     device = require_cuda(device)
     arch, config = load_config(folder)
     model = DecoderModel(arch.describe(config), torch_dtype, device)
-    model.bind(load_checkpoint(folder, model.weight_declarations(), torch_dtype, device))
+    wrapped = isinstance(read_config_json(folder).get("text_config"), dict)    # a multimodal wrapper's folder
+    model.bind(load_checkpoint(folder, model.weight_declarations(), torch_dtype, device, wrapped))
     return Runtime(folder, arch, config, model)
 
 

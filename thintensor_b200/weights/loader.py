@@ -8,6 +8,13 @@ src/convert_hf.rs:1907-1913, ``layer N missing roles`` thinruntime/execution_pla
 shape and byte checks thinruntime/torch_loader.py:99-113) and only warns about extra
 tensors (src/convert_hf.rs:1670-1723).
 
+A checkpoint of a multimodal wrapper (config.json keeps the decoder's numbers under
+``text_config``) stores the decoder as ``model.language_model.*`` or ``language_model.*``;
+those names are read without the prefix and everything outside it (the other towers)
+is left alone, as the reference's converter does (src/convert_hf.rs:613-675, Python
+mirror thinruntime/model_arch.py:595-655).  Its renumbering of layers around
+cross-attention layers belongs to another architecture and is not done here.
+
 dtype rule: a bfloat16 engine keeps bfloat16 tensors as they are, narrows float16 to
 bfloat16 and leaves a tensor that the checkpoint stores in 32-bit floating point in
 32 bits; a float32 engine widens every floating tensor to float32.  Integer tables
@@ -26,6 +33,24 @@ from .safetensors_io import Checkpoint, WeightError
 # stored by some exporters, never used: the rotary tables are recomputed
 # (the reference lists it as allowed-missing at thinruntime/hf_loader.py:20-25)
 IGNORED_PATTERNS = ("*.rotary_emb.inv_freq",)
+
+
+WRAPPER_PREFIXES = ("model.language_model.", "language_model.")
+
+
+def decoder_names(stored: list[str]) -> dict[str, str]:
+    """Decoder name -> stored name for a wrapper's checkpoint: the prefix goes, ``model.`` is put
+    in front of what is not the head and lacks it, tensors outside the prefix are not listed."""
+    out: dict[str, str] = {}
+    for name in stored:
+        suffix = next((name[len(prefix):] for prefix in WRAPPER_PREFIXES if name.startswith(prefix)), None)
+        if suffix is None:
+            continue
+        plain = suffix if suffix == "lm_head.weight" or suffix.startswith("lm_head.") or suffix.startswith("model.") else "model." + suffix
+        if plain in out:
+            raise WeightError(f"tensors {out[plain]!r} and {name!r} both stand for {plain!r}")
+        out[plain] = name
+    return out
 
 
 def compare(declared: dict[str, WeightDecl], stored: dict[str, tuple[int, ...]]) -> tuple[list[str], list[str], list[str]]:
@@ -78,12 +103,14 @@ def target_dtype(stored: torch.dtype, engine: torch.dtype) -> torch.dtype:
 
 
 def load_checkpoint(folder: str | Path, declared: dict[str, WeightDecl], engine_dtype: torch.dtype,
-                    device: torch.device | str) -> dict[str, torch.Tensor]:
+                    device: torch.device | str, wrapped: bool = False) -> dict[str, torch.Tensor]:
     """name -> device tensor for every declared tensor the checkpoint (or its alias)
-    provides.  An aliased tensor is returned once, under its source's name."""
+    provides.  An aliased tensor is returned once, under its source's name.  ``wrapped``: the
+    folder is a multimodal wrapper's, whose decoder tensors carry a prefix."""
     checkpoint = Checkpoint(folder)
     try:
-        stored = {name: entry.shape for name, entry in checkpoint.entries.items()}
+        stored_as = decoder_names(list(checkpoint.entries)) if wrapped else {name: name for name in checkpoint.entries}
+        stored = {name: checkpoint.entries[real].shape for name, real in stored_as.items()}
         check(declared, stored, str(folder))
         out: dict[str, torch.Tensor] = {}
         for name, decl in declared.items():
@@ -92,7 +119,7 @@ def load_checkpoint(folder: str | Path, declared: dict[str, WeightDecl], engine_
                 source = decl.alias_of
             if source not in stored or source in out:
                 continue
-            host = checkpoint.tensor(source)
+            host = checkpoint.tensor(stored_as[source])
             out[source] = host.to(device=device, dtype=target_dtype(host.dtype, engine_dtype)).contiguous()
         return out
     finally:
