@@ -67,8 +67,15 @@ TINY = {
         "intermediate_size": 160, "vocab_size": 257, "rope_theta": 10000.0, "rms_norm_eps": 1e-6,
         "max_position_embeddings": 4096, "tie_word_embeddings": False,
     },
+    # the options no checkpoint of the family switches on: biases on every projection; one key/value head per query head
+    "f": {
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+        "num_hidden_layers": 2, "hidden_size": 80, "num_attention_heads": 5, "num_key_value_heads": 5, "head_dim": 16,
+        "intermediate_size": 112, "vocab_size": 199, "rope_theta": 20000.0, "rms_norm_eps": 2e-5,
+        "attention_bias": True, "mlp_bias": True, "max_position_embeddings": 1024, "tie_word_embeddings": True,
+    },
 }
-SEEDS = {"a": 0, "b": 2, "c": 5, "d": 7, "e": 8}
+SEEDS = {"a": 0, "b": 2, "c": 5, "d": 7, "e": 8, "f": 9}
 
 
 def write_tiny_model(folder: Path, name: str, stored: str = "float32", sharpen: float = 8.0) -> Path:
@@ -89,6 +96,8 @@ def write_tiny_model(folder: Path, name: str, stored: str = "float32", sharpen: 
             tensors[key] = tensors[key] * sharpen
         elif key.endswith("embed_tokens.weight") or key.endswith("lm_head.weight"):
             tensors[key] = tensors[key] * 20.0          # hidden states and logits of order one
+        elif key.endswith(".bias"):
+            tensors[key] = tensors[key] * 10.0          # a bias that is dropped or put on the wrong rows shows
     tensors = {k: v.to(STORED_DTYPES[stored]) if v.is_floating_point() else v for k, v in tensors.items()}
     folder.mkdir(parents=True, exist_ok=True)
     raw = dict(TINY[name])

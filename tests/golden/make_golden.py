@@ -1,11 +1,11 @@
 """Make tests/golden/reference_logits.npz: logits of random-unknown-username/Thintensor's
-OWN runtime, on the CPU, for two tiny random Llama models.
+OWN runtime, on the CPU, for three tiny random Llama models.
 
 Run once, by hand, from the repository root, with the reference checkout on the path:
 
     PYTHONPATH=/path/to/Thintensor python tests/golden/make_golden.py
 
-What it does.  For each tiny configuration (the two of tests/conftest.py) it draws
+What it does.  For each tiny configuration (tiny A, B and F of tests/conftest.py) it draws
 weights from a seeded CPU generator (function ``golden_weights`` below, which
 tests/test_plain.py imports so that the oracle gets the very same numbers), writes them
 as a float32 ``.thin`` archive in a temporary folder (the archive layout is read off
@@ -40,8 +40,11 @@ CONFIGS = {
           "theta": 500000.0, "eps": 1e-6, "tied": False, "max_pos": 512, "seed": 2,
           "scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
                       "original_max_position_embeddings": 64}},
+    # biases on every projection (the reference adds them where the tensors exist), one key/value head per query head
+    "f": {"layers": 2, "hidden": 80, "heads": 5, "kv_heads": 5, "head_dim": 16, "inter": 112, "vocab": 199,
+          "theta": 20000.0, "eps": 2e-5, "tied": True, "scaling": None, "max_pos": 1024, "seed": 9, "bias": True},
 }
-PROMPTS = {"a": [(5, 11), (9, 12), (2, 13)], "b": [(17, 21), (1, 22), (40, 23), (70, 24)]}   # (length, seed)
+PROMPTS = {"a": [(5, 11), (9, 12), (2, 13)], "b": [(17, 21), (1, 22), (40, 23), (70, 24)], "f": [(6, 31), (23, 32)]}   # (length, seed)
 
 
 def prompt_tokens(vocab: int, length: int, seed: int) -> list[int]:
@@ -51,7 +54,8 @@ def prompt_tokens(vocab: int, length: int, seed: int) -> list[int]:
 def golden_weights(c: dict) -> dict[str, torch.Tensor]:
     """float32 weights by checkpoint name: matrices N(0, 0.02) (queries and keys times 8,
     tables times 20, so that attention is peaked and logits are of order one), norm
-    weights 1 + N(0, 0.1)."""
+    weights 1 + N(0, 0.1); with ``bias`` every projection also gets a bias N(0, 0.2), drawn
+    right after its matrix."""
     g = torch.Generator().manual_seed(c["seed"])
 
     def normal(*shape, scale=0.02):
@@ -59,17 +63,23 @@ def golden_weights(c: dict) -> dict[str, torch.Tensor]:
 
     q, kv = c["heads"] * c["head_dim"], c["kv_heads"] * c["head_dim"]
     w = {"model.embed_tokens.weight": normal(c["vocab"], c["hidden"], scale=0.4)}
+
+    def projection(name, rows, cols, scale=0.02):
+        w[name + ".weight"] = normal(rows, cols, scale=scale)
+        if c.get("bias"):
+            w[name + ".bias"] = normal(rows, scale=0.2)
+
     for layer in range(c["layers"]):
         p = f"model.layers.{layer}."
         w[p + "input_layernorm.weight"] = 1.0 + normal(c["hidden"], scale=0.1)
-        w[p + "self_attn.q_proj.weight"] = normal(q, c["hidden"], scale=0.16)
-        w[p + "self_attn.k_proj.weight"] = normal(kv, c["hidden"], scale=0.16)
-        w[p + "self_attn.v_proj.weight"] = normal(kv, c["hidden"])
-        w[p + "self_attn.o_proj.weight"] = normal(c["hidden"], q)
+        projection(p + "self_attn.q_proj", q, c["hidden"], 0.16)
+        projection(p + "self_attn.k_proj", kv, c["hidden"], 0.16)
+        projection(p + "self_attn.v_proj", kv, c["hidden"])
+        projection(p + "self_attn.o_proj", c["hidden"], q)
         w[p + "post_attention_layernorm.weight"] = 1.0 + normal(c["hidden"], scale=0.1)
-        w[p + "mlp.gate_proj.weight"] = normal(c["inter"], c["hidden"])
-        w[p + "mlp.up_proj.weight"] = normal(c["inter"], c["hidden"])
-        w[p + "mlp.down_proj.weight"] = normal(c["hidden"], c["inter"])
+        projection(p + "mlp.gate_proj", c["inter"], c["hidden"])
+        projection(p + "mlp.up_proj", c["inter"], c["hidden"])
+        projection(p + "mlp.down_proj", c["hidden"], c["inter"])
     w["model.norm.weight"] = 1.0 + normal(c["hidden"], scale=0.1)
     if not c["tied"]:
         w["lm_head.weight"] = normal(c["vocab"], c["hidden"], scale=0.4)
@@ -84,6 +94,8 @@ def write_thin(path: Path, c: dict, weights: dict[str, torch.Tensor]) -> None:
         "rope_theta": c["theta"], "tie_word_embeddings": c["tied"], "activation": "silu",
         "max_position_embeddings": c["max_pos"],
     }
+    if c.get("bias"):
+        model.update({"attention_bias": True, "mlp_bias": True})
     if c["scaling"]:
         model.update({"rope_variant": "llama3", "rope_scaling": c["scaling"], "rope_parameters": dict(c["scaling"], rope_theta=c["theta"]),
                       "original_max_position_embeddings": c["scaling"]["original_max_position_embeddings"]})

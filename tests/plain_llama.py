@@ -226,11 +226,16 @@ def attention_block(x, w: dict, prefix: str, cfg: dict, positions, inv_freq, win
 
 def swiglu(x, w: dict, prefix: str) -> torch.Tensor:
     """down(silu(gate(x)) * up(x)), silu(g) = g / (1 + exp(-g))
-    (thinruntime/gpu_runtime.py:10286-10366, activation at :10351)."""
-    gate = x @ w[prefix + "gate_proj.weight"].T
-    up = x @ w[prefix + "up_proj.weight"].T
+    (thinruntime/gpu_runtime.py:10286-10366, activation at :10351), each projection with its
+    bias where the checkpoint stores one (:10312-10319 gate and up, :10361-10366 down)."""
+    def proj(name, y):
+        out = y @ w[prefix + name + ".weight"].T
+        bias = w.get(prefix + name + ".bias")
+        return out if bias is None else out + bias
+
+    gate, up = proj("gate_proj", x), proj("up_proj", x)
     act = gate / (1.0 + torch.exp(-gate)) * up
-    return act @ w[prefix + "down_proj.weight"].T
+    return proj("down_proj", act)
 
 
 def decoder_layer(h, w: dict, layer: int, cfg: dict, positions, inv_freq) -> torch.Tensor:

@@ -12,7 +12,7 @@ from conftest import TINY, assert_close, oracle_logits, token_ids
 pytestmark = pytest.mark.gpu
 
 DTYPES = ["float32", "bfloat16"]
-NAMES = ["a", "b", "c", "d", "e"]
+NAMES = ["a", "b", "c", "d", "e", "f"]
 
 
 def load(folder, dtype):

@@ -24,7 +24,7 @@ def golden_config(c: dict) -> dict:
             "tied": c["tied"]}
 
 
-@pytest.mark.parametrize("name", ["a", "b"])
+@pytest.mark.parametrize("name", ["a", "b", "f"])
 def test_plain_matches_reference_runtime(name):
     """Same weights, same tokens: the reference's CPU runtime (token by token through its
     cache) and the plain implementation (whole sequence, no cache) give the same logits."""

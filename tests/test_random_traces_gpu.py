@@ -30,7 +30,7 @@ def random_batches(rng: random.Random, n_batches: int):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name,seed", [("a", 1), ("b", 2), ("c", 3), ("b", 4), ("d", 5), ("e", 6), ("d", 7)])
+@pytest.mark.parametrize("name,seed", [("a", 1), ("b", 2), ("c", 3), ("b", 4), ("d", 5), ("e", 6), ("d", 7), ("f", 8)])
 def test_random_traces(model_folders, name, seed, dtype):
     import thintensor_b200
     from thintensor_b200.engine.engine import Entry
