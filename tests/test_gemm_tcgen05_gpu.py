@@ -66,6 +66,37 @@ def test_tokens_on_m_persistent_sliced(tokens, features, k, splits):
     run(tokens, features, k, splits, with_bias=(k % 3 != 0), seed=11)
 
 
+@pytest.mark.parametrize("tokens,features,k", [
+    (300, 2100, 320),            # persistent kernel, tiles hang over both edges, rows of 2100 floats (vector loads)
+    (1500, 2000, 1000),          # persistent kernel, several tiles per CTA
+    (700, 1001, 136),            # rows that are no multiple of four floats: element-wise loads and stores
+    (2048, 2048, 2048),          # CTA pairs
+    (2500, 530, 8192),           # CTA pairs, ragged
+])
+def test_product_added_into_its_output(tokens, features, k):
+    """The accumulate form: out += x @ w.T (+ bias), every tile read and written once by its epilogue."""
+    from thintensor_b200.kernels import api
+
+    assert api.gemm_tcgen05_accumulates(tokens, features, k)
+    x, w = randn(tokens, k, seed=21), randn(features, k, seed=22)
+    bias = torch.randn(features, device=DEV) if k % 3 == 0 else None
+    before = torch.randn(tokens, features, device=DEV) * 3.0
+    out = before.clone().unsqueeze(0)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    api.gemm_tcgen05(x, w, bias, out, status, accumulate=True)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    plain = torch.empty(1, tokens, features, dtype=torch.float32, device=DEV)
+    api.gemm_tcgen05(x, w, bias, plain, status)
+    # the same accumulators plus the old value, in float32: bit for bit the sum of the two
+    assert torch.equal(out[0], before + plain[0])
+    want = before.double() + x.double() @ w.double().T + (bias.double() if bias is not None else 0)
+    torch.testing.assert_close(out[0].double(), want, rtol=1e-4, atol=1e-4 * k ** 0.5)
+    assert not api.gemm_tcgen05_accumulates(64, features, k) and not api.gemm_tcgen05_accumulates(512, 2048, 2048)   # few tokens; sliced k
+    with pytest.raises(api.KernelError):
+        api.gemm_tcgen05(x[:64], w, None, out[:, :64], status, accumulate=True)
+
+
 def test_split_policy_and_refusals():
     from thintensor_b200.kernels import api
 

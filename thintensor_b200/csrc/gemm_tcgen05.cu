@@ -72,6 +72,7 @@ struct Args {
     int tokens, features, k;
     int k_blocks_per_split;
     int up_row_offset;       // SWIGLU: row of w where the up projection starts (= features of the output)
+    int accumulate;          // persistent and pair kernels, plain form: out += product instead of out = product
     unsigned* status;
 };
 
@@ -291,6 +292,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 }
 
 
+// An epilogue thread asks for its row of the output tile into the L2 while the products still run
+// (accumulate form: the row is read before it is written).
+__device__ __forceinline__ void prefetch_output_row(int token, int f_base, const Args& args) {
+    if (!args.accumulate || token >= args.tokens) return;
+    const float* row = (const float*)args.out + (size_t)token * args.ld_out;
+    for (int c = 0; c < 256 && f_base + c < args.features; c += 32)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(row + f_base + c));
+}
+
 // What an epilogue thread does with its row of a 128 x 256 accumulator (lane_addr: the row's
 // first column): plain form, 256 features from f_base as float32 (+ bias); SwiGLU form, columns
 // 0..127 the gate and 128..255 the up projection of 128 features from f_base, stored as bfloat16.
@@ -323,12 +333,25 @@ __device__ __forceinline__ void store_accumulator(uint32_t lane_addr, int token,
         const bool vec = (args.ld_out & 3) == 0 && (((uintptr_t)args.out) & 15) == 0;
         for (int c = 0; c < 256; c += 32) {
             float v[32];
+            const int f0 = f_base + c;
+            float4 old[8];
+            const bool add_vec = args.accumulate && token < args.tokens && vec && f0 + 32 <= args.features;
+            if (add_vec) {                                  // on their way while the accumulator is read
+#pragma unroll
+                for (int e = 0; e < 8; ++e) old[e] = *reinterpret_cast<const float4*>(out + f0 + 4 * e);
+            }
             tmem_load32(lane_addr + c, v);
             if (token < args.tokens) {
-                const int f0 = f_base + c;
                 if (args.bias) {
 #pragma unroll
                     for (int e = 0; e < 32; ++e) if (f0 + e < args.features) v[e] += args.bias[f0 + e];
+                }
+                if (add_vec) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) { v[4 * e] += old[e].x; v[4 * e + 1] += old[e].y; v[4 * e + 2] += old[e].z; v[4 * e + 3] += old[e].w; }
+                } else if (args.accumulate) {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) if (f0 + e < args.features) v[e] += out[f0 + e];
                 }
                 if (vec && f0 + 32 <= args.features) {
 #pragma unroll
@@ -471,6 +494,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
             const int buf = j & 1;
             const int item = (int)blockIdx.x + j * (int)gridDim.x, tile = item % tiles_total, slice = item / tiles_total;
             const int token = (tile % tiles_m) * BM + row, f_base = (tile / tiles_m) * TILE_N;
+            if (!dual) prefetch_output_row(token, f_base, args);
             if (!mbar_wait(smem_u32(&acc_full[buf]), (uint32_t)((j >> 1) & 1))) {
                 if (lane == 0) atomicOr(args.status, TT_STATUS_WAIT_EXPIRED);
                 break;
@@ -611,6 +635,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             const int buf = j & 1;
             const int tile = pair + j * n_pairs;
             const int token = (tile % tiles_m) * 2 * BM + rank * BM + row, f_base = (tile / tiles_m) * TILE_N;
+            if (!dual) prefetch_output_row(token, f_base, args);
             if (!mbar_wait(smem_u32(&acc_full[buf]), (uint32_t)((j >> 1) & 1))) {
                 if (lane == 0) atomicOr(args.status, TT_STATUS_WAIT_EXPIRED);
                 break;
@@ -714,7 +739,9 @@ extern "C" int tt_gemm_tcgen05_max_skinny_tokens() { return 128; }
 
 // Operands must be 16-byte aligned with row strides that are multiples of 8 elements.
 // form: 0 float32 partial sums out[splits][tokens][features]; 1 SwiGLU, out bfloat16
-// [tokens][features] with w holding `features` gate rows then `features` up rows.
+// [tokens][features] with w holding `features` gate rows then `features` up rows; 2 the product
+// (+ bias) is added to float32 out[tokens][features]: prompts that run the persistent or the
+// CTA-pair kernel with one k-slice only (every tile has one writer), anything else is refused.
 // Returns a cudaError_t value, or -1 if the driver's tensor-map encoder is unavailable
 // or refused the operands.
 extern "C" int tt_gemm_tcgen05(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* out,
@@ -730,8 +757,10 @@ extern "C" int tt_gemm_tcgen05(const void* x, long long ldx, const void* w, long
     args.tokens = tokens; args.features = features; args.k = k;
     args.k_blocks_per_split = (k_blocks + splits - 1) / splits;
     args.up_row_offset = features; args.status = status;
+    args.accumulate = form == 2 ? 1 : 0;
     CUtensorMap map_a, map_b;
     const int tiles_m = (tokens + BM - 1) / BM;
+    if (form == 2 && !(tokens > 128 && tiles_m * ((features + 255) / 256) >= 8 && splits == 1)) return (int)cudaErrorInvalidValue;
     if (form == 1) {
         if (splits != 1 || bias) return (int)cudaErrorInvalidValue;
         if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, 2LL * features, k, ldw, 128)) return -1;

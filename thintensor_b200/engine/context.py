@@ -68,6 +68,7 @@ class StepContext:
     host_new: list[int] = field(default_factory=list)       # tokens each sequence brings
     host_before: list[int] = field(default_factory=list)    # lengths before the step (unknown inside a replayed graph)
     logits_out: torch.Tensor | None = None                  # float32 [wanted rows, vocab] the head may write directly
+    residual: torch.Tensor | None = None                    # float32 [n_tokens, hidden]: set by an arrangement whose parts may add into the stream themselves
 
     def scratch(self, name: str, shape: tuple[int, ...], dtype: torch.dtype | None = None) -> torch.Tensor:
         return self.workspace.get(name, shape, dtype or self.act_dtype)

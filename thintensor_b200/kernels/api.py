@@ -367,14 +367,38 @@ def gemm_tcgen05_splits(tokens: int, features: int, k: int) -> int:
     return max(1, min(2 * SM_COUNT // tiles, k_blocks // 4, 16))
 
 
+def gemm_tcgen05_accumulates(tokens: int, features: int, k: int) -> bool:
+    """Whether the product of these sizes can be added into its output by the kernel itself: prompts
+    on the persistent or CTA-pair kernel whose k is not cut into slices, so that every output tile
+    has one writer."""
+    return (tokens > SKINNY_TOKENS and -(-tokens // 128) * -(-features // 256) >= PERSISTENT_TILES
+            and gemm_tcgen05_splits(tokens, features, k) == 1)
+
+
+def gemm_tcgen05_accumulate_pays(tokens: int, features: int, k: int) -> bool:
+    """Whether adding into the output inside the kernel is also the faster way: only where every CTA
+    (or CTA pair) has at least two tiles, so that a tile's epilogue, which now waits for the old
+    values, runs under the next tile's products.  Measured on a B200 with the 1B shape's output and
+    down projections: 2,048 tokens (one tile per CTA pair) 5.19 -> 5.27 ms per prefill, 8,192 tokens
+    (3.5 tiles per pair) 24.45 -> 24.13 ms."""
+    if not gemm_tcgen05_accumulates(tokens, features, k):
+        return False
+    if tokens >= PAIR_TOKENS:
+        return -(-tokens // 256) * -(-features // 256) >= 2 * (SM_COUNT // 2)
+    return -(-tokens // 128) * -(-features // 256) >= 2 * SM_COUNT
+
+
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor, status: torch.Tensor,
-                 operands_checked: bool = False) -> None:
+                 operands_checked: bool = False, accumulate: bool = False) -> None:
     """out[s] = x @ w[:, k-slice s].T on the tensor cores; bfloat16 operands, float32
     ``out`` [splits, tokens, features]; bias (float32) goes into slice 0.  ``operands_checked``: the
-    caller has already called :func:`gemm_tcgen05_usable` on these operands."""
+    caller has already called :func:`gemm_tcgen05_usable` on these operands.  ``accumulate``: the
+    product is added to ``out`` [1, tokens, features] (only where :func:`gemm_tcgen05_accumulates`)."""
     _need(out, torch.float32, "gemm output")
     tokens, k = x.shape
     features = w.shape[0]
+    if accumulate and (out.shape[0] != 1 or not gemm_tcgen05_accumulates(tokens, features, k)):
+        raise KernelError(f"tcgen05 gemm cannot add a product of {tokens} x {features} x {k} into its output")
     if not (operands_checked or gemm_tcgen05_usable(x, w)) or w.shape[1] != k or tuple(out.shape[1:]) != (tokens, features):
         raise KernelError(f"tcgen05 gemm cannot take x {tuple(x.shape)} / w {tuple(w.shape)} / out {tuple(out.shape)} (k and strides must be multiples of 8)")
     if out.shape[0] > -(-k // 64):
@@ -384,7 +408,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, ou
     fn = _fn("gemm_tcgen05", "tt_gemm_tcgen05", [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_longlong,
                                                  c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
     _check(fn(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(bias), _ptr(out), out.stride(1), out.stride(0), tokens, features, k,
-              out.shape[0], 0, _ptr(status), _stream()), "gemm_tcgen05")
+              out.shape[0], 2 if accumulate else 0, _ptr(status), _stream()), "gemm_tcgen05")
 
 
 def gemm_tcgen05_swiglu(x: torch.Tensor, w: torch.Tensor, act: torch.Tensor, status: torch.Tensor) -> None:

@@ -4,7 +4,9 @@
 thinruntime/gpu_runtime.py:10114-10390.  The residual stream is float32; a part's
 output is handed on as a :class:`Delta` and added by the next norm's kernel, so the
 layer's second addition is done by the following layer's first norm (or by the final
-norm).
+norm).  For long prompts the output projections add their product into the stream themselves
+(their tensor-core kernel's epilogue reads and writes the tile once, which spares the
+norm kernel a read of the product and a write of the stream); the delta is then empty.
 """
 from __future__ import annotations
 
@@ -20,6 +22,9 @@ class PreNorm(Arrangement):
 
     def run(self, ctx, residual, pending: Delta | None, cache, state) -> Delta:
         hidden = residual.shape[-1]
+        # Between a part's output and the norm that follows nothing else reads the stream, so a part
+        # may add its output into it directly instead of handing it on.
+        ctx.residual = residual
         normed = ctx.scratch("block.normed", (ctx.n_tokens, hidden))
         self.parts["mixer_norm"].forward(ctx, residual, pending, normed)
         mixed = self.parts["mixer"].forward(ctx, normed, cache, state)

@@ -94,13 +94,13 @@ class CausalAttention(Mixer):
             api.attention_decode_rope(projection, position.inv_freq, position.rotary_dim, position.attention_scaling, cache.writes,
                                       cache.k_pool, cache.v_pool, table, ctx.len_before, ctx.sequences, self.heads, self.kv_heads,
                                       self.head_dim, self.scale, self.window or 0, splits, mixed, part_acc, part_ml, ctx.status)
-            return Delta(self.out(ctx, mixed, "attention.out"))
+            return self.out.delta(ctx, mixed, "attention.out")
         q = ctx.scratch("attention.q", (ctx.n_tokens, q_cols))
         api.rope_append(projection, self.position.inv_freq, self.position.rotary_dim, self.position.attention_scaling, q,
                         cache.k_pool if cache.writes else None, cache.v_pool if cache.writes else None, table, ctx.cu,
                         ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads, self.kv_heads, self.head_dim, ctx.status)
         self.attend(ctx, q, cache, table, mixed)
-        return Delta(self.out(ctx, mixed, "attention.out"))
+        return self.out.delta(ctx, mixed, "attention.out")
 
     def decode_slices(self, ctx) -> int:
         """Slices of the keys for the tensor-core decode kernel, which runs one CTA per (sequence, kv

@@ -66,13 +66,14 @@ class StateNeed:
 class Delta:
     """What a mixer or feed-forward adds to the residual stream: float32
     ``[splits, tokens, hidden]``; the sum over ``splits`` is the value.  The norm that
-    follows does the sum and the addition."""
+    follows does the sum and the addition.  ``tensor`` is None when the part has already
+    added its result into the stream itself (``ctx.residual``, where the arrangement offers it)."""
 
-    tensor: torch.Tensor
+    tensor: torch.Tensor | None
 
     @property
     def splits(self) -> int:
-        return self.tensor.shape[0]
+        return 0 if self.tensor is None else self.tensor.shape[0]
 
 
 class Part:

@@ -32,4 +32,4 @@ class SwiGLU(FeedForward):
 
     def forward(self, ctx, x) -> Delta:
         act = self.gate_up(ctx, x, "ffn.gate_up")
-        return Delta(self.down(ctx, act, "ffn.down"))
+        return self.down.delta(ctx, act, "ffn.down")

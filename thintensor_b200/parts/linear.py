@@ -16,6 +16,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import api
+from .base import Delta
 
 
 class Linear:
@@ -50,6 +51,18 @@ class Linear:
         out = into.unsqueeze(0) if into is not None else ctx.scratch(name, (1, tokens, self.out_features), torch.float32)
         api.gemm_simt(x, self.weight, self.bias, out)
         return out
+
+
+    def delta(self, ctx, x: torch.Tensor, name: str) -> Delta:
+        """The product as an addition to the residual stream.  Where the step offers the stream
+        (``ctx.residual``) and the tensor-core kernel can add into its output at no cost of its own
+        (long prompts), the product is added there at once and the delta is empty; otherwise the delta holds the product's k-slices."""
+        residual = getattr(ctx, "residual", None)
+        if (residual is not None and residual.shape == (x.shape[0], self.out_features) and api.gemm_tcgen05_usable(x, self.weight)
+                and api.gemm_tcgen05_accumulate_pays(x.shape[0], self.out_features, self.in_features)):
+            api.gemm_tcgen05(x, self.weight, self.bias, residual.unsqueeze(0), ctx.status, operands_checked=True, accumulate=True)
+            return Delta(None)
+        return Delta(self(ctx, x, name))
 
 
 class GatedLinear:

@@ -28,4 +28,4 @@ class RMSNorm(Norm):
         self.weight = tensors["weight"].to(torch.float32).contiguous()
 
     def forward(self, ctx, residual, delta: Delta | None, out, rows=None) -> None:
-        api.add_rmsnorm(residual, None if delta is None else delta.tensor, self.weight, self.eps, out, rows, self.weight_offset)
+        api.add_rmsnorm(residual, None if delta is None else delta.tensor, self.weight, self.eps, out, rows, self.weight_offset)   # an empty delta is already in the stream
