@@ -128,7 +128,10 @@ def run_generation(backend: Backend, prompts: Sequence[Sequence[int]], max_new_t
         try:
             _run_batch(backend, batch, prompts, totals, max_new_tokens, stop, results, stats)
         except BaseException:
-            backend.abandon()
+            try:
+                backend.abandon()
+            except Exception:           # the first error is the one to report
+                pass
             raise
     stats.new_tokens = sum(len(r) for r in results)
     return results
