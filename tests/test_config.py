@@ -112,3 +112,25 @@ def test_named_shapes_are_whole_configurations():
         assert arch.name == "LlamaForCausalLM" and config.hidden_size == raw["hidden_size"], name
     one_b = load_config(shapes["llama-3.2-1b"])[1]
     assert (one_b.num_hidden_layers, one_b.num_attention_heads, one_b.num_key_value_heads, one_b.head_dim) == (16, 32, 8, 64)
+
+
+def test_stop_ids_come_from_both_files(tmp_path):
+    """End-of-sequence ids: config.json's (int or list) and generation_config.json's, without
+    duplicates; a model that was not read from a folder looks at no file."""
+    from thintensor_b200.runtime import stop_ids_of
+
+    config = LlamaConfig.from_dict(dict(TINY["b"]))                      # eos_token_id [3, 11]
+    assert stop_ids_of(None, config) == (3, 11)
+    assert stop_ids_of(tmp_path, config) == (3, 11)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": [11, 17]}))
+    assert stop_ids_of(tmp_path, config) == (3, 11, 17)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": 5}))
+    assert stop_ids_of(tmp_path, LlamaConfig.from_dict(dict(TINY["a"]))) == (7, 5)
+
+
+def test_run_command_takes_random_weights():
+    from thintensor_b200.cli import build_parser
+
+    args = build_parser().parse_args(["run", "folder", "--prompt-token-ids", "1,2", "--random-weights", "3", "--steps", "4"])
+    assert args.random_weights == 3 and args.max_new_tokens == 4 and args.prompt_token_ids == ["1,2"]
+    assert build_parser().parse_args(["run", "folder"]).random_weights is None

@@ -43,6 +43,7 @@ def build_parser() -> argparse.ArgumentParser:
     run.add_argument("--tokenizer", help="Tokenizer directory")
     run.add_argument("--batch-size", type=int, default=8, help="Most sequences decoded together")
     run.add_argument("--ignore-eos", action="store_true", help="Always generate --max-new-tokens tokens")
+    run.add_argument("--random-weights", type=int, metavar="SEED", help="Read only config.json from the folder and draw the weights from this seed")
     run.add_argument("--json", action="store_true", help="JSON output")
 
     bench = sub.add_parser("bench", help="Benchmark prefill and decode", formatter_class=argparse.ArgumentDefaultsHelpFormatter)
@@ -114,7 +115,12 @@ def cmd_run(args) -> int:
     else:
         tokenizer = load_tokenizer(Path(args.model), args.tokenizer)
         prompts = [tokenizer(args.prompt)["input_ids"]]
-    runtime = thintensor_b200.load_model(args.model, dtype=args.dtype, device=args.device)
+    if args.random_weights is not None:
+        from thintensor_b200.config.base import read_config_json
+
+        runtime = thintensor_b200.random_model(read_config_json(args.model), seed=args.random_weights, dtype=args.dtype, device=args.device)
+    else:
+        runtime = thintensor_b200.load_model(args.model, dtype=args.dtype, device=args.device)
     started = time.perf_counter()
     outputs = runtime.generate(
         prompts, max_new_tokens=args.max_new_tokens, temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,

@@ -51,12 +51,13 @@ def require_cuda(device) -> torch.device:
     return device
 
 
-def stop_ids_of(folder: Path, config) -> tuple[int, ...]:
+def stop_ids_of(folder: Path | None, config) -> tuple[int, ...]:
     """End-of-sequence ids from generation_config.json and config.json, int or list, as
-    the reference collects them (thinruntime/cli.py:4822-4888)."""
+    the reference collects them (thinruntime/cli.py:4822-4888).  ``folder`` is None for a
+    model that was not read from one."""
     ids = list(getattr(config, "eos_token_ids", ()))
-    extra = folder / "generation_config.json"
-    if extra.is_file():
+    extra = None if folder is None else folder / "generation_config.json"
+    if extra is not None and extra.is_file():
         eos = json.loads(extra.read_text(encoding="utf-8")).get("eos_token_id")
         if isinstance(eos, int):
             ids.append(eos)
@@ -68,7 +69,7 @@ def stop_ids_of(folder: Path, config) -> tuple[int, ...]:
 class Runtime:
     """A loaded model on one GPU."""
 
-    def __init__(self, folder: Path, arch, config, model: DecoderModel):
+    def __init__(self, folder: Path | None, arch, config, model: DecoderModel):
         self.folder = folder
         self.architecture = arch
         self.config = config
@@ -157,4 +158,4 @@ def random_model(config, seed: int = 0, dtype="bf16", device="cuda") -> Runtime:
         tensors[name] = value.to(torch_dtype)
         del noise, value
     model.bind(tensors)
-    return Runtime(Path("."), arch, config, model)
+    return Runtime(None, arch, config, model)
