@@ -20,9 +20,6 @@ limit, fewer of the 8 sequences are run and the line says how many.
 """
 from __future__ import annotations
 
-import hashlib
-import json
-import struct
 import sys
 import tempfile
 import time
@@ -32,72 +29,47 @@ HERE = Path(__file__).resolve().parent
 REF = HERE / "_ref"
 
 
-def write_thin(path: Path, shape: dict, seed: int) -> None:
+def write_random_archive(path: Path, shape: dict, seed: int) -> None:
     """A bfloat16 ``.thin`` archive of random weights (N(0, 0.02), norms 1 + N(0, 0.1))."""
     import torch
+
+    from thin_archive import llama_manifest_model, write_thin
 
     g = torch.Generator().manual_seed(seed)
     hidden, layers = shape["hidden_size"], shape["num_hidden_layers"]
     heads, kv_heads, head_dim = shape["num_attention_heads"], shape["num_key_value_heads"], shape["head_dim"]
     inter, vocab = shape["intermediate_size"], shape["vocab_size"]
-    specs = [("model.embed_tokens.weight", (vocab, hidden), "normal")]
+    specs = [("model.embed_tokens.weight", (vocab, hidden))]
     for layer in range(layers):
         p = f"model.layers.{layer}."
         specs += [
-            (p + "input_layernorm.weight", (hidden,), "norm"),
-            (p + "self_attn.q_proj.weight", (heads * head_dim, hidden), "normal"),
-            (p + "self_attn.k_proj.weight", (kv_heads * head_dim, hidden), "normal"),
-            (p + "self_attn.v_proj.weight", (kv_heads * head_dim, hidden), "normal"),
-            (p + "self_attn.o_proj.weight", (hidden, heads * head_dim), "normal"),
-            (p + "post_attention_layernorm.weight", (hidden,), "norm"),
-            (p + "mlp.gate_proj.weight", (inter, hidden), "normal"),
-            (p + "mlp.up_proj.weight", (inter, hidden), "normal"),
-            (p + "mlp.down_proj.weight", (hidden, inter), "normal"),
+            (p + "input_layernorm.weight", (hidden,)),
+            (p + "self_attn.q_proj.weight", (heads * head_dim, hidden)),
+            (p + "self_attn.k_proj.weight", (kv_heads * head_dim, hidden)),
+            (p + "self_attn.v_proj.weight", (kv_heads * head_dim, hidden)),
+            (p + "self_attn.o_proj.weight", (hidden, heads * head_dim)),
+            (p + "post_attention_layernorm.weight", (hidden,)),
+            (p + "mlp.gate_proj.weight", (inter, hidden)),
+            (p + "mlp.up_proj.weight", (inter, hidden)),
+            (p + "mlp.down_proj.weight", (hidden, inter)),
         ]
-    specs.append(("model.norm.weight", (hidden,), "norm"))
-    scaling = shape["rope_scaling"]
-    model = {
-        "model_type": "llama", "arch": "LlamaForCausalLM", "hidden_size": hidden, "layers": layers, "heads": heads,
-        "kv_heads": kv_heads, "head_dim": head_dim, "intermediate_size": inter, "vocab_size": vocab,
-        "rms_norm_eps": shape["rms_norm_eps"], "norm_eps": shape["rms_norm_eps"], "norm_kind": "rms_norm",
-        "rope_theta": shape["rope_theta"], "tie_word_embeddings": True, "activation": "silu",
-        "max_position_embeddings": shape["max_position_embeddings"], "rope_variant": "llama3", "rope_scaling": scaling,
-        "rope_parameters": dict(scaling, rope_theta=shape["rope_theta"]),
-        "original_max_position_embeddings": scaling["original_max_position_embeddings"],
-    }
-    pages = []
-    for name, dims, _ in specs:
-        count = 1
-        for d in dims:
-            count *= d
-        layer = int(name.split(".")[2]) if name.startswith("model.layers.") else None
-        pages.append({"id": name, "kind": "tensor", "layer": layer, "op": name.rsplit(".", 2)[-2], "dtype": "BF16",
-                      "shape": list(dims), "backend_layout": "row_major", "size": count * 2,
-                      "checksum": hashlib.sha256(name.encode()).hexdigest()})      # distinct per page: equal checksums would alias pages
-    manifest = json.dumps({"format": "thin", "version": 0, "model": model, "execution_tape": [], "pages": pages, "memory_plan": {}}).encode()
-    tail = struct.calcsize("<QQQI32s")
-    table_len = sum(2 + len(p["id"].encode()) + tail for p in pages)
-    table_off = 88 + len(manifest)
-    data_off = table_off + table_len
-    table, offset = b"", data_off
-    for page in pages:
-        ident = page["id"].encode()
-        table += struct.pack("<H", len(ident)) + ident + struct.pack("<QQQI32s", offset, page["size"], page["size"], 0, bytes(32))
-        offset += page["size"]
-    with path.open("wb") as out:
-        out.write(struct.pack("<8sIIQQQQQ32s", b"THINv0\0\0", 88, 0, 88, len(manifest), table_off, len(pages), data_off, bytes(32)))
-        out.write(manifest)
-        out.write(table)
-        for name, dims, kind in specs:
-            noise = torch.randn(dims, generator=g)
-            value = (1.0 + 0.1 * noise) if kind == "norm" else 0.02 * noise
-            out.write(value.to(torch.bfloat16).view(torch.int16).numpy().tobytes())
+    specs.append(("model.norm.weight", (hidden,)))
+    model = llama_manifest_model(hidden=hidden, layers=layers, heads=heads, kv_heads=kv_heads, head_dim=head_dim, inter=inter, vocab=vocab,
+                                 eps=shape["rms_norm_eps"], theta=shape["rope_theta"], tied=True,
+                                 max_pos=shape["max_position_embeddings"], scaling=shape["rope_scaling"])
+
+    def draw(name, dims):
+        noise = torch.randn(dims, generator=g)
+        return (1.0 + 0.1 * noise) if name.endswith("norm.weight") else 0.02 * noise
+
+    write_thin(path, model, specs, "BF16", draw)
 
 
 def run(shape: dict, metric: str, batch: int, prompt_len: int, context: int, steps: int, warmup: int, limit_s: float = 150.0) -> dict:
     if not (REF / "thinruntime").is_dir():
         return {"impl": "reference", "unavailable": f"the reference is not installed under {REF} (pip install --target baseline/_ref was not run here)"}
     sys.path.insert(0, str(REF))
+    sys.path.insert(0, str(HERE))
     import torch
     from thinruntime.gpu_runtime import PagedKVCache, ThinGpuCausalLMRuntime, ThinGpuWeights
 
@@ -105,12 +77,13 @@ def run(shape: dict, metric: str, batch: int, prompt_len: int, context: int, ste
     prompts = [torch.randint(0, shape["vocab_size"], (prompt_len,), generator=g).tolist() for _ in range(batch)]
     with tempfile.TemporaryDirectory() as folder:
         archive = Path(folder) / "model.thin"
-        write_thin(archive, shape, seed=0)
+        write_random_archive(archive, shape, seed=0)
         weights = ThinGpuWeights(archive, device="cuda", dtype=torch.bfloat16)
         cache = PagedKVCache(layers=shape["num_hidden_layers"], kv_heads=shape["num_key_value_heads"], head_dim=shape["head_dim"],
                              device=weights.device, dtype=torch.bfloat16, old_codec="bf16")
         runtime = ThinGpuCausalLMRuntime(weights, kv_cache=cache)
         decoded, decode_ms, prefill_s, sequences_run = 0, 0.0, 0.0, 0
+        e2e_decoded, e2e_s, e2e_d2h = 0, 0.0, 8
         started = time.perf_counter()
         for prompt in prompts:
             if sequences_run and (time.perf_counter() - started) * (sequences_run + 1) / sequences_run > limit_s:
@@ -139,6 +112,20 @@ def run(shape: dict, metric: str, batch: int, prompt_len: int, context: int, ste
             decode_ms += start.elapsed_time(stop)
             decoded += steps
             sequences_run += 1
+            # end to end, the way the reference's own `run` command decodes (thinruntime/cli.py:2826-2858):
+            # next_token_tensor -> synchronize -> .item() on the host -> forward_token(int)
+            e2e_steps = min(steps, context - position - 1)
+            clock = time.perf_counter()
+            for _ in range(e2e_steps):
+                token_tensor = runtime.next_token_tensor(hidden)
+                torch.cuda.synchronize()
+                token = int(token_tensor.item())
+                e2e_d2h = token_tensor.element_size()
+                hidden = runtime.forward_token(token, token_index=position)
+                position += 1
+            torch.cuda.synchronize()
+            e2e_s += time.perf_counter() - clock
+            e2e_decoded += e2e_steps
         weights.close()
     value = decoded / (decode_ms / 1e3)
     return {
@@ -148,4 +135,10 @@ def run(shape: dict, metric: str, batch: int, prompt_len: int, context: int, ste
         "config": {"model": "Llama-3.2-1B shape", "layers": shape["num_hidden_layers"], "global_batch": batch, "prompt_len": prompt_len,
                    "seq_len": context, "served": "one sequence at a time (the engine has no batching)", "sequences_run": sequences_run,
                    "prefill": "token by token", "prefill_tokens_per_s": round(prompt_len * sequences_run / prefill_s, 1)},
+        # the reference's own generation loop: one host read of the token per step, the id handed back as a Python int
+        "e2e": {"value": round(e2e_decoded / e2e_s, 1) if e2e_s > 0 else None, "unit": "tokens/s", "steps": e2e_decoded,
+                "h2d_bytes_per_step": 8, "d2h_bytes_per_step": e2e_d2h,
+                "how": "next_token_tensor, synchronize, .item(), forward_token(int) per token, as thinruntime/cli.py:2826-2858"},
+        # the engine serves one sequence at a time, so its value is also its rate at batch 1
+        "points": {"decode_b1": round(value, 1)},
     }

@@ -36,12 +36,11 @@ METRIC = "decode tok/s at batch 8 (Llama-3.2-1B bf16, 2,048-token prompts, conte
 
 
 def peaks() -> dict:
-    """Measured peaks if the driver wrote them, else the stated fallback."""
+    """Measured peaks if the driver wrote them next to this file, else the stated fallback."""
+    from thintensor_b200.benchmark import peaks as read_peaks
+
     file = ROOT / "MEASURED_PEAKS.json"
-    if file.is_file():
-        raw = json.loads(file.read_text())
-        return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]), "source": "measured"}
-    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    return read_peaks(file if file.is_file() else None)
 
 
 class ClockSampler:

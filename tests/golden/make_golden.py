@@ -20,9 +20,6 @@ the llama3 frequency scaling, which it calls as a black box.
 """
 from __future__ import annotations
 
-import hashlib
-import json
-import struct
 import sys
 import tempfile
 from pathlib import Path
@@ -87,40 +84,15 @@ def golden_weights(c: dict) -> dict[str, torch.Tensor]:
 
 
 def write_thin(path: Path, c: dict, weights: dict[str, torch.Tensor]) -> None:
-    model = {
-        "model_type": "llama", "arch": "LlamaForCausalLM", "hidden_size": c["hidden"], "layers": c["layers"],
-        "heads": c["heads"], "kv_heads": c["kv_heads"], "head_dim": c["head_dim"], "intermediate_size": c["inter"],
-        "vocab_size": c["vocab"], "rms_norm_eps": c["eps"], "norm_eps": c["eps"], "norm_kind": "rms_norm",
-        "rope_theta": c["theta"], "tie_word_embeddings": c["tied"], "activation": "silu",
-        "max_position_embeddings": c["max_pos"],
-    }
-    if c.get("bias"):
-        model.update({"attention_bias": True, "mlp_bias": True})
-    if c["scaling"]:
-        model.update({"rope_variant": "llama3", "rope_scaling": c["scaling"], "rope_parameters": dict(c["scaling"], rope_theta=c["theta"]),
-                      "original_max_position_embeddings": c["scaling"]["original_max_position_embeddings"]})
-    pages, blobs = [], []
-    for name, tensor in weights.items():
-        raw = tensor.to(torch.float32).contiguous().numpy().tobytes()
-        layer = int(name.split(".")[2]) if name.startswith("model.layers.") else None
-        pages.append({"id": name, "kind": "tensor", "layer": layer, "op": name.rsplit(".", 2)[-2], "dtype": "F32",
-                      "shape": list(tensor.shape), "backend_layout": "row_major", "size": len(raw),
-                      "checksum": hashlib.sha256(raw).hexdigest()})
-        blobs.append(raw)
-    manifest = json.dumps({"format": "thin", "version": 0, "model": model, "execution_tape": [], "pages": pages,
-                           "memory_plan": {}}).encode("utf-8")
-    table_len = sum(2 + len(p["id"].encode()) + struct.calcsize("<QQQI32s") for p in pages)
-    manifest_off = 88
-    table_off = manifest_off + len(manifest)
-    data_off = table_off + table_len
-    table = b""
-    offset = data_off
-    for page, raw in zip(pages, blobs):
-        ident = page["id"].encode()
-        table += struct.pack("<H", len(ident)) + ident + struct.pack("<QQQI32s", offset, len(raw), len(raw), 0, bytes(32))
-        offset += len(raw)
-    header = struct.pack("<8sIIQQQQQ32s", b"THINv0\0\0", 88, 0, manifest_off, len(manifest), table_off, len(pages), data_off, bytes(32))
-    path.write_bytes(header + manifest + table + b"".join(blobs))
+    """The weights as a float32 archive, through the one archive writer this repository has
+    (baseline/thin_archive.py, shared with the benchmark's reference arm)."""
+    sys.path.insert(0, str(HERE.parent.parent / "baseline"))
+    from thin_archive import llama_manifest_model, write_thin as write_archive
+
+    model = llama_manifest_model(hidden=c["hidden"], layers=c["layers"], heads=c["heads"], kv_heads=c["kv_heads"], head_dim=c["head_dim"],
+                                 inter=c["inter"], vocab=c["vocab"], eps=c["eps"], theta=c["theta"], tied=c["tied"], max_pos=c["max_pos"],
+                                 scaling=c["scaling"], bias=bool(c.get("bias")))
+    write_archive(path, model, [(name, tuple(t.shape)) for name, t in weights.items()], "F32", lambda name, shape: weights[name])
 
 
 def reference_logits(archive: Path, c: dict, tokens: list[int]) -> np.ndarray:

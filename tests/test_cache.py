@@ -94,6 +94,24 @@ def test_groups_have_storage_of_their_own():
         SequenceCache([None, KVNeed(1, 16)], [None, None], [None, 0], 4, 2, torch.float32, None)
 
 
+def test_a_reader_may_not_look_further_back_than_its_source_keeps():
+    """A run that reads another run's cache sees what that run's group keeps: blocks that have slid out
+    of the source's window are given back, so a reader without a window, or with a wider one, is refused;
+    a narrower window (or the same) is fine."""
+    windowed, full = KVNeed(2, 16, window=128), KVNeed(2, 16)
+    for reader in (full, KVNeed(2, 16, window=256)):
+        with pytest.raises(CacheError, match="keeps only the last 128 tokens"):
+            SequenceCache([windowed, reader], [None, None], [None, 0], 8, 2, torch.float32, None)
+    for reader in (windowed, KVNeed(2, 16, window=64)):
+        cache = SequenceCache([windowed, reader], [None, None], [None, 0], 8, 2, torch.float32, None)
+        assert cache.run_cache(1).group == cache.run_cache(0).group and not cache.run_cache(1).writes
+    cache = SequenceCache([full, windowed], [None, None], [None, 0], 8, 2, torch.float32, None)     # a window onto a full cache
+    slot = cache.alloc_slot()
+    cache.reserve(slot, 400)
+    cache.advance(slot, 400)
+    assert all(b >= 0 for b in cache.table_rows(0, [slot], 7)[0]), "the full source keeps every block"
+
+
 def test_sequences_come_and_go():
     cache = make_cache(num_blocks=8, max_slots=3)
     a, b = cache.alloc_slot(), cache.alloc_slot()

@@ -301,7 +301,7 @@ def test_attention_mma_decode_many_sequences(splits):
     part_ml = torch.full((n * heads * splits * 2,), float("nan"), dtype=torch.float32, device=DEV)
     st = status()
     scale = head_dim ** -0.5
-    assert n * kv_heads * splits > api.SM_COUNT
+    assert n * kv_heads * splits > api.sm_count()
     api.attention_mma(q.view(n, -1), k_pool, v_pool, table, cu, before, n, n, heads, kv_heads, head_dim, scale, 0, splits, out,
                       part_acc, part_ml, st, one_token_each=True)
     want = attention_reference(q.float().cpu(), keys, values, [1] * n, heads, kv_heads, scale, 0)

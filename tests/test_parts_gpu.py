@@ -93,14 +93,14 @@ def test_attention_and_ffn_parts(name, dtype):
     first = [70, 3, 128]
     ctx = context_for(engine, slots, first)
     x = torch.cat([xs[i][: first[i]] for i in range(3)]).to(DEV)
-    got = mixer.forward(ctx, x, engine.cache.run_cache(0), None).tensor.sum(0).double().cpu()
+    got = mixer.forward(ctx, x, engine.cache.run_cache(0), []).tensor.sum(0).double().cpu()
     for s, n in zip(slots, first):
         engine.cache.advance(s, n)
     wants = [plain_llama.attention_block(xs[i].double(), weights, "model.layers.0.self_attn.", cfg, torch.arange(lengths[i]), inv_freq)
              for i in range(3)]
     torch.testing.assert_close(got, torch.cat([wants[i][: first[i]] for i in range(3)]), rtol=tol, atol=tol)
     ctx = context_for(engine, [slots[2]], [2])
-    got = mixer.forward(ctx, xs[2][128:].to(DEV), engine.cache.run_cache(0), None).tensor.sum(0).double().cpu()
+    got = mixer.forward(ctx, xs[2][128:].to(DEV), engine.cache.run_cache(0), []).tensor.sum(0).double().cpu()
     torch.testing.assert_close(got, wants[2][128:], rtol=tol, atol=tol)
 
     ctx = context_for(engine, [slots[1]], [5])
@@ -190,9 +190,10 @@ def test_schedule_repeats_layers_shares_caches_and_mixes_windows():
 
 
 def test_toy_mixer_with_state_of_its_own():
-    """A mixer that keeps, per sequence, the running sum of its inputs and their count
-    (fixed-size state, no keys) and outputs W @ (mean of the inputs so far).  Defined
-    here, registered here, used for one layer next to an attention layer."""
+    """A mixer that keeps, per sequence, the running sum of its inputs (float32) and their count
+    (int32): two fixed-size states of different shape and dtype, no keys.  It outputs
+    W @ (mean of the inputs so far).  Defined here, registered here, used for one layer next to
+    an attention layer."""
     from dataclasses import replace
 
     from thintensor_b200.engine.engine import Entry
@@ -208,22 +209,24 @@ def test_toy_mixer_with_state_of_its_own():
         def weights(self):
             return {"mix.weight": WeightDecl((self.hidden, self.hidden))}
 
-        def state_need(self):
-            return StateNeed((self.hidden + 1,), torch.float32)
+        def state_needs(self):
+            return [StateNeed((self.hidden,), torch.float32), StateNeed((1,), torch.int32)]
 
         def bind(self, tensors, dtype, device):
             self.w = tensors["mix.weight"].float()
 
-        def forward(self, ctx, x, cache, state):
+        def forward(self, ctx, x, cache, states):
+            total, count = states
+            assert total.dtype == torch.float32 and count.dtype == torch.int32 and cache.k_pool is None
             out = torch.empty(1, ctx.n_tokens, self.hidden, dtype=torch.float32, device=x.device)
             at = 0
             for slot, new in zip(ctx.host_slots, ctx.host_new):
                 xs = x[at: at + new].float()
-                sums = state[slot, : self.hidden] + xs.cumsum(0)
-                counts = state[slot, self.hidden] + torch.arange(1, new + 1, device=x.device)
-                out[0, at: at + new] = (sums / counts[:, None]) @ self.w.T
-                state[slot, : self.hidden] = sums[-1]
-                state[slot, self.hidden] = counts[-1]
+                sums = total[slot] + xs.cumsum(0)
+                counts = count[slot] + torch.arange(1, new + 1, device=x.device, dtype=torch.int32)
+                out[0, at: at + new] = (sums / counts[:, None].float()) @ self.w.T
+                total[slot] = sums[-1]
+                count[slot] = counts[-1]
                 at += new
             return Delta(out)
 
@@ -234,7 +237,7 @@ def test_toy_mixer_with_state_of_its_own():
         spec = replace(spec, layers=tuple(layers))
         engine, host = make_engine(spec, torch.float32, seed=9, scale=SHARP)
         assert "model.layers.0.toy.mix.weight" in host and "model.layers.0.self_attn.q_proj.weight" not in host
-        assert len(engine.cache.state_groups) == 1 and len(engine.cache.kv_groups) == 1
+        assert len(engine.cache.state_groups) == 2 and len(engine.cache.kv_groups) == 1
         cfg = plain_llama.normalise_config(TINY["a"])
         w = {k: v.double() for k, v in host.items()}
 
@@ -366,18 +369,23 @@ def test_toy_position_encoding(dtype):
 
     from thintensor_b200.engine.engine import Entry
     from thintensor_b200.parts import POSITION_ENCODINGS
-    from thintensor_b200.parts.base import PositionEncoding
+    from thintensor_b200.parts.base import PositionEncoding, RotaryTable
     from thintensor_b200.parts.spec import PartSpec
 
     @POSITION_ENCODINGS.register("toy_interpolated")
     class Interpolated(PositionEncoding):
+        kind = "rotary"
+
         def __init__(self, head_dim, theta, factor):
-            self.head_dim, self.rotary_dim, self.attention_scaling = head_dim, head_dim // 2, 1.0
+            self.rotary_dim = head_dim // 2
             index = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32)
             self.table = theta ** (-index / self.rotary_dim) / factor
 
         def bind(self, tensors, dtype, device):
-            self.inv_freq = self.table.to(device)
+            self.device_table = self.table.to(device)
+
+        def rotary(self):
+            return RotaryTable(self.device_table, self.rotary_dim, 1.0)
 
     try:
         name = "d"

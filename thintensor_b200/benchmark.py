@@ -23,29 +23,46 @@ from .sampling.sampler import SamplingParams
 SHAPES: dict[str, dict] = json.loads((Path(__file__).resolve().parent / "config" / "shapes.json").read_text(encoding="utf-8"))
 
 
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks(file: str | Path | None = None) -> dict:
+    """The denominators of the roofline fractions: a measured copy bandwidth (GB/s) and a measured
+    dense bfloat16 matrix-product rate (TFLOP/s) from ``file`` (JSON with ``hbm_gbs`` and
+    ``bf16_tflops``; default ``MEASURED_PEAKS.json`` in the working directory) if it exists, else
+    an earlier measurement on a B200 (6.65 TB/s, 1.59 PFLOP/s), marked ``fallback``."""
+    path = Path(file) if file is not None else Path("MEASURED_PEAKS.json")
+    if path.is_file():
+        raw = json.loads(path.read_text(encoding="utf-8"))
+        return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]), "source": "measured"}
+    if file is not None:
+        raise FileNotFoundError(f"no peaks file at {path}")
+    return dict(FALLBACK_PEAKS)
+
+
+def _tensor_bytes(t) -> int:
+    return 0 if t is None else t.numel() * t.element_size()
+
+
+def _step_parts(model):
+    """Every part a step runs, once per run of the schedule, then the final norm and the head.
+    The embedding is left out: a step gathers one row per token from it."""
+    for run in model.spec.schedule:
+        yield from model.layers[run.layer].parts.values()
+    yield model.final_norm.part
+    yield model.head.part
+
+
 def weight_bytes_per_step(model) -> int:
-    """Bytes of weights a decode step reads: every matrix and vector once; of the
-    embedding table only when it also serves as the head."""
-    seen: set[int] = set()
+    """Bytes of weights a decode step reads: every projection (``Part.projections``) and every
+    vector (``Part.vectors``) of every run once.  A tied head is the embedding table, which is
+    counted there, as the head."""
     total = 0
-
-    def add(t):
-        nonlocal total
-        if t is not None and t.data_ptr() not in seen:
-            seen.add(t.data_ptr())
-            total += t.numel() * t.element_size()
-
-    for arrangement in model.layers:
-        for part in arrangement.parts.values():
-            for value in vars(part).values():
-                for linear in (value, getattr(value, "fused", None)):
-                    if hasattr(linear, "weight") and hasattr(linear, "out_features"):
-                        add(linear.weight)
-                        add(linear.bias)
-            if hasattr(part, "weight") and isinstance(part.weight, torch.Tensor):
-                add(part.weight)
-    add(model.head.part.linear.weight)
-    add(model.final_norm.part.weight)
+    for part in _step_parts(model):
+        for linear in part.projections():
+            total += _tensor_bytes(linear.weight) + _tensor_bytes(linear.bias)
+        for vector in part.vectors():
+            total += _tensor_bytes(vector)
     return total
 
 
@@ -53,7 +70,15 @@ def kv_bytes_per_token(model) -> int:
     """Bytes of keys and values one cached token takes over all layers."""
     kv, _, source = model.cache_needs()
     width = torch.empty((), dtype=model.dtype).element_size()
-    return sum(2 * need.kv_heads * need.head_dim * width for need, src in zip(kv, source) if need is not None)
+    return sum(2 * need.kv_heads * need.head_dim * width for need, src in zip(kv, source) if need is not None and src is None)
+
+
+def kv_read_bytes_per_token(model) -> int:
+    """Bytes of keys and values a decode step reads per cached token: every run that attends reads
+    them, also one that reads another run's cache."""
+    kv, _, _ = model.cache_needs()
+    width = torch.empty((), dtype=model.dtype).element_size()
+    return sum(2 * need.kv_heads * need.head_dim * width for need in kv if need is not None)
 
 
 def linear_flops_per_token(model) -> int:
@@ -61,45 +86,97 @@ def linear_flops_per_token(model) -> int:
     total = 0
     for run in model.spec.schedule:
         for part in model.layers[run.layer].parts.values():
-            for value in vars(part).values():
-                for linear in (value, getattr(value, "fused", None)):
-                    if hasattr(linear, "out_features"):
-                        total += 2 * linear.out_features * linear.in_features
+            for linear in part.projections():
+                total += 2 * linear.out_features * linear.in_features
     return total
 
 
-def prefill_flops(model, tokens: int) -> float:
-    """Projections for every token, causal attention (QK^T and PV over t(t+1)/2 pairs),
-    and the head at one position."""
-    flops = float(linear_flops_per_token(model)) * tokens
+def attention_flops(model, tokens: int) -> float:
+    """Causal attention of one sequence of ``tokens`` tokens: QK^T and PV over t(t+1)/2 pairs."""
+    flops = 0.0
     kv, _, _ = model.cache_needs()
-    for run, need in zip(model.spec.schedule, kv):
-        if need is None:
-            continue
-        mixer = model.layers[run.layer].mixer()
-        flops += 2.0 * 2.0 * (tokens * (tokens + 1) / 2) * need.head_dim * mixer.heads
-    flops += 2.0 * model.spec.vocab_size * model.spec.hidden_size
+    for index, run in enumerate(model.spec.schedule):
+        for user, mixer in zip(model.users[index], model.layers[run.layer].mixers()):
+            if kv[user] is not None:
+                flops += 2.0 * 2.0 * (tokens * (tokens + 1) / 2) * kv[user].head_dim * getattr(mixer, "heads", kv[user].kv_heads)
     return flops
 
 
-def measure_prefill(runtime, prompt: list[int], repeats: int = 3, warmup: int = 2) -> dict:
-    """One sequence's whole prompt in one step, logits at its last position."""
-    engine = runtime.new_engine(max_tokens=len(prompt) + 64, max_sequences=1, max_step_tokens=max(8192, len(prompt)))
+def prefill_flops(model, tokens: int) -> float:
+    """Projections for every token, causal attention, and the head at one position."""
+    return float(linear_flops_per_token(model)) * tokens + attention_flops(model, tokens) + 2.0 * model.spec.vocab_size * model.spec.hidden_size
+
+
+def measure_prefill(runtime, prompt, repeats: int = 3, warmup: int = 2) -> dict:
+    """Whole prompts in one step, logits at each one's last position.  ``prompt`` is one list of
+    token ids or a list of them (a batch of prompts of any lengths, packed into the one step)."""
+    prompts = [prompt] if prompt and isinstance(prompt[0], int) else [list(p) for p in prompt]
+    total = sum(len(p) for p in prompts)
+    room = sum(-(-(len(p) + 1) // 64) * 64 for p in prompts)
+    engine = runtime.new_engine(max_tokens=room, max_sequences=len(prompts), max_step_tokens=8192)
     times = []
     for i in range(warmup + repeats):
-        slot = engine.open()
+        slots = [engine.open() for _ in prompts]
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         start.record()
-        engine.step([Entry(slot, prompt, [len(prompt) - 1])])
+        engine.step([Entry(slot, p, [len(p) - 1]) for slot, p in zip(slots, prompts)])
         stop.record()
         torch.cuda.synchronize()
-        engine.close(slot)
+        for slot in slots:
+            engine.close(slot)
         if i >= warmup:
             times.append(start.elapsed_time(stop))
     engine.check_status()
     ms = sum(times) / len(times)
-    return {"ms": ms, "tokens": len(prompt), "tokens_per_s": len(prompt) / (ms / 1e3), "flops": prefill_flops(runtime.model, len(prompt))}
+    model = runtime.model
+    flops = (float(linear_flops_per_token(model)) * total + sum(attention_flops(model, len(p)) for p in prompts)
+             + 2.0 * model.spec.vocab_size * model.spec.hidden_size * len(prompts))
+    return {"ms": ms, "tokens": total, "sequences": len(prompts), "tokens_per_s": total / (ms / 1e3), "flops": flops}
+
+
+def roofline(decode: dict | None, prefill: dict | None, pk: dict) -> dict:
+    """Achieved rates and their fractions of the peaks: a decode step against the copy bandwidth
+    (the bytes it has to read: every weight once and the live sequences' cache), a prefill against
+    the matrix-product rate."""
+    out: dict = {"peaks": pk["source"]}
+    if decode is not None:
+        gbs = decode["bytes_per_step"] / (decode["ms_per_step"] / 1e3) / 1e9
+        out["decode"] = {"bound": "hbm", "bytes_per_step": int(decode["bytes_per_step"]), "achieved_gbs": gbs, "peak_gbs": pk["hbm_gbs"],
+                         "frac": gbs / pk["hbm_gbs"]}
+    if prefill is not None:
+        tflops = prefill["flops"] / (prefill["ms"] / 1e3) / 1e12
+        out["prefill"] = {"bound": "tensor", "flops": prefill["flops"], "achieved_tflops": tflops, "peak_tflops": pk["bf16_tflops"],
+                          "frac": tflops / pk["bf16_tflops"]}
+    return out
+
+
+def measure_classes(runtime, prompts: list[list[int]], context: int) -> dict:
+    """Where the time of one prefill step and of one decode step goes, by class of kernel: both are
+    run eagerly with every kernel call bracketed by CUDA events (:class:`~thintensor_b200.kernels.api.ClassTimer`).
+    The kernels then run one after another without overlapping, so the sums are larger than the
+    steps' real durations; the shares are what to read."""
+    batch = len(prompts)
+    per_sequence = -(-context // 64) * 64
+    engine = runtime.new_engine(max_tokens=per_sequence * batch, max_sequences=batch)
+    backend = EngineBackend(engine, SamplingParams(), use_graph=False)
+    backend.start_batch(list(range(batch)), prompts, [context] * batch)          # compiles and sizes scratch memory
+    state = backend._state_for(list(range(batch)))
+    state.step(backend.params, False)
+    with api.timed_classes() as timer:
+        state.step(backend.params, False)
+    decode = timer.summary()
+    for position in range(batch):
+        backend.finish(position)
+    with api.timed_classes() as timer:
+        slots = [engine.open() for _ in prompts]
+        engine.step([Entry(slot, p, [len(p) - 1]) for slot, p in zip(slots, prompts)])
+    prefill = timer.summary()
+    for slot in slots:
+        engine.close(slot)
+    engine.check_status()
+    return {"decode_step": decode, "prefill_step": prefill,
+            "decode_ms_serialised": sum(c["ms"] for c in decode.values()), "prefill_ms_serialised": sum(c["ms"] for c in prefill.values())}
 
 
 def measure_decode(runtime, prompts: list[list[int]], context: int, warmup: int, steps: int, use_graph: bool = True) -> dict:
@@ -132,7 +209,7 @@ def measure_decode(runtime, prompts: list[list[int]], context: int, warmup: int,
     engine.check_status()
     ms = start.elapsed_time(stop)
     mean_context = sum(lengths_before) / batch + (steps - 1) / 2.0
-    bytes_per_step = weight_bytes_per_step(runtime.model) + kv_bytes_per_token(runtime.model) * mean_context * batch
+    bytes_per_step = weight_bytes_per_step(runtime.model) + kv_read_bytes_per_token(runtime.model) * mean_context * batch
     result = {
         "ms_per_step": ms / steps,
         "tokens_per_s": batch * steps / (ms / 1e3),

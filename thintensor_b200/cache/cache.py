@@ -57,13 +57,14 @@ class RunCache:
 class SequenceCache:
     """Slots, block tables, pools and state for one model on one device.
 
-    ``kv_needs[i]`` / ``state_needs[i]`` are what run ``i`` of the schedule asks for
-    (None for nothing); ``cache_from[i]`` names the run whose keys run ``i`` reads
-    instead of keeping its own.  ``num_blocks`` blocks of 64 tokens are shared by all
+    ``kv_needs[i]`` (None for nothing) and ``state_needs[i]`` (a list of StateNeed, or one, or
+    None) are what run ``i`` of the schedule asks for (a run with several mixers has an entry
+    for each of them); ``cache_from[i]`` names the entry whose keys entry ``i`` reads instead
+    of keeping its own.  ``num_blocks`` blocks of 64 tokens are shared by all
     live sequences of a group; ``device=None`` keeps the bookkeeping only.
     """
 
-    def __init__(self, kv_needs: list[KVNeed | None], state_needs: list[StateNeed | None], cache_from: list[int | None],
+    def __init__(self, kv_needs: list[KVNeed | None], state_needs: list, cache_from: list[int | None],
                  num_blocks: int, max_slots: int, dtype: torch.dtype, device: torch.device | str | None):
         self.block_tokens = BLOCK_TOKENS
         self.num_blocks = int(num_blocks)
@@ -76,7 +77,7 @@ class SequenceCache:
         self.state_groups: list[StateGroup] = []
         self._run_group: list[int | None] = [None] * len(kv_needs)
         self._run_index: list[int | None] = [None] * len(kv_needs)     # position in its group's storage
-        self._run_state: list[tuple[int, int] | None] = [None] * len(kv_needs)
+        self._run_state: list[list[tuple[int, int]]] = [[] for _ in kv_needs]
         self._cache_from = list(cache_from)
 
         by_need: dict[KVNeed, int] = {}
@@ -98,19 +99,24 @@ class SequenceCache:
             a, b = kv_needs[run], kv_needs[source]
             if (a.kv_heads, a.head_dim) != (b.kv_heads, b.head_dim):
                 raise CacheError(f"run {run} reads the cache of run {source}, whose key/value shape differs")
+            if b.window is not None and (a.window is None or a.window > b.window):
+                # the source's group gives blocks back by the source's window; a reader that looks
+                # further back would meet blocks that are gone
+                raise CacheError(f"run {run} reads the cache of run {source}, which keeps only the last {b.window} tokens, "
+                                 f"but wants {'all of them' if a.window is None else 'the last ' + str(a.window)}")
             self._run_group[run] = self._run_group[source]
             self._run_index[run] = self._run_index[source]
 
         by_state: dict[StateNeed, int] = {}
-        for run, need in enumerate(state_needs):
-            if need is None:
-                continue
-            if need not in by_state:
-                by_state[need] = len(self.state_groups)
-                self.state_groups.append(StateGroup(need, [], None))
-            group = self.state_groups[by_state[need]]
-            self._run_state[run] = (by_state[need], len(group.runs))
-            group.runs.append(run)
+        for run, needs in enumerate(state_needs):
+            needs = [] if needs is None else ([needs] if isinstance(needs, StateNeed) else list(needs))
+            for need in needs:
+                if need not in by_state:
+                    by_state[need] = len(self.state_groups)
+                    self.state_groups.append(StateGroup(need, [], None))
+                group = self.state_groups[by_state[need]]
+                self._run_state[run].append((by_state[need], len(group.runs)))     # a run may hold several states of one shape
+                group.runs.append(run)
 
         if self.device is not None:
             for group in self.kv_groups:
@@ -191,13 +197,15 @@ class SequenceCache:
             v = g.storage[index, 1].view(self.num_blocks, need.kv_heads, need.head_dim, BLOCK_TOKENS)
         return RunCache(group, k, v, self._cache_from[run] is None, g.need.window)
 
-    def run_state(self, run: int) -> torch.Tensor | None:
-        """[slots, *shape] state of run ``run``, or None."""
-        where = self._run_state[run]
-        if where is None:
-            return None
-        storage = self.state_groups[where[0]].storage
-        return None if storage is None else storage[where[1]]
+    def run_state(self, run: int) -> list[torch.Tensor]:
+        """The state tensors of entry ``run``, each ``[slots, *shape]``, in the order it declared
+        them (empty without a device or without states)."""
+        out = []
+        for group, index in self._run_state[run]:
+            storage = self.state_groups[group].storage
+            if storage is not None:
+                out.append(storage[index])
+        return out
 
     def bytes(self) -> int:
         total = sum(g.bytes() for g in self.kv_groups)

@@ -52,21 +52,30 @@ def build_parser() -> argparse.ArgumentParser:
     bench.add_argument("--steps", "--decode-steps", dest="steps", type=int, default=200, help="Timed decode steps")
     bench.add_argument("--warmup", type=int, default=10, help="Warmup decode steps")
     bench.add_argument("--prompt-token-ids", help="Comma-separated explicit prompt token ids used by every sequence")
-    bench.add_argument("--prompt-len", type=int, default=128, help="Length of the synthetic prompt when no ids are given")
+    bench.add_argument("--prompt-len", default="128", help="Length of the synthetic prompts when no ids are given; LO:HI draws every "
+                       "sequence's length uniformly from [LO, HI] with the seed (an unequal batch)")
     bench.add_argument("--batch", default="1", help="Sequences decoded together; a comma-separated list measures each")
     bench.add_argument("--context", type=int, help="Context length of a sequence (default: prompt + warm-up + steps)")
+    bench.add_argument("--to-context", action="store_true", help="Decode until the longest sequence fills --context (sets --steps)")
+    bench.add_argument("--peaks", help="JSON file with hbm_gbs and bf16_tflops, the denominators of the roofline fractions "
+                       "(default: MEASURED_PEAKS.json in the working directory, else a stated fallback)")
+    bench.add_argument("--profile-classes", action="store_true", help="Also time one decode step and one prefill step kernel class by "
+                       "kernel class (CUDA events around every kernel, which then run one after another)")
     bench.add_argument("--seed", type=int, default=0)
     bench.add_argument("--device", choices=["cuda"], default="cuda")
     bench.add_argument("--dtype", choices=["bf16", "fp32"], default="bf16")
     bench.add_argument("--json", action="store_true")
     bench.add_argument("--out", help="Write JSON results to this file")
 
-    validate = sub.add_parser("validate", help="Compare the engine's ways of running with its 32-bit path",
+    validate = sub.add_parser("validate", help="Compare the engine's ways of running with reference logits (or its own 32-bit path)",
                               formatter_class=argparse.ArgumentDefaultsHelpFormatter)
     validate.add_argument("model", nargs="?", help="model folder (or --shape)")
     validate.add_argument("--shape", choices=SHAPE_NAMES, help="Random weights of a named shape, written to a temporary folder")
     validate.add_argument("--require-tier", choices=["ranking", "exact"], default="ranking", help="Minimum accepted correctness tier")
     validate.add_argument("--prompt-token-ids", help="Comma-separated token ids; default is a seeded synthetic sequence")
+    validate.add_argument("--reference-logits", metavar="PATH", help="Logits from outside this engine to compare with: an .npz (logits [n, vocab], "
+                          "optional positions [n] and tokens) or a folder of bin/trace_run output with the trace.jsonl that made it")
+    validate.add_argument("--request", help="With a trace folder: the id of the request to compare (default: the trace's first)")
     validate.add_argument("--length", type=int, default=96, help="Length of the synthetic sequence")
     validate.add_argument("--seed", type=int, default=0)
     validate.add_argument("--device", choices=["cuda"], default="cuda")
@@ -142,13 +151,17 @@ def cmd_run(args) -> int:
 
 
 def cmd_bench(args) -> int:
+    """Prefill and decode rates with the bytes and FLOP behind them and the fraction of the device's
+    peaks they reach, after the reference's per-shape bandwidth report (scripts/thin_runtime.py:602-645)
+    and its static byte model (thinruntime/gpu_runtime.py:10781-10885)."""
     import torch
 
     import thintensor_b200
-    from thintensor_b200.benchmark import SHAPES, measure_decode, measure_prefill
+    from thintensor_b200.benchmark import SHAPES, measure_classes, measure_decode, measure_prefill, peaks, roofline
 
     if (args.model is None) == (args.shape is None):
         raise SystemExit("bench needs a model folder or --shape, not both")
+    pk = peaks(args.peaks)
     if args.shape:
         runtime = thintensor_b200.random_model(SHAPES[args.shape], seed=args.seed, dtype=args.dtype, device=args.device)
     else:
@@ -157,24 +170,59 @@ def cmd_bench(args) -> int:
     if not batches or min(batches) <= 0:
         raise SystemExit("--batch must name positive numbers of sequences")
     vocab = runtime.model.spec.vocab_size
-    if args.prompt_token_ids:
-        prompt = parse_ids(args.prompt_token_ids)
-    else:
-        g = torch.Generator().manual_seed(args.seed)
-        prompt = torch.randint(0, vocab, (args.prompt_len,), generator=g).tolist()
-    context = args.context or len(prompt) + max(args.warmup, 2) + args.steps + 1
-    prefill = measure_prefill(runtime, prompt, repeats=3)
-    runs = [measure_decode(runtime, [prompt] * batch, context, args.warmup, args.steps) for batch in batches]
-    decode = runs[0]
+    g = torch.Generator().manual_seed(args.seed)
+
+    def prompts_for(batch: int) -> list[list[int]]:
+        if args.prompt_token_ids:
+            return [parse_ids(args.prompt_token_ids)] * batch
+        try:
+            low, _, high = args.prompt_len.partition(":")
+            low, high = int(low), int(high or low)
+        except ValueError:
+            raise SystemExit("--prompt-len takes N or LO:HI")
+        if not 0 < low <= high:
+            raise SystemExit("--prompt-len needs 0 < LO <= HI")
+        lengths = [low] * batch if low == high else torch.randint(low, high + 1, (batch,), generator=g).tolist()
+        return [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lengths]
+
+    runs = []
+    for batch in batches:
+        prompts = prompts_for(batch)
+        longest = max(len(p) for p in prompts)
+        warmup = max(args.warmup, 2)
+        steps = args.steps
+        if args.to_context:
+            if not args.context:
+                raise SystemExit("--to-context needs --context")
+            steps = args.context - longest - warmup - 1
+            if steps <= 0:
+                raise SystemExit(f"a prompt of {longest} tokens leaves no room to decode in a context of {args.context}")
+        context = args.context or longest + warmup + steps + 1
+        prefill = measure_prefill(runtime, prompts, repeats=3)
+        decode = measure_decode(runtime, prompts, context, warmup, steps)
+        lines = roofline(decode, prefill if args.dtype == "bf16" else None, pk)
+        run = {
+            "batch_size": batch, "prompt_tokens": [len(p) for p in prompts] if len({len(p) for p in prompts}) > 1 else longest,
+            "steps": steps, "warmup_steps": warmup, "context": context, "mean_context": decode["mean_context"],
+            "tokens_per_s": decode["tokens_per_s"], "ms_per_step": decode["ms_per_step"], "launches_per_step": decode["launches_per_step"],
+            "bytes_per_step": int(decode["bytes_per_step"]), "decode_gbs": lines["decode"]["achieved_gbs"],
+            "decode_frac_of_hbm_peak": lines["decode"]["frac"] if args.dtype == "bf16" else None,
+            "prefill_tokens": prefill["tokens"], "prefill_tokens_per_s": prefill["tokens_per_s"], "prefill_ms": prefill["ms"],
+            "prefill_flops": prefill["flops"], "prefill_tflops": prefill["flops"] / (prefill["ms"] / 1e3) / 1e12,
+            "prefill_frac_of_tensor_peak": lines["prefill"]["frac"] if "prefill" in lines else None,
+        }
+        if args.profile_classes:
+            run["classes"] = measure_classes(runtime, prompts, context)
+        runs.append(run)
+    first = runs[0]
     result = {
-        "model": str(args.model or args.shape), "dtype": args.dtype, "batch_size": batches[0], "prompt_tokens": len(prompt),
-        "steps": args.steps, "warmup_steps": args.warmup, "context": context,
-        "tokens_per_s": decode["tokens_per_s"], "ms_per_token": decode["ms_per_step"],
-        "prefill_tokens_per_s": prefill["tokens_per_s"], "prefill_ms": prefill["ms"],
+        "model": str(args.model or args.shape), "dtype": args.dtype, "peaks": pk,
+        "batch_size": first["batch_size"], "prompt_tokens": first["prompt_tokens"], "steps": first["steps"],
+        "warmup_steps": first["warmup_steps"], "context": first["context"],
+        "tokens_per_s": first["tokens_per_s"], "ms_per_token": first["ms_per_step"],
+        "prefill_tokens_per_s": first["prefill_tokens_per_s"], "prefill_ms": first["prefill_ms"],
+        "batches": runs,
     }
-    if len(runs) > 1:
-        result["batches"] = [{"batch_size": r["batch"], "tokens_per_s": r["tokens_per_s"], "ms_per_step": r["ms_per_step"],
-                              "bytes_per_step": r["bytes_per_step"]} for r in runs]
     text = json.dumps(result, indent=None if args.json else 2)
     if args.out:
         Path(args.out).write_text(text + "\n")
@@ -196,9 +244,11 @@ def cmd_validate(args) -> int:
 
         with tempfile.TemporaryDirectory() as folder:      # both dtypes are read from the same file
             thintensor_b200.save_random_model(folder, SHAPES[args.shape], seed=args.seed, dtype="bfloat16")
-            report = validate_model(folder, dtype=args.dtype, tokens=ids, length=args.length, seed=args.seed)
+            report = validate_model(folder, dtype=args.dtype, tokens=ids, length=args.length, seed=args.seed,
+                                    reference_logits=args.reference_logits, request=args.request)
     else:
-        report = validate_model(args.model, dtype=args.dtype, tokens=ids, length=args.length, seed=args.seed)
+        report = validate_model(args.model, dtype=args.dtype, tokens=ids, length=args.length, seed=args.seed,
+                                reference_logits=args.reference_logits, request=args.request)
     print(json.dumps(report) if args.json else json.dumps(report, indent=2))
     order = {"fail": 0, "ranking_pass": 1, "exact_pass": 2}
     needed = {"ranking": 1, "exact": 2}[args.require_tier]

@@ -20,10 +20,21 @@ static thread_local char last_error[256] = "no error";
 
 extern "C" const char* tt_attention_static_last_error(void) { return last_error; }
 
+// Bytes of scratch for these sizes, or ~0ull when a size is not positive or the count is beyond
+// 2^40 entries (65,000 times the array).  Every multiplication is preceded by a division that shows
+// it cannot pass that bound, so no product can wrap around and come back small enough to be accepted.
 extern "C" unsigned long long tt_attention_static_bytes_needed(int n_tokens, int heads, int head_dim, int splits) {
-    const unsigned long long slots = (unsigned long long)n_tokens * heads * splits;
+    const unsigned long long never = ~0ull;
+    const unsigned long long limit = 1ull << 40;
+    if (n_tokens <= 0 || heads <= 0 || head_dim <= 0 || splits <= 0) return never;
+    unsigned long long slots = (unsigned long long)n_tokens;
+    if (slots > limit / (unsigned long long)heads) return never;
+    slots *= (unsigned long long)heads;
+    if (slots > limit / (unsigned long long)splits) return never;
+    slots *= (unsigned long long)splits;
+    if (slots > limit / (unsigned long long)head_dim) return never;
     // accumulators, then (max, sum) pairs, the second part starting on a 256-byte boundary
-    const unsigned long long acc = (slots * head_dim * sizeof(float) + 255ull) & ~255ull;
+    const unsigned long long acc = (slots * (unsigned long long)head_dim * sizeof(float) + 255ull) & ~255ull;
     return acc + slots * 2 * sizeof(float);
 }
 
@@ -32,7 +43,10 @@ extern "C" unsigned long long tt_attention_static_bytes_needed(int n_tokens, int
 static int scratch_for_current_device(float** out) {
     int device = 0;
     cudaError_t err = cudaGetDevice(&device);
-    if (err != cudaSuccess) return (int)err;
+    if (err != cudaSuccess) {
+        snprintf(last_error, sizeof(last_error), "cudaGetDevice failed: %s", cudaGetErrorString(err));
+        return (int)err;
+    }
     if (device < 0 || device >= TT_STATIC_MAX_DEVICES) {
         snprintf(last_error, sizeof(last_error), "device index %d is beyond the %d this entry point keeps addresses for", device, TT_STATIC_MAX_DEVICES);
         return TT_STATIC_NO_SYMBOL;
@@ -57,7 +71,7 @@ extern "C" int tt_attention_decode_static(const void* q, const void* k_pool, con
                                           int head_dim, float scale, int window, int splits, void* out,
                                           unsigned* status, cudaStream_t stream) {
     if (n_tokens <= 0) return TT_STATIC_OK;
-    if (head_dim <= 0 || head_dim % 16 || head_dim > ATTN_MAX_HEAD_DIM || heads <= 0 || kv_heads <= 0 ||
+    if (sequences <= 0 || table_width <= 0 || pool_blocks <= 0 || head_dim <= 0 || head_dim % 16 || head_dim > ATTN_MAX_HEAD_DIM || heads <= 0 || kv_heads <= 0 ||
         heads % kv_heads || splits < 1 || splits > 65535 || (dtype != TT_F32 && dtype != TT_BF16)) {
         snprintf(last_error, sizeof(last_error), "sizes not taken: head_dim %d (multiples of 16 up to %d), heads %d, kv_heads %d, splits %d, dtype %d",
                  head_dim, ATTN_MAX_HEAD_DIM, heads, kv_heads, splits, dtype);

@@ -479,16 +479,17 @@ extern "C" int tt_advance_lengths(int* len, const int* cu, int* counters, int se
 // address (token ids in, sampled ids out): as a kernel in the chain of a step this costs
 // a fraction of a copy node in a CUDA graph.  Host memory is read and written uncached.
 // ------------------------------------------------------------------------------------
-__global__ void copy_int32_kernel(int* __restrict__ dst, const int* __restrict__ src, int n) {
+__global__ void copy_int32_kernel(int* __restrict__ dst, const int* __restrict__ src, int n, const int* __restrict__ extra) {
     tt_pdl_wait();
     tt_pdl_launch_dependents();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) __stcg(dst + i, __ldcv(src + i));
+    if (extra && i == n) __stcg(dst + n, __ldcv(extra));
 }
 
-extern "C" int tt_copy_int32(int* dst, const int* src, int n, cudaStream_t stream) {
+// extra: one more int32 (the device status word, say) that is copied to dst[n]; may be null.
+extern "C" int tt_copy_int32(int* dst, const int* src, int n, const int* extra, cudaStream_t stream) {
     if (n <= 0) return 0;
-    tt_launch_pdl(copy_int32_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, dst, src, n);
+    tt_launch_pdl(copy_int32_kernel, dim3((n + 1 + 127) / 128), dim3(128), 0, stream, dst, src, n, extra);
     TT_LAUNCH_CHECK();
 }
-

@@ -16,7 +16,9 @@ import torch
 class Workspace:
     """Named scratch buffers that persist between steps.  A buffer grows when a step
     asks for more than it holds and otherwise keeps its address, so steps of a shape
-    that has run before allocate nothing (a requirement for graph replay)."""
+    that has run before allocate nothing (a requirement for graph replay).  A buffer that
+    has to grow at least doubles, so a run of slightly longer and longer steps moves it
+    (and makes every captured decode step be captured again) only a few times."""
 
     def __init__(self, device: torch.device):
         self.device = device
@@ -35,7 +37,10 @@ class Workspace:
         nbytes = count * torch.empty((), dtype=dtype).element_size()
         buffer = self._buffers.get(name)
         if buffer is None or buffer.numel() < nbytes:
-            grow = max(nbytes, 256)
+            grow = max(nbytes, 2 * buffer.numel() if buffer is not None else 0, 256)
+            grow = -(-grow // 256) * 256
+            buffer = None                                                    # the old one goes before the new one comes
+            self._buffers.pop(name, None)
             buffer = torch.empty(grow, dtype=torch.uint8, device=self.device)
             self._buffers[name] = buffer
             self.generation += 1

@@ -246,8 +246,6 @@ class Engine:
         return ctx, d_rows, d_targets
 
     def _forward_without_logits(self, ctx: StepContext) -> None:
-        """A piece none of whose logits are wanted still has to fill the cache: run it
-        with its last token as the wanted row and drop the result."""
-        rows = self.workspace.get("step.last_row", (1,), torch.int32)
-        rows.fill_(ctx.n_tokens - 1)
-        self.model.forward(ctx, self.cache, rows)
+        """A piece none of whose logits are wanted still has to fill the cache; it runs
+        without the final norm and the head."""
+        self.model.forward(ctx, self.cache, None)

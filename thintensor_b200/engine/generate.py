@@ -223,9 +223,10 @@ class _DecodeState:
         self.tables = [cut(b * self.width).view(b, self.width) for _ in range(groups)]
         self.rows, self.requests, self.steps = cut(b), cut(b), cut(b)
         self.graphs: dict[bool, tuple[torch.cuda.CUDAGraph, int]] = {}   # by whether the step copies tokens from and to the host
-        pinned = torch.empty((2, b), dtype=torch.int32, pin_memory=True)
-        self.host_in, self.host_out = pinned[0], pinned[1]    # tokens fed by the host, tokens sampled
+        pinned = torch.zeros(2 * b + 1, dtype=torch.int32, pin_memory=True)
+        self.host_in, self.host_out = pinned[:b], pinned[b:]  # tokens fed by the host; tokens sampled, then the status word
         self.feed = self.host_in.numpy()                      # the same memory, written without a tensor in between
+        self.fetched = self.host_out.numpy()
         self.warm = False
         self.launches_per_step = 0              # kernels of this library in one decode step
 
@@ -277,11 +278,12 @@ class _DecodeState:
 
     def body_with_host(self, params: SamplingParams) -> None:
         """The step with the host as the authority on tokens: ``host_in`` goes up before it,
-        the samples come down into ``host_out`` after it, both by small kernels that address
-        the pinned host memory (a copy node in a graph costs several times as much)."""
+        the samples come down into ``host_out`` after it together with the device status word, both
+        by small kernels that address the pinned host memory (a copy node in a graph costs several
+        times as much)."""
         api.copy_int32(self.tokens, self.host_in)
         self.body(params)
-        api.copy_int32(self.host_out, self.tokens)
+        api.copy_int32(self.host_out, self.tokens, self.engine.status)
 
     def step(self, params: SamplingParams, use_graph: bool, host_io: bool = False) -> None:
         e = self.engine
@@ -372,7 +374,12 @@ class EngineBackend:
         state.feed[:] = [self._last[p] for p in live]
         state.step(self.params, self.use_graph, host_io=True)
         torch.cuda.current_stream(self.engine.device).synchronize()
-        tokens = state.host_out.tolist()
+        fetched = state.fetched.tolist()
+        tokens, status = fetched[:-1], fetched[-1]
+        if status:
+            # a kernel of this step flagged a fault: the tokens are not to be trusted, and the sequence
+            # that caused it is in this batch, not in a later one
+            self.engine.check_status()
         for position, token in zip(live, tokens):
             self._last[position] = token
             self._steps[position] += 1

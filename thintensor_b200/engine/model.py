@@ -55,6 +55,7 @@ class DecoderModel:
             self._layer_parts.append(built)
             self.layers.append(arrangement_cls({role: b.part for role, b in built.items()}))
         self.bound = False
+        self.cache_needs()          # sets self.users
 
     # ------------------------------------------------------------------ weights
     def _all_parts(self) -> list[BuiltPart]:
@@ -93,12 +94,24 @@ class DecoderModel:
 
     # -------------------------------------------------------------------- cache
     def cache_needs(self):
+        """What the cache must hold, one entry for every mixer of every run of the schedule (in
+        schedule order; a layer's mixers in the order its arrangement lists them): keys and values,
+        state tensors, and the entry whose keys this one reads instead of keeping its own.  Also
+        sets ``self.users``: for each run, the entries of its mixers."""
         kv, state, source = [], [], []
+        self.users: list[list[int]] = []
         for run in self.spec.schedule:
-            mixer = self.layers[run.layer].mixer()
-            kv.append(mixer.cache_need() if mixer is not None else None)
-            state.append(mixer.state_need() if mixer is not None else None)
-            source.append(run.cache_from)
+            mixers = self.layers[run.layer].mixers()
+            mine = list(range(len(kv), len(kv) + len(mixers)))
+            if run.cache_from is not None and len(self.users[run.cache_from]) != len(mixers):
+                raise ValueError(f"a run of layer {run.layer} reads the cache of a run with another number of mixers")
+            for i, mixer in enumerate(mixers):
+                need = mixer.cache_need()
+                kv.append(need)
+                state.append(list(mixer.state_needs()))
+                # only keys are shared: a mixer without keys has nothing to read there, and states are always a run's own
+                source.append(None if run.cache_from is None or need is None else self.users[run.cache_from][i])
+            self.users.append(mine)
         return kv, state, source
 
     def new_cache(self, num_blocks: int, max_slots: int, device: torch.device | str | None = "default") -> SequenceCache:
@@ -107,16 +120,21 @@ class DecoderModel:
         return SequenceCache(kv, state, source, num_blocks, max_slots, self.dtype, where)
 
     # ------------------------------------------------------------------ forward
-    def forward(self, ctx: StepContext, cache: SequenceCache, rows: torch.Tensor) -> torch.Tensor:
+    def forward(self, ctx: StepContext, cache: SequenceCache, rows: torch.Tensor | None) -> torch.Tensor | None:
         """Run the packed tokens of ``ctx`` through the schedule and return float32
-        logits ``[len(rows), vocab]`` at the packed token indices ``rows``."""
+        logits ``[len(rows), vocab]`` at the packed token indices ``rows``.  Without ``rows`` the
+        step only fills the cache: the final norm and the head (which reads every row of its
+        matrix whatever the number of positions) are not run and nothing is returned."""
         if not self.bound:
             raise RuntimeError("the model has no weights yet")
         residual = ctx.scratch("model.residual", (ctx.n_tokens, self.spec.hidden_size), torch.float32)
         self.embedding.part.forward(ctx, ctx.tokens, residual)
         pending: Delta | None = None
         for index, run in enumerate(self.spec.schedule):
-            pending = self.layers[run.layer].run(ctx, residual, pending, cache.run_cache(index), cache.run_state(index))
+            users = self.users[index]
+            pending = self.layers[run.layer].run(ctx, residual, pending, [cache.run_cache(u) for u in users], [cache.run_state(u) for u in users])
+        if rows is None:
+            return None
         wanted = ctx.scratch("model.final", (rows.numel(), self.spec.hidden_size))
         self.final_norm.part.forward(ctx, residual, pending, wanted, rows)
         return self.head.part.forward(ctx, wanted)

@@ -76,6 +76,71 @@ def _need(t: torch.Tensor, dtype: torch.dtype, name: str) -> None:
 _functions: dict[str, object] = {}
 
 
+class ClassTimer:
+    """Device time per class of kernel, for looking at where a step's time goes: while one is
+    active (``with api.timed_classes() as timer``) every call of an entry point of this library is
+    bracketed by two CUDA events on the current stream, and ``timer.summary()`` adds the spans up
+    by entry point and label (parts label their matrix products: ``attention.qkv``, ``ffn.down``
+    ...).  The events keep a kernel from starting under the tail of the one before it, so the
+    spans are those of kernels run one after another, like a profiler's: compare shares, and take
+    a step's duration from an untimed run.  Not for use while a CUDA graph is being captured.
+    The reference's counterpart brackets layers the same way (LayerProfileEvents,
+    thinruntime/gpu_runtime.py:4770-4797, summed at :7464-7543)."""
+
+    def __init__(self):
+        self.spans: list[tuple[str, torch.cuda.Event, torch.cuda.Event]] = []
+
+    def wrap(self, name: str, fn):
+        def timed(*args):
+            global _label
+            key = name if _label is None else f"{name}[{_label}]"
+            _label = None
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            code = fn(*args)
+            stop.record()
+            self.spans.append((key, start, stop))
+            return code
+
+        return timed
+
+    def summary(self) -> dict[str, dict]:
+        """class -> {"calls": n, "ms": total}; synchronises."""
+        torch.cuda.synchronize()
+        out: dict[str, dict] = {}
+        for key, start, stop in self.spans:
+            entry = out.setdefault(key, {"calls": 0, "ms": 0.0})
+            entry["calls"] += 1
+            entry["ms"] += start.elapsed_time(stop)
+        return dict(sorted(out.items(), key=lambda item: -item[1]["ms"]))
+
+
+_timer: ClassTimer | None = None
+_label: str | None = None
+
+
+def set_label(label: str) -> None:
+    """Name the next kernel call for an active :class:`ClassTimer` (no effect otherwise)."""
+    global _label
+    if _timer is not None:
+        _label = label
+
+
+class timed_classes:
+    """Context manager that switches a :class:`ClassTimer` on for the calls inside it."""
+
+    def __enter__(self) -> ClassTimer:
+        global _timer
+        if _timer is not None:
+            raise KernelError("a class timer is already active")
+        _timer = ClassTimer()
+        return _timer
+
+    def __exit__(self, *exc) -> None:
+        global _timer, _label
+        _timer, _label = None, None
+
+
 def _fn(lib: str, name: str, argtypes: list):
     """The C entry point ``name`` of library ``lib`` (built and loaded at first use), with its prototype set."""
     fn = _functions.get(name)
@@ -84,6 +149,8 @@ def _fn(lib: str, name: str, argtypes: list):
         fn.argtypes = argtypes
         fn.restype = c_int
         _functions[name] = fn
+    if _timer is not None:
+        return _timer.wrap(name, fn)
     return fn
 
 
@@ -152,15 +219,18 @@ def swiglu(gate_up: torch.Tensor, act: torch.Tensor) -> None:
     _check(fn(_ptr(gate_up), gate_up.shape[0], gate_up.stride(0), _ptr(act), dtype_code(act.dtype), gate_up.shape[1], inter, _stream()), "swiglu")
 
 
-def copy_int32(dst: torch.Tensor, src: torch.Tensor) -> None:
-    """dst[:] = src for small int32 vectors; either side may be pinned host memory."""
+def copy_int32(dst: torch.Tensor, src: torch.Tensor, extra: torch.Tensor | None = None) -> None:
+    """dst[:n] = src for small int32 vectors; either side may be pinned host memory.  With ``extra``
+    (one int32 on the device, the status word say) ``dst`` has n + 1 entries and dst[n] = extra[0]."""
     for t, name in ((dst, "dst"), (src, "src")):
         if t.dtype != torch.int32 or not t.is_contiguous() or not (t.is_cuda or t.is_pinned()):
             raise KernelError(f"copy_int32: {name} must be contiguous int32 on the device or in pinned host memory")
-    if dst.numel() != src.numel():
+    if dst.numel() != src.numel() + (1 if extra is not None else 0):
         raise KernelError("copy_int32: sizes differ")
-    fn = _fn("elementwise", "tt_copy_int32", [c_void_p, c_void_p, c_int, c_void_p])
-    _check(fn(c_void_p(dst.data_ptr()), c_void_p(src.data_ptr()), dst.numel(), _stream()), "copy_int32")
+    if extra is not None and (extra.dtype != torch.int32 or extra.numel() != 1 or not extra.is_cuda):
+        raise KernelError("copy_int32: the extra word must be one int32 on the device")
+    fn = _fn("elementwise", "tt_copy_int32", [c_void_p, c_void_p, c_int, c_void_p, c_void_p])
+    _check(fn(c_void_p(dst.data_ptr()), c_void_p(src.data_ptr()), src.numel(), _ptr(extra), _stream()), "copy_int32")
 
 
 def advance_lengths(lengths: torch.Tensor, cu: torch.Tensor, sequences: int, counters: torch.Tensor | None = None) -> None:
@@ -332,7 +402,20 @@ def sample_rows(logits: torch.Tensor, temperature: float, top_k: int, top_p: flo
 
 
 # ----------------------------------------------------------------- tensor-core kernels
-SM_COUNT = 148              # B200
+_sm_counts: dict[int, int] = {}
+
+
+def sm_count(device: torch.device | int | None = None) -> int:
+    """Streaming multiprocessors of a CUDA device (the current one by default), asked of the device
+    once: it sizes the k-slices of few-token products and the key slices of decode attention, which
+    the launchers in C++ size from the same attribute."""
+    index = torch.cuda.current_device() if device is None else (device if isinstance(device, int) else (device.index if device.index is not None else torch.cuda.current_device()))
+    count = _sm_counts.get(index)
+    if count is None:
+        count = _sm_counts[index] = int(torch.cuda.get_device_properties(index).multi_processor_count)
+    return count
+
+
 SKINNY_TOKENS = 128         # up to this many tokens the weights go on the 128-row side of the tile
 
 
@@ -348,44 +431,47 @@ PAIR_TOKENS = 2048          # from this many tokens on, CTA pairs run them, whic
 PERSISTENT_SLICE_BLOCKS = 8  # a k-slice of the persistent kernel has at least this many 64-wide k-blocks
 
 
-def gemm_tcgen05_splits(tokens: int, features: int, k: int) -> int:
+def gemm_tcgen05_splits(tokens: int, features: int, k: int, sms: int | None = None) -> int:
     """Into how many slices k is cut so that few output tiles still fill the GPU.  Few tokens:
     about two CTAs per SM, at least four 64-wide k-blocks per slice, at most 16 slices.
     Prompts (more than 128 tokens) with at least 8 tiles of 128 x 256 run the persistent kernel,
     one CTA per SM: as many slices as keep its work items within one round of the SMs (a
-    512-token prompt has 32 tiles in the 1B shape's output projection), none of them empty."""
+    512-token prompt has 32 tiles in the 1B shape's output projection), none of them empty.
+    ``sms``: the device's multiprocessors (asked of the current device when not given)."""
+    sms = sm_count() if sms is None else sms
     k_blocks = -(-k // 64)
     if tokens > SKINNY_TOKENS and -(-tokens // 128) * -(-features // 256) >= PERSISTENT_TILES:
         if tokens >= PAIR_TOKENS:
             return 1
         tiles = -(-tokens // 128) * -(-features // 256)
-        splits = max(1, min(SM_COUNT // tiles, k_blocks // PERSISTENT_SLICE_BLOCKS, 16))
+        splits = max(1, min(sms // tiles, k_blocks // PERSISTENT_SLICE_BLOCKS, 16))
         while splits > 1 and (splits - 1) * -(-k_blocks // splits) >= k_blocks:
             splits -= 1
         return splits
     tiles = -(-features // 128) * (1 if tokens <= SKINNY_TOKENS else -(-tokens // 128))
-    return max(1, min(2 * SM_COUNT // tiles, k_blocks // 4, 16))
+    return max(1, min(2 * sms // tiles, k_blocks // 4, 16))
 
 
-def gemm_tcgen05_accumulates(tokens: int, features: int, k: int) -> bool:
+def gemm_tcgen05_accumulates(tokens: int, features: int, k: int, sms: int | None = None) -> bool:
     """Whether the product of these sizes can be added into its output by the kernel itself: prompts
     on the persistent or CTA-pair kernel whose k is not cut into slices, so that every output tile
     has one writer."""
     return (tokens > SKINNY_TOKENS and -(-tokens // 128) * -(-features // 256) >= PERSISTENT_TILES
-            and gemm_tcgen05_splits(tokens, features, k) == 1)
+            and gemm_tcgen05_splits(tokens, features, k, sms) == 1)
 
 
-def gemm_tcgen05_accumulate_pays(tokens: int, features: int, k: int) -> bool:
+def gemm_tcgen05_accumulate_pays(tokens: int, features: int, k: int, sms: int | None = None) -> bool:
     """Whether adding into the output inside the kernel is also the faster way: only where every CTA
     (or CTA pair) has at least two tiles, so that a tile's epilogue, which now waits for the old
     values, runs under the next tile's products.  Measured on a B200 with the 1B shape's output and
     down projections: 2,048 tokens (one tile per CTA pair) 5.19 -> 5.27 ms per prefill, 8,192 tokens
     (3.5 tiles per pair) 24.45 -> 24.13 ms."""
-    if not gemm_tcgen05_accumulates(tokens, features, k):
+    sms = sm_count() if sms is None else sms
+    if not gemm_tcgen05_accumulates(tokens, features, k, sms):
         return False
     if tokens >= PAIR_TOKENS:
-        return -(-tokens // 256) * -(-features // 256) >= 2 * (SM_COUNT // 2)
-    return -(-tokens // 128) * -(-features // 256) >= 2 * SM_COUNT
+        return -(-tokens // 256) * -(-features // 256) >= 2 * (sms // 2)
+    return -(-tokens // 128) * -(-features // 256) >= 2 * sms
 
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor, status: torch.Tensor,

@@ -14,6 +14,7 @@ import ctypes
 import hashlib
 import os
 import shutil
+import stat
 import subprocess
 import sys
 import tempfile
@@ -82,13 +83,46 @@ def build_dir() -> Path:
         return _build_dir
 
 
+def _temp_folder() -> Path:
+    return Path(tempfile.gettempdir()) / f"thintensor_b200-build-{os.getuid()}"
+
+
+def _is_private(folder: Path) -> bool:
+    """Whether libraries found in ``folder`` can be trusted: a real directory (no symbolic link)
+    that this user owns and that neither its group nor others may write to.  The system's temporary
+    directory is writable by everyone, so another user could have made a folder of the expected
+    name there first and put a library of the expected file name in it."""
+    try:
+        info = os.lstat(folder)
+    except OSError:
+        return False
+    return stat.S_ISDIR(info.st_mode) and info.st_uid == os.getuid() and not info.st_mode & (stat.S_IWGRP | stat.S_IWOTH)
+
+
+def _private_temp_folder() -> Path:
+    """The per-user folder under the temporary directory, made with mode 0700; if a folder of that
+    name exists that is not this user's alone, a fresh one that is (its libraries are then built
+    anew by every process)."""
+    folder = _temp_folder()
+    try:
+        os.mkdir(folder, 0o700)
+    except FileExistsError:
+        pass
+    if _is_private(folder):
+        return folder
+    return Path(tempfile.mkdtemp(prefix="thintensor_b200-build-"))     # mode 0700, owned by this user
+
+
 def _choose_build_dir() -> Path:
     override = os.environ.get("THINTENSOR_B200_BUILD_DIR")
-    candidates = [Path(override)] if override else []
-    candidates.append(CSRC.parent / "_build")
-    candidates.append(Path(tempfile.gettempdir()) / f"thintensor_b200-build-{os.getuid()}")
-    for folder in candidates:
+    candidates = [lambda: Path(override)] if override else []
+    candidates.append(lambda: CSRC.parent / "_build")
+    candidates.append(_private_temp_folder)
+    tried = []
+    for make in candidates:
         try:
+            folder = make()
+            tried.append(str(folder))
             folder.mkdir(parents=True, exist_ok=True)
             probe = folder / f".write-{os.getpid()}"
             probe.write_bytes(b"")
@@ -96,7 +130,7 @@ def _choose_build_dir() -> Path:
             return folder
         except OSError:
             continue
-    raise KernelBuildError(f"no writable folder for compiled kernels among {[str(c) for c in candidates]}")
+    raise KernelBuildError(f"no writable folder for compiled kernels among {tried}")
 
 
 def _digest(name: str) -> str:
@@ -113,14 +147,14 @@ def library_path(name: str, folder: Path | None = None) -> Path:
 
 
 def _find_built(name: str) -> Path | None:
-    """A current library for ``name`` in any of the places one may have been built."""
+    """A current library for ``name`` in the folder this process builds into, or in the package's
+    own folder (a library built there earlier serves a later user who may only read it).  The
+    folder under the temporary directory is searched only as the chosen build folder, which
+    :func:`_private_temp_folder` has checked to be this user's alone."""
     file = f"tt_{name}-{_digest(name)}.so"
-    for folder in (CSRC.parent / "_build", Path(tempfile.gettempdir()) / f"thintensor_b200-build-{os.getuid()}"):
+    for folder in (build_dir(), CSRC.parent / "_build"):
         if (folder / file).is_file():
             return folder / file
-    override = os.environ.get("THINTENSOR_B200_BUILD_DIR")
-    if override and (Path(override) / file).is_file():
-        return Path(override) / file
     return None
 
 

@@ -17,16 +17,16 @@ from .base import ARRANGEMENTS, Arrangement, Delta
 class PreNorm(Arrangement):
     roles = {"mixer_norm": "norm", "mixer": "mixer", "ffn_norm": "norm", "ffn": "ffn"}
 
-    def mixer(self):
-        return self.parts["mixer"]
+    def mixers(self):
+        return [self.parts["mixer"]]
 
-    def run(self, ctx, residual, pending: Delta | None, cache, state) -> Delta:
+    def run(self, ctx, residual, pending: Delta | None, caches, states) -> Delta:
         hidden = residual.shape[-1]
         # Between a part's output and the norm that follows nothing else reads the stream, so a part
         # may add its output into it directly instead of handing it on.
         ctx.residual = residual
         normed = ctx.scratch("block.normed", (ctx.n_tokens, hidden))
         self.parts["mixer_norm"].forward(ctx, residual, pending, normed)
-        mixed = self.parts["mixer"].forward(ctx, normed, cache, state)
+        mixed = self.parts["mixer"].forward(ctx, normed, caches[0], states[0])
         self.parts["ffn_norm"].forward(ctx, residual, mixed, normed)
         return self.parts["ffn"].forward(ctx, normed)

@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import api
-from .base import MIXERS, POSITION_ENCODINGS, Delta, KVNeed, Mixer, WeightDecl
+from .base import MIXERS, POSITION_ENCODINGS, Delta, KVNeed, Mixer, RotaryTable, WeightDecl
 from .linear import Linear
 from .spec import PartSpec
 
@@ -42,6 +42,9 @@ class CausalAttention(Mixer):
         self.scale = float(scale) if scale is not None else self.head_dim ** -0.5
         position = position or PartSpec("none", {"head_dim": self.head_dim})
         self.position = POSITION_ENCODINGS.build(position.kind, dict(position.params))
+        if self.position.kind not in ("rotary", "none"):
+            raise ValueError(f"attention applies rotary position encodings or none, not one of kind {self.position.kind!r}")
+        self.rot: RotaryTable | None = None         # what the kernels rotate by; rotary_dim 0 switches rotation off
         self.qkv: Linear | None = None
         self.q_only: Linear | None = None
         self.out: Linear | None = None
@@ -67,6 +70,12 @@ class CausalAttention(Mixer):
 
     def bind(self, tensors, dtype, device) -> None:
         self.position.bind({}, dtype, device)
+        if self.position.kind == "rotary":
+            self.rot = self.position.rotary()
+            if self.rot.rotary_dim % 2 or not 0 <= self.rot.rotary_dim <= self.head_dim:
+                raise ValueError(f"the rotary part must be even and at most the head size {self.head_dim}, got {self.rot.rotary_dim}")
+        else:
+            self.rot = RotaryTable(torch.zeros(1, dtype=torch.float32, device=device), 0, 1.0)
         weight = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]], dim=0)
         bias = None
         if self.bias:
@@ -75,28 +84,31 @@ class CausalAttention(Mixer):
         self.q_only = self.qkv.rows(0, self.heads * self.head_dim)
         self.out = Linear(tensors["o_proj.weight"], tensors["o_proj.bias"] if self.bias else None)
 
+    def projections(self) -> list:
+        return [self.qkv, self.out]             # q_only is a view of qkv's first rows
+
     # ------------------------------------------------------------------- running
-    def forward(self, ctx, x, cache, state) -> Delta:
+    def forward(self, ctx, x, cache, states) -> Delta:
         if cache is None or cache.k_pool is None:
             raise RuntimeError("attention needs a cache with storage")
         table = ctx.tables[cache.group]
         q_cols = self.heads * self.head_dim
         projection = (self.qkv if cache.writes else self.q_only)(ctx, x, "attention.qkv")
         mixed = ctx.scratch("attention.mixed", (ctx.n_tokens, q_cols))
-        position = self.position
+        rot = self.rot
         splits = self.decode_slices(ctx)
-        if (ctx.decode and ctx.sequences * self.kv_heads * splits <= api.SM_COUNT
-                and api.attention_decode_rope_supports(mixed.dtype, self.heads, self.kv_heads, self.head_dim, position.rotary_dim)):
+        if (ctx.decode and ctx.sequences * self.kv_heads * splits <= api.sm_count(x.device)
+                and api.attention_decode_rope_supports(mixed.dtype, self.heads, self.kv_heads, self.head_dim, rot.rotary_dim)):
             # decoding: rotation, cache write and attention in one kernel.  Every CTA pays the
             # rotation's latency before it can start on its keys, which is hidden while all CTAs
             # run at once (measured on a B200: 2 % faster at 32 and at 64 CTAs, 8 % slower at 512).
             part_acc, part_ml = self.slice_scratch(ctx, splits)
-            api.attention_decode_rope(projection, position.inv_freq, position.rotary_dim, position.attention_scaling, cache.writes,
+            api.attention_decode_rope(projection, rot.inv_freq, rot.rotary_dim, rot.attention_scaling, cache.writes,
                                       cache.k_pool, cache.v_pool, table, ctx.len_before, ctx.sequences, self.heads, self.kv_heads,
                                       self.head_dim, self.scale, self.window or 0, splits, mixed, part_acc, part_ml, ctx.status)
             return self.out.delta(ctx, mixed, "attention.out")
         q = ctx.scratch("attention.q", (ctx.n_tokens, q_cols))
-        api.rope_append(projection, self.position.inv_freq, self.position.rotary_dim, self.position.attention_scaling, q,
+        api.rope_append(projection, rot.inv_freq, rot.rotary_dim, rot.attention_scaling, q,
                         cache.k_pool if cache.writes else None, cache.v_pool if cache.writes else None, table, ctx.cu,
                         ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads, self.kv_heads, self.head_dim, ctx.status)
         self.attend(ctx, q, cache, table, mixed)
@@ -107,7 +119,7 @@ class CausalAttention(Mixer):
         head, slice).  Measured on a B200 from 1 to 64 sequences and 2,048 to 32,768 keys: a step is
         fastest when the slices just fill one wave of one CTA per SM and keep at least 8 blocks each; a
         second wave gains nothing."""
-        return kv_splits(ctx, ctx.sequences * self.kv_heads, 512, api.SM_COUNT)
+        return kv_splits(ctx, ctx.sequences * self.kv_heads, 512, api.sm_count(ctx.tokens.device))
 
     def slice_scratch(self, ctx, splits: int):
         """Where the slices of the keys leave their partial results (nothing for one slice)."""
@@ -128,7 +140,7 @@ class CausalAttention(Mixer):
         if tensor_cores:
             splits = self.decode_slices(ctx)
         else:
-            splits = kv_splits(ctx, ctx.n_tokens * self.heads, 256, 8 * api.SM_COUNT)
+            splits = kv_splits(ctx, ctx.n_tokens * self.heads, 256, 8 * api.sm_count(q.device))
         part_acc, part_ml = self.slice_scratch(ctx, splits)
         if tensor_cores:
             api.attention_mma(q, cache.k_pool, cache.v_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads,

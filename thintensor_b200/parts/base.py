@@ -11,10 +11,12 @@ Roles and what each must provide:
 * ``Norm``: ``forward(ctx, residual, delta, out, rows=None)`` adds ``delta`` (the not
   yet added output of the part before it, possibly several partial sums) into the
   float32 residual stream and writes the normalised rows to ``out``.
-* ``PositionEncoding``: an object a mixer is given at construction; for rotary
-  encodings a float32 table of inverse frequencies that the mixer's kernels use.
-* ``Mixer``: ``forward(ctx, x, cache, state) -> Delta``; declares with
-  ``cache_need()`` / ``state_need()`` what the cache must hold for it.
+* ``PositionEncoding``: an object a mixer is given at construction.  Its ``kind`` says how
+  positions enter the mixer (``"rotary"``: queries and keys are rotated, the mixer's kernels
+  take the table that ``rotary()`` returns; ``"none"``); a mixer refuses kinds it cannot apply.
+* ``Mixer``: ``forward(ctx, x, cache, states) -> Delta``; declares with ``cache_need()`` /
+  ``state_needs()`` what the cache must hold for it: keys and values, and any number of
+  per-sequence state tensors of fixed size, each with a shape and dtype of its own.
 * ``FeedForward``: ``forward(ctx, x) -> Delta``.
 * ``Embedding``: ``forward(ctx, tokens, residual)``; ``Head``: ``forward(ctx, x) -> logits``.
 * ``Arrangement``: wires norms, mixer and feed-forward around the residual stream.
@@ -87,24 +89,55 @@ class Part:
         unless the engine runs in float32, ``dtype`` being the activation dtype) and
         prepare what kernels need."""
 
+    def projections(self) -> list:
+        """The part's weight matrices as :class:`~thintensor_b200.parts.linear.Linear` objects, each
+        listed once and each multiplied with every token once per step: what the byte and FLOP
+        models of the benchmarks count.  A view of another projection's rows is not listed."""
+        return []
+
+    def vectors(self) -> list[torch.Tensor]:
+        """Other tensors a step reads once whatever its tokens (a norm's weight)."""
+        return []
+
 
 class Norm(Part):
     def forward(self, ctx, residual: torch.Tensor, delta: Delta | None, out: torch.Tensor, rows: torch.Tensor | None = None) -> None:
         raise NotImplementedError
 
 
+@dataclass(frozen=True)
+class RotaryTable:
+    """What a kernel needs to rotate queries and keys: ``inv_freq`` float32 ``[rotary_dim / 2]`` on
+    the device (the angle of pair i at position p is ``p * inv_freq[i]``), ``rotary_dim`` numbers at
+    the front of each head are rotated (0: none), cosine and sine are multiplied by
+    ``attention_scaling``."""
+
+    inv_freq: torch.Tensor
+    rotary_dim: int
+    attention_scaling: float = 1.0
+
+
 class PositionEncoding(Part):
-    pass
+    """``kind`` is one of ``"rotary"`` and ``"none"``.  A rotary encoding implements ``rotary()``
+    (valid after ``bind``); other kinds of encoding (learned tables, additive biases) would add a
+    kind and the method that goes with it, and the mixers that can apply it would accept the kind."""
+
+    kind: str = "none"
+
+    def rotary(self) -> RotaryTable:
+        raise NotImplementedError(f"a position encoding of kind {self.kind!r} has no rotary table")
 
 
 class Mixer(Part):
     def cache_need(self) -> KVNeed | None:
         return None
 
-    def state_need(self) -> StateNeed | None:
-        return None
+    def state_needs(self) -> list[StateNeed]:
+        """Per-sequence state tensors of fixed size, zero when a sequence starts; ``forward`` gets
+        one tensor ``[slots, *shape]`` for each, in this order."""
+        return []
 
-    def forward(self, ctx, x: torch.Tensor, cache, state) -> Delta:
+    def forward(self, ctx, x: torch.Tensor, cache, states: list[torch.Tensor]) -> Delta:
         raise NotImplementedError
 
 
@@ -132,10 +165,13 @@ class Arrangement:
     def __init__(self, parts: dict[str, Part]):
         self.parts = parts
 
-    def mixer(self) -> Mixer | None:
-        return None
+    def mixers(self) -> list[Mixer]:
+        """The layer's mixers (a layer with an attention and a recurrent branch side by side has
+        two); each gets a cache and states of its own."""
+        return []
 
-    def run(self, ctx, residual: torch.Tensor, pending: Delta | None, cache, state) -> Delta | None:
+    def run(self, ctx, residual: torch.Tensor, pending: Delta | None, caches: list, states: list[list[torch.Tensor]]) -> Delta | None:
+        """``caches[i]`` and ``states[i]`` belong to ``mixers()[i]``."""
         raise NotImplementedError
 
 

@@ -49,6 +49,9 @@ class LinearHead(Head):
     def bind(self, tensors, dtype, device) -> None:
         self.linear = Linear(tensors["weight"], tensors.get("bias"))
 
+    def projections(self) -> list:
+        return [self.linear]
+
     def forward(self, ctx, x) -> torch.Tensor:
         """Float32 logits ``[rows, vocab]``: in ``ctx.logits_out`` where the step gave one and the
         product could write there, else in scratch memory."""

@@ -30,6 +30,9 @@ class SwiGLU(FeedForward):
                                    tensors.get("gate_proj.bias"), tensors.get("up_proj.bias"))
         self.down = Linear(tensors["down_proj.weight"], tensors.get("down_proj.bias"))
 
+    def projections(self) -> list:
+        return [self.gate_up.fused, self.down]
+
     def forward(self, ctx, x) -> Delta:
         act = self.gate_up(ctx, x, "ffn.gate_up")
         return self.down.delta(ctx, act, "ffn.down")

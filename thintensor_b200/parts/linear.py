@@ -40,6 +40,7 @@ class Linear:
             raise ValueError(f"{name}: input has {x.shape[1]} features, the weight takes {self.in_features}")
         if into is not None and (into.dtype != torch.float32 or tuple(into.shape) != (tokens, self.out_features) or not into.is_contiguous()):
             raise ValueError(f"{name}: the given output must be contiguous float32 [{tokens}, {self.out_features}]")
+        api.set_label(name)
         if api.gemm_tcgen05_usable(x, self.weight):
             splits = api.gemm_tcgen05_splits(tokens, self.out_features, self.in_features)
             if splits == 1 and into is not None:
@@ -60,6 +61,7 @@ class Linear:
         residual = getattr(ctx, "residual", None)
         if (residual is not None and residual.shape == (x.shape[0], self.out_features) and api.gemm_tcgen05_usable(x, self.weight)
                 and api.gemm_tcgen05_accumulate_pays(x.shape[0], self.out_features, self.in_features)):
+            api.set_label(name)
             api.gemm_tcgen05(x, self.weight, self.bias, residual.unsqueeze(0), ctx.status, operands_checked=True, accumulate=True)
             return Delta(None)
         return Delta(self(ctx, x, name))
@@ -86,6 +88,7 @@ class GatedLinear:
             # the float32 gate/up never reach global memory.  With few tokens this form cannot cut k
             # into slices, so it is taken only where the plain product would not slice either
             # (measured on a B200: 3 % faster for 14336 x 4096 at 8 tokens, 2 % slower for 8192 x 2048).
+            api.set_label(name)
             api.gemm_tcgen05_swiglu(x, w.weight, act, ctx.status)
             return act
         api.swiglu(w(ctx, x, name), act)

@@ -27,5 +27,8 @@ class RMSNorm(Norm):
     def bind(self, tensors, dtype, device) -> None:
         self.weight = tensors["weight"].to(torch.float32).contiguous()
 
+    def vectors(self) -> list[torch.Tensor]:
+        return [self.weight]
+
     def forward(self, ctx, residual, delta: Delta | None, out, rows=None) -> None:
         api.add_rmsnorm(residual, None if delta is None else delta.tensor, self.weight, self.eps, out, rows, self.weight_offset)   # an empty delta is already in the stream

@@ -15,7 +15,7 @@ import math
 
 import torch
 
-from .base import POSITION_ENCODINGS, PositionEncoding
+from .base import POSITION_ENCODINGS, PositionEncoding, RotaryTable
 
 
 def llama3_scale(inv_freq: torch.Tensor, factor: float, low_freq_factor: float, high_freq_factor: float, original: int) -> torch.Tensor:
@@ -31,6 +31,8 @@ class RotaryEncoding(PositionEncoding):
     """``rotary_dim`` numbers at the front of each head are rotated (all of them by
     default); ``scaling`` is None or a dict with ``rope_type`` and that type's numbers."""
 
+    kind = "rotary"
+
     def __init__(self, head_dim: int, theta: float, rotary_dim: int | None = None, scaling: dict | None = None,
                  attention_scaling: float = 1.0):
         self.head_dim = int(head_dim)
@@ -41,7 +43,7 @@ class RotaryEncoding(PositionEncoding):
         self.scaling = dict(scaling) if scaling else None
         self.attention_scaling = float(attention_scaling)
         self.inv_freq_host = self._table()
-        self.inv_freq: torch.Tensor | None = None
+        self._rotary: RotaryTable | None = None
 
     def _table(self) -> torch.Tensor:
         index = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32)
@@ -56,18 +58,19 @@ class RotaryEncoding(PositionEncoding):
         raise ValueError(f"rotary scaling of type {kind!r} is not implemented")
 
     def bind(self, tensors, dtype, device) -> None:
-        self.inv_freq = self.inv_freq_host.to(device)
+        self._rotary = RotaryTable(self.inv_freq_host.to(device), self.rotary_dim, self.attention_scaling)
+
+    def rotary(self) -> RotaryTable:
+        if self._rotary is None:
+            raise RuntimeError("the rotary table exists once the encoding has been bound to a device")
+        return self._rotary
 
 
 @POSITION_ENCODINGS.register("none")
 class NoEncoding(PositionEncoding):
     """No position encoding: queries and keys go to the cache as projected."""
 
+    kind = "none"
+
     def __init__(self, head_dim: int):
         self.head_dim = int(head_dim)
-        self.rotary_dim = 0
-        self.attention_scaling = 1.0
-        self.inv_freq: torch.Tensor | None = None
-
-    def bind(self, tensors, dtype, device) -> None:
-        self.inv_freq = torch.zeros(1, dtype=torch.float32, device=device)

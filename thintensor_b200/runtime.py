@@ -139,7 +139,11 @@ def save_random_model(folder: str | Path, config, seed: int = 0, dtype: str = "b
 def random_model(config, seed: int = 0, dtype="bf16", device="cuda") -> Runtime:
     """A runtime whose weights are drawn on the device (N(0, 0.02), norm weights
     1 + N(0, 0.1)) without writing a folder: for benchmarks at sizes whose files would
-    take minutes to write.  ``config`` is a config.json dict or a typed configuration."""
+    take minutes to write.  ``config`` is a config.json dict or a typed configuration.
+
+    The numbers are NOT those :func:`save_random_model` writes for the same seed: this function
+    draws with the device's generator, that one with the host's, tensor by tensor in the same order.
+    Use a written folder wherever another implementation has to see the same weights."""
     torch_dtype = parse_dtype(dtype)
     device = require_cuda(device)
     arch, config = load_config(config if isinstance(config, dict) else config.to_dict())
