@@ -22,7 +22,7 @@ SHAPES = {
 }
 
 
-def write_model(folder, shape, stored):
+def write_model(folder, shape, stored, layers=2, vocab=4099):
     import thintensor_b200
     from thintensor_b200.weights.safetensors_io import write_safetensors
     from thintensor_b200.config.registry import load_config
@@ -30,7 +30,7 @@ def write_model(folder, shape, stored):
 
     s = SHAPES[shape]
     raw = {
-        "architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 2, "vocab_size": 4099,
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": layers, "vocab_size": vocab,
         "hidden_size": s["hidden_size"], "num_attention_heads": s["num_attention_heads"], "num_key_value_heads": s["num_key_value_heads"],
         "head_dim": s["head_dim"], "intermediate_size": s["intermediate_size"], "rope_theta": 500000.0, "rms_norm_eps": 1e-5,
         "rope_scaling": {"rope_type": "llama3", "factor": s["factor"], "low_freq_factor": 1.0, "high_freq_factor": 4.0,
@@ -93,11 +93,14 @@ def test_bfloat16_real_layer_sizes(tmp_path, shape):
     assert_close(torch.stack([got[p] for p in places]), want, "bfloat16", f"{shape} shape")
 
 
-def test_float32_real_layer_sizes(tmp_path):
+@pytest.mark.parametrize("shape", ["1b", "3b", "8b"])
+def test_float32_real_layer_sizes(tmp_path, shape):
+    """The true 32-bit path at the three layer sizes (two layers each): head sizes 64 and 128, groups of
+    3 and 4 query heads, k = 8,192 and 14,336 through the exact product and the exact attention."""
     import thintensor_b200
     from thintensor_b200.engine.engine import Entry
 
-    folder = write_model(tmp_path / "m", "1b", "float32")
+    folder = write_model(tmp_path / "m", shape, "float32")
     runtime = thintensor_b200.load_model(folder, dtype="fp32")
     engine = runtime.new_engine(max_tokens=512, max_sequences=1)
     tokens = token_ids(4099, 150, 33)
@@ -112,7 +115,7 @@ def test_float32_real_layer_sizes(tmp_path):
         got[t] = engine.step([Entry(slot, [tokens[t]], [0])])[0]
     engine.close(slot)
     engine.check_status()
-    assert_close(torch.stack([got[p] for p in places]), want, "float32", "1b shape in float32")
+    assert_close(torch.stack([got[p] for p in places]), want, "float32", f"{shape} shape in float32")
 
 
 def test_long_prompt_whole_and_in_pieces(tmp_path):

@@ -73,6 +73,7 @@ struct Args {
     int k_blocks_per_split;
     int up_row_offset;       // SWIGLU: row of w where the up projection starts (= features of the output)
     int accumulate;          // persistent and pair kernels, plain form: out += product instead of out = product
+    int undelivered_bytes;   // 0 in every real call; tests: the first stage's barrier expects this many bytes that no copy brings
     unsigned* status;
 };
 
@@ -128,7 +129,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int first = min(n_kb, STAGES);
             for (int i = 0; i < first; ++i) {               // stages are empty: nothing to wait for
                 const uint32_t bar = smem_u32(&full_bar[i]);
-                mbar_expect_tx(bar, S::stage_bytes);
+                mbar_expect_tx(bar, S::stage_bytes + (i == 0 ? args.undelivered_bytes : 0));
                 uint8_t* stage = smem + (size_t)i * S::stage_bytes;
                 const int kx = (kb_begin + i) * BK;
                 if (weights_are_a) {
@@ -732,7 +733,17 @@ int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const Args& 
     return err != cudaSuccess ? (int)err : (int)cudaGetLastError();
 }
 
+int undelivered_bytes_for_tests = 0;
+
 }  // namespace
+
+// For tests of the failure path only.  The limit of every bounded wait in this library, in
+// nanoseconds (0: back to the default of two seconds).
+extern "C" int tt_gemm_tcgen05_set_wait_limit_ns(unsigned long long ns) { return tc::set_wait_limit_ns(ns); }
+// From now on the first stage of every CTA of the few-token and small-prompt kernel expects `bytes`
+// more than its copies deliver (0: back to normal): its barrier never completes, every wait on
+// it runs out, and the kernel has to raise TT_STATUS_WAIT_EXPIRED, free its tensor memory and return.
+extern "C" void tt_gemm_tcgen05_expect_undelivered_bytes(int bytes) { undelivered_bytes_for_tests = bytes < 0 ? 0 : bytes; }
 
 // How many tokens the features-on-m form takes at most.
 extern "C" int tt_gemm_tcgen05_max_skinny_tokens() { return 128; }
@@ -758,6 +769,7 @@ extern "C" int tt_gemm_tcgen05(const void* x, long long ldx, const void* w, long
     args.k_blocks_per_split = (k_blocks + splits - 1) / splits;
     args.up_row_offset = features; args.status = status;
     args.accumulate = form == 2 ? 1 : 0;
+    args.undelivered_bytes = undelivered_bytes_for_tests;
     CUtensorMap map_a, map_b;
     const int tiles_m = (tokens + BM - 1) / BM;
     if (form == 2 && !(tokens > 128 && tiles_m * ((features + 255) / 256) >= 8 && splits == 1)) return (int)cudaErrorInvalidValue;

@@ -13,6 +13,9 @@ namespace tc {
 // data that can only be fetched once that kernel is done), so the limit is generous; it exists
 // so that a fault in the protocol ends in an error status within seconds, not in a hung GPU.
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+// The limit in force, one copy per library that includes this header; a library may offer an entry
+// point that sets it (set_wait_limit_ns below), which tests use to make a wait run out in milliseconds.
+static __device__ unsigned long long wait_limit_ns = WAIT_LIMIT_NS;
 
 __device__ __forceinline__ unsigned long long global_time_ns() {
     unsigned long long t;
@@ -48,7 +51,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     for (;;) {
         for (int i = 0; i < 64; ++i)
             if (mbar_try(bar, parity)) return true;
-        if (global_time_ns() - start > WAIT_LIMIT_NS) return false;
+        if (global_time_ns() - start > wait_limit_ns) return false;
     }
 }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
@@ -203,6 +206,12 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
 // Instruction descriptor: float32 accumulator, bfloat16 a and b, both k-major, M x N.
 __host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// Set this library's wait limit on the current device (0 restores the default); returns a cudaError_t value.
+inline int set_wait_limit_ns(unsigned long long ns) {
+    const unsigned long long value = ns ? ns : WAIT_LIMIT_NS;
+    return (int)cudaMemcpyToSymbol(wait_limit_ns, &value, sizeof(value));
 }
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda).

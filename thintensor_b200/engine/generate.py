@@ -228,6 +228,7 @@ class _DecodeState:
         self.feed = self.host_in.numpy()                      # the same memory, written without a tensor in between
         self.fetched = self.host_out.numpy()
         self.warm = False
+        self.logits: torch.Tensor | None = None  # the last step's logits
         self.launches_per_step = 0              # kernels of this library in one decode step
 
     @property
@@ -273,6 +274,7 @@ class _DecodeState:
         """One decode step, entirely on the device."""
         e = self.engine
         logits = e.model.forward(self.context(), e.cache, self.rows)
+        self.logits = logits                    # float32 [sequences, vocab]; a replayed step writes to the same place
         sample(logits, params, self.requests, self.steps, self.tokens)
         api.advance_lengths(self.lengths, self.cu, self.sequences, self.steps)
 

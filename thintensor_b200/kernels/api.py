@@ -497,6 +497,24 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, ou
               out.shape[0], 2 if accumulate else 0, _ptr(status), _stream()), "gemm_tcgen05")
 
 
+def gemm_tcgen05_failure_drill(wait_limit_ns: int, undelivered_bytes: int) -> None:
+    """For tests of the failure path, never for serving.  ``wait_limit_ns``: the limit of every
+    bounded wait in the tensor-core product kernels (0 restores the default of two seconds).
+    ``undelivered_bytes``: from now on the first stage of the few-token and small-prompt kernel
+    expects that many bytes more than its copies bring (0 restores normal operation), so its
+    barrier never completes; the kernel must then raise ``STATUS_WAIT_EXPIRED``, free what it
+    holds and return."""
+    lib = build.load("gemm_tcgen05")
+    lib.tt_gemm_tcgen05_set_wait_limit_ns.argtypes = [c_ulonglong]
+    lib.tt_gemm_tcgen05_set_wait_limit_ns.restype = c_int
+    lib.tt_gemm_tcgen05_expect_undelivered_bytes.argtypes = [c_int]
+    lib.tt_gemm_tcgen05_expect_undelivered_bytes.restype = None
+    code = lib.tt_gemm_tcgen05_set_wait_limit_ns(int(wait_limit_ns))
+    if code != 0:
+        raise KernelError(f"setting the wait limit failed: CUDA error {code}")
+    lib.tt_gemm_tcgen05_expect_undelivered_bytes(int(undelivered_bytes))
+
+
 def gemm_tcgen05_swiglu(x: torch.Tensor, w: torch.Tensor, act: torch.Tensor, status: torch.Tensor) -> None:
     """act = silu(x @ gate.T) * (x @ up.T) in bfloat16, where ``w`` [2 * inter, k] holds
     the gate rows followed by the up rows; the activation never exists in float32 in
