@@ -154,3 +154,85 @@ def test_linear_uses_it_and_matches_exact_kernel():
     api.gemm_simt(x, w, None, exact)
     torch.testing.assert_close(got, exact[0], rtol=1e-4, atol=1e-3)
     assert api.launch_count() - before == 2
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,k,news,before", [
+    (32, 8, 64, 2048, [2048], [0]),                       # CTA pairs, the 1B shape
+    (8, 2, 64, 512, [700, 1, 1400], [0, 130, 64]),        # persistent kernel below the pairs' range is not taken (few tiles) ...
+    (24, 8, 128, 1024, [1000, 1200], [5, 0]),             # ... but 2,200 tokens are: head size 128, two sequences, one with a cached prefix
+    (4, 2, 64, 256, [2300], [77]),                        # a tile that holds q heads, k heads and v heads side by side
+    (32, 8, 128, 4096, [1900], [0]),                      # the persistent kernel with at least as many tiles as SMs (8B shape)
+])
+def test_qkv_product_rotates_and_appends_in_its_epilogue(heads, kv_heads, head_dim, k, news, before):
+    """The qkv form of the prompt kernels against the separate path (product to float32, then the rotary/append
+    kernel) and against plain float64 arithmetic: rotated q, rotated k in the cache at every token's position,
+    v transposed inside its block; sequences packed back to back, some behind a cached prefix, blocks scattered."""
+    import math
+
+    from thintensor_b200.kernels import api
+
+    tokens = sum(news)
+    q_cols, kv_cols = heads * head_dim, kv_heads * head_dim
+    x = randn(tokens, k, seed=31, scale=0.5)
+    w = randn(q_cols + 2 * kv_cols, k, seed=32, scale=0.05)
+    bias = torch.randn(q_cols + 2 * kv_cols, device=DEV) * 0.3 if head_dim == 128 else None
+    if not api.gemm_tcgen05_qkv_rope_takes(x, w, head_dim, head_dim):
+        assert tokens < 2048 and -(-tokens // 128) * -(-(q_cols + 2 * kv_cols) // 256) < api.sm_count()
+        pytest.skip("few tiles below the pairs' range: the separate kernels serve this shape")
+    inv_freq = (10000.0 ** (-torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim)).to(DEV)
+    totals = [b + n for b, n in zip(before, news)]
+    blocks_per = [-(-t // 64) for t in totals]
+    g = torch.Generator().manual_seed(33)
+    order = torch.randperm(sum(blocks_per) + 2, generator=g).tolist()
+    table = torch.full((len(news), max(blocks_per)), -1, dtype=torch.int32)
+    at = 0
+    for b, count in enumerate(blocks_per):
+        for j in range(count):
+            table[b, j] = order[at]
+            at += 1
+    table = table.to(DEV)
+    pool_blocks = sum(blocks_per) + 2
+    cu = torch.tensor([0] + torch.tensor(news).cumsum(0).tolist(), dtype=torch.int32, device=DEV)
+    len_before = torch.tensor(before, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scaling = 0.75
+
+    def pools():
+        return (torch.zeros(pool_blocks, kv_heads, 64, head_dim, dtype=torch.bfloat16, device=DEV),
+                torch.zeros(pool_blocks, kv_heads, head_dim, 64, dtype=torch.bfloat16, device=DEV))
+
+    # the separate kernels
+    product = torch.empty(1, tokens, q_cols + 2 * kv_cols, dtype=torch.float32, device=DEV)
+    api.gemm_tcgen05(x, w, bias, product, status)
+    q_want = torch.empty(tokens, q_cols, dtype=torch.bfloat16, device=DEV)
+    k_want, v_want = pools()
+    api.rope_append(product, inv_freq, head_dim, scaling, q_want, k_want, v_want, table, cu, len_before, len(news), tokens, heads, kv_heads, head_dim, status)
+    # the fused form
+    cos_sin = torch.empty(tokens, head_dim // 2, 2, dtype=torch.float32, device=DEV)
+    where = torch.empty(tokens, 2, dtype=torch.int32, device=DEV)
+    api.rope_table(inv_freq, head_dim, cu, len_before, len(news), tokens, cos_sin, where)
+    q_got = torch.full((tokens, q_cols), float("nan"), dtype=torch.bfloat16, device=DEV)
+    k_got, v_got = pools()
+    api.gemm_tcgen05_qkv_rope(x, w, bias, q_got, k_got, v_got, cos_sin, where, table, heads, kv_heads, head_dim, scaling, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    positions = torch.cat([torch.arange(b, b + n) for b, n in zip(before, news)])
+    assert torch.equal(where[:, 0].cpu(), positions.to(torch.int32))
+    tolerance = dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(q_got.float(), q_want.float(), **tolerance)
+    torch.testing.assert_close(k_got.float(), k_want.float(), **tolerance)
+    torch.testing.assert_close(v_got.float(), v_want.float(), **tolerance)
+    # and the formula itself at a few tokens, float64
+    full = x.double().cpu() @ w.double().cpu().T + (bias.double().cpu() if bias is not None else 0)
+    for t in (0, tokens // 2, tokens - 1):
+        pos = int(positions[t])
+        angle = inv_freq.double().cpu() * pos
+        cos, sin = angle.cos() * scaling, angle.sin() * scaling
+        head = full[t, :head_dim]
+        a, b = head[: head_dim // 2], head[head_dim // 2:]
+        want = torch.cat([a * cos - b * sin, b * cos + a * sin])
+        torch.testing.assert_close(q_got[t, :head_dim].double().cpu(), want, rtol=3e-2, atol=3e-2)
+        sequence = next(i for i in range(len(news)) if t < int(cu[i + 1]))
+        block = int(table[sequence, pos // 64])
+        vrow = full[t, q_cols + kv_cols: q_cols + kv_cols + head_dim]
+        torch.testing.assert_close(v_got[block, 0, :, pos % 64].double().cpu(), vrow, rtol=3e-2, atol=3e-2)

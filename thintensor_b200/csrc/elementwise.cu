@@ -420,6 +420,38 @@ extern "C" int tt_rope_append(const float* qkv, int splits, long long split_stri
 }
 
 // ------------------------------------------------------------------------------------
+// What every layer's rotation of a step has in common, computed once per step: for packed token t
+// its position p = len_before[b] + (t - cu[b]), its sequence b, and cos and sin of inv_freq[i] * p
+// (float32 angle, as in the kernels above).  The tensor-core qkv product's epilogue reads these
+// instead of finding the sequence and calling sincosf again in each of the model's layers.
+//   cos_sin: float2 [tokens][half]; where: int2 [tokens] = (position, sequence)
+// ------------------------------------------------------------------------------------
+__global__ void rope_table_kernel(const float* __restrict__ inv_freq, int half, const int* __restrict__ cu,
+                                  const int* __restrict__ len_before, int sequences, float2* __restrict__ cos_sin,
+                                  int2* __restrict__ where) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
+    const int t = blockIdx.x;
+    const int b = tt_find_sequence(cu, sequences, t);
+    const int pos = len_before[b] + (t - cu[b]);
+    if (threadIdx.x == 0) where[t] = make_int2(pos, b);
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float si, co;
+        sincosf(__ldg(inv_freq + i) * (float)pos, &si, &co);
+        cos_sin[(size_t)t * half + i] = make_float2(co, si);
+    }
+}
+
+extern "C" int tt_rope_table(const float* inv_freq, int half, const int* cu, const int* len_before, int sequences, int n_tokens,
+                             void* cos_sin, void* where, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (half <= 0) return (int)cudaErrorInvalidValue;
+    const int threads = half >= 64 ? 64 : 32;
+    tt_launch_pdl(rope_table_kernel, dim3(n_tokens), dim3(threads), 0, stream, inv_freq, half, cu, len_before, sequences, (float2*)cos_sin, (int2*)where);
+    TT_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
 // SwiGLU: act[t, j] = silu(gate[t, j]) * up[t, j], silu(g) = g / (1 + exp(-g)).
 // gate_up: float32 [splits][tokens][2 * inter], gate columns first.
 // ------------------------------------------------------------------------------------

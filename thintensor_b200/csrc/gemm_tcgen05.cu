@@ -51,7 +51,7 @@ constexpr int BK = 64;           // k elements per stage: 128 bytes, one swizzle
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 
-enum Form { TOKENS_ON_M = 0, TOKENS_ON_M_SWIGLU = 1, FEATURES_ON_M = 2, FEATURES_ON_M_SWIGLU = 3 };
+enum Form { TOKENS_ON_M = 0, TOKENS_ON_M_SWIGLU = 1, FEATURES_ON_M = 2, FEATURES_ON_M_SWIGLU = 3, TOKENS_ON_M_QKV = 4 };
 
 using namespace tc;
 
@@ -64,6 +64,22 @@ template <int FORM, int BN> struct Shape {
     static constexpr int tmem_cols = acc_cols < 32 ? 32 : acc_cols;
 };
 
+// Where the qkv form of the prompt kernels sends its output instead of a float32 matrix: the columns
+// are q heads, then k heads, then v heads of head_dim numbers each; q and k are rotated (all of a head,
+// halves convention) with the step's table of cosines and sines, q goes to q_out in bfloat16 and k and v
+// into the block cache at the token's position (values transposed inside a block, see common.cuh).
+struct QkvRope {
+    __nv_bfloat16* q_out;    // [tokens][q_cols]
+    __nv_bfloat16* k_pool;
+    __nv_bfloat16* v_pool;
+    const float2* cos_sin;   // [tokens][head_dim / 2]: (cos, sin) of inv_freq[i] * position
+    const int2* where;       // [tokens]: (position, sequence)
+    const int* table;        // [sequences][table_width] block ids
+    int table_width, pool_blocks;
+    int q_cols, kv_cols, kv_heads;
+    float attention_scaling;
+};
+
 struct Args {
     const float* bias;       // float32 [features] or null
     void* out;               // float32 partial sums, or bfloat16 activations (SWIGLU)
@@ -73,6 +89,8 @@ struct Args {
     int k_blocks_per_split;
     int up_row_offset;       // SWIGLU: row of w where the up projection starts (= features of the output)
     int accumulate;          // persistent and pair kernels, plain form: out += product instead of out = product
+    QkvRope rope;            // qkv form only
+    int rope_head_dim;       // 64 or 128
     int undelivered_bytes;   // 0 in every real call; tests: the first stage's barrier expects this many bytes that no copy brings
     unsigned* status;
 };
@@ -366,6 +384,85 @@ __device__ __forceinline__ void store_accumulator(uint32_t lane_addr, int token,
     }
 }
 
+// The qkv form's epilogue for one thread = one token's row of a 128 x 256 accumulator, whose 256 / HD
+// heads each lie inside the tile (HD = 64 or 128).  A head's rotation pairs dimension d with d + HD / 2:
+// the two come from tensor-memory chunks j and j + HD / 64 of the head, so a thread holds both.  The
+// arithmetic is that of rope_append_vec_kernel (elementwise.cu).  Tensor-memory loads are
+// warp-collective: every lane runs them, valid row or not.
+template <int HD>
+__device__ __forceinline__ void store_qkv_rope(uint32_t lane_addr, int token, int f_base, const Args& args) {
+    constexpr int CH = HD / 32, HALF = HD / 2;
+    const QkvRope& r = args.rope;
+    const bool live = token < args.tokens;
+    int block = -1, slot = 0;
+    const float2* cs = r.cos_sin;
+    if (live) {
+        const int2 w = __ldg(r.where + token);
+        const int entry = __ldg(r.table + (size_t)w.y * r.table_width + w.x / TT_BLOCK_TOKENS);
+        if (entry < 0 || entry >= r.pool_blocks) atomicOr(args.status, TT_STATUS_BAD_BLOCK);
+        else block = entry;
+        slot = w.x % TT_BLOCK_TOKENS;
+        cs += (size_t)token * HALF;
+    }
+    const float k = r.attention_scaling;
+    for (int h = 0; h < 256 / HD; ++h) {
+        const int col0 = f_base + h * HD;                       // the head's first column: the same for the whole CTA
+        if (col0 >= args.features) break;
+        const uint32_t head_addr = lane_addr + h * HD;
+        if (col0 < r.q_cols + r.kv_cols) {
+            // a query head or a key head: rotate, narrow, store 64 contiguous bytes per chunk
+            __nv_bfloat16* dst = nullptr;
+            if (live) {
+                if (col0 < r.q_cols) dst = r.q_out + (size_t)token * r.q_cols + col0;
+                else if (block >= 0) dst = r.k_pool + (((size_t)block * r.kv_heads + (col0 - r.q_cols) / HD) * TT_BLOCK_TOKENS + slot) * HD;
+            }
+#pragma unroll
+            for (int j = 0; j < CH / 2; ++j) {
+                float a[32], b[32];
+                tmem_load32(head_addr + j * 32, a);
+                tmem_load32(head_addr + HALF + j * 32, b);
+                if (!dst) continue;
+                if (args.bias) {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) { a[e] += args.bias[col0 + j * 32 + e]; b[e] += args.bias[col0 + HALF + j * 32 + e]; }
+                }
+#pragma unroll
+                for (int e0 = 0; e0 < 32; e0 += 8) {                // eight pairs at a time: one 16-byte store for each half
+                    uint32_t lo[4], hi[4];
+#pragma unroll
+                    for (int e = e0; e < e0 + 8; e += 2) {
+                        const float4 t = __ldg(reinterpret_cast<const float4*>(cs + j * 32 + e));     // (cos, sin) of two neighbouring pairs
+                        const float ra0 = (a[e] * t.x - b[e] * t.y) * k, rb0 = (b[e] * t.x + a[e] * t.y) * k;
+                        const float ra1 = (a[e + 1] * t.z - b[e + 1] * t.w) * k, rb1 = (b[e + 1] * t.z + a[e + 1] * t.w) * k;
+                        const __nv_bfloat162 pa = __floats2bfloat162_rn(ra0, ra1), pb = __floats2bfloat162_rn(rb0, rb1);
+                        lo[(e - e0) / 2] = *reinterpret_cast<const uint32_t*>(&pa);
+                        hi[(e - e0) / 2] = *reinterpret_cast<const uint32_t*>(&pb);
+                    }
+                    *reinterpret_cast<uint4*>(dst + j * 32 + e0) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                    *reinterpret_cast<uint4*>(dst + HALF + j * 32 + e0) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                }
+            }
+        } else {
+            // a value head: one number per 64-token row of the transposed block; the warp's lanes are
+            // neighbouring tokens, so each of these stores covers neighbouring positions of a row
+            __nv_bfloat16* dst = nullptr;
+            if (live && block >= 0)
+                dst = r.v_pool + ((size_t)block * r.kv_heads + (col0 - r.q_cols - r.kv_cols) / HD) * HD * TT_BLOCK_TOKENS + slot;
+#pragma unroll
+            for (int c = 0; c < CH; ++c) {
+                float v[32];
+                tmem_load32(head_addr + c * 32, v);
+                if (!dst) continue;
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const float x = v[e] + (args.bias ? args.bias[col0 + c * 32 + e] : 0.0f);
+                    dst[(size_t)(c * 32 + e) * TT_BLOCK_TOKENS] = __float2bfloat16_rn(x);
+                }
+            }
+        }
+    }
+}
+
 // ------------------------------------------------------------------ persistent kernel
 // Tokens on M, for prompts.  One CTA per SM takes tiles blockIdx.x, blockIdx.x + gridDim.x,
 // ...; tile id -> (token tile = id % tiles_m, feature tile = id / tiles_m), so the CTAs that
@@ -502,7 +599,10 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
             }
             fence_after_sync();
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256;
-            if (dual || slice == 0) {
+            if (FORM == TOKENS_ON_M_QKV) {                      // never sliced along k
+                if (args.rope_head_dim == 64) store_qkv_rope<64>(lane_addr, token, f_base, args);
+                else store_qkv_rope<128>(lane_addr, token, f_base, args);
+            } else if (dual || slice == 0) {
                 store_accumulator<dual>(lane_addr, token, f_base, args);
             } else {                                            // a later k-slice: its own plane of the output, no bias
                 Args mine = args;
@@ -643,7 +743,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             }
             fence_after_sync();
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256;
-            store_accumulator<dual>(lane_addr, token, f_base, args);
+            if (FORM == TOKENS_ON_M_QKV) {
+                if (args.rope_head_dim == 64) store_qkv_rope<64>(lane_addr, token, f_base, args);
+                else store_qkv_rope<128>(lane_addr, token, f_base, args);
+            } else {
+                store_accumulator<dual>(lane_addr, token, f_base, args);
+            }
             // this warp is done with the accumulator: tell the issuer, who sits in the even CTA
             fence_before_sync();
             __syncwarp();
@@ -744,6 +849,54 @@ extern "C" int tt_gemm_tcgen05_set_wait_limit_ns(unsigned long long ns) { return
 // more than its copies deliver (0: back to normal): its barrier never completes, every wait on
 // it runs out, and the kernel has to raise TT_STATUS_WAIT_EXPIRED, free its tensor memory and return.
 extern "C" void tt_gemm_tcgen05_expect_undelivered_bytes(int bytes) { undelivered_bytes_for_tests = bytes < 0 ? 0 : bytes; }
+
+// The qkv projection of a prompt with rotation, narrowing and the cache append in the epilogue:
+// x [tokens, k] @ w[q_cols + 2 kv_cols, k]^T (+ bias); q rotated to q_out (bfloat16 [tokens, q_cols]), k rotated and
+// v as they are into the block pools at each token's position.  cos_sin and where come from tt_rope_table
+// (elementwise.cu).  Only for the shapes the persistent and CTA-pair kernels run without slicing k (the caller asks
+// tt_gemm_tcgen05_qkv_rope_takes first) and head sizes 64 and 128 rotated whole.  Returns a cudaError_t value, -1
+// if a tensor map could not be made, -2 if the shape is not taken.
+extern "C" int tt_gemm_tcgen05_qkv_rope_takes(int tokens, int features, int k, int head_dim) {
+    if (head_dim != 64 && head_dim != 128) return 0;
+    if (tokens <= 128 || features % head_dim) return 0;
+    const int tiles = ((tokens + BM - 1) / BM) * ((features + 255) / 256);
+    if (tiles < 8) return 0;
+    if (tokens >= PAIR_MIN_TOKENS) return 1;
+    // below the pairs' range the persistent kernel slices k while its tiles are fewer than the SMs: not taken then
+    int device = 0, sm_count = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+    return tiles >= sm_count ? 1 : 0;
+}
+
+extern "C" int tt_gemm_tcgen05_qkv_rope(const void* x, long long ldx, const void* w, long long ldw, const float* bias, int tokens, int k,
+                                        void* q_out, void* k_pool, void* v_pool, const void* cos_sin, const void* where, const int* table,
+                                        int table_width, int pool_blocks, int heads, int kv_heads, int head_dim, float attention_scaling,
+                                        unsigned* status, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    const int q_cols = heads * head_dim, kv_cols = kv_heads * head_dim, features = q_cols + 2 * kv_cols;
+    if (k <= 0 || (k % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)q_out & 15) ||
+        ((uintptr_t)k_pool & 15) || ((uintptr_t)cos_sin & 15))
+        return (int)cudaErrorInvalidValue;
+    if (!tt_gemm_tcgen05_qkv_rope_takes(tokens, features, k, head_dim)) return -2;
+    Args args = {};
+    args.bias = bias; args.tokens = tokens; args.features = features; args.k = k;
+    args.k_blocks_per_split = (k + BK - 1) / BK;
+    args.status = status;
+    args.rope_head_dim = head_dim;
+    args.rope.q_out = (__nv_bfloat16*)q_out; args.rope.k_pool = (__nv_bfloat16*)k_pool; args.rope.v_pool = (__nv_bfloat16*)v_pool;
+    args.rope.cos_sin = (const float2*)cos_sin; args.rope.where = (const int2*)where; args.rope.table = table;
+    args.rope.table_width = table_width; args.rope.pool_blocks = pool_blocks; args.rope.q_cols = q_cols; args.rope.kv_cols = kv_cols;
+    args.rope.kv_heads = kv_heads; args.rope.attention_scaling = attention_scaling;
+    CUtensorMap map_a, map_b;
+    const int tiles_m = (tokens + BM - 1) / BM;
+    if (tokens < PAIR_MIN_TOKENS) {
+        if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, features, k, ldw, 256)) return -1;
+        return launch_persistent<TOKENS_ON_M_QKV>(map_a, map_b, args, tiles_m, tiles_m * ((features + 255) / 256), 1, stream);
+    }
+    if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, features, k, ldw, 128)) return -1;
+    const int pair_tiles_m = (tokens + 2 * BM - 1) / (2 * BM);
+    return launch_pair<TOKENS_ON_M_QKV>(map_a, map_b, args, pair_tiles_m, pair_tiles_m * ((features + 255) / 256), stream);
+}
 
 // How many tokens the features-on-m form takes at most.
 extern "C" int tt_gemm_tcgen05_max_skinny_tokens() { return 128; }

@@ -74,6 +74,7 @@ class StepContext:
     host_before: list[int] = field(default_factory=list)    # lengths before the step (unknown inside a replayed graph)
     logits_out: torch.Tensor | None = None                  # float32 [wanted rows, vocab] the head may write directly
     residual: torch.Tensor | None = None                    # float32 [n_tokens, hidden]: set by an arrangement whose parts may add into the stream themselves
+    memo: dict = field(default_factory=dict)                # what a part computed for this step that its other layers can use again
 
     def scratch(self, name: str, shape: tuple[int, ...], dtype: torch.dtype | None = None) -> torch.Tensor:
         return self.workspace.get(name, shape, dtype or self.act_dtype)

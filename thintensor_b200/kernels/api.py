@@ -211,6 +211,20 @@ def rope_append(qkv: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, atte
               1 if write else 0, _ptr(status), _stream()), "rope_append")
 
 
+def rope_table(inv_freq: torch.Tensor, rotary_dim: int, cu: torch.Tensor, len_before: torch.Tensor, sequences: int, n_tokens: int,
+               cos_sin: torch.Tensor, where: torch.Tensor) -> None:
+    """What the rotations of all layers of a step share: ``where[t] = (position, sequence)`` of packed token t
+    (int32 [tokens, 2]) and ``cos_sin[t, i] = (cos, sin)(inv_freq[i] * position)`` (float32 [tokens, rotary_dim / 2, 2])."""
+    _need(inv_freq, torch.float32, "inv_freq")
+    _need(cos_sin, torch.float32, "cos/sin table")
+    _need(where, torch.int32, "token positions")
+    half = rotary_dim // 2
+    if tuple(cos_sin.shape) != (n_tokens, half, 2) or tuple(where.shape) != (n_tokens, 2) or inv_freq.numel() < half:
+        raise KernelError(f"rope_table: cos_sin must be [{n_tokens}, {half}, 2] and where [{n_tokens}, 2]")
+    fn = _fn("elementwise", "tt_rope_table", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(inv_freq), half, _ptr(cu), _ptr(len_before), sequences, n_tokens, _ptr(cos_sin), _ptr(where), _stream()), "rope_table")
+
+
 def swiglu(gate_up: torch.Tensor, act: torch.Tensor) -> None:
     """act = silu(gate) * up from float32 partial sums [splits, tokens, 2 * inter]."""
     _need(gate_up, torch.float32, "gate_up")
@@ -495,6 +509,46 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, ou
                                                  c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
     _check(fn(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(bias), _ptr(out), out.stride(1), out.stride(0), tokens, features, k,
               out.shape[0], 2 if accumulate else 0, _ptr(status), _stream()), "gemm_tcgen05")
+
+
+def gemm_tcgen05_qkv_rope_takes(x: torch.Tensor, w: torch.Tensor, head_dim: int, rotary_dim: int) -> bool:
+    """Whether the qkv product of these operands can rotate, narrow and append to the cache in its own epilogue:
+    a prompt on the persistent or CTA-pair kernel without k-slices, head size 64 or 128 rotated whole."""
+    if rotary_dim != head_dim or head_dim not in (64, 128) or not gemm_tcgen05_usable(x, w):
+        return False
+    lib = build.load("gemm_tcgen05")
+    lib.tt_gemm_tcgen05_qkv_rope_takes.argtypes = [c_int, c_int, c_int, c_int]
+    lib.tt_gemm_tcgen05_qkv_rope_takes.restype = c_int
+    return bool(lib.tt_gemm_tcgen05_qkv_rope_takes(x.shape[0], w.shape[0], x.shape[1], head_dim))
+
+
+def gemm_tcgen05_qkv_rope(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, q_out: torch.Tensor, k_pool: torch.Tensor,
+                          v_pool: torch.Tensor, cos_sin: torch.Tensor, where: torch.Tensor, table: torch.Tensor, heads: int,
+                          kv_heads: int, head_dim: int, attention_scaling: float, status: torch.Tensor) -> None:
+    """The qkv projection of a prompt with the rotation, the narrowing to bfloat16 and the cache append done by the
+    product's epilogue: q (rotated) to ``q_out`` [tokens, heads * head_dim], k (rotated) and v into the block pools at
+    each token's position.  ``cos_sin`` and ``where`` are the step's :func:`rope_table`.  Only where
+    :func:`gemm_tcgen05_qkv_rope_takes`."""
+    tokens, k = x.shape
+    q_cols, kv_cols = heads * head_dim, kv_heads * head_dim
+    if w.shape != (q_cols + 2 * kv_cols, k) or tuple(q_out.shape) != (tokens, q_cols):
+        raise KernelError(f"qkv product: w {tuple(w.shape)} / q_out {tuple(q_out.shape)} do not fit {heads}/{kv_heads} heads of {head_dim}")
+    for t, name in ((q_out, "q_out"), (k_pool, "key pool"), (v_pool, "value pool")):
+        _need(t, torch.bfloat16, name)
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+    _need(cos_sin, torch.float32, "cos/sin table")
+    _need(where, torch.int32, "token positions")
+    if tuple(cos_sin.shape) != (tokens, head_dim // 2, 2) or tuple(where.shape) != (tokens, 2):
+        raise KernelError("qkv product: the rope table does not fit the step")
+    fn = _fn("gemm_tcgen05", "tt_gemm_tcgen05_qkv_rope", [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                                          c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                                          c_void_p, c_void_p])
+    code = fn(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(bias), tokens, k, _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(cos_sin),
+              _ptr(where), _ptr(table), table.shape[1], k_pool.shape[0], heads, kv_heads, head_dim, attention_scaling, _ptr(status), _stream())
+    if code < 0:
+        raise KernelError("qkv product with rotation: " + ("a tensor map could not be made" if code == -1 else "the shape is not taken"))
+    _check(code, "gemm_tcgen05_qkv_rope")
 
 
 def gemm_tcgen05_failure_drill(wait_limit_ns: int, undelivered_bytes: int) -> None:

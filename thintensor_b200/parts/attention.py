@@ -93,9 +93,21 @@ class CausalAttention(Mixer):
             raise RuntimeError("attention needs a cache with storage")
         table = ctx.tables[cache.group]
         q_cols = self.heads * self.head_dim
-        projection = (self.qkv if cache.writes else self.q_only)(ctx, x, "attention.qkv")
-        mixed = ctx.scratch("attention.mixed", (ctx.n_tokens, q_cols))
         rot = self.rot
+        mixed = ctx.scratch("attention.mixed", (ctx.n_tokens, q_cols))
+        if (cache.writes and not ctx.decode and x.dtype == torch.bfloat16
+                and api.gemm_tcgen05_qkv_rope_takes(x, self.qkv.weight, self.head_dim, rot.rotary_dim)):
+            # long prompts: the qkv product's epilogue rotates, narrows and appends to the cache, so the float32
+            # product never goes to memory and back; positions, block lookups' inputs and the cosines and sines
+            # are the same for every layer and are made once per step
+            cos_sin, where = self.step_rope_table(ctx)
+            q = ctx.scratch("attention.q", (ctx.n_tokens, q_cols))
+            api.set_label("attention.qkv")
+            api.gemm_tcgen05_qkv_rope(x, self.qkv.weight, self.qkv.bias, q, cache.k_pool, cache.v_pool, cos_sin, where, table, self.heads,
+                                      self.kv_heads, self.head_dim, rot.attention_scaling, ctx.status)
+            self.attend(ctx, q, cache, table, mixed)
+            return self.out.delta(ctx, mixed, "attention.out")
+        projection = (self.qkv if cache.writes else self.q_only)(ctx, x, "attention.qkv")
         splits = self.decode_slices(ctx)
         if (ctx.decode and ctx.sequences * self.kv_heads * splits <= api.sm_count(x.device)
                 and api.attention_decode_rope_supports(mixed.dtype, self.heads, self.kv_heads, self.head_dim, rot.rotary_dim)):
@@ -113,6 +125,20 @@ class CausalAttention(Mixer):
                         ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads, self.kv_heads, self.head_dim, ctx.status)
         self.attend(ctx, q, cache, table, mixed)
         return self.out.delta(ctx, mixed, "attention.out")
+
+    def step_rope_table(self, ctx):
+        """(cos_sin, where) of this step for this layer's rotary table: made by the first layer that asks and kept
+        in ``ctx.memo`` for the layers that share the table."""
+        rot = self.rot
+        key = ("rope_table", rot.inv_freq.data_ptr(), rot.rotary_dim)
+        made = ctx.memo.get(key)
+        if made is None:
+            half = rot.rotary_dim // 2
+            cos_sin = ctx.scratch(f"attention.rope_table.{len(ctx.memo)}", (ctx.n_tokens, half, 2), torch.float32)
+            where = ctx.scratch(f"attention.rope_where.{len(ctx.memo)}", (ctx.n_tokens, 2), torch.int32)
+            api.rope_table(rot.inv_freq, rot.rotary_dim, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens, cos_sin, where)
+            made = ctx.memo[key] = (cos_sin, where)
+        return made
 
     def decode_slices(self, ctx) -> int:
         """Slices of the keys for the tensor-core decode kernel, which runs one CTA per (sequence, kv
