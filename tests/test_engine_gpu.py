@@ -252,3 +252,49 @@ def test_bfloat16_engine_keeps_float32_tensors(model_folders):
     engine.close(slot)
     engine.check_status()
     assert_close(torch.cat(got), want, "bfloat16", "float32 checkpoint in the bfloat16 engine")
+
+
+@pytest.mark.parametrize("name,dtype", [("a", "float32"), ("b", "float32"), ("d", "bfloat16"), ("e", "bfloat16")])
+def test_steps_of_a_known_shape_are_replayed_with_their_own_data(model_folders, name, dtype):
+    """The engine captures a step's launches when its shape (tokens, sequences, table width, wanted rows) comes a
+    second time and replays them from then on.  Replayed steps must serve other tokens, other slots and blocks, other
+    lengths and other wanted places: prompts of one shape for different requests in turn, then decoding token by
+    token across a block boundary, all against the plain implementation, with slots freed and reused in between."""
+    from thintensor_b200.engine.engine import Entry
+
+    folder = folder_for(model_folders, name, dtype)
+    runtime = load(folder, dtype)
+    engine = runtime.new_engine(max_tokens=1024, max_sequences=4)
+    assert engine.use_step_graphs
+    vocab = TINY[name]["vocab_size"]
+    # three pairs of prompts with the same packed shape (30 + 50 tokens, one block each, 3 wanted rows) but different cuts
+    for round_, (la, lb) in enumerate([(30, 50), (45, 35), (10, 70)]):
+        a_tokens, b_tokens = token_ids(vocab, la + 40, 500 + round_), token_ids(vocab, lb + 40, 600 + round_)
+        spare = engine.open() if round_ == 1 else None             # shifts the slots and blocks the round gets
+        a, b = engine.open(), engine.open()
+        logits = engine.step([Entry(a, a_tokens[:la], [0, la - 1]), Entry(b, b_tokens[:lb], [lb // 2])])
+        want = torch.cat([oracle_logits(folder, a_tokens)[[0, la - 1]], oracle_logits(folder, b_tokens)[[lb // 2]]])
+        assert_close(logits, want, dtype, f"{name} prompts of one shape, round {round_}")
+        got_a, got_b = [], []
+        for t in range(40):                                         # both cross position 64: the table grows a column, a new shape
+            logits = engine.step([Entry(a, [a_tokens[la + t]], [0]), Entry(b, [b_tokens[lb + t]], [0])])
+            got_a.append(logits[0])
+            got_b.append(logits[1])
+        assert_close(torch.stack(got_a), oracle_logits(folder, a_tokens)[la: la + 40], dtype, f"{name} decode a, round {round_}")
+        assert_close(torch.stack(got_b), oracle_logits(folder, b_tokens)[lb: lb + 40], dtype, f"{name} decode b, round {round_}")
+        for slot in (a, b, spare):
+            if slot is not None:
+                engine.close(slot)
+        engine.check_status()
+    assert engine.graph_replays > 100, "prompt rounds 2 and 3 and nearly all decode steps should have been replays"
+    assert engine.cache.free_blocks == engine.cache.num_blocks
+    # an engine that never replays gives the same prompt logits bit for bit (the same kernels, launched one by one)
+    plain = runtime.new_engine(max_tokens=1024, max_sequences=4, step_graphs=False)
+    tokens = token_ids(vocab, 80, 700)
+    results = []
+    for e in (engine, plain, engine):
+        slot = e.open()
+        results.append(e.step([Entry(slot, tokens, [0, 40, 79])]).clone())
+        e.close(slot)
+    assert plain.graph_replays == 0
+    assert torch.equal(results[0], results[1]) and torch.equal(results[1], results[2])

@@ -66,8 +66,22 @@ class _Staging:
         self._events[index] = event
 
 
+MAX_STEP_GRAPHS = 32         # shapes of steps whose captured launches an engine keeps
+MAX_GRAPH_ROWS = 64          # a step that wants more logits rows than this is not replayed (its rows are copied once more)
+
+
+@dataclass
+class _StepGraph:
+    """A step shape's kernels, captured once: replaying them costs the host one call instead of one
+    per kernel.  ``logits`` is where the captured step leaves its wanted rows."""
+
+    graph: torch.cuda.CUDAGraph | None      # None: the shape has run once, eagerly; its next step is captured
+    generation: int = -1                    # of the scratch memory whose addresses the graph holds
+    logits: torch.Tensor | None = None
+
+
 class Engine:
-    def __init__(self, model: DecoderModel, cache: SequenceCache, max_step_tokens: int = 8192):
+    def __init__(self, model: DecoderModel, cache: SequenceCache, max_step_tokens: int = 8192, step_graphs: bool = True):
         if model.device is None or model.device.type != "cuda":
             raise RuntimeError("the engine runs on a CUDA device only; there is no CPU path")
         if not model.bound:
@@ -82,6 +96,11 @@ class Engine:
         self.vocab_size = model.spec.vocab_size
         self.launch_count = 0
         self.decode_states: dict = {}        # the generation loop's captured decode steps, by shape
+        # Steps through `step` of a shape that has run before are replayed from a CUDA graph: everything that
+        # differs between two steps of one shape (tokens, lengths, slots, tables, wanted rows) is device data.
+        self.step_graphs: dict[tuple, _StepGraph] = {}
+        self.use_step_graphs = bool(step_graphs) and model.device_driven
+        self.graph_replays = 0
 
     # ------------------------------------------------------------- sequences
     def open(self) -> int:
@@ -136,8 +155,13 @@ class Engine:
 
         pieces = self._pieces(entries)
         for piece in pieces:
-            ctx, rows, targets = self._prepare(entries, arrays, piece, out_base)
-            if rows is not None:
+            replayable = self.use_step_graphs and len(pieces) == 1 and total_wanted <= MAX_GRAPH_ROWS
+            ctx, rows, targets = self._prepare(entries, arrays, piece, out_base, replayable)
+            if replayable:
+                logits = self._forward_replayed(ctx, rows)
+                if logits is not None:
+                    out.copy_(logits)               # one piece: its wanted rows are the result's rows, in order
+            elif rows is not None:
                 if len(pieces) == 1:
                     ctx.logits_out = out            # one piece: its wanted rows are the result's rows, in order
                 logits = self.model.forward(ctx, self.cache, rows)
@@ -148,6 +172,34 @@ class Engine:
             for index, start, count in piece:
                 self.cache.advance(entries[index].slot, count)
         return out
+
+    def _forward_replayed(self, ctx: StepContext, rows: torch.Tensor | None) -> torch.Tensor | None:
+        """Run a one-piece step whose shape is its key: eagerly the first time, captured into a CUDA graph
+        the second time, replayed from then on (and captured again if scratch memory has moved since).
+        The step's integers are already in their place on the device; the wanted rows come back in a
+        buffer of the engine's."""
+        n_rows = 0 if rows is None else rows.numel()
+        key = (ctx.n_tokens, ctx.sequences, tuple(t.shape[1] for t in ctx.tables), n_rows, ctx.decode)
+        if n_rows:
+            ctx.logits_out = self.workspace.get("step.logits", (n_rows, self.vocab_size), torch.float32)
+        entry = self.step_graphs.get(key)
+        if entry is None:
+            while len(self.step_graphs) >= MAX_STEP_GRAPHS:
+                self.step_graphs.pop(next(iter(self.step_graphs)))          # the one used longest ago
+            self.step_graphs[key] = _StepGraph(None)
+            return self.model.forward(ctx, self.cache, rows)
+        self.step_graphs[key] = self.step_graphs.pop(key)                   # most recently used last
+        if entry.graph is None or entry.generation != self.workspace.generation:
+            entry.generation = self.workspace.generation
+            entry.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(entry.graph):                             # captures; the step runs at the replay below
+                entry.logits = self.model.forward(ctx, self.cache, rows)
+            if self.workspace.generation != entry.generation:
+                self.step_graphs.pop(key)
+                raise RuntimeError("scratch memory moved while a step was being captured")
+        entry.graph.replay()
+        self.graph_replays += 1
+        return entry.logits
 
     def check_status(self) -> None:
         """Read the device status word (synchronises) and raise if a kernel flagged a
@@ -184,7 +236,7 @@ class Engine:
                 room -= count
         return pieces
 
-    def _prepare(self, entries, arrays, piece, out_base):
+    def _prepare(self, entries, arrays, piece, out_base, replayable: bool = False):
         slots = [entries[i].slot for i, _, _ in piece]
         before = [self.cache.length(s) for s in slots]
         new = [count for _, _, count in piece]
@@ -239,7 +291,8 @@ class Engine:
         d_targets = cut(len(rows)) if rows else None
         ctx = StepContext(
             n_tokens=n_tokens, sequences=sequences, decode=all(c == 1 for c in new), max_new=max(new),
-            max_total=max(b + c for b, c in zip(before, new)), tokens=d_tokens, cu=d_cu, len_before=d_before, slots=d_slots,
+            # a step that may be replayed must not bake this step's lengths into its launches: the bound is what the tables can describe
+            max_total=width * self.cache.block_tokens if replayable else max(b + c for b, c in zip(before, new)), tokens=d_tokens, cu=d_cu, len_before=d_before, slots=d_slots,
             tables=d_tables, act_dtype=self.model.dtype, workspace=self.workspace, status=self.status,
             host_slots=slots, host_new=new, host_before=before,
         )

@@ -55,6 +55,7 @@ class DecoderModel:
             self._layer_parts.append(built)
             self.layers.append(arrangement_cls({role: b.part for role, b in built.items()}))
         self.bound = False
+        self.device_driven = False
         self.cache_needs()          # sets self.users
 
     # ------------------------------------------------------------------ weights
@@ -91,6 +92,9 @@ class DecoderModel:
                     raise KeyError(f"tensor {name!r} was not loaded")
             built.part.bind(mine, self.dtype, self.device)
         self.bound = True
+        # a step of a shape that has run before may be replayed from a CUDA graph if no part computes on the host
+        self.device_driven = all(b.part.device_driven() for b in (self.embedding, self.final_norm, self.head)) and all(
+            layer.device_driven() for layer in self.layers)
 
     # -------------------------------------------------------------------- cache
     def cache_needs(self):

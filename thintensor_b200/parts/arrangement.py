@@ -20,6 +20,9 @@ class PreNorm(Arrangement):
     def mixers(self):
         return [self.parts["mixer"]]
 
+    def device_driven(self) -> bool:
+        return all(part.device_driven() for part in self.parts.values())
+
     def run(self, ctx, residual, pending: Delta | None, caches, states) -> Delta:
         hidden = residual.shape[-1]
         # Between a part's output and the norm that follows nothing else reads the stream, so a part

@@ -87,6 +87,9 @@ class CausalAttention(Mixer):
     def projections(self) -> list:
         return [self.qkv, self.out]             # q_only is a view of qkv's first rows
 
+    def device_driven(self) -> bool:
+        return True
+
     # ------------------------------------------------------------------- running
     def forward(self, ctx, x, cache, states) -> Delta:
         if cache is None or cache.k_pool is None:

@@ -99,6 +99,15 @@ class Part:
         """Other tensors a step reads once whatever its tokens (a norm's weight)."""
         return []
 
+    def device_driven(self) -> bool:
+        """Whether ``forward`` takes everything that changes from step to step from device memory
+        (``ctx.tokens``, ``ctx.cu``, ``ctx.len_before``, ``ctx.slots``, the block tables) and, for steps
+        of one shape (tokens, sequences, table width, wanted rows), launches the same kernels with
+        the same host-side arguments.  Such a step can be captured in a CUDA graph once and
+        replayed; a part that looks at ``ctx.host_slots`` / ``host_new`` / ``host_before`` or
+        computes on the host must say no.  The engine replays only if every part says yes."""
+        return False
+
 
 class Norm(Part):
     def forward(self, ctx, residual: torch.Tensor, delta: Delta | None, out: torch.Tensor, rows: torch.Tensor | None = None) -> None:
@@ -173,6 +182,10 @@ class Arrangement:
     def run(self, ctx, residual: torch.Tensor, pending: Delta | None, caches: list, states: list[list[torch.Tensor]]) -> Delta | None:
         """``caches[i]`` and ``states[i]`` belong to ``mixers()[i]``."""
         raise NotImplementedError
+
+    def device_driven(self) -> bool:
+        """See :meth:`Part.device_driven`: an arrangement answers for itself and its parts."""
+        return False
 
 
 class Registry:

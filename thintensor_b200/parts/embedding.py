@@ -26,6 +26,9 @@ class TokenEmbedding(Embedding):
     def bind(self, tensors, dtype, device) -> None:
         self.table = tensors["weight"].contiguous()
 
+    def device_driven(self) -> bool:
+        return True
+
     def forward(self, ctx, tokens, residual) -> None:
         api.embed_gather(self.table, tokens, residual, self.scale, ctx.status)
 
@@ -51,6 +54,9 @@ class LinearHead(Head):
 
     def projections(self) -> list:
         return [self.linear]
+
+    def device_driven(self) -> bool:
+        return True
 
     def forward(self, ctx, x) -> torch.Tensor:
         """Float32 logits ``[rows, vocab]``: in ``ctx.logits_out`` where the step gave one and the

@@ -33,6 +33,9 @@ class SwiGLU(FeedForward):
     def projections(self) -> list:
         return [self.gate_up.fused, self.down]
 
+    def device_driven(self) -> bool:
+        return True
+
     def forward(self, ctx, x) -> Delta:
         act = self.gate_up(ctx, x, "ffn.gate_up")
         return self.down.delta(ctx, act, "ffn.down")

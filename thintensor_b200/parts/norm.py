@@ -30,5 +30,8 @@ class RMSNorm(Norm):
     def vectors(self) -> list[torch.Tensor]:
         return [self.weight]
 
+    def device_driven(self) -> bool:
+        return True
+
     def forward(self, ctx, residual, delta: Delta | None, out, rows=None) -> None:
         api.add_rmsnorm(residual, None if delta is None else delta.tensor, self.weight, self.eps, out, rows, self.weight_offset)   # an empty delta is already in the stream

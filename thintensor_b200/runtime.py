@@ -78,12 +78,13 @@ class Runtime:
         self._engine: Engine | None = None
         self._engine_key: tuple[int, int] | None = None
 
-    def new_engine(self, max_tokens: int, max_sequences: int = 64, max_step_tokens: int = 8192) -> Engine:
+    def new_engine(self, max_tokens: int, max_sequences: int = 64, max_step_tokens: int = 8192, step_graphs: bool = True) -> Engine:
         """An engine whose cache holds ``max_tokens`` tokens (each sequence's count
-        rounded up to whole blocks of 64) for up to ``max_sequences`` live sequences."""
+        rounded up to whole blocks of 64) for up to ``max_sequences`` live sequences.
+        ``step_graphs``: whether steps of a shape that has run before are replayed from a CUDA graph."""
         blocks = max(1, -(-int(max_tokens) // BLOCK_TOKENS))
         cache = self.model.new_cache(blocks, max_sequences)
-        return Engine(self.model, cache, max_step_tokens)
+        return Engine(self.model, cache, max_step_tokens, step_graphs)
 
     def engine_for(self, max_tokens: int, max_sequences: int) -> Engine:
         """The runtime's own engine, kept from call to call (with its cache, its scratch memory and
