@@ -132,7 +132,7 @@ def main() -> int:
     import torch
 
     import thintensor_b200
-    from thintensor_b200.benchmark import measure_decode, measure_prefill
+    from thintensor_b200.benchmark import class_fractions, measure_classes, measure_decode, measure_prefill
     from thintensor_b200.engine.generate import GenerationStats
 
     pk = peaks()
@@ -174,6 +174,10 @@ def main() -> int:
     runtime.generate(prompts[:BATCH], max_new_tokens=e2e_steps + 1, stop_ids=(-1,), batch_size=BATCH, context=CONTEXT, stats=stats)
     e2e_value = stats.decoded_tokens / stats.decode_seconds if stats.decode_seconds > 0 else None
 
+    # where the two steps' time goes, by class of kernel, each against its own bound
+    spans = measure_classes(runtime, prompts[:BATCH], CONTEXT, prefill_prompts=prompts[:1])
+    classes = class_fractions(runtime.model, spans, pk, prompts[:1], BATCH, spans["mean_context"])
+
     achieved = decode["bytes_per_step"] / (decode["ms_per_step"] / 1e3) / 1e9
     line = {
         "metric": METRIC,
@@ -206,6 +210,7 @@ def main() -> int:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "of": pk["source"]},
         "points": points,
+        "classes": classes,
     }
     print(json.dumps(line))
     return 0

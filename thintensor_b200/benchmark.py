@@ -151,7 +151,39 @@ def roofline(decode: dict | None, prefill: dict | None, pk: dict) -> dict:
     return out
 
 
-def measure_classes(runtime, prompts: list[list[int]], context: int) -> dict:
+def class_fractions(model, classes: dict, pk: dict, prefill_prompts: list[list[int]], batch: int, mean_context: float) -> dict:
+    """The classes' times against their own bounds: a prefill's products and attention against the
+    matrix-product rate (their FLOP), a decode step's products against the copy bandwidth (the weights)
+    and its attention against it too (the cache it reads); the rest (norms, rotation, embedding,
+    sampling) has no bound worth naming and is given as time alone.  Times are those of kernels run
+    one after another (see :func:`measure_classes`)."""
+    def split(spans: dict) -> dict:
+        out = {"products": 0.0, "attention": 0.0, "rest": 0.0}
+        for name, entry in spans.items():
+            kind = "products" if name.startswith("tt_gemm") else "attention" if name.startswith("tt_attention") else "rest"
+            out[kind] += entry["ms"]
+        return out
+
+    tokens = sum(len(p) for p in prefill_prompts)
+    prefill, decode = split(classes["prefill_step"]), split(classes["decode_step"])
+    linear = float(linear_flops_per_token(model)) * tokens + 2.0 * model.spec.vocab_size * model.spec.hidden_size * len(prefill_prompts)
+    attention = sum(attention_flops(model, len(p)) for p in prefill_prompts)
+    peak_flops, peak_bytes = pk["bf16_tflops"] * 1e12, pk["hbm_gbs"] * 1e9
+    frac = lambda amount, ms, peak: round(amount / (ms / 1e3) / peak, 4) if ms > 0 else None
+    return {
+        "prefill": {"tokens": tokens, "products_ms": round(prefill["products"], 4), "products_frac": frac(linear, prefill["products"], peak_flops),
+                    "attention_ms": round(prefill["attention"], 4), "attention_frac": frac(attention, prefill["attention"], peak_flops),
+                    "rest_ms": round(prefill["rest"], 4)},
+        "decode": {"batch": batch, "products_ms": round(decode["products"], 4),
+                   "products_frac": frac(weight_bytes_per_step(model), decode["products"], peak_bytes),
+                   "attention_ms": round(decode["attention"], 4),
+                   "attention_frac": frac(kv_read_bytes_per_token(model) * mean_context * batch, decode["attention"], peak_bytes),
+                   "rest_ms": round(decode["rest"], 4)},
+        "how": "CUDA events around every kernel, kernels run one after another (no overlap between them)",
+    }
+
+
+def measure_classes(runtime, prompts: list[list[int]], context: int, prefill_prompts: list[list[int]] | None = None) -> dict:
     """Where the time of one prefill step and of one decode step goes, by class of kernel: both are
     run eagerly with every kernel call bracketed by CUDA events (:class:`~thintensor_b200.kernels.api.ClassTimer`).
     The kernels then run one after another without overlapping, so the sums are larger than the
@@ -168,14 +200,20 @@ def measure_classes(runtime, prompts: list[list[int]], context: int) -> dict:
     decode = timer.summary()
     for position in range(batch):
         backend.finish(position)
+    prefill_prompts = prompts if prefill_prompts is None else prefill_prompts
+    slots = [engine.open() for _ in prefill_prompts]                 # once untimed: compiles and sizes what this shape needs
+    engine.step([Entry(slot, p, [len(p) - 1]) for slot, p in zip(slots, prefill_prompts)])
+    for slot in slots:
+        engine.close(slot)
+    engine.use_step_graphs = False                                    # the timed step runs kernel by kernel
     with api.timed_classes() as timer:
-        slots = [engine.open() for _ in prompts]
-        engine.step([Entry(slot, p, [len(p) - 1]) for slot, p in zip(slots, prompts)])
+        slots = [engine.open() for _ in prefill_prompts]
+        engine.step([Entry(slot, p, [len(p) - 1]) for slot, p in zip(slots, prefill_prompts)])
     prefill = timer.summary()
     for slot in slots:
         engine.close(slot)
     engine.check_status()
-    return {"decode_step": decode, "prefill_step": prefill,
+    return {"decode_step": decode, "prefill_step": prefill, "mean_context": sum(len(p) for p in prompts) / batch + 2,
             "decode_ms_serialised": sum(c["ms"] for c in decode.values()), "prefill_ms_serialised": sum(c["ms"] for c in prefill.values())}
 
 

@@ -221,13 +221,13 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     tt_pdl_launch_dependents();
     tt_pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const int kh = blockIdx.y;
+    const int kh = blockIdx.x;                  // heads on x, tiles on y: every head's heavy tiles are handed out before anybody's light ones
     const int group = heads / kv_heads;
     const int tokens_per_cta = tokens_per_tile * MMA_WARPS;
 
     // which sequence and which of its CTA tiles: lanes look at 32 sequences at a time, a warp
     // scan of their tile counts finds the owner.  Late tiles of a sequence come first.
-    int tile = cta_tiles - 1 - (int)blockIdx.x;
+    int tile = cta_tiles - 1 - (int)blockIdx.y;
     int b = -1;
     for (int base = 0; base < sequences && b < 0; base += 32) {
         const int mine = base + lane;
@@ -723,7 +723,8 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* tab
         const int tokens_per_tile = 16 / group;
         const int tokens_per_cta = tokens_per_tile * MMA_WARPS;
         const int cta_tiles = (n_tokens + tokens_per_cta - 1) / tokens_per_cta + sequences;   // upper bound; spare CTAs leave at once
-        err = tt_launch_pdl(kernel, dim3(cta_tiles, kv_heads, 1), dim3(MMA_WARPS * 32), shared, stream,
+        if (cta_tiles > 65535) return (int)cudaErrorInvalidValue;                             // the grid's y extent; steps are cut into pieces long before
+        err = tt_launch_pdl(kernel, dim3(kv_heads, cta_tiles, 1), dim3(MMA_WARPS * 32), shared, stream,
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, table, table_width, pool_blocks, cu,
             len_before, sequences, heads, kv_heads, scale_log2, window, tokens_per_tile, cta_tiles, (__nv_bfloat16*)out, status);
     }

@@ -88,11 +88,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
     tt_pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int kh = blockIdx.y;
+    // The grid is (kv heads, tiles) and blocks are handed out with x running fastest: the heaviest tile of every
+    // head comes first, then the next heaviest of every head, so the CTAs that start last are the lightest ones
+    // (with the heads on y, whole heads, heavy tiles included, started behind others' light tiles).
+    const int kh = blockIdx.x;
 
     if (warp == 0) {
         // which sequence and which of its tiles (late tiles, which see most keys, first)
-        int tile = args.cta_tiles - 1 - (int)blockIdx.x;
+        int tile = args.cta_tiles - 1 - (int)blockIdx.y;
         int b = -1;
         for (int base = 0; base < args.sequences && b < 0; base += 32) {
             const int mine = base + lane;
@@ -355,7 +358,7 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const Args& ar
         if (err != cudaSuccess) return (int)err;
         configured = true;
     }
-    tt_launch_pdl(kernel, dim3(args.cta_tiles, args.kv_heads), dim3(L::THREADS), (size_t)L::SMEM, stream, map_q, map_k, map_v, args);
+    tt_launch_pdl(kernel, dim3(args.kv_heads, args.cta_tiles), dim3(L::THREADS), (size_t)L::SMEM, stream, map_q, map_k, map_v, args);
     return (int)cudaGetLastError();
 }
 
@@ -381,6 +384,7 @@ extern "C" int tt_attention_tcgen05(const void* q, const void* k_pool, const voi
     args.sequences = sequences; args.heads = heads; args.kv_heads = kv_heads; args.group = heads / kv_heads;
     args.tokens_per_tile = ROWS / args.group;
     args.cta_tiles = (n_tokens + args.tokens_per_tile - 1) / args.tokens_per_tile + sequences;   // upper bound; spare CTAs leave at once
+    if (args.cta_tiles > 65535) return (int)cudaErrorInvalidValue;                               // the grid's y extent; steps are cut into pieces long before
     args.scale_log2 = scale * 1.4426950408889634f; args.window = window; args.out = (__nv_bfloat16*)out; args.status = status;
     if (head_dim == 64) return launch<64>(q, k_pool, v_pool, args, n_tokens, stream);
     return launch<128>(q, k_pool, v_pool, args, n_tokens, stream);
