@@ -384,13 +384,14 @@ __device__ __forceinline__ void store_accumulator(uint32_t lane_addr, int token,
     }
 }
 
-// The qkv form's epilogue for one thread = one token's row of a 128 x 256 accumulator, whose 256 / HD
+// The qkv form's epilogue for one thread = one token's row of a 128 x WIDE accumulator, whose WIDE / HD
 // heads each lie inside the tile (HD = 64 or 128).  A head's rotation pairs dimension d with d + HD / 2:
 // the two come from tensor-memory chunks j and j + HD / 64 of the head, so a thread holds both.  The
 // arithmetic is that of rope_append_vec_kernel (elementwise.cu).  Tensor-memory loads are
 // warp-collective: every lane runs them, valid row or not.
-template <int HD>
+template <int HD, int WIDE = 256>
 __device__ __forceinline__ void store_qkv_rope(uint32_t lane_addr, int token, int f_base, const Args& args) {
+    static_assert(WIDE % HD == 0, "a tile holds whole heads");
     constexpr int CH = HD / 32, HALF = HD / 2;
     const QkvRope& r = args.rope;
     const bool live = token < args.tokens;
@@ -405,7 +406,7 @@ __device__ __forceinline__ void store_qkv_rope(uint32_t lane_addr, int token, in
         cs += (size_t)token * HALF;
     }
     const float k = r.attention_scaling;
-    for (int h = 0; h < 256 / HD; ++h) {
+    for (int h = 0; h < WIDE / HD; ++h) {
         const int col0 = f_base + h * HD;                       // the head's first column: the same for the whole CTA
         if (col0 >= args.features) break;
         const uint32_t head_addr = lane_addr + h * HD;
@@ -638,12 +639,18 @@ constexpr int PAIR_MIN_TOKENS = 2048, PAIR_MIN_TOKENS_SWIGLU = 512;
 constexpr int PAIR_STAGES = 6;
 constexpr int PAIR_STAGE_BYTES = BM * BK * 2 + 128 * BK * 2;    // 128 rows of A + 128 rows of B
 
-template <int FORM>
+// WIDE: the features of a plain tile, 256, or (qkv form, head size 64) 192 where that leaves the last round of the
+// CTA pairs fuller: 2,048 tokens x 3,072 features are 96 tiles of 256 for 74 pairs, two rounds of which the second
+// is a third full, or 128 tiles of 192, two rounds of three quarters the length.
+template <int FORM, int WIDE = 256>
 __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Args args,
                          int tiles_m, int tiles_total) {
     constexpr bool dual = FORM == TOKENS_ON_M_SWIGLU;
-    constexpr int TILE_N = dual ? 128 : 256;                    // output features per tile
+    static_assert(WIDE == 256 || (FORM == TOKENS_ON_M_QKV && WIDE == 192), "only the qkv form has a narrower tile");
+    constexpr int TILE_N = dual ? 128 : WIDE;                   // output features per tile
+    constexpr int B_ROWS = dual ? 128 : WIDE / 2;               // weight rows each CTA of the pair fetches per k-block
+    constexpr int STAGE_TX = BM * BK * 2 + B_ROWS * BK * 2;     // bytes one CTA's copies bring per stage
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     __shared__ uint64_t full_bar[PAIR_STAGES], empty_bar[PAIR_STAGES], acc_full[2], acc_empty[2];
@@ -679,14 +686,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 const int tile = pair + j * n_pairs;
                 const int a_row = (tile % tiles_m) * 2 * BM + rank * BM;
                 const int b_row = dual ? (rank == 0 ? 0 : args.up_row_offset) + (tile / tiles_m) * TILE_N
-                                       : (tile / tiles_m) * TILE_N + rank * 128;
+                                       : (tile / tiles_m) * TILE_N + rank * B_ROWS;
                 for (int i = 0; i < n_kb; ++i, ++it) {
                     const int s = (int)(it % PAIR_STAGES);
                     if (!mbar_wait(smem_u32(&empty_bar[s]), (uint32_t)(((it / PAIR_STAGES) & 1) ^ 1))) {
                         atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; break;
                     }
                     const uint32_t bar = smem_u32(&full_bar[s]);
-                    if (rank == 0) mbar_expect_tx(bar, 2 * PAIR_STAGE_BYTES);        // both CTAs' copies
+                    if (rank == 0) mbar_expect_tx(bar, 2 * STAGE_TX);                // both CTAs' copies
                     uint8_t* stage = smem + (size_t)s * PAIR_STAGE_BYTES;
                     const int kx = i * BK;
                     tma_load_2d_pair(smem_u32(stage), &map_a, kx, a_row, bar);
@@ -699,7 +706,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer (the even CTA's)
         if (lane == 0 && rank == 0) {
-            constexpr uint32_t idesc = instr_desc(2 * BM, 256);
+            constexpr uint32_t idesc = instr_desc(2 * BM, dual ? 256 : WIDE);
             long long it = 0;
             bool ok = true;
             for (int j = 0; j < my_tiles && ok; ++j) {
@@ -743,8 +750,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             }
             fence_after_sync();
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256;
-            if (FORM == TOKENS_ON_M_QKV) {
-                if (args.rope_head_dim == 64) store_qkv_rope<64>(lane_addr, token, f_base, args);
+            if constexpr (FORM == TOKENS_ON_M_QKV) {
+                if constexpr (WIDE == 192) store_qkv_rope<64, 192>(lane_addr, token, f_base, args);
+                else if (args.rope_head_dim == 64) store_qkv_rope<64>(lane_addr, token, f_base, args);
                 else store_qkv_rope<128>(lane_addr, token, f_base, args);
             } else {
                 store_accumulator<dual>(lane_addr, token, f_base, args);
@@ -805,12 +813,12 @@ int launch_persistent(const CUtensorMap& map_a, const CUtensorMap& map_b, const 
     return (int)cudaGetLastError();
 }
 
-template <int FORM>
+template <int FORM, int WIDE = 256>
 int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const Args& args, int tiles_m, int tiles_total, cudaStream_t stream) {
     constexpr int shared = PAIR_STAGE_BYTES * PAIR_STAGES + 1024;
     static bool configured = false;
     static int sm_count = 0;
-    auto kernel = gemm_tcgen05_pair_kernel<FORM>;
+    auto kernel = gemm_tcgen05_pair_kernel<FORM, WIDE>;
     if (!configured) {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
         if (err != cudaSuccess) return (int)err;
@@ -893,8 +901,19 @@ extern "C" int tt_gemm_tcgen05_qkv_rope(const void* x, long long ldx, const void
         if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, features, k, ldw, 256)) return -1;
         return launch_persistent<TOKENS_ON_M_QKV>(map_a, map_b, args, tiles_m, tiles_m * ((features + 255) / 256), 1, stream);
     }
-    if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, features, k, ldw, 128)) return -1;
     const int pair_tiles_m = (tokens + 2 * BM - 1) / (2 * BM);
+    if (head_dim == 64) {
+        // tiles of 192 features where the pairs' rounds times the tile's width come out shorter than with 256
+        int device = 0, sm_count = 0;
+        if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return -1;
+        const long long pairs = sm_count / 2 > 0 ? sm_count / 2 : 1;
+        auto cost = [&](int wide) { return ((long long)pair_tiles_m * ((features + wide - 1) / wide) + pairs - 1) / pairs * wide; };
+        if (cost(192) < cost(256)) {
+            if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, features, k, ldw, 96)) return -1;
+            return launch_pair<TOKENS_ON_M_QKV, 192>(map_a, map_b, args, pair_tiles_m, pair_tiles_m * ((features + 191) / 192), stream);
+        }
+    }
+    if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, features, k, ldw, 128)) return -1;
     return launch_pair<TOKENS_ON_M_QKV>(map_a, map_b, args, pair_tiles_m, pair_tiles_m * ((features + 255) / 256), stream);
 }
 
