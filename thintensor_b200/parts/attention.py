@@ -133,7 +133,7 @@ class CausalAttention(Mixer):
         """(cos_sin, where) of this step for this layer's rotary table: made by the first layer that asks and kept
         in ``ctx.memo`` for the layers that share the table."""
         rot = self.rot
-        key = ("rope_table", rot.inv_freq.data_ptr(), rot.rotary_dim)
+        key = ("rope_table", rot.signature or rot.inv_freq.data_ptr(), rot.rotary_dim)       # the model's layers usually share one table
         made = ctx.memo.get(key)
         if made is None:
             half = rot.rotary_dim // 2

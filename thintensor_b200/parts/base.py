@@ -119,11 +119,12 @@ class RotaryTable:
     """What a kernel needs to rotate queries and keys: ``inv_freq`` float32 ``[rotary_dim / 2]`` on
     the device (the angle of pair i at position p is ``p * inv_freq[i]``), ``rotary_dim`` numbers at
     the front of each head are rotated (0: none), cosine and sine are multiplied by
-    ``attention_scaling``."""
+    ``attention_scaling``.  ``signature`` identifies the table's contents."""
 
     inv_freq: torch.Tensor
     rotary_dim: int
     attention_scaling: float = 1.0
+    signature: int = 0      # equal for tables with equal numbers (0: unknown): layers with equal tables can share what a step derives from them
 
 
 class PositionEncoding(Part):

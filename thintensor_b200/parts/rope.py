@@ -58,7 +58,8 @@ class RotaryEncoding(PositionEncoding):
         raise ValueError(f"rotary scaling of type {kind!r} is not implemented")
 
     def bind(self, tensors, dtype, device) -> None:
-        self._rotary = RotaryTable(self.inv_freq_host.to(device), self.rotary_dim, self.attention_scaling)
+        signature = hash((self.inv_freq_host.numpy().tobytes(), self.rotary_dim)) or 1
+        self._rotary = RotaryTable(self.inv_freq_host.to(device), self.rotary_dim, self.attention_scaling, signature)
 
     def rotary(self) -> RotaryTable:
         if self._rotary is None:
