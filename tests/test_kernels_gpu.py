@@ -279,6 +279,18 @@ def test_attention_mma_decode_splits_and_window(splits, window, heads, kv_heads,
     torch.testing.assert_close(out.double().cpu().view(len(totals), heads, head_dim), want, **tol(dtype))
     assert torch.allclose(want[0, 0], values[0][far, 0].double(), atol=0.35)
     assert int(st.item()) == 0
+    if shared_tile and splits > 8:
+        # more slices than a cluster holds: with tickets the last CTA of a (sequence, kv head) combines them itself
+        # (one launch instead of two), twice in a row because the tickets have to be back at zero for the next call
+        tickets = torch.zeros(len(totals) * kv_heads, dtype=torch.int32, device=DEV)
+        for _ in range(2):
+            again = torch.full_like(out, float("nan"))
+            launches = api.launch_count()
+            api.attention_mma(q.view(len(totals), -1), k_pool, v_pool, table, cu, before, len(totals), len(totals), heads, kv_heads, head_dim,
+                              scale, window, splits, again, part_acc, part_ml, st, one_token_each=True, tickets=tickets)
+            assert api.launch_count() - launches == 1
+            torch.testing.assert_close(again.double().cpu().view(len(totals), heads, head_dim), want, **tol(dtype))
+            assert int(tickets.abs().sum().item()) == 0 and int(st.item()) == 0
 
 
 @pytest.mark.parametrize("splits", [1, 2, 3])
@@ -356,9 +368,10 @@ def test_attention_decode_with_rotation_and_cache_write(splits, window, heads, k
     part_ml = torch.full((rows * splits * 2,), float("nan"), dtype=torch.float32, device=DEV)
     st = status()
     scale = head_dim ** -0.5
+    tickets = torch.zeros(n * kv_heads, dtype=torch.int32, device=DEV) if splits > 8 and heads % 2 == 0 else None     # both ways of combining many slices
     api.attention_decode_rope(qkv, inv_freq, head_dim, scaling, write_cache, k_pool, v_pool, table, before, n, heads, kv_heads, head_dim,
-                              scale, window, splits, out, part_acc, part_ml, st)
-    assert int(st.item()) == 0
+                              scale, window, splits, out, part_acc, part_ml, st, tickets=tickets)
+    assert int(st.item()) == 0 and (tickets is None or int(tickets.abs().sum().item()) == 0)
     want = attention_reference(q.to(dtype).float(), keys, values, [1] * n, heads, kv_heads, scale, window)
     torch.testing.assert_close(out.double().cpu().view(n, heads, head_dim), want, **tol(dtype))
     if write_cache:

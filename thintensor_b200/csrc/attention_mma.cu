@@ -394,7 +394,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
                         __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ table, int table_width,
                         int pool_blocks, const int* __restrict__ len_before, int heads, int kv_heads, float scale_log2,
                         int window, int splits, int cluster_merge, __nv_bfloat16* __restrict__ out,
-                        float* __restrict__ part_acc, float* __restrict__ part_ml, unsigned* status) {
+                        float* __restrict__ part_acc, float* __restrict__ part_ml, unsigned* __restrict__ tickets, unsigned* status) {
     constexpr int WARPS = DecodeShape<HD, SHAPE>::WARPS, STAGES = DecodeShape<HD, SHAPE>::STAGES;
     constexpr int KC = HD / 32, NT = HD / 8;
     constexpr int K_LOADS = 8 * KC, V_LOADS = NT * 2, LOADS = K_LOADS + V_LOADS;    // 16-byte pieces per thread and block
@@ -605,6 +605,48 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
             }
         }
     }
+    if (splits > 1 && !cluster_merge && tickets) {
+        // More slices than a cluster holds: every CTA has left its partial result in scratch memory; the one that
+        // finishes last for this (sequence, kv head) combines them all, in slice order, so that no merge kernel has
+        // to be launched and waited for.  Its stores are fenced before it draws its ticket, and the last CTA fences
+        // again before it reads the others': the usual last-block reduction, without any waiting.
+        __shared__ int is_last;
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            unsigned* ticket = tickets + (size_t)b * kv_heads + kh;
+            const unsigned drawn = atomicAdd(ticket, 1u);
+            is_last = drawn == (unsigned)splits - 1u;
+            if (is_last) *ticket = 0u;                  // nobody else touches it any more: ready for the next launch
+        }
+        __syncthreads();
+        if (is_last) {
+            __threadfence();
+            for (int idx = threadIdx.x; idx < group * (HD / 2); idx += WARPS * 32) {
+                const int r = idx / (HD / 2), d = 2 * (idx - r * (HD / 2));
+                const size_t row_index = (size_t)b * heads + kh * group + r;
+                const float* ml = part_ml + row_index * splits * 2;
+                const float* acc = part_acc + row_index * splits * HD + d;
+                float m = -INFINITY;
+#pragma unroll 8
+                for (int sl = 0; sl < splits; ++sl) m = fmaxf(m, __ldcg(ml + 2 * sl));
+                float l = 0.0f, acc0 = 0.0f, acc1 = 0.0f;
+                if (m != -INFINITY) {
+#pragma unroll 8
+                    for (int sl = 0; sl < splits; ++sl) {
+                        const float2 state = __ldcg(reinterpret_cast<const float2*>(ml + 2 * sl));     // (maximum in natural units, sum)
+                        const float2 o = __ldcg(reinterpret_cast<const float2*>(acc + (size_t)sl * HD));
+                        const float weight = state.x == -INFINITY ? 0.0f : expf(state.x - m);
+                        l = fmaf(state.y, weight, l);
+                        acc0 = fmaf(o.x, weight, acc0);
+                        acc1 = fmaf(o.y, weight, acc1);
+                    }
+                }
+                const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+                *reinterpret_cast<__nv_bfloat162*>(out + row_index * HD + d) = __floats2bfloat162_rn(acc0 * inv, acc1 * inv);
+            }
+        }
+    }
     if (splits > 1 && cluster_merge) {
         cg::cluster_group cluster = cg::this_cluster();
         cluster.sync();                                // every slice's result is in its shared memory
@@ -642,7 +684,7 @@ inline bool slices_form_cluster(int splits) { return splits > 1 && splits <= 8; 
 template <int HD, bool ROPE, int SHAPE = ONE_PER_SM>
 cudaError_t launch_decode(const void* q, const DecodeRope& rope, void* k_pool, void* v_pool, const int* table, int table_width,
                           int pool_blocks, const int* len_before, int sequences, int heads, int kv_heads, float scale_log2,
-                          int window, int splits, void* out, float* part_acc, float* part_ml, unsigned* status,
+                          int window, int splits, void* out, float* part_acc, float* part_ml, unsigned* tickets, unsigned* status,
                           cudaStream_t stream) {
     using D = DecodeShape<HD, SHAPE>;
     constexpr int shared = D::WARPS * D::STAGES * (8 * (HD / 32) + (HD / 8) * 2) * 32 * 16;
@@ -657,10 +699,10 @@ cudaError_t launch_decode(const void* q, const DecodeRope& rope, void* k_pool, v
     if (slices_form_cluster(splits))
         return tt_launch_pdl_cluster(kernel, dim3(sequences, kv_heads, splits), dim3(D::WARPS * 32), shared, stream, (unsigned)splits,
             (const __nv_bfloat16*)q, rope, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks,
-            len_before, heads, kv_heads, scale_log2, window, splits, 1, (__nv_bfloat16*)out, part_acc, part_ml, status);
+            len_before, heads, kv_heads, scale_log2, window, splits, 1, (__nv_bfloat16*)out, part_acc, part_ml, tickets, status);
     return tt_launch_pdl(kernel, dim3(sequences, kv_heads, splits), dim3(D::WARPS * 32), shared, stream,
         (const __nv_bfloat16*)q, rope, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks,
-        len_before, heads, kv_heads, scale_log2, window, splits, 0, (__nv_bfloat16*)out, part_acc, part_ml, status);
+        len_before, heads, kv_heads, scale_log2, window, splits, 0, (__nv_bfloat16*)out, part_acc, part_ml, tickets, status);
 }
 
 template <int HD>
@@ -677,7 +719,7 @@ int merge_slices(int n_rows_tokens, int heads, int splits, void* out, float* par
 template <int HD>
 int launch(const void* q, const void* k_pool, const void* v_pool, const int* table, int table_width, int pool_blocks,
            const int* cu, const int* len_before, int sequences, int n_tokens, int heads, int kv_heads, float scale,
-           int window, int splits, int one_token_each, void* out, float* part_acc, float* part_ml, unsigned* status,
+           int window, int splits, int one_token_each, void* out, float* part_acc, float* part_ml, unsigned* tickets, unsigned* status,
            cudaStream_t stream) {
     const int group = heads / kv_heads;
     const float scale_log2 = scale * 1.4426950408889634f;
@@ -695,19 +737,19 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* tab
             if (ctas > 2 * sm_count && ctas <= 3 * sm_count) {          // one wave of three CTAs per SM
                 err = launch_decode<HD, false, THREE_PER_SM>(q, DecodeRope{}, const_cast<void*>(k_pool), const_cast<void*>(v_pool), table,
                                                              table_width, pool_blocks, len_before, sequences, heads, kv_heads, scale_log2,
-                                                             window, splits, out, part_acc, part_ml, status, stream);
+                                                             window, splits, out, part_acc, part_ml, tickets, status, stream);
                 done = true;
             } else if (ctas > sm_count) {                               // several waves
                 err = launch_decode<HD, false, TWO_PER_SM>(q, DecodeRope{}, const_cast<void*>(k_pool), const_cast<void*>(v_pool), table,
                                                            table_width, pool_blocks, len_before, sequences, heads, kv_heads, scale_log2,
-                                                           window, splits, out, part_acc, part_ml, status, stream);
+                                                           window, splits, out, part_acc, part_ml, tickets, status, stream);
                 done = true;
             }
         }
         if (!done)
             err = launch_decode<HD, false>(q, DecodeRope{}, const_cast<void*>(k_pool), const_cast<void*>(v_pool), table, table_width,
                                            pool_blocks, len_before, sequences, heads, kv_heads, scale_log2, window, splits, out,
-                                           part_acc, part_ml, status, stream);
+                                           part_acc, part_ml, tickets, status, stream);
     } else {
         // packed prompts: keys are not sliced (a prompt has tiles enough); a CTA is 64 query rows
         if (splits != 1) return (int)cudaErrorInvalidValue;
@@ -729,13 +771,16 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* tab
             len_before, sequences, heads, kv_heads, scale_log2, window, tokens_per_tile, cta_tiles, (__nv_bfloat16*)out, status);
     }
     if (err != cudaSuccess) return (int)err;
-    return merge_slices<HD>(n_tokens, heads, splits, out, part_acc, part_ml, stream, one_token_each && slices_form_cluster(splits));
+    return merge_slices<HD>(n_tokens, heads, splits, out, part_acc, part_ml, stream, one_token_each && (slices_form_cluster(splits) || tickets));
 }
 
 }  // namespace
 
 // one_token_each: 0 = packed prompts (any number of tokens per sequence); 1 = every
 // sequence brings exactly one token (n_tokens == sequences) and the decode kernel runs.
+// tickets: null, or sequences * kv_heads words that are zero (and are zero again when the kernel is done): with
+// more slices than a cluster holds, the CTA that finishes last for a (sequence, kv head) then combines the
+// slices itself and no merge kernel is launched.
 // 1 if this kernel takes the sizes, 0 if the exact kernel has to serve them.
 extern "C" int tt_attention_mma_supports(int heads, int kv_heads, int head_dim) {
     if (kv_heads <= 0 || heads % kv_heads || heads / kv_heads > 16) return 0;
@@ -745,13 +790,13 @@ extern "C" int tt_attention_mma_supports(int heads, int kv_heads, int head_dim) 
 extern "C" int tt_attention_mma(const void* q, const void* k_pool, const void* v_pool, const int* table, int table_width,
                                 int pool_blocks, const int* cu, const int* len_before, int sequences, int n_tokens,
                                 int heads, int kv_heads, int head_dim, float scale, int window, int splits,
-                                int one_token_each, void* out, float* part_acc, float* part_ml, unsigned* status,
+                                int one_token_each, void* out, float* part_acc, float* part_ml, unsigned* tickets, unsigned* status,
                                 cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (!tt_attention_mma_supports(heads, kv_heads, head_dim) || splits < 1 || splits > 65535 || kv_heads > 65535)
         return (int)cudaErrorInvalidValue;
     if (splits > 1 && (!part_acc || !part_ml)) return (int)cudaErrorInvalidValue;
-#define TT_LAUNCH(HD) return launch<HD>(q, k_pool, v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, scale, window, splits, one_token_each, out, part_acc, part_ml, status, stream)
+#define TT_LAUNCH(HD) return launch<HD>(q, k_pool, v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, scale, window, splits, one_token_each, out, part_acc, part_ml, tickets, status, stream)
     switch (head_dim) {
         case 32: TT_LAUNCH(32);
         case 64: TT_LAUNCH(64);
@@ -777,7 +822,7 @@ extern "C" int tt_attention_decode_rope(const float* qkv, int qkv_splits, long l
                                         int rotary_dim, float attention_scaling, int write_cache, void* k_pool, void* v_pool,
                                         const int* table, int table_width, int pool_blocks, const int* len_before,
                                         int sequences, int heads, int kv_heads, int head_dim, float scale, int window,
-                                        int splits, void* out, float* part_acc, float* part_ml, unsigned* status,
+                                        int splits, void* out, float* part_acc, float* part_ml, unsigned* tickets, unsigned* status,
                                         cudaStream_t stream) {
     if (sequences <= 0) return 0;
     if (!tt_attention_decode_rope_supports(heads, kv_heads, head_dim, rotary_dim) || splits < 1 || splits > 65535 || kv_heads > 65535 ||
@@ -787,7 +832,7 @@ extern "C" int tt_attention_decode_rope(const float* qkv, int qkv_splits, long l
     const DecodeRope rope{qkv, qkv_splits, (size_t)split_stride, inv_freq, attention_scaling, write_cache};
     const float scale_log2 = scale * 1.4426950408889634f;
     const cudaError_t err = launch_decode<64, true>(nullptr, rope, k_pool, v_pool, table, table_width, pool_blocks, len_before, sequences,
-                                                    heads, kv_heads, scale_log2, window, splits, out, part_acc, part_ml, status, stream);
+                                                    heads, kv_heads, scale_log2, window, splits, out, part_acc, part_ml, tickets, status, stream);
     if (err != cudaSuccess) return (int)err;
-    return merge_slices<64>(sequences, heads, splits, out, part_acc, part_ml, stream, slices_form_cluster(splits));
+    return merge_slices<64>(sequences, heads, splits, out, part_acc, part_ml, stream, slices_form_cluster(splits) || tickets);
 }

@@ -50,6 +50,15 @@ class Workspace:
             self._views[key] = view
         return view
 
+    def get_zeroed(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        """Like :meth:`get`, for a buffer that is zero when it is first handed out (and again whenever it has had
+        to move); afterwards its users leave it as they found it."""
+        buffer = self._buffers.get(name)
+        view = self.get(name, shape, dtype)
+        if self._buffers.get(name) is not buffer:
+            self._buffers[name].zero_()
+        return view
+
     def bytes(self) -> int:
         return sum(b.numel() for b in self._buffers.values())
 

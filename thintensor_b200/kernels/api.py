@@ -278,10 +278,17 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table
               _ptr(part_acc), _ptr(part_ml), _ptr(status), _stream()), "attention", 2 if splits > 1 else 1)
 
 
-def _attention_launches(splits: int, decode: bool) -> int:
+def _attention_launches(splits: int, decode: bool, tickets: bool = False) -> int:
     """Kernels one call launches: the decode kernel combines up to 8 slices itself (a thread-block
-    cluster), more slices need the merge kernel."""
-    return 1 if splits == 1 or (decode and splits <= 8) else 2
+    cluster) and, given tickets, any number; otherwise more slices need the merge kernel."""
+    return 1 if splits == 1 or (decode and (splits <= 8 or tickets)) else 2
+
+
+def _check_tickets(tickets: torch.Tensor | None, sequences: int, kv_heads: int) -> None:
+    if tickets is not None:
+        _need(tickets, torch.int32, "tickets")
+        if tickets.numel() < sequences * kv_heads:
+            raise KernelError(f"decode attention needs {sequences * kv_heads} tickets, got {tickets.numel()}")
 
 
 def attention_mma_supports(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int) -> bool:
@@ -293,21 +300,26 @@ def attention_mma_supports(dtype: torch.dtype, heads: int, kv_heads: int, head_d
 def attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor, cu: torch.Tensor,
                   len_before: torch.Tensor, sequences: int, n_tokens: int, heads: int, kv_heads: int, head_dim: int,
                   scale: float, window: int, splits: int, out: torch.Tensor, part_acc: torch.Tensor | None,
-                  part_ml: torch.Tensor | None, status: torch.Tensor, one_token_each: bool = False) -> None:
+                  part_ml: torch.Tensor | None, status: torch.Tensor, one_token_each: bool = False,
+                  tickets: torch.Tensor | None = None) -> None:
     """Causal attention of packed bfloat16 query tokens over the block cache on tensor cores.
-    ``one_token_each`` (decoding): the warps of a CTA share a sequence's tile and split its keys."""
+    ``one_token_each`` (decoding): the warps of a CTA share a sequence's tile and split its keys.
+    ``tickets`` (decoding; int32, one per sequence and key/value head, zero before the call and after it): with
+    more slices than a cluster combines, the CTA that finishes last combines them and no second kernel runs."""
     if not attention_mma_supports(q.dtype, heads, kv_heads, head_dim):
         raise KernelError(f"the tensor-core attention kernel does not take {q.dtype}, {heads}/{kv_heads} heads of size {head_dim}")
     if not (k_pool.dtype == v_pool.dtype == out.dtype == torch.bfloat16):
         raise KernelError("queries, cache and output must all be bfloat16")
     if one_token_each and n_tokens != sequences:
         raise KernelError("one_token_each needs exactly one token per sequence")
+    tickets = tickets if one_token_each else None
+    _check_tickets(tickets, sequences, kv_heads)
     fn = _fn("attention_mma", "tt_attention_mma", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
-                                                   c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+                                                   c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
     _check(fn(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(table), table.shape[1], k_pool.shape[0], _ptr(cu), _ptr(len_before), sequences,
               n_tokens, heads, kv_heads, head_dim, scale, window, splits, sequences if one_token_each else 0, _ptr(out), _ptr(part_acc),
-              _ptr(part_ml), _ptr(status),
-              _stream()), "attention_mma", _attention_launches(splits, one_token_each))
+              _ptr(part_ml), _ptr(tickets), _ptr(status),
+              _stream()), "attention_mma", _attention_launches(splits, one_token_each, tickets is not None))
 
 
 def attention_decode_rope_supports(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int, rotary_dim: int) -> bool:
@@ -320,7 +332,7 @@ def attention_decode_rope(qkv: torch.Tensor, inv_freq: torch.Tensor, rotary_dim:
                           k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor, len_before: torch.Tensor,
                           sequences: int, heads: int, kv_heads: int, head_dim: int, scale: float, window: int, splits: int,
                           out: torch.Tensor, part_acc: torch.Tensor | None, part_ml: torch.Tensor | None,
-                          status: torch.Tensor) -> None:
+                          status: torch.Tensor, tickets: torch.Tensor | None = None) -> None:
     """One decode step of attention straight from the float32 partial sums ``qkv``
     [slices, sequences, cols] of the qkv product: q and k are rotated, k and v are written to
     the cache (``write_cache``; else ``qkv`` holds queries only), then every sequence's token
@@ -334,13 +346,14 @@ def attention_decode_rope(qkv: torch.Tensor, inv_freq: torch.Tensor, rotary_dim:
     cols = heads * head_dim + (2 * kv_heads * head_dim if write_cache else 0)
     if qkv.shape[-1] != cols or qkv.shape[1] != sequences:
         raise KernelError(f"qkv is {tuple(qkv.shape)}, expected [slices, {sequences}, {cols}]")
+    _check_tickets(tickets, sequences, kv_heads)
     fn = _fn("attention_mma", "tt_attention_decode_rope", [c_void_p, c_int, c_longlong, c_void_p, c_int, c_float, c_int, c_void_p, c_void_p,
                                                            c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
-                                                           c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+                                                           c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
     _check(fn(_ptr(qkv), qkv.shape[0], qkv.stride(0), _ptr(inv_freq), rotary_dim, attention_scaling, 1 if write_cache else 0, _ptr(k_pool),
               _ptr(v_pool), _ptr(table), table.shape[1], k_pool.shape[0], _ptr(len_before), sequences, heads, kv_heads, head_dim, scale,
-              window, splits, _ptr(out), _ptr(part_acc), _ptr(part_ml), _ptr(status), _stream()), "attention_decode_rope",
-           _attention_launches(splits, True))
+              window, splits, _ptr(out), _ptr(part_acc), _ptr(part_ml), _ptr(tickets), _ptr(status), _stream()), "attention_decode_rope",
+           _attention_launches(splits, True, tickets is not None))
 
 
 def attention_tcgen05_supports(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int) -> bool:

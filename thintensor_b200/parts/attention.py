@@ -120,7 +120,8 @@ class CausalAttention(Mixer):
             part_acc, part_ml = self.slice_scratch(ctx, splits)
             api.attention_decode_rope(projection, rot.inv_freq, rot.rotary_dim, rot.attention_scaling, cache.writes,
                                       cache.k_pool, cache.v_pool, table, ctx.len_before, ctx.sequences, self.heads, self.kv_heads,
-                                      self.head_dim, self.scale, self.window or 0, splits, mixed, part_acc, part_ml, ctx.status)
+                                      self.head_dim, self.scale, self.window or 0, splits, mixed, part_acc, part_ml, ctx.status,
+                                      tickets=self.tickets(ctx, splits))
             return self.out.delta(ctx, mixed, "attention.out")
         q = ctx.scratch("attention.q", (ctx.n_tokens, q_cols))
         api.rope_append(projection, rot.inv_freq, rot.rotary_dim, rot.attention_scaling, q,
@@ -157,6 +158,13 @@ class CausalAttention(Mixer):
         return (ctx.scratch("attention.part_acc", (ctx.n_tokens * self.heads * splits * self.head_dim,), torch.float32),
                 ctx.scratch("attention.part_ml", (ctx.n_tokens * self.heads * splits * 2,), torch.float32))
 
+    def tickets(self, ctx, splits: int):
+        """With more key slices than a thread-block cluster combines (8), the decode kernel's CTAs draw tickets and
+        the last one of a (sequence, kv head) combines the slices: one word each, zero between launches."""
+        if splits <= 8:
+            return None
+        return ctx.workspace.get_zeroed("attention.tickets", (max(ctx.sequences * self.kv_heads, 64),), torch.int32)
+
     def attend(self, ctx, q, cache, table, mixed) -> None:
         """Prompts in bfloat16 with head size 64 or 128: the tcgen05 kernel.  Other bfloat16
         sizes up to 128 and all decoding: the mma.sync kernels.  Everything else (float32,
@@ -174,7 +182,7 @@ class CausalAttention(Mixer):
         if tensor_cores:
             api.attention_mma(q, cache.k_pool, cache.v_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads,
                               self.kv_heads, self.head_dim, self.scale, self.window or 0, splits, mixed, part_acc, part_ml, ctx.status,
-                              one_token_each=ctx.decode)
+                              one_token_each=ctx.decode, tickets=self.tickets(ctx, splits) if ctx.decode else None)
         else:
             api.attention(q, cache.k_pool, cache.v_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads,
                           self.kv_heads, self.head_dim, self.scale, self.window or 0, splits, mixed, part_acc, part_ml, ctx.status)
