@@ -388,7 +388,55 @@ struct DecodeRope {
     int write_cache;
 };
 
-template <int HD, bool ROPE, int SHAPE>
+// More key slices than a cluster holds: every CTA of a (sequence, kv head) has left its partial result in scratch
+// memory; the one that finishes last combines them all, in slice order, so that no merge kernel has to be launched
+// and waited for.  A CTA's stores are fenced before it draws its ticket, and the last CTA fences again before it
+// reads the others': the usual last-block reduction, without any waiting.
+template <int HD>
+__device__ __noinline__ void combine_by_last_cta(unsigned* __restrict__ tickets, const float* __restrict__ part_acc,
+                                                 const float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out, int b, int kh,
+                                                 int heads, int kv_heads, int group, int splits, int threads) {
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned* ticket = tickets + (size_t)b * kv_heads + kh;
+        const unsigned drawn = atomicAdd(ticket, 1u);
+        is_last = drawn == (unsigned)splits - 1u;
+        if (is_last) *ticket = 0u;                      // nobody else touches it any more: ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int idx = threadIdx.x; idx < group * (HD / 2); idx += threads) {
+        const int r = idx / (HD / 2), d = 2 * (idx - r * (HD / 2));
+        const size_t row_index = (size_t)b * heads + kh * group + r;
+        const float* ml = part_ml + row_index * splits * 2;
+        const float* acc = part_acc + row_index * splits * HD + d;
+        float m = -INFINITY;
+#pragma unroll 8
+        for (int sl = 0; sl < splits; ++sl) m = fmaxf(m, __ldcg(ml + 2 * sl));
+        float l = 0.0f, acc0 = 0.0f, acc1 = 0.0f;
+        if (m != -INFINITY) {
+#pragma unroll 8
+            for (int sl = 0; sl < splits; ++sl) {
+                const float2 state = __ldcg(reinterpret_cast<const float2*>(ml + 2 * sl));     // (maximum in natural units, sum)
+                const float2 o = __ldcg(reinterpret_cast<const float2*>(acc + (size_t)sl * HD));
+                const float weight = state.x == -INFINITY ? 0.0f : expf(state.x - m);
+                l = fmaf(state.y, weight, l);
+                acc0 = fmaf(o.x, weight, acc0);
+                acc1 = fmaf(o.y, weight, acc1);
+            }
+        }
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+        *reinterpret_cast<__nv_bfloat162*>(out + row_index * HD + d) = __floats2bfloat162_rn(acc0 * inv, acc1 * inv);
+    }
+}
+
+// TICKETS: the instance that can combine more slices than a cluster holds by itself (see combine_by_last_cta).  It
+// is a kernel of its own because the mere presence of that path cost the others' main loop 8 to 28 % (measured on a
+// B200: 0.853 -> 0.92 ms per step at batch 8, 2.09 -> 2.65 ms with 32,768 cached tokens), whether inlined or not.
+template <int HD, bool ROPE, int SHAPE, bool TICKETS = false>
 __global__ void __launch_bounds__(DecodeShape<HD, SHAPE>::WARPS * 32)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __nv_bfloat16* __restrict__ k_pool,
                         __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ table, int table_width,
@@ -605,47 +653,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
             }
         }
     }
-    if (splits > 1 && !cluster_merge && tickets) {
-        // More slices than a cluster holds: every CTA has left its partial result in scratch memory; the one that
-        // finishes last for this (sequence, kv head) combines them all, in slice order, so that no merge kernel has
-        // to be launched and waited for.  Its stores are fenced before it draws its ticket, and the last CTA fences
-        // again before it reads the others': the usual last-block reduction, without any waiting.
-        __shared__ int is_last;
-        __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            unsigned* ticket = tickets + (size_t)b * kv_heads + kh;
-            const unsigned drawn = atomicAdd(ticket, 1u);
-            is_last = drawn == (unsigned)splits - 1u;
-            if (is_last) *ticket = 0u;                  // nobody else touches it any more: ready for the next launch
-        }
-        __syncthreads();
-        if (is_last) {
-            __threadfence();
-            for (int idx = threadIdx.x; idx < group * (HD / 2); idx += WARPS * 32) {
-                const int r = idx / (HD / 2), d = 2 * (idx - r * (HD / 2));
-                const size_t row_index = (size_t)b * heads + kh * group + r;
-                const float* ml = part_ml + row_index * splits * 2;
-                const float* acc = part_acc + row_index * splits * HD + d;
-                float m = -INFINITY;
-#pragma unroll 8
-                for (int sl = 0; sl < splits; ++sl) m = fmaxf(m, __ldcg(ml + 2 * sl));
-                float l = 0.0f, acc0 = 0.0f, acc1 = 0.0f;
-                if (m != -INFINITY) {
-#pragma unroll 8
-                    for (int sl = 0; sl < splits; ++sl) {
-                        const float2 state = __ldcg(reinterpret_cast<const float2*>(ml + 2 * sl));     // (maximum in natural units, sum)
-                        const float2 o = __ldcg(reinterpret_cast<const float2*>(acc + (size_t)sl * HD));
-                        const float weight = state.x == -INFINITY ? 0.0f : expf(state.x - m);
-                        l = fmaf(state.y, weight, l);
-                        acc0 = fmaf(o.x, weight, acc0);
-                        acc1 = fmaf(o.y, weight, acc1);
-                    }
-                }
-                const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-                *reinterpret_cast<__nv_bfloat162*>(out + row_index * HD + d) = __floats2bfloat162_rn(acc0 * inv, acc1 * inv);
-            }
-        }
+    if constexpr (TICKETS) {
+        if (splits > 1 && !cluster_merge && tickets)
+            combine_by_last_cta<HD>(tickets, part_acc, part_ml, out, b, kh, heads, kv_heads, group, splits, WARPS * 32);
     }
     if (splits > 1 && cluster_merge) {
         cg::cluster_group cluster = cg::this_cluster();
@@ -689,6 +699,20 @@ cudaError_t launch_decode(const void* q, const DecodeRope& rope, void* k_pool, v
     using D = DecodeShape<HD, SHAPE>;
     constexpr int shared = D::WARPS * D::STAGES * (8 * (HD / 32) + (HD / 8) * 2) * 32 * 16;
     static_assert(shared >= D::WARPS * 16 * (HD + 6) * 4 + 16 * (HD + 2) * 4, "the slots must also hold the warps' and the CTA's partial results");
+    if constexpr (SHAPE == ONE_PER_SM) {
+        if (tickets && splits > 1 && !slices_form_cluster(splits)) {
+            static bool configured_tickets = false;
+            auto with_tickets = attention_decode_kernel<HD, ROPE, SHAPE, true>;
+            if (!configured_tickets) {
+                const cudaError_t err = cudaFuncSetAttribute(with_tickets, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
+                if (err != cudaSuccess) return err;
+                configured_tickets = true;
+            }
+            return tt_launch_pdl(with_tickets, dim3(sequences, kv_heads, splits), dim3(D::WARPS * 32), shared, stream,
+                (const __nv_bfloat16*)q, rope, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks,
+                len_before, heads, kv_heads, scale_log2, window, splits, 0, (__nv_bfloat16*)out, part_acc, part_ml, tickets, status);
+        }
+    }
     static bool configured = false;
     auto kernel = attention_decode_kernel<HD, ROPE, SHAPE>;
     if (!configured) {
@@ -732,6 +756,7 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* tab
             if ((err = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device)) != cudaSuccess) return (int)err;
         }
         const long long ctas = (long long)sequences * kv_heads * splits;
+        if (ctas > sm_count) tickets = nullptr;         // several CTAs per SM: the variants without tickets, and the merge kernel
         bool done = false;
         if constexpr (decode_has_small_shapes<HD>) {
             if (ctas > 2 * sm_count && ctas <= 3 * sm_count) {          // one wave of three CTAs per SM
