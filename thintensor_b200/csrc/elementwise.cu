@@ -108,7 +108,9 @@ __device__ __forceinline__ void tt_store4(__nv_bfloat16* p, float a, float b, fl
 // (up to four) float4 pieces of the row in registers, all loads of the k-slices are
 // independent, and the order of additions is the one of the kernel above.
 #define NORM_VEC_MAX 4
-template <typename TOut>
+// PIECES: float4 pieces of a row per thread: 1 when the block is as wide as the row (few rows: decoding), else up to
+// NORM_VEC_MAX (prompts).  BATCH: how many k-slices' loads are in flight together.
+template <typename TOut, int PIECES, int BATCH>
 __global__ void __launch_bounds__(1024)
 add_rmsnorm_vec_kernel(float* __restrict__ residual, const float* __restrict__ delta, int splits, size_t split_stride,
                        const float* __restrict__ weight, float weight_offset, float eps, TOut* __restrict__ out,
@@ -119,9 +121,9 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const float* __restrict__ d
     const int quads = hidden >> 2;
     // the norm's weight is written by no kernel: it is fetched while the previous kernel still runs
     const float4* w4 = reinterpret_cast<const float4*>(weight);
-    float4 w[NORM_VEC_MAX];
+    float4 w[PIECES];
 #pragma unroll
-    for (int v = 0; v < NORM_VEC_MAX; ++v) {
+    for (int v = 0; v < PIECES; ++v) {
         const int j = threadIdx.x + v * blockDim.x;
         if (j < quads) w[v] = __ldg(w4 + j);
     }
@@ -130,25 +132,23 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const float* __restrict__ d
     float4* res = reinterpret_cast<float4*>(residual + (size_t)r * hidden);
     const float4* del = delta ? reinterpret_cast<const float4*>(delta + (size_t)r * hidden) : nullptr;
     const size_t stride4 = split_stride >> 2;
-    float4 x[NORM_VEC_MAX];
+    float4 x[PIECES];
     float sumsq = 0.0f;
 #pragma unroll
-    for (int v = 0; v < NORM_VEC_MAX; ++v) {
+    for (int v = 0; v < PIECES; ++v) {
         const int j = threadIdx.x + v * blockDim.x;
         if (j < quads) {
             float4 a = res[j];
-            int s = 0;
-            for (; s + 4 <= splits; s += 4) {
-                const float4 d0 = __ldg(del + (size_t)s * stride4 + j), d1 = __ldg(del + (size_t)(s + 1) * stride4 + j);
-                const float4 d2 = __ldg(del + (size_t)(s + 2) * stride4 + j), d3 = __ldg(del + (size_t)(s + 3) * stride4 + j);
-                a.x = (((a.x + d0.x) + d1.x) + d2.x) + d3.x;
-                a.y = (((a.y + d0.y) + d1.y) + d2.y) + d3.y;
-                a.z = (((a.z + d0.z) + d1.z) + d2.z) + d3.z;
-                a.w = (((a.w + d0.w) + d1.w) + d2.w) + d3.w;
-            }
-            for (; s < splits; ++s) {
-                const float4 d0 = __ldg(del + (size_t)s * stride4 + j);
-                a.x += d0.x; a.y += d0.y; a.z += d0.z; a.w += d0.w;
+            // BATCH slices' loads are in flight together (one after the other they cost a round trip to the L2
+            // each: a decode step's norm after a product of 16 k-slices); the additions keep the slices' order
+            for (int s0 = 0; s0 < splits; s0 += BATCH) {
+                float4 d[BATCH];
+#pragma unroll
+                for (int i = 0; i < BATCH; ++i)
+                    if (s0 + i < splits) d[i] = __ldg(del + (size_t)(s0 + i) * stride4 + j);
+#pragma unroll
+                for (int i = 0; i < BATCH; ++i)
+                    if (s0 + i < splits) { a.x += d[i].x; a.y += d[i].y; a.z += d[i].z; a.w += d[i].w; }
             }
             if (!rows && splits > 0) res[j] = a;
             x[v] = a;
@@ -159,7 +159,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const float* __restrict__ d
     const float rstd = rsqrtf(total / (float)hidden + eps);
     TOut* o = out + (size_t)i * hidden;
 #pragma unroll
-    for (int v = 0; v < NORM_VEC_MAX; ++v) {
+    for (int v = 0; v < PIECES; ++v) {
         const int j = threadIdx.x + v * blockDim.x;
         if (j < quads) {
             const float y0 = x[v].x * rstd * (w[v].x + weight_offset), y1 = x[v].y * rstd * (w[v].y + weight_offset);
@@ -185,10 +185,11 @@ extern "C" int tt_add_rmsnorm(float* residual, const float* delta, int splits, l
             threads = fewest < 128 ? 128 : fewest;
             if (threads > 1024) threads = 1024;
         }
-        if (out_dtype == TT_F32)
-            tt_launch_pdl(add_rmsnorm_vec_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, residual, delta, splits, (size_t)split_stride, weight, weight_offset, eps, (float*)out, rows, hidden);
-        else
-            tt_launch_pdl(add_rmsnorm_vec_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, residual, delta, splits, (size_t)split_stride, weight, weight_offset, eps, (__nv_bfloat16*)out, rows, hidden);
+        const bool one_piece = threads * 4 >= hidden;         // the block covers the row: one piece per thread, eight slices at a time
+#define TT_NORM(T, P, B) tt_launch_pdl(add_rmsnorm_vec_kernel<T, P, B>, dim3(n_rows), dim3(threads), 0, stream, residual, delta, splits, (size_t)split_stride, weight, weight_offset, eps, (T*)out, rows, hidden)
+        if (out_dtype == TT_F32) { if (one_piece) TT_NORM(float, 1, 8); else TT_NORM(float, NORM_VEC_MAX, 2); }
+        else { if (one_piece) TT_NORM(__nv_bfloat16, 1, 8); else TT_NORM(__nv_bfloat16, NORM_VEC_MAX, 2); }
+#undef TT_NORM
         TT_LAUNCH_CHECK();
     }
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
