@@ -512,11 +512,17 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
         const bool append = rope.write_cache && my_begin <= block1 && block1 < my_end;   // this CTA reads the new key
         const int pair_rows = group + (append ? 1 : 0);
         const int items = pair_rows * HALF + (append ? HALF : 0);      // the value's numbers go two to an item, like the pairs
-        auto sum_slices = [&](const float* p) {
-            float total = 0.0f;
+        // two numbers HALF apart, each summed over the product's k-slices in slice order; the loads of both and of
+        // up to eight slices are in flight together (one loop per number cost a second round trip to the L2)
+        auto sum_slices_pair = [&](const float* p, float& first, float& second) {
+            float x = 0.0f, y = 0.0f;
 #pragma unroll 8
-            for (int s = 0; s < rope.splits; ++s) total += __ldg(p + (size_t)s * rope.split_stride);
-            return total;
+            for (int s = 0; s < rope.splits; ++s) {
+                x += __ldg(p + (size_t)s * rope.split_stride);
+                y += __ldg(p + HALF + (size_t)s * rope.split_stride);
+            }
+            first = x;
+            second = y;
         };
         long long k_off = -1, v_off = -1;
         if (append) {
@@ -527,7 +533,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
             if (item < pair_rows * HALF) {
                 const int r = item / HALF, i = item - r * HALF;
                 const float* p = r < group ? row + (size_t)(kh * group + r) * HD + i : row + q_cols + (size_t)kh * HD + i;
-                const float a = sum_slices(p), bb = sum_slices(p + HALF);
+                float a, bb;
+                sum_slices_pair(p, a, bb);
                 float si, co;
                 sincosf(rope.inv_freq[i] * (float)pos, &si, &co);
                 co *= rope.attention_scaling;
@@ -543,7 +550,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
             } else {
                 const int d = item - pair_rows * HALF;
                 const float* p = row + q_cols + kv_cols + (size_t)kh * HD + d;
-                const float a = sum_slices(p), bb = sum_slices(p + HALF);
+                float a, bb;
+                sum_slices_pair(p, a, bb);
                 if (v_off >= 0) {
                     v_pool[v_off + (long long)d * TT_BLOCK_TOKENS] = __float2bfloat16_rn(a);
                     v_pool[v_off + (long long)(d + HALF) * TT_BLOCK_TOKENS] = __float2bfloat16_rn(bb);

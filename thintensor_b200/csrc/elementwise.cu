@@ -467,9 +467,10 @@ __global__ void swiglu_kernel(const float* __restrict__ gate_up, int splits, siz
     const int j = (int)(idx - t * inter);
     const float* row = gate_up + t * (size_t)(2 * inter);
     float g = 0.0f, u = 0.0f;
-    for (int s = 0; s < splits; ++s) {
-        g += row[s * split_stride + j];
-        u += row[s * split_stride + inter + j];
+#pragma unroll 4
+    for (int s = 0; s < splits; ++s) {                  // gate and up of up to four slices in flight together
+        g += __ldg(row + s * split_stride + j);
+        u += __ldg(row + s * split_stride + inter + j);
     }
     act[idx] = tt_from_float<TAct>(g / (1.0f + expf(-g)) * u);
 }
