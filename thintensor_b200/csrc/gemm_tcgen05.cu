@@ -95,13 +95,20 @@ struct Args {
     unsigned* status;
 };
 
-template <int FORM, int BN, int STAGES>
+// GROUP: k-blocks that share one round of the full / empty barriers (STAGES is a multiple of it).  With few tokens
+// a k-block is four short products; waiting, fencing and committing once per k-block cost the issuing thread more
+// than the products themselves (520 cycles a k-block of which the products are 234, measured with a one-CTA probe),
+// so the form for up to 16 tokens takes two k-blocks per round.  Measured on a B200, decode step of the 1B shape:
+// batch 16 0.923 -> 0.908 ms, batch 1 and 8 unchanged within noise (there the tiles' arrival paces the loop).
+template <int FORM, int BN, int STAGES, int GROUP = 1>
 __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Args args) {
     using S = Shape<FORM, BN>;
+    static_assert(STAGES % GROUP == 0, "whole groups of stages");
+    constexpr int RING = STAGES / GROUP;                       // barrier rounds the ring holds
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle groups need 1024-byte alignment
-    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
+    __shared__ uint64_t full_bar[RING], empty_bar[RING], acc_bar;
     __shared__ uint32_t tmem_base_shared;
 
     tt_pdl_launch_dependents();
@@ -111,9 +118,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int kb_begin = split * args.k_blocks_per_split;
     const int kb_end = min(k_blocks_total, kb_begin + args.k_blocks_per_split);
     const int n_kb = max(0, kb_end - kb_begin);
+    const int n_groups = (n_kb + GROUP - 1) / GROUP;
+    auto blocks_of = [&](int group) { return min(GROUP, n_kb - group * GROUP); };      // k-blocks of a barrier round (the last may be short)
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
+        for (int s = 0; s < RING; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
         mbar_init(smem_u32(&acc_bar), 1);
         fence_barrier_init();
     }
@@ -144,63 +153,68 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // activations; under programmatic dependent launch that fetch overlaps the
         // tail of the previous kernel.
         if (lane == 0) {
-            const int first = min(n_kb, STAGES);
-            for (int i = 0; i < first; ++i) {               // stages are empty: nothing to wait for
-                const uint32_t bar = smem_u32(&full_bar[i]);
-                mbar_expect_tx(bar, S::stage_bytes + (i == 0 ? args.undelivered_bytes : 0));
-                uint8_t* stage = smem + (size_t)i * S::stage_bytes;
-                const int kx = (kb_begin + i) * BK;
+            auto load_weights = [&](uint8_t* stage, int kx, uint32_t bar) {
                 if (weights_are_a) {
                     load_a(stage, kx, bar);
                 } else {
                     tma_load_2d(smem_u32(stage + S::a_bytes), &map_b, kx, b_row, bar);
                     if (S::dual) tma_load_2d(smem_u32(stage + S::a_bytes + BN * BK * 2), &map_b, kx, args.up_row_offset + b_row, bar);
                 }
-            }
-            tt_pdl_wait();
-            for (int i = 0; i < first; ++i) {
-                const uint32_t bar = smem_u32(&full_bar[i]);
-                uint8_t* stage = smem + (size_t)i * S::stage_bytes;
-                const int kx = (kb_begin + i) * BK;
+            };
+            auto load_activations = [&](uint8_t* stage, int kx, uint32_t bar) {
                 if (weights_are_a) tma_load_2d(smem_u32(stage + S::a_bytes), &map_b, kx, b_row, bar);
                 else load_a(stage, kx, bar);
+            };
+            const int first = min(n_groups, RING);
+            for (int g = 0; g < first; ++g) {               // the ring is empty: nothing to wait for
+                const uint32_t bar = smem_u32(&full_bar[g]);
+                mbar_expect_tx(bar, blocks_of(g) * S::stage_bytes + (g == 0 ? args.undelivered_bytes : 0));
+                for (int q = 0; q < blocks_of(g); ++q)
+                    load_weights(smem + (size_t)(g * GROUP + q) * S::stage_bytes, (kb_begin + g * GROUP + q) * BK, bar);
             }
+            tt_pdl_wait();
+            for (int g = 0; g < first; ++g)
+                for (int q = 0; q < blocks_of(g); ++q)
+                    load_activations(smem + (size_t)(g * GROUP + q) * S::stage_bytes, (kb_begin + g * GROUP + q) * BK, smem_u32(&full_bar[g]));
             int issued = first;
-            for (int i = first; i < n_kb; ++i) {
-                const int s = i % STAGES;
-                const uint32_t parity = ((i / STAGES) & 1) ^ 1;
+            for (int g = first; g < n_groups; ++g) {
+                const int s = g % RING;
+                const uint32_t parity = ((g / RING) & 1) ^ 1;
                 if (!mbar_wait(smem_u32(&empty_bar[s]), parity)) { atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); break; }
                 const uint32_t bar = smem_u32(&full_bar[s]);
-                mbar_expect_tx(bar, S::stage_bytes);
-                uint8_t* stage = smem + (size_t)s * S::stage_bytes;
-                const int kx = (kb_begin + i) * BK;
-                load_a(stage, kx, bar);
-                tma_load_2d(smem_u32(stage + S::a_bytes), &map_b, kx, b_row, bar);
-                if (S::dual) tma_load_2d(smem_u32(stage + S::a_bytes + BN * BK * 2), &map_b, kx, args.up_row_offset + b_row, bar);
+                mbar_expect_tx(bar, blocks_of(g) * S::stage_bytes);
+                for (int q = 0; q < blocks_of(g); ++q) {
+                    uint8_t* stage = smem + (size_t)(s * GROUP + q) * S::stage_bytes;
+                    const int kx = (kb_begin + g * GROUP + q) * BK;
+                    load_weights(stage, kx, bar);
+                    load_activations(stage, kx, bar);
+                }
                 ++issued;
             }
             // drain: every copy issued must have landed before shared memory is given up
-            for (int i = max(0, issued - STAGES); i < issued; ++i)
-                if (!mbar_wait(smem_u32(&full_bar[i % STAGES]), (i / STAGES) & 1)) { atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); break; }
+            for (int g = max(0, issued - RING); g < issued; ++g)
+                if (!mbar_wait(smem_u32(&full_bar[g % RING]), (g / RING) & 1)) { atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); break; }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc = instr_desc(BM, S::dual ? 2 * BN : BN);   // gate and up tiles lie like one tile of 2 BN rows
             bool ok = true;
-            for (int i = 0; i < n_kb && ok; ++i) {
-                const int s = i % STAGES;
-                if (!mbar_wait(smem_u32(&full_bar[s]), (i / STAGES) & 1)) { atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; break; }
+            for (int g = 0; g < n_groups && ok; ++g) {
+                const int s = g % RING;
+                if (!mbar_wait(smem_u32(&full_bar[s]), (g / RING) & 1)) { atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; break; }
                 fence_after_sync();
-                const uint32_t a_addr = smem_u32(smem + (size_t)s * S::stage_bytes);
-                const uint32_t b_addr = a_addr + S::a_bytes;
+                for (int q = 0; q < blocks_of(g); ++q) {
+                    const uint32_t a_addr = smem_u32(smem + (size_t)(s * GROUP + q) * S::stage_bytes);
+                    const uint32_t b_addr = a_addr + S::a_bytes;
 #pragma unroll
-                for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-                    const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
-                    const uint64_t da = smem_desc(a_addr + kk * UMMA_K * 2);
-                    umma_bf16(tmem_base, da, smem_desc(b_addr + kk * UMMA_K * 2), idesc, acc);
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                        const uint32_t acc = (g > 0 || q > 0 || kk > 0) ? 1u : 0u;
+                        const uint64_t da = smem_desc(a_addr + kk * UMMA_K * 2);
+                        umma_bf16(tmem_base, da, smem_desc(b_addr + kk * UMMA_K * 2), idesc, acc);
+                    }
                 }
-                umma_commit(smem_u32(&empty_bar[s]));     // the stage is free once these products have read it
+                umma_commit(smem_u32(&empty_bar[s]));     // the round's stages are free once these products have read them
             }
             if (ok) umma_commit(smem_u32(&acc_bar));      // the accumulator is complete once all products are done
         }
@@ -778,11 +792,11 @@ bool make_map(CUtensorMap* map, const void* base, long long rows, long long k, l
     return tc::make_map(map, base, 2, dims, strides, box);
 }
 
-template <int FORM, int BN, int STAGES>
+template <int FORM, int BN, int STAGES, int GROUP = 1>
 int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const Args& args, dim3 grid, cudaStream_t stream) {
     constexpr int shared = Shape<FORM, BN>::stage_bytes * STAGES + 1024;
     static bool configured = false;
-    auto kernel = gemm_tcgen05_kernel<FORM, BN, STAGES>;
+    auto kernel = gemm_tcgen05_kernel<FORM, BN, STAGES, GROUP>;
     if (!configured) {
         const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
         if (err != cudaSuccess) return (int)err;
@@ -990,7 +1004,7 @@ extern "C" int tt_gemm_tcgen05(const void* x, long long ldx, const void* w, long
     if (!make_map(&map_a, w, features, k, ldw, BM) || !make_map(&map_b, x, tokens, k, ldx, bn)) return -1;
     const dim3 grid(1, (features + BM - 1) / BM, splits);
     switch (bn) {
-        case 16: return launch<FEATURES_ON_M, 16, 6>(map_a, map_b, args, grid, stream);
+        case 16: return launch<FEATURES_ON_M, 16, 6, 2>(map_a, map_b, args, grid, stream);
         case 32: return launch<FEATURES_ON_M, 32, 5>(map_a, map_b, args, grid, stream);
         case 64: return launch<FEATURES_ON_M, 64, 4>(map_a, map_b, args, grid, stream);
         default: return launch<FEATURES_ON_M, 128, 3>(map_a, map_b, args, grid, stream);
