@@ -32,7 +32,7 @@ class Entry:
     these tokens whose logits are wanted."""
 
     slot: int
-    tokens: list[int]
+    tokens: list[int]           # or a one-dimensional integer numpy array
     want: list[int]
 
 
@@ -124,14 +124,17 @@ class Engine:
                 raise StepError(f"slot {entry.slot} appears twice in one step")
             seen.add(entry.slot)
             self.cache.length(entry.slot)  # raises if the slot is not live
-            if not entry.tokens:
+            if len(entry.tokens) == 0:
                 raise StepError(f"slot {entry.slot} brings no tokens")
             try:
-                tokens = np.fromiter(entry.tokens, dtype=np.int64, count=len(entry.tokens))
+                if isinstance(entry.tokens, np.ndarray) and entry.tokens.dtype.kind in "iu" and entry.tokens.ndim == 1:
+                    tokens = entry.tokens.astype(np.int64, copy=False)     # an integer array is taken as it is (a list costs 30 ns a token)
+                else:
+                    tokens = np.fromiter(entry.tokens, dtype=np.int64, count=len(entry.tokens))
             except (OverflowError, TypeError, ValueError) as exc:
                 raise StepError(f"slot {entry.slot}: token ids must be integers ({exc})") from None
             if tokens.min() < 0 or tokens.max() >= self.vocab_size:
-                token = next(t for t in entry.tokens if not 0 <= t < self.vocab_size)
+                token = next(int(t) for t in entry.tokens if not 0 <= t < self.vocab_size)
                 raise StepError(f"token id {token} is outside the vocabulary of {self.vocab_size}")
             arrays.append(tokens.astype(np.int32))
             if entry.want and (min(entry.want) < 0 or max(entry.want) >= len(entry.tokens)):
