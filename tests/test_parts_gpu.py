@@ -430,3 +430,104 @@ def test_toy_position_encoding(dtype):
         assert_close(torch.cat(got), want, "float32" if dtype == torch.float32 else "bfloat16", "toy position encoding")
     finally:
         POSITION_ENCODINGS.unregister("toy_interpolated")
+
+
+def test_toy_arrangement_with_two_mixers_side_by_side():
+    """A layer whose arrangement, defined and registered here, runs an attention and a recurrent toy mixer on the same
+    normed input and adds both outputs: the model gives each mixer a cache and states of its own (keys for the one,
+    a float32 sum and an int32 count for the other), per run of the schedule; whole prompts in a batch and token by
+    token agree with the plain parts wired the same way."""
+    from dataclasses import replace
+
+    from thintensor_b200.engine.engine import Entry
+    from thintensor_b200.parts import ARRANGEMENTS, MIXERS
+    from thintensor_b200.parts.base import Arrangement, Delta, Mixer, StateNeed, WeightDecl
+    from thintensor_b200.parts.spec import LayerSpec, PartSpec
+
+    @MIXERS.register("toy_memory")
+    class Memory(Mixer):
+        def __init__(self, hidden):
+            self.hidden = hidden
+
+        def weights(self):
+            return {"mix.weight": WeightDecl((self.hidden, self.hidden))}
+
+        def state_needs(self):
+            return [StateNeed((self.hidden,), torch.float32), StateNeed((1,), torch.int32)]
+
+        def bind(self, tensors, dtype, device):
+            self.w = tensors["mix.weight"].float()
+
+        def forward(self, ctx, x, cache, states):
+            total, count = states
+            assert cache.k_pool is None, "this mixer asked for no keys"
+            out = torch.empty(1, ctx.n_tokens, self.hidden, dtype=torch.float32, device=x.device)
+            at = 0
+            for slot, new in zip(ctx.host_slots, ctx.host_new):
+                sums = total[slot] + x[at: at + new].float().cumsum(0)
+                counts = count[slot] + torch.arange(1, new + 1, device=x.device, dtype=torch.int32)
+                out[0, at: at + new] = (sums / counts[:, None].float()) @ self.w.T
+                total[slot], count[slot] = sums[-1], counts[-1]
+                at += new
+            return Delta(out)
+
+    @ARRANGEMENTS.register("toy_side_by_side")
+    class SideBySide(Arrangement):
+        roles = {"norm": "norm", "attention": "mixer", "memory": "mixer", "ffn_norm": "norm", "ffn": "ffn"}
+
+        def mixers(self):
+            return [self.parts["attention"], self.parts["memory"]]
+
+        def run(self, ctx, residual, pending, caches, states):
+            hidden = residual.shape[-1]
+            normed = ctx.scratch("toy.normed", (ctx.n_tokens, hidden))
+            self.parts["norm"].forward(ctx, residual, pending, normed)
+            a = self.parts["attention"].forward(ctx, normed, caches[0], states[0])
+            b = self.parts["memory"].forward(ctx, normed, caches[1], states[1])
+            both = Delta(torch.cat([a.tensor, b.tensor]))             # the next norm adds every plane
+            self.parts["ffn_norm"].forward(ctx, residual, both, normed)
+            return self.parts["ffn"].forward(ctx, normed)
+
+    try:
+        spec = llama_spec("a")
+        base = spec.layers[0].parts
+        layer = LayerSpec("toy_side_by_side", {"norm": base["mixer_norm"], "attention": base["mixer"], "ffn_norm": base["ffn_norm"], "ffn": base["ffn"],
+                                               "memory": PartSpec("toy_memory", {"hidden": 64}, "model.layers.0.memory.")})
+        spec = replace(spec, layers=(layer, spec.layers[1]))
+        engine, host = make_engine(spec, torch.float32, seed=21, scale=SHARP)
+        assert not engine.use_step_graphs, "a part that computes on the host keeps the engine from replaying steps"
+        assert engine.model.users == [[0, 1], [2]] and len(engine.cache.kv_groups) == 1 and len(engine.cache.state_groups) == 2
+        cfg = plain_llama.normalise_config(TINY["a"])
+        w = {k: v.double() for k, v in host.items()}
+
+        def plain(tokens):
+            positions = torch.arange(len(tokens))
+            inv_freq = plain_llama.rope_inv_freq(cfg["head_dim"], cfg["theta"], cfg["scaling"])
+            h = plain_llama.embed(w["model.embed_tokens.weight"], tokens)
+            p = "model.layers.0."
+            x = plain_llama.rms_norm(h, w[p + "input_layernorm.weight"], cfg["eps"])
+            mean = x.cumsum(0) / torch.arange(1, len(tokens) + 1)[:, None]
+            h = h + plain_llama.attention_block(x, w, p + "self_attn.", cfg, positions, inv_freq) + mean @ w[p + "memory.mix.weight"].T
+            h = h + plain_llama.swiglu(plain_llama.rms_norm(h, w[p + "post_attention_layernorm.weight"], cfg["eps"]), w, p + "mlp.")
+            h = plain_llama.decoder_layer(h, w, 1, cfg, positions, inv_freq)
+            return plain_llama.head(plain_llama.rms_norm(h, w["model.norm.weight"], cfg["eps"]), w)
+
+        prompts = [token_ids(256, n, 230 + n) for n in (44, 9, 80)]
+        wants = [plain(p) for p in prompts]
+        slots = [engine.open() for _ in prompts]
+        heads = [30, 9, 70]
+        logits = engine.step([Entry(s, p[:h], [0, h - 1]) for s, p, h in zip(slots, prompts, heads)])
+        for i in range(3):
+            got = logits[2 * i: 2 * i + 2].double().cpu()
+            assert float((got - wants[i][[0, heads[i] - 1]]).abs().max()) <= 2e-4 * float(wants[i].abs().max())
+        engine.close(slots[1])
+        for t in range(10):
+            logits = engine.step([Entry(slots[0], [prompts[0][30 + t]], [0]), Entry(slots[2], [prompts[2][70 + t]], [0])])
+            for row, (i, place) in enumerate([(0, 30 + t), (2, 70 + t)]):
+                assert float((logits[row].double().cpu() - wants[i][place]).abs().max()) <= 2e-4 * float(wants[i].abs().max())
+        engine.close(slots[0])
+        engine.close(slots[2])
+        assert engine.cache.free_blocks == engine.cache.num_blocks
+    finally:
+        MIXERS.unregister("toy_memory")
+        ARRANGEMENTS.unregister("toy_side_by_side")
