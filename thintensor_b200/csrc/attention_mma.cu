@@ -4,11 +4,12 @@
 // does not take.
 //
 // A warp owns a tile of 16 query rows that share one sequence and one key/value head:
-// rows are (token, head of the group) pairs, 16 / group tokens by `group` heads, so a
-// decode step puts all heads of a group into one tile and reads each key and value once
-// for the whole group.  The warp walks the sequence's cache blocks (64 keys each) within
-// its slice of the keys; per block S = Q K^T and O += P V run as m16n8k16 mma.sync with a
-// running softmax in float32.
+// rows are (token, head of the group) pairs, 16 / group tokens by `group` heads, so every
+// key and value is read once for the whole group.  The warp walks the sequence's cache
+// blocks (64 keys each) within its slice of the keys; per block S = Q K^T and O += P V run
+// as m16n8k16 mma.sync with a running softmax in float32.  A decode step has only `group`
+// rows per tile, so its products are transposed (16 keys on the rows, the group's queries on
+// the 8 columns: key_tile_math), which halves the products and the exponentials.
 //
 // No ldmatrix and no transposes: both products take their B operand as 16-byte pieces of
 // cache rows.  That works because (1) a dot product does not care in which order its terms
@@ -167,6 +168,157 @@ __device__ __forceinline__ void block_math(TileState<HD>& st, int key_base, int 
             mma_bf16(st.o[n], pa[2 * half + 1][0], pa[2 * half + 1][1], pa[2 * half + 1][2], pa[2 * half + 1][3], vr.z, vr.w);
         }
     }
+}
+
+// ------------------------------------------------------------------ one token per sequence: keys on the 16-row side
+// A decode step has `group` query rows per key/value head (4 in the Llama shapes), so a 16-row tile of queries is
+// mostly padding, and mma.sync runs at a small fraction of the tensor cores' rate on this architecture (8 cycles per
+// m16n8k16 per SM, measured): with queries on the rows the products of a 64-key block keep the tensor pipe busy for
+// 512 cycles per SM, which bounds the step at about 5 TB/s.  Here the products are transposed: S^T = K Q^T has 16 keys
+// on the rows and 8 queries on the columns (NQ column tiles for groups of more than 8), O^T = V^T P^T has 16 head
+// dimensions on the rows; a block then takes half the products and half the exponentials.  K and V pieces are the
+// very same 16 bytes per thread as in block_math (key tile mt, rows g and g + 8, are load_k(2 mt, c) and
+// load_k(2 mt + 1, c); dimension tile dt, rows g and g + 8, are load_v(2 dt, half) and load_v(2 dt + 1, half)), so the
+// copies into shared memory do not change.  P^T reaches the second product's B operand through movmatrix (an 8 x 8
+// transpose across the warp), the one step that the other orientation gets for free.
+__device__ __forceinline__ uint32_t transpose_8x8(uint32_t v) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(v));
+    return d;
+}
+
+template <int HD, int NQ> struct KeyTileState {
+    static constexpr int KC = HD / 32, DT = HD / 16;
+    uint32_t q[NQ][KC][4];              // this lane's query (8 nq + g), 16 bytes per 32-wide chunk of the head dimension
+    float o[DT][NQ][4];                 // [0], [1]: dimension 16 dt + g, queries 8 nq + 2 t and + 1; [2], [3]: dimension + 8
+    float m_run[NQ][2], l_run[NQ][2];   // queries 8 nq + 2 t + e; l is this lane's share (its keys) until finish_sums
+    int pos, first;                     // the step's token sees keys first .. pos
+};
+
+template <int HD, int NQ>
+__device__ __forceinline__ void start_queries(KeyTileState<HD, NQ>& st, const __nv_bfloat16* rows, int row_stride, int group, int g, int t,
+                                              int pos, int first) {
+#pragma unroll
+    for (int nq = 0; nq < NQ; ++nq) {
+        const int query = 8 * nq + g;
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+            const uint4 v = query < group ? *reinterpret_cast<const uint4*>(rows + (size_t)query * row_stride + 32 * c + 8 * t) : make_uint4(0, 0, 0, 0);
+            st.q[nq][c][0] = v.x; st.q[nq][c][1] = v.y; st.q[nq][c][2] = v.z; st.q[nq][c][3] = v.w;
+        }
+#pragma unroll
+        for (int dt = 0; dt < HD / 16; ++dt) st.o[dt][nq][0] = st.o[dt][nq][1] = st.o[dt][nq][2] = st.o[dt][nq][3] = 0.0f;
+        st.m_run[nq][0] = st.m_run[nq][1] = -INFINITY;
+        st.l_run[nq][0] = st.l_run[nq][1] = 0.0f;
+    }
+    st.pos = pos;
+    st.first = first;
+}
+
+// One block of 64 keys, as four key tiles of 16; load_k and load_v as in block_math.
+template <int HD, int NQ, typename LoadK, typename LoadV>
+__device__ __forceinline__ void key_tile_math(KeyTileState<HD, NQ>& st, int key_base, int g, int t, float scale_log2,
+                                              LoadK load_k, LoadV load_v) {
+    constexpr int KC = HD / 32, DT = HD / 16, N_MT = TT_BLOCK_TOKENS / 16;
+    float s[N_MT][NQ][4];
+#pragma unroll
+    for (int m = 0; m < N_MT; ++m) {
+#pragma unroll
+        for (int nq = 0; nq < NQ; ++nq) s[m][nq][0] = s[m][nq][1] = s[m][nq][2] = s[m][nq][3] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < KC; ++c) {
+            const uint4 ka = load_k(2 * m, c), kb = load_k(2 * m + 1, c);
+#pragma unroll
+            for (int nq = 0; nq < NQ; ++nq) {
+                mma_bf16(s[m][nq], ka.x, kb.x, ka.y, kb.y, st.q[nq][c][0], st.q[nq][c][1]);
+                mma_bf16(s[m][nq], ka.z, kb.z, ka.w, kb.w, st.q[nq][c][2], st.q[nq][c][3]);
+            }
+        }
+    }
+    if (!(key_base + TT_BLOCK_TOKENS - 1 <= st.pos && key_base >= st.first)) {     // a sequence's end or a window's edge: key by key
+#pragma unroll
+        for (int m = 0; m < N_MT; ++m)
+#pragma unroll
+            for (int hi = 0; hi < 2; ++hi) {
+                const int key = key_base + key_of(2 * m + hi, g);
+                if (!(key <= st.pos && key >= st.first)) {
+#pragma unroll
+                    for (int nq = 0; nq < NQ; ++nq) s[m][nq][2 * hi] = s[m][nq][2 * hi + 1] = -INFINITY;
+                }
+            }
+    }
+    float corr[NQ][2];
+    bool grew = false;
+#pragma unroll
+    for (int nq = 0; nq < NQ; ++nq)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            float mx = -INFINITY;
+#pragma unroll
+            for (int m = 0; m < N_MT; ++m) mx = fmaxf(mx, fmaxf(s[m][nq][e], s[m][nq][2 + e]));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            const float m_new = fmaxf(st.m_run[nq][e], mx * scale_log2);     // the scale is positive
+            corr[nq][e] = (m_new == -INFINITY) ? 1.0f : fast_exp2(st.m_run[nq][e] - m_new);
+            grew = grew || corr[nq][e] != 1.0f;
+            const float nbase = (m_new == -INFINITY) ? 0.0f : -m_new;
+            float sum = 0.0f;
+#pragma unroll
+            for (int m = 0; m < N_MT; ++m)
+#pragma unroll
+                for (int hi = 0; hi < 2; ++hi) {
+                    const float p = fast_exp2(fmaf(s[m][nq][2 * hi + e], scale_log2, nbase));
+                    s[m][nq][2 * hi + e] = p;
+                    sum += p;
+                }
+            st.l_run[nq][e] = st.l_run[nq][e] * corr[nq][e] + sum;
+            st.m_run[nq][e] = m_new;
+        }
+    // the accumulator is rescaled only where some query's maximum has grown (after a sequence's first blocks it rarely does)
+    if (__any_sync(0xffffffffu, grew)) {
+#pragma unroll
+        for (int dt = 0; dt < DT; ++dt)
+#pragma unroll
+            for (int nq = 0; nq < NQ; ++nq) {
+                st.o[dt][nq][0] *= corr[nq][0]; st.o[dt][nq][1] *= corr[nq][1];
+                st.o[dt][nq][2] *= corr[nq][0]; st.o[dt][nq][3] *= corr[nq][1];
+            }
+    }
+    uint32_t pb[N_MT][NQ][2];           // P^T as the second product's B operand: keys 2 t, 2 t + 1 (and + 8) of the tile, query g
+#pragma unroll
+    for (int m = 0; m < N_MT; ++m)
+#pragma unroll
+        for (int nq = 0; nq < NQ; ++nq) {
+            pb[m][nq][0] = transpose_8x8(pack_bf16(s[m][nq][0], s[m][nq][1]));
+            pb[m][nq][1] = transpose_8x8(pack_bf16(s[m][nq][2], s[m][nq][3]));
+        }
+#pragma unroll
+    for (int dt = 0; dt < DT; ++dt)
+#pragma unroll
+        for (int half = 0; half < N_MT / 2; ++half) {
+            const uint4 va = load_v(2 * dt, half), vb = load_v(2 * dt + 1, half);
+#pragma unroll
+            for (int nq = 0; nq < NQ; ++nq) {
+                mma_bf16(st.o[dt][nq], va.x, vb.x, va.y, vb.y, pb[2 * half][nq][0], pb[2 * half][nq][1]);
+                mma_bf16(st.o[dt][nq], va.z, vb.z, va.w, vb.w, pb[2 * half + 1][nq][0], pb[2 * half + 1][nq][1]);
+            }
+        }
+}
+
+// Every lane's share of the row sums becomes the whole sum (the lanes of one t hold the same queries).
+template <int HD, int NQ>
+__device__ __forceinline__ void finish_sums(KeyTileState<HD, NQ>& st) {
+#pragma unroll
+    for (int nq = 0; nq < NQ; ++nq)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            float l = st.l_run[nq][e];
+            l += __shfl_xor_sync(0xffffffffu, l, 4);
+            l += __shfl_xor_sync(0xffffffffu, l, 8);
+            l += __shfl_xor_sync(0xffffffffu, l, 16);
+            st.l_run[nq][e] = l;
+        }
 }
 
 template <int HD>
@@ -436,7 +588,7 @@ __device__ __noinline__ void combine_by_last_cta(unsigned* __restrict__ tickets,
 // TICKETS: the instance that can combine more slices than a cluster holds by itself (see combine_by_last_cta).  It
 // is a kernel of its own because the mere presence of that path cost the others' main loop 8 to 28 % (measured on a
 // B200: 0.853 -> 0.92 ms per step at batch 8, 2.09 -> 2.65 ms with 32,768 cached tokens), whether inlined or not.
-template <int HD, bool ROPE, int SHAPE, bool TICKETS = false>
+template <int HD, bool ROPE, int SHAPE, bool TICKETS = false, int NQ = 1>
 __global__ void __launch_bounds__(DecodeShape<HD, SHAPE>::WARPS * 32)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __nv_bfloat16* __restrict__ k_pool,
                         __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ table, int table_width,
@@ -469,6 +621,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
     // block1, if it is this warp's, is its last; it is copied only after the wait
     const int n_early = (n_mine > 0 && my_begin + warp + (n_mine - 1) * WARPS == block1) ? n_mine - 1 : n_mine;
     uint4* my_slots = slots + (size_t)warp * STAGES * LOADS * 32 + lane;
+    const int k_lane = (key_of(0, g) * HD + 8 * t) * 2, v_lane = (g * TT_BLOCK_TOKENS + 8 * t) * 2;   // bytes, inside a tile
     unsigned valid = 0;                                // bit i % 32: block i of this warp has usable data
     int issued = 0;                                    // blocks of this warp whose copies have started, one group each
 
@@ -477,18 +630,21 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
         const int kb = my_begin + warp + i * WARPS;
         const int block = kb < DECODE_TABLE_CACHE ? table_sh[kb] : table_row[kb];
         if (block >= 0 && block < pool_blocks) {
-            const __nv_bfloat16* kbase = k_pool + ((size_t)block * kv_heads + kh) * TT_BLOCK_TOKENS * HD + 8 * t;
-            const __nv_bfloat16* vbase = v_pool + ((size_t)block * kv_heads + kh) * HD * TT_BLOCK_TOKENS + (size_t)g * TT_BLOCK_TOKENS + 8 * t;
+            // key_of(j, g) = key_of(0, g) + 32 (j >> 2) + 2 (j & 3): every piece lies at a compile-time distance from
+            // one address per tile, so a copy costs its own instruction and nothing for its addresses
+            const size_t tile = ((size_t)block * kv_heads + kh) * (TT_BLOCK_TOKENS * HD);     // a K tile and a V tile have the same size
+            const char* kbase = reinterpret_cast<const char*>(k_pool + tile) + k_lane;
+            const char* vbase = reinterpret_cast<const char*>(v_pool + tile) + v_lane;
             uint4* dst = my_slots + (size_t)(i % STAGES) * LOADS * 32;
 #pragma unroll
             for (int j = 0; j < 8; ++j)
 #pragma unroll
-                for (int c = 0; c < KC; ++c) cp_async16(dst + (j * KC + c) * 32, kbase + (size_t)key_of(j, g) * HD + 32 * c);
+                for (int c = 0; c < KC; ++c) cp_async16(dst + (j * KC + c) * 32, kbase + ((32 * (j >> 2) + 2 * (j & 3)) * HD * 2 + 64 * c));
 #pragma unroll
             for (int n = 0; n < NT; ++n)
 #pragma unroll
                 for (int half = 0; half < 2; ++half)
-                    cp_async16(dst + (K_LOADS + n * 2 + half) * 32, vbase + (size_t)(8 * n) * TT_BLOCK_TOKENS + 32 * half);
+                    cp_async16(dst + (K_LOADS + n * 2 + half) * 32, vbase + (n * 8 * TT_BLOCK_TOKENS * 2 + 64 * half));
             valid |= 1u << (i & 31);
         } else {
             valid &= ~(1u << (i & 31));
@@ -500,7 +656,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
     while (issued < min(STAGES - 1, n_early)) issue_next();
     tt_pdl_wait();                                     // the queries (or the qkv product) come from the previous kernel
 
-    TileState<HD> st;
+    KeyTileState<HD, NQ> st;
     if constexpr (ROPE) {
         // All threads share the work: one item is a rotated pair (d, d + HD / 2) of a query head
         // or of the new key, or one number of the new value.  Queries go to shared memory, from
@@ -560,35 +716,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
         }
         if (append) __threadfence();                   // key and value are in memory before their block is copied
         __syncthreads();
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int r = g + 8 * i;
-            const bool ok = r < group;
-            st.row_pos[i] = ok ? pos : -1;
-            st.row_first[i] = lo_key;
-            uint32_t (*frag)[4] = i == 0 ? st.qa : st.qb;
-#pragma unroll
-            for (int c = 0; c < KC; ++c) {
-                const uint4 v = ok ? *reinterpret_cast<const uint4*>(q_sh + r * PITCH_Q + 32 * c + 8 * t) : make_uint4(0, 0, 0, 0);
-                frag[c][0] = v.x; frag[c][1] = v.y; frag[c][2] = v.z; frag[c][3] = v.w;
-            }
-        }
-#pragma unroll
-        for (int n = 0; n < NT; ++n) { st.o[n][0] = st.o[n][1] = st.o[n][2] = st.o[n][3] = 0.0f; }
-        st.m_run[0] = st.m_run[1] = -INFINITY;
-        st.l_run[0] = st.l_run[1] = 0.0f;
+        start_queries<HD, NQ>(st, q_sh, PITCH_Q, group, g, t, pos, lo_key);
     } else {
-        size_t row_q[2];
-        bool row_ok[2];
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int r = g + 8 * i;
-            row_ok[i] = r < group;                     // one token: the tile's rows are the heads of the group
-            row_q[i] = ((size_t)b * heads + kh * group + r) * HD;
-            st.row_pos[i] = row_ok[i] ? pos : -1;
-            st.row_first[i] = lo_key;
-        }
-        load_queries<HD>(st, q, row_q, row_ok, t);
+        start_queries<HD, NQ>(st, q + ((size_t)b * heads + kh * group) * HD, HD, group, g, t, pos, lo_key);
     }
 
     for (int i = 0; i < n_mine; ++i) {
@@ -598,16 +728,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
         if (!((valid >> (i & 31)) & 1u)) continue;
         const uint4* src = my_slots + (size_t)(i % STAGES) * LOADS * 32;
         const int kb = my_begin + warp + i * WARPS;
-        block_math<HD>(st, kb * TT_BLOCK_TOKENS, t, scale_log2,
-                       [&](int j, int c) { return src[(j * KC + c) * 32]; },
-                       [&](int n, int half) { return src[(K_LOADS + n * 2 + half) * 32]; });
+        key_tile_math<HD, NQ>(st, kb * TT_BLOCK_TOKENS, g, t, scale_log2,
+                              [&](int j, int c) { return src[(j * KC + c) * 32]; },
+                              [&](int n, int half) { return src[(K_LOADS + n * 2 + half) * 32]; });
     }
     cp_async_wait<0>();
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        st.l_run[i] += __shfl_xor_sync(0xffffffffu, st.l_run[i], 1);
-        st.l_run[i] += __shfl_xor_sync(0xffffffffu, st.l_run[i], 2);
-    }
+    finish_sums<HD, NQ>(st);
 
     // the warps' partial results meet in shared memory (the slots are free now)
     __syncthreads();
@@ -616,13 +742,15 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
     float* sh_m = sh_o + WARPS * 16 * PITCH;           // [WARPS][16]
     float* sh_l = sh_m + WARPS * 16;
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const int r = g + 8 * i;
-        float* dst = sh_o + ((size_t)warp * 16 + r) * PITCH + 2 * t;
+    for (int nq = 0; nq < NQ; ++nq)
 #pragma unroll
-        for (int n = 0; n < NT; ++n) { dst[8 * n] = st.o[n][2 * i]; dst[8 * n + 1] = st.o[n][2 * i + 1]; }
-        if (t == 0) { sh_m[warp * 16 + r] = st.m_run[i]; sh_l[warp * 16 + r] = st.l_run[i]; }
-    }
+        for (int e = 0; e < 2; ++e) {
+            const int r = 8 * nq + 2 * t + e;
+            float* dst = sh_o + ((size_t)warp * 16 + r) * PITCH + g;
+#pragma unroll
+            for (int dt = 0; dt < HD / 16; ++dt) { dst[16 * dt] = st.o[dt][nq][e]; dst[16 * dt + 8] = st.o[dt][nq][2 + e]; }
+            if (g == 0) { sh_m[warp * 16 + r] = st.m_run[nq][e]; sh_l[warp * 16 + r] = st.l_run[nq][e]; }
+        }
     __syncthreads();
     // cluster_merge: the slices of a (sequence, kv head) form a thread-block cluster; each leaves its
     // result in its own shared memory and the CTAs combine them over distributed shared memory
@@ -699,18 +827,18 @@ inline bool slices_form_cluster(int splits) { return splits > 1 && splits <= 8; 
 
 // The decode kernel, plain (ROPE = false: rotated queries in q, the cache already holds the
 // step's keys and values) or fused with the rotation and the cache write.
-template <int HD, bool ROPE, int SHAPE = ONE_PER_SM>
-cudaError_t launch_decode(const void* q, const DecodeRope& rope, void* k_pool, void* v_pool, const int* table, int table_width,
-                          int pool_blocks, const int* len_before, int sequences, int heads, int kv_heads, float scale_log2,
-                          int window, int splits, void* out, float* part_acc, float* part_ml, unsigned* tickets, unsigned* status,
-                          cudaStream_t stream) {
+template <int HD, bool ROPE, int SHAPE, int NQ>
+cudaError_t launch_decode_tiles(const void* q, const DecodeRope& rope, void* k_pool, void* v_pool, const int* table, int table_width,
+                                int pool_blocks, const int* len_before, int sequences, int heads, int kv_heads, float scale_log2,
+                                int window, int splits, void* out, float* part_acc, float* part_ml, unsigned* tickets, unsigned* status,
+                                cudaStream_t stream) {
     using D = DecodeShape<HD, SHAPE>;
     constexpr int shared = D::WARPS * D::STAGES * (8 * (HD / 32) + (HD / 8) * 2) * 32 * 16;
     static_assert(shared >= D::WARPS * 16 * (HD + 6) * 4 + 16 * (HD + 2) * 4, "the slots must also hold the warps' and the CTA's partial results");
     if constexpr (SHAPE == ONE_PER_SM) {
         if (tickets && splits > 1 && !slices_form_cluster(splits)) {
             static bool configured_tickets = false;
-            auto with_tickets = attention_decode_kernel<HD, ROPE, SHAPE, true>;
+            auto with_tickets = attention_decode_kernel<HD, ROPE, SHAPE, true, NQ>;
             if (!configured_tickets) {
                 const cudaError_t err = cudaFuncSetAttribute(with_tickets, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
                 if (err != cudaSuccess) return err;
@@ -722,7 +850,7 @@ cudaError_t launch_decode(const void* q, const DecodeRope& rope, void* k_pool, v
         }
     }
     static bool configured = false;
-    auto kernel = attention_decode_kernel<HD, ROPE, SHAPE>;
+    auto kernel = attention_decode_kernel<HD, ROPE, SHAPE, false, NQ>;
     if (!configured) {
         const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
         if (err != cudaSuccess) return err;
@@ -735,6 +863,19 @@ cudaError_t launch_decode(const void* q, const DecodeRope& rope, void* k_pool, v
     return tt_launch_pdl(kernel, dim3(sequences, kv_heads, splits), dim3(D::WARPS * 32), shared, stream,
         (const __nv_bfloat16*)q, rope, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks,
         len_before, heads, kv_heads, scale_log2, window, splits, 0, (__nv_bfloat16*)out, part_acc, part_ml, tickets, status);
+}
+
+// One column tile of 8 queries serves groups of up to 8 query heads per key/value head, two serve up to 16.
+template <int HD, bool ROPE, int SHAPE = ONE_PER_SM>
+cudaError_t launch_decode(const void* q, const DecodeRope& rope, void* k_pool, void* v_pool, const int* table, int table_width,
+                          int pool_blocks, const int* len_before, int sequences, int heads, int kv_heads, float scale_log2,
+                          int window, int splits, void* out, float* part_acc, float* part_ml, unsigned* tickets, unsigned* status,
+                          cudaStream_t stream) {
+    if (heads / kv_heads > 8)
+        return launch_decode_tiles<HD, ROPE, SHAPE, 2>(q, rope, k_pool, v_pool, table, table_width, pool_blocks, len_before, sequences, heads,
+                                                       kv_heads, scale_log2, window, splits, out, part_acc, part_ml, tickets, status, stream);
+    return launch_decode_tiles<HD, ROPE, SHAPE, 1>(q, rope, k_pool, v_pool, table, table_width, pool_blocks, len_before, sequences, heads,
+                                                   kv_heads, scale_log2, window, splits, out, part_acc, part_ml, tickets, status, stream);
 }
 
 template <int HD>
