@@ -254,8 +254,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             if (ok && !mbar_wait(smem_u32(&s_full[i & 1]), (uint32_t)((i >> 1) & 1))) expired();
             fence_after_sync();
             float s[HALF_KEYS];
+            {
+                // both halves of the row are asked for before either is waited for (one round trip to tensor memory, not two)
+                uint32_t raw[HALF_KEYS / 32][32];
 #pragma unroll
-            for (int c = 0; c < HALF_KEYS; c += 32) tmem_load32(lane_base + (i & 1) * 64 + half * HALF_KEYS + c, s + c);
+                for (int c = 0; c < HALF_KEYS / 32; ++c) tmem_load32_issue(lane_base + (i & 1) * 64 + half * HALF_KEYS + 32 * c, raw[c]);
+                tmem_load_wait();
+#pragma unroll
+                for (int c = 0; c < HALF_KEYS / 32; ++c)
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) s[32 * c + j] = tmem_loaded(raw[c][j]);
+            }
             const int key_base = (block0 + i) * KEYS + half * HALF_KEYS;
             const bool all_visible = __all_sync(0xffffffffu, key_base + HALF_KEYS - 1 <= pos && key_base >= first);
             if (!all_visible) {
@@ -265,13 +274,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     s[j] = (key <= pos && key >= first) ? s[j] : -INFINITY;
                 }
             }
-            float mxa = -INFINITY, mxb = -INFINITY;                 // two chains of three-input maxima
+            float mxa = -INFINITY, mxb = -INFINITY, mxc = -INFINITY, mxd = -INFINITY;   // four chains of three-input maxima
 #pragma unroll
-            for (int j = 0; j < HALF_KEYS; j += 4) {
+            for (int j = 0; j < HALF_KEYS; j += 8) {
                 mxa = max3(mxa, s[j], s[j + 1]);
                 mxb = max3(mxb, s[j + 2], s[j + 3]);
+                mxc = max3(mxc, s[j + 4], s[j + 5]);
+                mxd = max3(mxd, s[j + 6], s[j + 7]);
             }
-            float mx = fmaxf(mxa, mxb);
+            float mx = fmaxf(max3(mxa, mxb, mxc), mxd);
             if (SPLIT == 2) {
                 pair_max[i & 1][half][r] = mx;
                 pair_barrier();

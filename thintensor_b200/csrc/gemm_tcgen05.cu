@@ -884,10 +884,14 @@ extern "C" int tt_gemm_tcgen05_qkv_rope_takes(int tokens, int features, int k, i
     const int tiles = ((tokens + BM - 1) / BM) * ((features + 255) / 256);
     if (tiles < 8) return 0;
     if (tokens >= PAIR_MIN_TOKENS) return 1;
-    // below the pairs' range the persistent kernel slices k while its tiles are fewer than the SMs: not taken then
+    // below the pairs' range the persistent kernel slices k while its tiles are fewer than the SMs
     int device = 0, sm_count = 0;
     if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
-    return tiles >= sm_count ? 1 : 0;
+    // Taken where the plain product would not slice k either (more tiles than half the SMs).  Where it would, slices and a
+    // rotation kernel of its own are faster than one SM per tile for all of k (measured on a B200, 1B shape, whole prefill:
+    // 1,024 tokens = 96 tiles 2.91 -> 2.77 ms and 1,536 tokens 4.02 -> 3.83 ms with this form; 768 tokens = 72 tiles
+    // 2.43 -> 2.46 ms and 512 tokens 2.00 -> 2.07 ms, so not there)
+    return tiles * 2 > sm_count ? 1 : 0;
 }
 
 extern "C" int tt_gemm_tcgen05_qkv_rope(const void* x, long long ldx, const void* w, long long ldw, const float* bias, int tokens, int k,
