@@ -27,21 +27,23 @@
 // fragments from there.
 // Decoding (attention_decode_kernel): one token per sequence, a tile is one CTA; its warps
 // split the tile's blocks of keys among themselves (warp w takes blocks w, w + WARPS, ...).
-// The step is bound by reading the cache once, so every thread streams exactly the 16-byte
-// pieces it will later use as fragments into private shared-memory slots with cp.async, a
-// block ahead of the arithmetic (no registers held, no synchronisation needed: a thread
-// reads only what it copied itself); copies of blocks that the step does not write start
-// before the wait for the previous kernel.  The warps' (max, sum, accumulator) meet in
-// shared memory at the end.  grid.z may cut the keys into slices as well: up to 8 slices
-// form a thread-block cluster and are combined by its first CTA over distributed shared
-// memory, more leave partial results in scratch for attention_merge_kernel.  For head size
-// 64 the kernel can also do what comes before attention in a step: rotate q and k and
-// write the new key and value into the cache (DecodeRope).
+// The step is bound by reading the cache once.  A block's keys of one head are 8 to 16 KB of
+// contiguous memory and so are its values, so a warp asks the copy engine for both
+// (cp.async.bulk, completion on an mbarrier per stage) into its own ring of shared-memory
+// stages, a block ahead of the arithmetic, and every thread reads its fragments as 16-byte
+// pieces of the tiles' rows; copies of blocks that the step does not write start before the
+// wait for the previous kernel.  The warps' (max, sum, accumulator) meet in shared memory at
+// the end.  grid.z may cut the keys into slices as well: up to 8 slices form a thread-block
+// cluster and are combined over distributed shared memory, more leave partial results in
+// scratch for the CTA that finishes last (or for attention_merge_kernel).  For head size 64
+// the kernel can also do what comes before attention in a step: rotate q and k and write the
+// new key and value into the cache (DecodeRope).
 //
 // Counterparts in random-unknown-username/Thintensor: _single_token_gqa_attention_kernel and
 // the split pair, thinruntime/triton_kernels.py:14-245 (one token, one program per query
 // head, SIMT); prompts are fed token by token there.
 #include "attention_kernels.cuh"
+#include "tcgen05.cuh"
 
 #include <cooperative_groups.h>
 namespace cg = cooperative_groups;
@@ -352,6 +354,12 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* src) {
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// One contiguous piece of global memory into shared memory by the copy engine (both 16-byte aligned, a multiple of 16
+// bytes); its bytes are counted on the mbarrier.
+__device__ __forceinline__ void bulk_copy(void* smem_dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(tc::smem_u32(smem_dst)), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
 
 template <int HD> struct PromptShape {
     static constexpr int K_ROW = HD * 2;                       // bytes of one key row
@@ -596,13 +604,17 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
                         int window, int splits, int cluster_merge, __nv_bfloat16* __restrict__ out,
                         float* __restrict__ part_acc, float* __restrict__ part_ml, unsigned* __restrict__ tickets, unsigned* status) {
     constexpr int WARPS = DecodeShape<HD, SHAPE>::WARPS, STAGES = DecodeShape<HD, SHAPE>::STAGES;
-    constexpr int KC = HD / 32, NT = HD / 8;
-    constexpr int K_LOADS = 8 * KC, V_LOADS = NT * 2, LOADS = K_LOADS + V_LOADS;    // 16-byte pieces per thread and block
-    static_assert(STAGES <= 3, "the wait below knows three depths");
-    extern __shared__ uint4 slots[];                  // [WARPS][STAGES][LOADS][32 lanes]
+    constexpr int TILE = TT_BLOCK_TOKENS * HD * 2;     // bytes of a block's keys of one head, and of its values
+    extern __shared__ __align__(128) uint4 slots[];   // [WARPS][STAGES]: a K tile [64 keys][HD], then a V tile [HD][64 keys], as they lie in the cache
+    __shared__ uint64_t landed[WARPS][STAGES];        // a stage's two copies have arrived
     tt_pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int b = blockIdx.x, kh = blockIdx.y, split = blockIdx.z;
+    if (threadIdx.x == 0) {
+        for (int w = 0; w < WARPS; ++w)
+            for (int s = 0; s < STAGES; ++s) tc::mbar_init(tc::smem_u32(&landed[w][s]), 1);
+        tc::fence_barrier_init();
+    }
     const int group = heads / kv_heads;
     // Lengths and tables were written before this step's first kernel started (by the step
     // before, or by the host), so they may be read ahead of the wait; so may every block but
@@ -620,37 +632,36 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
     const int n_mine = my_begin + warp < my_end ? (my_end - my_begin - warp + WARPS - 1) / WARPS : 0;   // blocks of this warp
     // block1, if it is this warp's, is its last; it is copied only after the wait
     const int n_early = (n_mine > 0 && my_begin + warp + (n_mine - 1) * WARPS == block1) ? n_mine - 1 : n_mine;
-    uint4* my_slots = slots + (size_t)warp * STAGES * LOADS * 32 + lane;
-    const int k_lane = (key_of(0, g) * HD + 8 * t) * 2, v_lane = (g * TT_BLOCK_TOKENS + 8 * t) * 2;   // bytes, inside a tile
+    char* my_slots = reinterpret_cast<char*>(slots) + (size_t)warp * STAGES * 2 * TILE;
+    // this lane's 16-byte pieces inside the tiles: key_of(j, g) = key_of(0, g) + 32 (j >> 2) + 2 (j & 3), so every piece
+    // lies at a compile-time distance from one address per tile
+    const int k_lane = (key_of(0, g) * HD + 8 * t) * 2, v_lane = TILE + (g * TT_BLOCK_TOKENS + 8 * t) * 2;
     unsigned valid = 0;                                // bit i % 32: block i of this warp has usable data
-    int issued = 0;                                    // blocks of this warp whose copies have started, one group each
+    int issued = 0;                                    // blocks of this warp whose copies have started
+    bool waits_ok = true;
 
+    // A block's keys of one head are contiguous in the cache and so are its values: one lane asks the copy engine for
+    // both, no thread computes an address per piece, and the load/store unit is left to the fragment reads.
     auto issue_next = [&]() {
         const int i = issued++;
         const int kb = my_begin + warp + i * WARPS;
         const int block = kb < DECODE_TABLE_CACHE ? table_sh[kb] : table_row[kb];
-        if (block >= 0 && block < pool_blocks) {
-            // key_of(j, g) = key_of(0, g) + 32 (j >> 2) + 2 (j & 3): every piece lies at a compile-time distance from
-            // one address per tile, so a copy costs its own instruction and nothing for its addresses
-            const size_t tile = ((size_t)block * kv_heads + kh) * (TT_BLOCK_TOKENS * HD);     // a K tile and a V tile have the same size
-            const char* kbase = reinterpret_cast<const char*>(k_pool + tile) + k_lane;
-            const char* vbase = reinterpret_cast<const char*>(v_pool + tile) + v_lane;
-            uint4* dst = my_slots + (size_t)(i % STAGES) * LOADS * 32;
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-#pragma unroll
-                for (int c = 0; c < KC; ++c) cp_async16(dst + (j * KC + c) * 32, kbase + ((32 * (j >> 2) + 2 * (j & 3)) * HD * 2 + 64 * c));
-#pragma unroll
-            for (int n = 0; n < NT; ++n)
-#pragma unroll
-                for (int half = 0; half < 2; ++half)
-                    cp_async16(dst + (K_LOADS + n * 2 + half) * 32, vbase + (n * 8 * TT_BLOCK_TOKENS * 2 + 64 * half));
-            valid |= 1u << (i & 31);
-        } else {
-            valid &= ~(1u << (i & 31));
-            if (lane == 0) atomicOr(status, TT_STATUS_BAD_BLOCK);
+        const bool good = block >= 0 && block < pool_blocks;
+        __syncwarp();                                  // every lane has read what the stage held before
+        if (lane == 0) {
+            const uint32_t bar = tc::smem_u32(&landed[warp][i % STAGES]);
+            if (good) {
+                const size_t tile = ((size_t)block * kv_heads + kh) * (TT_BLOCK_TOKENS * HD);     // a K tile and a V tile have the same size
+                char* dst = my_slots + (size_t)(i % STAGES) * 2 * TILE;
+                tc::mbar_expect_tx(bar, 2 * TILE);
+                bulk_copy(dst, k_pool + tile, TILE, bar);
+                bulk_copy(dst + TILE, v_pool + tile, TILE, bar);
+            } else {
+                tc::mbar_arrive(bar);                  // the stage's phase still ends, so the parities stay in step
+                atomicOr(status, TT_STATUS_BAD_BLOCK);
+            }
         }
-        cp_async_commit();
+        if (good) valid |= 1u << (i & 31); else valid &= ~(1u << (i & 31));
     };
 
     while (issued < min(STAGES - 1, n_early)) issue_next();
@@ -714,25 +725,34 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
                 }
             }
         }
-        if (append) __threadfence();                   // key and value are in memory before their block is copied
+        if (append) {                                  // key and value are in memory, and visible to the copy engine, before their block is copied
+            __threadfence();
+            asm volatile("fence.proxy.async;" ::: "memory");
+        }
         __syncthreads();
         start_queries<HD, NQ>(st, q_sh, PITCH_Q, group, g, t, pos, lo_key);
     } else {
         start_queries<HD, NQ>(st, q + ((size_t)b * heads + kh * group) * HD, HD, group, g, t, pos, lo_key);
     }
 
+    int waited = 0;                                    // blocks of this warp whose copies have been waited for
     for (int i = 0; i < n_mine; ++i) {
         while (issued < min(n_mine, i + STAGES)) issue_next();     // block i and up to STAGES - 1 beyond it
-        const int newer = issued - i - 1;              // groups that may stay in flight while block i is used
-        if (newer >= 2) cp_async_wait<2>(); else if (newer == 1) cp_async_wait<1>(); else cp_async_wait<0>();
+        if (waits_ok && !tc::mbar_wait(tc::smem_u32(&landed[warp][i % STAGES]), (uint32_t)((i / STAGES) & 1))) {
+            if (lane == 0) atomicOr(status, TT_STATUS_WAIT_EXPIRED);
+            waits_ok = false;
+        }
+        waited = i + 1;
+        if (!waits_ok) break;
         if (!((valid >> (i & 31)) & 1u)) continue;
-        const uint4* src = my_slots + (size_t)(i % STAGES) * LOADS * 32;
+        const char* src = my_slots + (size_t)(i % STAGES) * 2 * TILE;
         const int kb = my_begin + warp + i * WARPS;
         key_tile_math<HD, NQ>(st, kb * TT_BLOCK_TOKENS, g, t, scale_log2,
-                              [&](int j, int c) { return src[(j * KC + c) * 32]; },
-                              [&](int n, int half) { return src[(K_LOADS + n * 2 + half) * 32]; });
+                              [&](int j, int c) { return *reinterpret_cast<const uint4*>(src + k_lane + ((32 * (j >> 2) + 2 * (j & 3)) * HD * 2 + 64 * c)); },
+                              [&](int n, int half) { return *reinterpret_cast<const uint4*>(src + v_lane + (n * 8 * TT_BLOCK_TOKENS * 2 + 64 * half)); });
     }
-    cp_async_wait<0>();
+    // after a wait that ran out: the copies still under way get one more bounded wait each before shared memory is reused
+    for (int i = waited; i < issued; ++i) tc::mbar_wait(tc::smem_u32(&landed[warp][i % STAGES]), (uint32_t)((i / STAGES) & 1));
     finish_sums<HD, NQ>(st);
 
     // the warps' partial results meet in shared memory (the slots are free now)
