@@ -149,7 +149,7 @@ class CausalAttention(Mixer):
         head, slice).  Measured on a B200 from 1 to 64 sequences and 2,048 to 32,768 keys: a step is
         fastest when the slices just fill one wave of one CTA per SM and keep at least 8 blocks each; a
         second wave gains nothing."""
-        return kv_splits(ctx, ctx.sequences * self.kv_heads, 512, api.sm_count(ctx.tokens.device))
+        return kv_splits(ctx, ctx.sequences * self.kv_heads, 512, api.sm_count(ctx.status.device))
 
     def slice_scratch(self, ctx, splits: int):
         """Where the slices of the keys leave their partial results (nothing for one slice)."""
