@@ -247,7 +247,7 @@ def test_attention_tcgen05_prompts(heads, kv_heads, head_dim, window):
 @pytest.mark.parametrize("shared_tile", [False, True])
 @pytest.mark.parametrize("splits", [1, 2, 5, 16])
 @pytest.mark.parametrize("window", [0, 100])
-@pytest.mark.parametrize("heads,kv_heads,head_dim", [(8, 2, 64), (3, 1, 128), (5, 1, 96)])
+@pytest.mark.parametrize("heads,kv_heads,head_dim", [(8, 2, 64), (3, 1, 128), (5, 1, 96), (4, 4, 32), (16, 1, 64), (24, 2, 128), (9, 1, 32)])
 def test_attention_mma_decode_splits_and_window(splits, window, heads, kv_heads, head_dim, shared_tile):
     """The tensor-core kernels with one token per sequence, through the decode kernel (keys may
     be sliced) and through the prompt kernel: the same far-key construction as for the exact kernel."""
@@ -534,3 +534,33 @@ def test_advance_lengths_and_step_counters(sequences):
     api.advance_lengths(lengths, cu, sequences)
     assert torch.equal(lengths.cpu(), before + 2 * new.to(torch.int32))
     assert torch.equal(counters.cpu(), torch.arange(sequences, dtype=torch.int32) + 1)
+
+
+def test_attention_mma_decode_beyond_the_cached_table_row():
+    """A sequence of more blocks than the decode kernel keeps of a table row in shared memory (1,024): the entries beyond
+    come from global memory; a far key among 70,000 must still be found, with and without slices."""
+    from thintensor_b200.kernels import api
+
+    dtype, heads, kv_heads, head_dim = torch.bfloat16, 4, 1, 64
+    totals = [70000, 130]
+    k_pool, v_pool, table, keys, values = make_cache(totals, kv_heads, head_dim, dtype, seed=70)
+    n = len(totals)
+    q = randn(n, heads, head_dim, dtype=dtype, seed=71)
+    far = 69000                                                  # block 1,078
+    spike = (q[0, 0].float() * (40.0 * head_dim ** 0.5 / float(q[0, 0].float().norm()) ** 2)).to(dtype)
+    k_pool[int(table[0, far // 64]), 0, far % 64] = spike
+    keys[0][far, 0] = spike.float().cpu()
+    cu = torch.arange(n + 1, dtype=torch.int32, device=DEV)
+    before = torch.tensor([t - 1 for t in totals], dtype=torch.int32, device=DEV)
+    scale = head_dim ** -0.5
+    want = attention_reference(q.float().cpu(), keys, values, [1] * n, heads, kv_heads, scale, 0)
+    assert torch.allclose(want[0, 0], values[0][far, 0].double(), atol=0.35)
+    for splits in (1, 6, 40):
+        out = torch.full((n, heads * head_dim), float("nan"), dtype=dtype, device=DEV)
+        part_acc = torch.full((n * heads * splits * head_dim,), float("nan"), dtype=torch.float32, device=DEV)
+        part_ml = torch.full((n * heads * splits * 2,), float("nan"), dtype=torch.float32, device=DEV)
+        st = status()
+        api.attention_mma(q.view(n, -1), k_pool, v_pool, table, cu, before, n, n, heads, kv_heads, head_dim, scale, 0, splits, out,
+                          part_acc, part_ml, st, one_token_each=True)
+        torch.testing.assert_close(out.double().cpu().view(n, heads, head_dim), want, **tol(dtype))
+        assert int(st.item()) == 0
