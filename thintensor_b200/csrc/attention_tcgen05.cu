@@ -156,7 +156,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     fence_after_sync();
     const uint32_t tmem_base = tmem_base_shared;
 
-    tt_pdl_wait();                                                // queries and this step's keys come from the previous kernel
+    // offsets and lengths were written before the step's first kernel started: the tile's place is found ahead of the wait
     const int seq_begin = args.cu[b], seq_new = args.cu[b + 1] - seq_begin, before = args.len_before[b];
     const int tok0 = tile * args.tokens_per_tile;
     const int tile_tokens = min(args.tokens_per_tile, seq_new - tok0);
@@ -164,6 +164,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int lo_key = (args.window > 0 && lo_pos - args.window + 1 > 0) ? lo_pos - args.window + 1 : 0;
     const int block0 = lo_key / KEYS, block1 = hi_pos / KEYS;
     const int n_blocks = block1 - block0 + 1;
+    tt_pdl_wait();                                                // queries and this step's keys come from the previous kernel
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer

@@ -316,9 +316,12 @@ __global__ void rope_append_vec_kernel(const float* __restrict__ qkv, int splits
                                        const int* __restrict__ cu, const int* __restrict__ len_before, int sequences,
                                        int heads, int kv_heads, int head_dim, int write_cache, unsigned* status) {
     tt_pdl_launch_dependents();
-    tt_pdl_wait();
+    // Lengths, offsets and tables were written before the step's first kernel started: the token's sequence, position,
+    // cache block and angles are found ahead of the wait for the qkv product (five dependent round trips to the L2 that
+    // would otherwise follow it); only the product's slices are read after it.
     const int t = blockIdx.x;
-    const int b = tt_find_sequence(cu, sequences, t);
+    // one token per sequence (a decode step): token t is sequence t, which two independent loads confirm
+    const int b = (sequences == (int)gridDim.x && cu[t] == t && cu[t + 1] == t + 1) ? t : tt_find_sequence(cu, sequences, t);
     const int pos = len_before[b] + (t - cu[b]);
     const int half = rotary_dim >> 1, half4 = half >> 2;
     const int q_cols = heads * head_dim;
@@ -332,7 +335,23 @@ __global__ void rope_append_vec_kernel(const float* __restrict__ qkv, int splits
     // the angles depend on the position only: one table per block instead of one sincosf per head and pair
     __shared__ float cos_sh[ROPE_MAX_HALF], sin_sh[ROPE_MAX_HALF];
     for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(__ldg(inv_freq + i) * (float)pos, &sin_sh[i], &cos_sh[i]);
+    // the token's cache block, looked up once: -1 where the table entry lies outside the pool (reported when a write needs it)
+    int block = -1;
+    if (write_cache) {
+        block = table_row[pos / TT_BLOCK_TOKENS];
+        if (block < 0 || block >= pool_blocks) block = -1;
+    }
+    const int slot = pos % TT_BLOCK_TOKENS;
+    auto key_offset = [&](int kv_head) -> long long {
+        if (block < 0) { atomicOr(status, TT_STATUS_BAD_BLOCK); return -1; }
+        return (((long long)block * kv_heads + kv_head) * TT_BLOCK_TOKENS + slot) * head_dim;
+    };
+    auto value_offset = [&](int kv_head) -> long long {
+        if (block < 0) { atomicOr(status, TT_STATUS_BAD_BLOCK); return -1; }
+        return ((long long)block * kv_heads + kv_head) * head_dim * TT_BLOCK_TOKENS + slot;
+    };
     __syncthreads();
+    tt_pdl_wait();
     const int n_val = kv_cols >> 2;
     // the token's blocks (one when there are many tokens, several when there are few) walk over its items
     for (int item = blockIdx.y * blockDim.x + threadIdx.x; item < n_rot + n_pass + n_val; item += gridDim.y * blockDim.x) {
@@ -353,7 +372,7 @@ __global__ void rope_append_vec_kernel(const float* __restrict__ qkv, int splits
             if (head < heads) {
                 dst = q_out + (size_t)t * q_cols + col;
             } else {
-                const long long off = tt_cache_offset(table_row, pos, head - heads, kv_heads, head_dim, pool_blocks, status);
+                const long long off = key_offset(head - heads);
                 if (off < 0) continue;
                 dst = k_pool + off + i;
             }
@@ -369,7 +388,7 @@ __global__ void rope_append_vec_kernel(const float* __restrict__ qkv, int splits
             if (head < heads) {
                 tt_store4(q_out + (size_t)t * q_cols + col, a.x, a.y, a.z, a.w);
             } else {
-                const long long off = tt_cache_offset(table_row, pos, head - heads, kv_heads, head_dim, pool_blocks, status);
+                const long long off = key_offset(head - heads);
                 if (off >= 0) tt_store4(k_pool + off + i, a.x, a.y, a.z, a.w);
             }
             continue;
@@ -377,7 +396,7 @@ __global__ void rope_append_vec_kernel(const float* __restrict__ qkv, int splits
         w -= n_pass;
         const int e = w * 4, kh = e / head_dim, i = e - kh * head_dim;
         const float4 a = sum_slices4(row + q_cols + kv_cols + e, splits, split_stride);
-        const long long off = tt_value_offset(table_row, pos, kh, kv_heads, head_dim, pool_blocks, status);
+        const long long off = value_offset(kh);
         if (off >= 0) {
             TAct* dst = v_pool + off + (long long)i * TT_BLOCK_TOKENS;      // values lie transposed: one number per 64-token row
             dst[0] = tt_from_float<TAct>(a.x);
