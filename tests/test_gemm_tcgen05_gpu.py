@@ -163,7 +163,9 @@ def test_linear_uses_it_and_matches_exact_kernel():
     (4, 2, 64, 256, [2300], [77]),                        # a tile that holds q heads, k heads and v heads side by side
     (32, 8, 128, 4096, [1900], [0]),                      # the persistent kernel with at least as many tiles as SMs (8B shape)
     (32, 8, 64, 2048, [1100], [3]),                       # the persistent kernel with fewer tiles than SMs but more than half (108)
-    (32, 8, 64, 2048, [700], [0]),                        # 72 tiles: fewer than half the SMs, the separate kernels serve it
+    (32, 8, 64, 2048, [700], [0]),                        # 72 tiles of 256 features are too few, 144 of 128 are not: the narrow tiles
+    (8, 2, 128, 512, [900], [10]),                        # narrow tiles at head size 128: one head per tile
+    (32, 8, 64, 2048, [300], [0]),                        # 3 x 24 tiles of 128: fewer than half the SMs, the separate kernels serve it
 ])
 def test_qkv_product_rotates_and_appends_in_its_epilogue(heads, kv_heads, head_dim, k, news, before):
     """The qkv form of the prompt kernels against the separate path (product to float32, then the rotary/append
@@ -179,7 +181,7 @@ def test_qkv_product_rotates_and_appends_in_its_epilogue(heads, kv_heads, head_d
     w = randn(q_cols + 2 * kv_cols, k, seed=32, scale=0.05)
     bias = torch.randn(q_cols + 2 * kv_cols, device=DEV) * 0.3 if head_dim == 128 else None
     if not api.gemm_tcgen05_qkv_rope_takes(x, w, head_dim, head_dim):
-        assert tokens < 2048 and 2 * (-(-tokens // 128) * -(-(q_cols + 2 * kv_cols) // 256)) <= api.sm_count()
+        assert tokens < 2048 and 2 * (-(-tokens // 128) * -(-(q_cols + 2 * kv_cols) // 128)) <= api.sm_count()
         pytest.skip("few tiles below the pairs' range: the separate kernels serve this shape")
     inv_freq = (10000.0 ** (-torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim)).to(DEV)
     totals = [b + n for b, n in zip(before, news)]

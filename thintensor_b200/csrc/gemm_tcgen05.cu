@@ -492,12 +492,14 @@ __device__ __forceinline__ void store_qkv_rope(uint32_t lane_addr, int token, in
 constexpr int P_STAGES = 4;
 constexpr int P_STAGE_BYTES = BM * BK * 2 + 256 * BK * 2;       // A tile + 256 rows of B
 
-template <int FORM>
+template <int FORM, int WIDE = 256>
 __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Args args,
                                int tiles_m, int tiles_total, int splits) {
     constexpr bool dual = FORM == TOKENS_ON_M_SWIGLU;
-    constexpr int TILE_N = dual ? 128 : 256;                    // output features per tile
+    static_assert(WIDE == 256 || (FORM == TOKENS_ON_M_QKV && WIDE == 128), "only the qkv form has a narrower tile");
+    constexpr int TILE_N = dual ? 128 : WIDE;                   // output features per tile
+    constexpr int STAGE_TX = BM * BK * 2 + (dual ? 256 : WIDE) * BK * 2;       // bytes a stage's copies bring
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     __shared__ uint64_t full_bar[P_STAGES], empty_bar[P_STAGES], acc_full[2], acc_empty[2];
@@ -543,7 +545,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                         atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; break;
                     }
                     const uint32_t bar = smem_u32(&full_bar[s]);
-                    mbar_expect_tx(bar, P_STAGE_BYTES);
+                    mbar_expect_tx(bar, STAGE_TX);
                     uint8_t* stage = smem + (size_t)s * P_STAGE_BYTES;
                     const int kx = (kb_begin + i) * BK;
                     tma_load_2d(smem_u32(stage), &map_a, kx, a_row, bar);
@@ -551,7 +553,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                         tma_load_2d(smem_u32(stage + BM * BK * 2), &map_b, kx, b_row, bar);
                         tma_load_2d(smem_u32(stage + BM * BK * 2 + 128 * BK * 2), &map_b, kx, args.up_row_offset + b_row, bar);
                     } else {
-                        tma_load_2d(smem_u32(stage + BM * BK * 2), &map_b, kx, b_row, bar);       // one box of 256 rows
+                        tma_load_2d(smem_u32(stage + BM * BK * 2), &map_b, kx, b_row, bar);       // one box of WIDE rows
                     }
                 }
             }
@@ -566,7 +568,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
             // exactly like one box of 256 rows, so both forms issue one product of N = 256 per k step
             // (gate in accumulator columns 0..127, up in 128..255); two of N = 128 would cost twice the
             // issue time, which is what bounds this kernel.
-            constexpr uint32_t idesc = instr_desc(BM, 256);
+            constexpr uint32_t idesc = instr_desc(BM, dual ? 256 : WIDE);
             long long it = 0;
             bool ok = true;
             for (int j = 0; j < my_tiles && ok; ++j) {
@@ -615,8 +617,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
             fence_after_sync();
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256;
             if (FORM == TOKENS_ON_M_QKV) {                      // never sliced along k
-                if (args.rope_head_dim == 64) store_qkv_rope<64>(lane_addr, token, f_base, args);
-                else store_qkv_rope<128>(lane_addr, token, f_base, args);
+                if (args.rope_head_dim == 64) store_qkv_rope<64, WIDE>(lane_addr, token, f_base, args);
+                else store_qkv_rope<128, WIDE>(lane_addr, token, f_base, args);
             } else if (dual || slice == 0) {
                 store_accumulator<dual>(lane_addr, token, f_base, args);
             } else {                                            // a later k-slice: its own plane of the output, no bias
@@ -806,13 +808,13 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const Args& args,
     return (int)cudaGetLastError();
 }
 
-template <int FORM>
+template <int FORM, int WIDE = 256>
 int launch_persistent(const CUtensorMap& map_a, const CUtensorMap& map_b, const Args& args, int tiles_m, int tiles_total,
                       int splits, cudaStream_t stream) {
     constexpr int shared = P_STAGE_BYTES * P_STAGES + 1024;
     static bool configured = false;
     static int sm_count = 0;
-    auto kernel = gemm_tcgen05_persistent_kernel<FORM>;
+    auto kernel = gemm_tcgen05_persistent_kernel<FORM, WIDE>;
     if (!configured) {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
         if (err != cudaSuccess) return (int)err;
@@ -878,20 +880,27 @@ extern "C" void tt_gemm_tcgen05_expect_undelivered_bytes(int bytes) { undelivere
 // (elementwise.cu).  Only for the shapes the persistent and CTA-pair kernels run without slicing k (the caller asks
 // tt_gemm_tcgen05_qkv_rope_takes first) and head sizes 64 and 128 rotated whole.  Returns a cudaError_t value, -1
 // if a tensor map could not be made, -2 if the shape is not taken.
+// Tile width of the qkv form below the pairs' range, 0 where the form is not taken.  The form does not slice k, so it is
+// taken where the plain product would not slice either: with more tiles of 256 features than half the SMs, or, failing
+// that, with more tiles of 128 features than half the SMs.  Slices and a rotation kernel of its own are faster only where
+// even those are few (measured on a B200, 1B shape, whole prefill: 1,024 tokens = 96 tiles of 256: 2.91 -> 2.77 ms with
+// this form; 768 and 512 tokens with tiles of 256: 2.43 -> 2.46 and 2.00 -> 2.07 ms, one SM per tile for all of k).
+static int qkv_rope_tile_width(int tokens, int features) {
+    int device = 0, sm_count = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+    const int tiles_m = (tokens + BM - 1) / BM;
+    if (tiles_m * ((features + 255) / 256) * 2 > sm_count) return 256;
+    if (tiles_m * ((features + 127) / 128) * 2 > sm_count) return 128;
+    return 0;
+}
+
 extern "C" int tt_gemm_tcgen05_qkv_rope_takes(int tokens, int features, int k, int head_dim) {
     if (head_dim != 64 && head_dim != 128) return 0;
     if (tokens <= 128 || features % head_dim) return 0;
     const int tiles = ((tokens + BM - 1) / BM) * ((features + 255) / 256);
     if (tiles < 8) return 0;
     if (tokens >= PAIR_MIN_TOKENS) return 1;
-    // below the pairs' range the persistent kernel slices k while its tiles are fewer than the SMs
-    int device = 0, sm_count = 0;
-    if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
-    // Taken where the plain product would not slice k either (more tiles than half the SMs).  Where it would, slices and a
-    // rotation kernel of its own are faster than one SM per tile for all of k (measured on a B200, 1B shape, whole prefill:
-    // 1,024 tokens = 96 tiles 2.91 -> 2.77 ms and 1,536 tokens 4.02 -> 3.83 ms with this form; 768 tokens = 72 tiles
-    // 2.43 -> 2.46 ms and 512 tokens 2.00 -> 2.07 ms, so not there)
-    return tiles * 2 > sm_count ? 1 : 0;
+    return qkv_rope_tile_width(tokens, features) ? 1 : 0;
 }
 
 extern "C" int tt_gemm_tcgen05_qkv_rope(const void* x, long long ldx, const void* w, long long ldw, const float* bias, int tokens, int k,
@@ -916,6 +925,10 @@ extern "C" int tt_gemm_tcgen05_qkv_rope(const void* x, long long ldx, const void
     CUtensorMap map_a, map_b;
     const int tiles_m = (tokens + BM - 1) / BM;
     if (tokens < PAIR_MIN_TOKENS) {
+        if (qkv_rope_tile_width(tokens, features) == 128) {
+            if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, features, k, ldw, 128)) return -1;
+            return launch_persistent<TOKENS_ON_M_QKV, 128>(map_a, map_b, args, tiles_m, tiles_m * ((features + 127) / 128), 1, stream);
+        }
         if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, features, k, ldw, 256)) return -1;
         return launch_persistent<TOKENS_ON_M_QKV>(map_a, map_b, args, tiles_m, tiles_m * ((features + 255) / 256), 1, stream);
     }
