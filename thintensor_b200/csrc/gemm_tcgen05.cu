@@ -403,22 +403,47 @@ __device__ __forceinline__ void store_accumulator(uint32_t lane_addr, int token,
 // the two come from tensor-memory chunks j and j + HD / 64 of the head, so a thread holds both.  The
 // arithmetic is that of rope_append_vec_kernel (elementwise.cu).  Tensor-memory loads are
 // warp-collective: every lane runs them, valid row or not.
+//
+// What the row needs besides the accumulator depends on the token only: where it goes in the cache (position,
+// sequence, table entry: two dependent loads) and its cosines and sines (HD / 2 pairs, 256 or 512 bytes that every
+// head of the tile would otherwise fetch again, past an L1 that the stages leave a few KB).  QkvRow holds them in
+// registers; a thread fills it BEFORE it waits for the accumulator, so all of that is in flight while the tile's
+// products still run (measured on a B200, tiles of 256 x 192: 12,000 to 15,000 cycles per tile's epilogue with the
+// loads inside it, against 12,300 for the tile's products, so the epilogues bounded the kernel).
+template <int HD> struct QkvRow {
+    int block, slot;
+    bool live;
+    float4 cs[HD / 4];          // (cos, sin) of two neighbouring pairs each
+};
+
+template <int HD>
+__device__ __forceinline__ void prepare_qkv_row(QkvRow<HD>& row, int token, const Args& args) {
+    const QkvRope& r = args.rope;
+    row.live = token < args.tokens;
+    row.block = -1;
+    row.slot = 0;
+    if (row.live) {
+        const int2 w = __ldg(r.where + token);
+        const float4* cs = reinterpret_cast<const float4*>(r.cos_sin + (size_t)token * (HD / 2));
+#pragma unroll
+        for (int i = 0; i < HD / 4; ++i) row.cs[i] = __ldg(cs + i);
+        const int entry = __ldg(r.table + (size_t)w.y * r.table_width + w.x / TT_BLOCK_TOKENS);
+        if (entry < 0 || entry >= r.pool_blocks) atomicOr(args.status, TT_STATUS_BAD_BLOCK);
+        else row.block = entry;
+        row.slot = w.x % TT_BLOCK_TOKENS;
+    } else {
+#pragma unroll
+        for (int i = 0; i < HD / 4; ++i) row.cs[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+}
+
 template <int HD, int WIDE = 256>
-__device__ __forceinline__ void store_qkv_rope(uint32_t lane_addr, int token, int f_base, const Args& args) {
+__device__ __forceinline__ void store_qkv_rope(const QkvRow<HD>& row, uint32_t lane_addr, int token, int f_base, const Args& args) {
     static_assert(WIDE % HD == 0, "a tile holds whole heads");
     constexpr int CH = HD / 32, HALF = HD / 2;
     const QkvRope& r = args.rope;
-    const bool live = token < args.tokens;
-    int block = -1, slot = 0;
-    const float2* cs = r.cos_sin;
-    if (live) {
-        const int2 w = __ldg(r.where + token);
-        const int entry = __ldg(r.table + (size_t)w.y * r.table_width + w.x / TT_BLOCK_TOKENS);
-        if (entry < 0 || entry >= r.pool_blocks) atomicOr(args.status, TT_STATUS_BAD_BLOCK);
-        else block = entry;
-        slot = w.x % TT_BLOCK_TOKENS;
-        cs += (size_t)token * HALF;
-    }
+    const bool live = row.live;
+    const int block = row.block, slot = row.slot;
     const float k = r.attention_scaling;
     for (int h = 0; h < WIDE / HD; ++h) {
         const int col0 = f_base + h * HD;                       // the head's first column: the same for the whole CTA
@@ -434,8 +459,14 @@ __device__ __forceinline__ void store_qkv_rope(uint32_t lane_addr, int token, in
 #pragma unroll
             for (int j = 0; j < CH / 2; ++j) {
                 float a[32], b[32];
-                tmem_load32(head_addr + j * 32, a);
-                tmem_load32(head_addr + HALF + j * 32, b);
+                {
+                    uint32_t ra[32], rb[32];
+                    tmem_load32_issue(head_addr + j * 32, ra);
+                    tmem_load32_issue(head_addr + HALF + j * 32, rb);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) { a[e] = tmem_loaded(ra[e]); b[e] = tmem_loaded(rb[e]); }
+                }
                 if (!dst) continue;
                 if (args.bias) {
 #pragma unroll
@@ -446,7 +477,7 @@ __device__ __forceinline__ void store_qkv_rope(uint32_t lane_addr, int token, in
                     uint32_t lo[4], hi[4];
 #pragma unroll
                     for (int e = e0; e < e0 + 8; e += 2) {
-                        const float4 t = __ldg(reinterpret_cast<const float4*>(cs + j * 32 + e));     // (cos, sin) of two neighbouring pairs
+                        const float4 t = row.cs[(j * 32 + e) / 2];                                     // (cos, sin) of two neighbouring pairs
                         const float ra0 = (a[e] * t.x - b[e] * t.y) * k, rb0 = (b[e] * t.x + a[e] * t.y) * k;
                         const float ra1 = (a[e + 1] * t.z - b[e + 1] * t.w) * k, rb1 = (b[e + 1] * t.z + a[e + 1] * t.w) * k;
                         const __nv_bfloat162 pa = __floats2bfloat162_rn(ra0, ra1), pb = __floats2bfloat162_rn(rb0, rb1);
@@ -476,6 +507,18 @@ __device__ __forceinline__ void store_qkv_rope(uint32_t lane_addr, int token, in
             }
         }
     }
+}
+
+// One row's epilogue of the qkv form: ask for what the row needs, wait for the tile's accumulator, rotate and store.
+// False if the wait ran out.
+template <int HD, int WIDE>
+__device__ __forceinline__ bool qkv_row_epilogue(uint32_t acc_bar, uint32_t parity, uint32_t lane_addr, int token, int f_base, const Args& args) {
+    QkvRow<HD> row;
+    prepare_qkv_row<HD>(row, token, args);
+    if (!mbar_wait(acc_bar, parity)) return false;
+    fence_after_sync();
+    store_qkv_rope<HD, WIDE>(row, lane_addr, token, f_base, args);
+    return true;
 }
 
 // ------------------------------------------------------------------ persistent kernel
@@ -610,15 +653,22 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
             const int item = (int)blockIdx.x + j * (int)gridDim.x, tile = item % tiles_total, slice = item / tiles_total;
             const int token = (tile % tiles_m) * BM + row, f_base = (tile / tiles_m) * TILE_N;
             if (!dual) prefetch_output_row(token, f_base, args);
-            if (!mbar_wait(smem_u32(&acc_full[buf]), (uint32_t)((j >> 1) & 1))) {
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256;
+            const uint32_t acc_bar = smem_u32(&acc_full[buf]), acc_parity = (uint32_t)((j >> 1) & 1);
+            bool ok;
+            if constexpr (FORM == TOKENS_ON_M_QKV) {            // never sliced along k
+                ok = args.rope_head_dim == 64 ? qkv_row_epilogue<64, WIDE>(acc_bar, acc_parity, lane_addr, token, f_base, args)
+                                              : qkv_row_epilogue<128, WIDE>(acc_bar, acc_parity, lane_addr, token, f_base, args);
+            } else {
+                ok = mbar_wait(acc_bar, acc_parity);
+                fence_after_sync();
+            }
+            if (!ok) {
                 if (lane == 0) atomicOr(args.status, TT_STATUS_WAIT_EXPIRED);
                 break;
             }
-            fence_after_sync();
-            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256;
-            if (FORM == TOKENS_ON_M_QKV) {                      // never sliced along k
-                if (args.rope_head_dim == 64) store_qkv_rope<64, WIDE>(lane_addr, token, f_base, args);
-                else store_qkv_rope<128, WIDE>(lane_addr, token, f_base, args);
+            if constexpr (FORM == TOKENS_ON_M_QKV) {
+                // stored by qkv_row_epilogue
             } else if (dual || slice == 0) {
                 store_accumulator<dual>(lane_addr, token, f_base, args);
             } else {                                            // a later k-slice: its own plane of the output, no bias
@@ -760,19 +810,22 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             const int tile = pair + j * n_pairs;
             const int token = (tile % tiles_m) * 2 * BM + rank * BM + row, f_base = (tile / tiles_m) * TILE_N;
             if (!dual) prefetch_output_row(token, f_base, args);
-            if (!mbar_wait(smem_u32(&acc_full[buf]), (uint32_t)((j >> 1) & 1))) {
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256;
+            const uint32_t acc_bar = smem_u32(&acc_full[buf]), acc_parity = (uint32_t)((j >> 1) & 1);
+            bool ok;
+            if constexpr (FORM == TOKENS_ON_M_QKV) {
+                if constexpr (WIDE == 192) ok = qkv_row_epilogue<64, 192>(acc_bar, acc_parity, lane_addr, token, f_base, args);
+                else ok = args.rope_head_dim == 64 ? qkv_row_epilogue<64, WIDE>(acc_bar, acc_parity, lane_addr, token, f_base, args)
+                                                   : qkv_row_epilogue<128, WIDE>(acc_bar, acc_parity, lane_addr, token, f_base, args);
+            } else {
+                ok = mbar_wait(acc_bar, acc_parity);
+                fence_after_sync();
+            }
+            if (!ok) {
                 if (lane == 0) atomicOr(args.status, TT_STATUS_WAIT_EXPIRED);
                 break;
             }
-            fence_after_sync();
-            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256;
-            if constexpr (FORM == TOKENS_ON_M_QKV) {
-                if constexpr (WIDE == 192) store_qkv_rope<64, 192>(lane_addr, token, f_base, args);
-                else if (args.rope_head_dim == 64) store_qkv_rope<64>(lane_addr, token, f_base, args);
-                else store_qkv_rope<128>(lane_addr, token, f_base, args);
-            } else {
-                store_accumulator<dual>(lane_addr, token, f_base, args);
-            }
+            if constexpr (FORM != TOKENS_ON_M_QKV) store_accumulator<dual>(lane_addr, token, f_base, args);     // the qkv form has stored its row
             // this warp is done with the accumulator: tell the issuer, who sits in the even CTA
             fence_before_sync();
             __syncwarp();
