@@ -341,22 +341,42 @@ __device__ __forceinline__ void prefetch_output_row(int token, int f_base, const
 template <bool dual>
 __device__ __forceinline__ void store_accumulator(uint32_t lane_addr, int token, int f_base, const Args& args) {
     if (dual) {
+        // A tile's epilogue has to fit under the next tile's products (16,400 cycles for k = 2,048): with one round trip to
+        // tensor memory per half chunk and 4-byte stores (every lane its own row: 32 sectors an instruction for 128 bytes)
+        // it took 19,200 cycles and bounded the kernel (clock stamps on a B200).  So the next chunk's gate and up are on
+        // their way while this one is worked on, and eight results go out as one 16-byte store.
         __nv_bfloat16* out = (__nv_bfloat16*)args.out + (size_t)token * args.ld_out;
-        for (int c = 0; c < 128; c += 32) {
-            float gate[32], up[32];
-            tmem_load32(lane_addr + c, gate);
-            tmem_load32(lane_addr + 128 + c, up);
+        const bool vec = (args.ld_out & 7) == 0 && (((uintptr_t)args.out) & 15) == 0 && (f_base & 7) == 0;
+        uint32_t gate[2][32], up[2][32];
+        tmem_load32_issue(lane_addr, gate[0]);
+        tmem_load32_issue(lane_addr + 128, up[0]);
+#pragma unroll
+        for (int ci = 0; ci < 4; ++ci) {
+            const int c = 32 * ci, cur = ci & 1;
+            tmem_load_wait();
+            if (ci + 1 < 4) {
+                tmem_load32_issue(lane_addr + c + 32, gate[cur ^ 1]);
+                tmem_load32_issue(lane_addr + 128 + c + 32, up[cur ^ 1]);
+            }
             if (token < args.tokens) {
 #pragma unroll
-                for (int e = 0; e < 32; e += 2) {
-                    const int f = f_base + c + e;
-                    const float y0 = gate[e] / (1.0f + __expf(-gate[e])) * up[e];
-                    const float y1 = gate[e + 1] / (1.0f + __expf(-gate[e + 1])) * up[e + 1];
-                    if (f + 1 < args.features && (args.ld_out & 1) == 0) {
-                        *reinterpret_cast<__nv_bfloat162*>(out + f) = __floats2bfloat162_rn(y0, y1);
+                for (int e0 = 0; e0 < 32; e0 += 8) {
+                    const int f = f_base + c + e0;
+                    float y[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const float g = tmem_loaded(gate[cur][e0 + e]), u = tmem_loaded(up[cur][e0 + e]);
+                        y[e] = __fdividef(g, 1.0f + __expf(-g)) * u;
+                    }
+                    if (vec && f + 8 <= args.features) {
+                        const __nv_bfloat162 p0 = __floats2bfloat162_rn(y[0], y[1]), p1 = __floats2bfloat162_rn(y[2], y[3]);
+                        const __nv_bfloat162 p2 = __floats2bfloat162_rn(y[4], y[5]), p3 = __floats2bfloat162_rn(y[6], y[7]);
+                        *reinterpret_cast<uint4*>(out + f) = make_uint4(*reinterpret_cast<const uint32_t*>(&p0), *reinterpret_cast<const uint32_t*>(&p1),
+                                                                        *reinterpret_cast<const uint32_t*>(&p2), *reinterpret_cast<const uint32_t*>(&p3));
                     } else {
-                        if (f < args.features) out[f] = __float2bfloat16_rn(y0);
-                        if (f + 1 < args.features) out[f + 1] = __float2bfloat16_rn(y1);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e)
+                            if (f + e < args.features) out[f + e] = __float2bfloat16_rn(y[e]);
                     }
                 }
             }
@@ -364,7 +384,11 @@ __device__ __forceinline__ void store_accumulator(uint32_t lane_addr, int token,
     } else {
         float* out = (float*)args.out + (size_t)token * args.ld_out;
         const bool vec = (args.ld_out & 3) == 0 && (((uintptr_t)args.out) & 15) == 0;
-        for (int c = 0; c < 256; c += 32) {
+        uint32_t acc[2][32];                                // the next chunk is on its way while this one is stored
+        tmem_load32_issue(lane_addr, acc[0]);
+#pragma unroll
+        for (int ci = 0; ci < 8; ++ci) {
+            const int c = 32 * ci, cur = ci & 1;
             float v[32];
             const int f0 = f_base + c;
             float4 old[8];
@@ -373,7 +397,10 @@ __device__ __forceinline__ void store_accumulator(uint32_t lane_addr, int token,
 #pragma unroll
                 for (int e = 0; e < 8; ++e) old[e] = *reinterpret_cast<const float4*>(out + f0 + 4 * e);
             }
-            tmem_load32(lane_addr + c, v);
+            tmem_load_wait();
+            if (ci + 1 < 8) tmem_load32_issue(lane_addr + c + 32, acc[cur ^ 1]);
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = tmem_loaded(acc[cur][e]);
             if (token < args.tokens) {
                 if (args.bias) {
 #pragma unroll
