@@ -384,11 +384,7 @@ __device__ __forceinline__ void store_accumulator(uint32_t lane_addr, int token,
     } else {
         float* out = (float*)args.out + (size_t)token * args.ld_out;
         const bool vec = (args.ld_out & 3) == 0 && (((uintptr_t)args.out) & 15) == 0;
-        uint32_t acc[2][32];                                // the next chunk is on its way while this one is stored
-        tmem_load32_issue(lane_addr, acc[0]);
-#pragma unroll
-        for (int ci = 0; ci < 8; ++ci) {
-            const int c = 32 * ci, cur = ci & 1;
+        for (int c = 0; c < 256; c += 32) {
             float v[32];
             const int f0 = f_base + c;
             float4 old[8];
@@ -397,10 +393,7 @@ __device__ __forceinline__ void store_accumulator(uint32_t lane_addr, int token,
 #pragma unroll
                 for (int e = 0; e < 8; ++e) old[e] = *reinterpret_cast<const float4*>(out + f0 + 4 * e);
             }
-            tmem_load_wait();
-            if (ci + 1 < 8) tmem_load32_issue(lane_addr + c + 32, acc[cur ^ 1]);
-#pragma unroll
-            for (int e = 0; e < 32; ++e) v[e] = tmem_loaded(acc[cur][e]);
+            tmem_load32(lane_addr + c, v);
             if (token < args.tokens) {
                 if (args.bias) {
 #pragma unroll
