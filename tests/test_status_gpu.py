@@ -51,6 +51,53 @@ def test_a_wait_that_runs_out_raises_the_status_and_leaves_the_gpu_usable():
     torch.testing.assert_close(out.double().sum(0), want, rtol=1e-4, atol=1e-2)
 
 
+def test_a_wait_that_runs_out_in_decode_attention_raises_the_status_and_leaves_the_gpu_usable():
+    """The decode attention streams the cache through mbarriers that count the copies' bytes.  Its warps' first stage is told
+    to expect bytes that no copy brings, with a wait limit of 3 ms: every warp's wait runs out, the kernel returns with
+    STATUS_WAIT_EXPIRED (the copies themselves have landed, so nothing is in flight when shared memory is given up), and
+    the same call run normally right after gives the right numbers."""
+    from test_kernels_gpu import attention_reference, make_cache, randn, tol
+    from thintensor_b200.kernels import api
+
+    dtype, heads, kv_heads, head_dim = torch.bfloat16, 8, 2, 64
+    totals = [300, 70, 1]
+    n = len(totals)
+    k_pool, v_pool, table, keys, values = make_cache(totals, kv_heads, head_dim, dtype, seed=80)
+    q = randn(n, heads, head_dim, dtype=dtype, seed=81)
+    cu = torch.arange(n + 1, dtype=torch.int32, device=DEV)
+    before = torch.tensor([t - 1 for t in totals], dtype=torch.int32, device=DEV)
+    scale = head_dim ** -0.5
+    want = attention_reference(q.float().cpu(), keys, values, [1] * n, heads, kv_heads, scale, 0)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+
+    def run():
+        out = torch.full((n, heads * head_dim), float("nan"), dtype=dtype, device=DEV)
+        api.attention_mma(q.view(n, -1), k_pool, v_pool, table, cu, before, n, n, heads, kv_heads, head_dim, scale, 0, 1, out, None, None,
+                          status, one_token_each=True)
+        return out
+
+    first = run()
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    torch.testing.assert_close(first.double().cpu().view(n, heads, head_dim), want, **tol(dtype))
+    try:
+        api.attention_mma_failure_drill(wait_limit_ns=3_000_000, undelivered_bytes=256)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        run()
+        stop.record()
+        torch.cuda.synchronize()                                  # returns: the kernel gave up by itself
+        assert start.elapsed_time(stop) < 1000.0, "the waits should have run out within milliseconds"
+    finally:
+        api.attention_mma_failure_drill(wait_limit_ns=0, undelivered_bytes=0)
+    assert int(status.item()) & api.STATUS_WAIT_EXPIRED
+    status.zero_()
+    again = run()
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    torch.testing.assert_close(again.double().cpu().view(n, heads, head_dim), want, **tol(dtype))
+
+
 def test_the_engine_turns_an_expired_wait_into_an_exception(model_folders):
     import thintensor_b200
     from thintensor_b200.engine.engine import Entry

@@ -48,6 +48,10 @@
 #include <cooperative_groups.h>
 namespace cg = cooperative_groups;
 
+// Tests of the failure path only: every decode warp's first stage expects this many bytes more than its copies bring, so its
+// barrier never completes and the bounded wait has to run out (0 in every real run; handed to the kernel as an argument).
+static int decode_undelivered_bytes_for_tests = 0;
+
 namespace {
 
 constexpr int MMA_WARPS = 4;          // warps of a CTA of the prompt kernel
@@ -602,7 +606,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
                         __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ table, int table_width,
                         int pool_blocks, const int* __restrict__ len_before, int heads, int kv_heads, float scale_log2,
                         int window, int splits, int cluster_merge, __nv_bfloat16* __restrict__ out,
-                        float* __restrict__ part_acc, float* __restrict__ part_ml, unsigned* __restrict__ tickets, unsigned* status) {
+                        float* __restrict__ part_acc, float* __restrict__ part_ml, unsigned* __restrict__ tickets, int undelivered_bytes,
+                        unsigned* status) {
     constexpr int WARPS = DecodeShape<HD, SHAPE>::WARPS, STAGES = DecodeShape<HD, SHAPE>::STAGES;
     constexpr int TILE = TT_BLOCK_TOKENS * HD * 2;     // bytes of a block's keys of one head, and of its values
     extern __shared__ __align__(128) uint4 slots[];   // [WARPS][STAGES]: a K tile [64 keys][HD], then a V tile [HD][64 keys], as they lie in the cache
@@ -653,7 +658,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
             if (good) {
                 const size_t tile = ((size_t)block * kv_heads + kh) * (TT_BLOCK_TOKENS * HD);     // a K tile and a V tile have the same size
                 char* dst = my_slots + (size_t)(i % STAGES) * 2 * TILE;
-                tc::mbar_expect_tx(bar, 2 * TILE);
+                tc::mbar_expect_tx(bar, 2 * TILE + (i == 0 ? undelivered_bytes : 0));
                 bulk_copy(dst, k_pool + tile, TILE, bar);
                 bulk_copy(dst + TILE, v_pool + tile, TILE, bar);
             } else {
@@ -866,7 +871,7 @@ cudaError_t launch_decode_tiles(const void* q, const DecodeRope& rope, void* k_p
             }
             return tt_launch_pdl(with_tickets, dim3(sequences, kv_heads, splits), dim3(D::WARPS * 32), shared, stream,
                 (const __nv_bfloat16*)q, rope, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks,
-                len_before, heads, kv_heads, scale_log2, window, splits, 0, (__nv_bfloat16*)out, part_acc, part_ml, tickets, status);
+                len_before, heads, kv_heads, scale_log2, window, splits, 0, (__nv_bfloat16*)out, part_acc, part_ml, tickets, decode_undelivered_bytes_for_tests, status);
         }
     }
     static bool configured = false;
@@ -879,10 +884,10 @@ cudaError_t launch_decode_tiles(const void* q, const DecodeRope& rope, void* k_p
     if (slices_form_cluster(splits))
         return tt_launch_pdl_cluster(kernel, dim3(sequences, kv_heads, splits), dim3(D::WARPS * 32), shared, stream, (unsigned)splits,
             (const __nv_bfloat16*)q, rope, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks,
-            len_before, heads, kv_heads, scale_log2, window, splits, 1, (__nv_bfloat16*)out, part_acc, part_ml, tickets, status);
+            len_before, heads, kv_heads, scale_log2, window, splits, 1, (__nv_bfloat16*)out, part_acc, part_ml, tickets, decode_undelivered_bytes_for_tests, status);
     return tt_launch_pdl(kernel, dim3(sequences, kv_heads, splits), dim3(D::WARPS * 32), shared, stream,
         (const __nv_bfloat16*)q, rope, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks,
-        len_before, heads, kv_heads, scale_log2, window, splits, 0, (__nv_bfloat16*)out, part_acc, part_ml, tickets, status);
+        len_before, heads, kv_heads, scale_log2, window, splits, 0, (__nv_bfloat16*)out, part_acc, part_ml, tickets, decode_undelivered_bytes_for_tests, status);
 }
 
 // One column tile of 8 queries serves groups of up to 8 query heads per key/value head, two serve up to 16.
@@ -969,6 +974,15 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* tab
 }
 
 }  // namespace
+
+// For tests of the failure path, never for serving: the limit of the decode kernel's bounded waits (0: the default of two
+// seconds) and bytes that every warp's first stage expects beyond what its copies bring (0: normal operation).
+extern "C" int tt_attention_mma_failure_drill(unsigned long long wait_limit_ns, int undelivered_bytes) {
+    const int code = tc::set_wait_limit_ns(wait_limit_ns);
+    if (code != 0) return code;
+    decode_undelivered_bytes_for_tests = undelivered_bytes < 0 ? 0 : undelivered_bytes;
+    return 0;
+}
 
 // one_token_each: 0 = packed prompts (any number of tokens per sequence); 1 = every
 // sequence brings exactly one token (n_tokens == sequences) and the decode kernel runs.

@@ -322,6 +322,19 @@ def attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, t
               _stream()), "attention_mma", _attention_launches(splits, one_token_each, tickets is not None))
 
 
+def attention_mma_failure_drill(wait_limit_ns: int, undelivered_bytes: int) -> None:
+    """For tests of the failure path, never for serving.  ``wait_limit_ns``: the limit of the bounded waits in the
+    tensor-core decode attention (0 restores the default of two seconds).  ``undelivered_bytes``: from now on the first
+    stage of every warp expects that many bytes more than its copies bring (0 restores normal operation), so its barrier
+    never completes; the kernel must then raise ``STATUS_WAIT_EXPIRED`` and return."""
+    lib = build.load("attention_mma")
+    lib.tt_attention_mma_failure_drill.argtypes = [c_ulonglong, c_int]
+    lib.tt_attention_mma_failure_drill.restype = c_int
+    code = lib.tt_attention_mma_failure_drill(int(wait_limit_ns), int(undelivered_bytes))
+    if code != 0:
+        raise KernelError(f"the decode attention's failure drill could not be set: CUDA error {code}")
+
+
 def attention_decode_rope_supports(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int, rotary_dim: int) -> bool:
     """Whether decoding may rotate q and k and write the cache inside the attention kernel
     (bfloat16, head size 64 rotated whole, at most 16 query heads per key/value head)."""
