@@ -105,7 +105,8 @@ def test_split_policy_and_refusals():
     assert api.gemm_tcgen05_splits(8, 128256, 2048) == 1
     assert api.gemm_tcgen05_splits(2048, 3072, 2048) == 1
     assert api.gemm_tcgen05_splits(300, 2048, 8192) == 6        # 3 x 8 tiles of 128 x 256: the persistent kernel, 144 work items
-    assert api.gemm_tcgen05_splits(512, 2048, 2048) == 4        # 32 tiles, 32 k-blocks
+    assert api.gemm_tcgen05_splits(256, 2048, 8192) == 4        # 2 x 16 tiles of 128 x 128 (the 16 of 256 are too few): 128 work items
+    assert api.gemm_tcgen05_splits(512, 2048, 2048) == 4        # 32 tiles of 128 x 256, 32 k-blocks
     assert api.gemm_tcgen05_splits(1024, 3072, 2048) == 1       # 96 tiles: one round of the SMs already
     assert api.gemm_tcgen05_splits(4096, 256, 8192) == 1        # CTA pairs do not slice
     assert api.gemm_tcgen05_splits(300, 200, 4096) > 1          # too few tiles for it

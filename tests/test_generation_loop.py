@@ -182,7 +182,7 @@ def test_product_policies_need_no_device():
     from thintensor_b200.kernels import api
 
     assert api.gemm_tcgen05_splits(8, 2048, 2048, sms=148) == 8 and api.gemm_tcgen05_splits(8, 128256, 2048, sms=148) == 1
-    assert api.gemm_tcgen05_splits(512, 2048, 2048, sms=148) == 4 and api.gemm_tcgen05_splits(2048, 2048, 8192, sms=148) == 1
+    assert api.gemm_tcgen05_splits(512, 2048, 2048, sms=148) == 4 and api.gemm_tcgen05_splits(256, 2048, 2048, sms=148) == 4 and api.gemm_tcgen05_splits(2048, 2048, 8192, sms=148) == 1
     for tokens in (1, 8, 64, 128, 512, 1024, 2048, 4096):
         assert not api.gemm_tcgen05_accumulate_pays(tokens, 2048, 2048, sms=148), tokens       # 1B output projection: one tile per CTA pair or sliced k
     assert api.gemm_tcgen05_accumulate_pays(4736, 2048, 2048, sms=148) and api.gemm_tcgen05_accumulate_pays(8192, 2048, 8192, sms=148)

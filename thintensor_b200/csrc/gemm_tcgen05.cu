@@ -338,7 +338,7 @@ __device__ __forceinline__ void prefetch_output_row(int token, int f_base, const
 // first column): plain form, 256 features from f_base as float32 (+ bias); SwiGLU form, columns
 // 0..127 the gate and 128..255 the up projection of 128 features from f_base, stored as bfloat16.
 // The tensor-memory loads are warp-collective: every lane runs them, valid row or not.
-template <bool dual>
+template <bool dual, int WIDE = 256>
 __device__ __forceinline__ void store_accumulator(uint32_t lane_addr, int token, int f_base, const Args& args) {
     if (dual) {
         // A tile's epilogue has to fit under the next tile's products (16,400 cycles for k = 2,048): with one round trip to
@@ -384,7 +384,7 @@ __device__ __forceinline__ void store_accumulator(uint32_t lane_addr, int token,
     } else {
         float* out = (float*)args.out + (size_t)token * args.ld_out;
         const bool vec = (args.ld_out & 3) == 0 && (((uintptr_t)args.out) & 15) == 0;
-        for (int c = 0; c < 256; c += 32) {
+        for (int c = 0; c < WIDE; c += 32) {
             float v[32];
             const int f0 = f_base + c;
             float4 old[8];
@@ -560,7 +560,7 @@ __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Args args,
                                int tiles_m, int tiles_total, int splits) {
     constexpr bool dual = FORM == TOKENS_ON_M_SWIGLU;
-    static_assert(WIDE == 256 || (FORM == TOKENS_ON_M_QKV && WIDE == 128), "only the qkv form has a narrower tile");
+    static_assert(WIDE == 256 || (!dual && WIDE == 128), "the SwiGLU form has no narrower tile");
     constexpr int TILE_N = dual ? 128 : WIDE;                   // output features per tile
     constexpr int STAGE_TX = BM * BK * 2 + (dual ? 256 : WIDE) * BK * 2;       // bytes a stage's copies bring
     extern __shared__ uint8_t smem_raw[];
@@ -690,12 +690,12 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
             if constexpr (FORM == TOKENS_ON_M_QKV) {
                 // stored by qkv_row_epilogue
             } else if (dual || slice == 0) {
-                store_accumulator<dual>(lane_addr, token, f_base, args);
+                store_accumulator<dual, WIDE>(lane_addr, token, f_base, args);
             } else {                                            // a later k-slice: its own plane of the output, no bias
                 Args mine = args;
                 mine.out = (float*)args.out + (size_t)slice * args.split_stride;
                 mine.bias = nullptr;
-                store_accumulator<dual>(lane_addr, token, f_base, mine);
+                store_accumulator<dual, WIDE>(lane_addr, token, f_base, mine);
             }
             // this warp is done with the accumulator: tell the issuer
             fence_before_sync();
@@ -1078,6 +1078,18 @@ extern "C" int tt_gemm_tcgen05(const void* x, long long ldx, const void* w, long
     if (tokens > 128 && tiles_m * ((features + 255) / 256) >= 8 && (splits == 1 || (tokens < PAIR_MIN_TOKENS && slices_full))) {
         // from 8 tiles of 128 x 256 on the persistent kernel wins (measured); fewer tiles than SMs are cut along k
         if (tokens < PAIR_MIN_TOKENS) {
+            // Where tiles of 256 features would fill at most an eighth of the SMs (prompts of up to 256 tokens at the 1B
+            // shape), tiles of 128 features are taken and k is sliced half as often: an item's epilogue (10,200 cycles for
+            // 128 x 256 numbers) then weighs half as much against its few products.  Measured on a B200, 1B shape, whole
+            // prefill: 200 tokens 1.54 -> 1.43 ms, 256 tokens 1.60 -> 1.44; at 320 and 384 tokens nothing either way, and
+            // from 512 tokens on the narrow tiles lose (512: 1.76 -> 1.83, 768: 2.16 -> 2.50: a k-block then brings 32 KB
+            // into shared memory for half the products).  gemm_tcgen05_splits (kernels/api.py) counts the tiles the same way.
+            int device = 0, sm_count = 0;
+            if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return -1;
+            if (form == 0 && tiles_m * ((features + 255) / 256) * 8 <= sm_count) {
+                if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, features, k, ldw, 128)) return -1;
+                return launch_persistent<TOKENS_ON_M, 128>(map_a, map_b, args, tiles_m, tiles_m * ((features + 127) / 128), splits, stream);
+            }
             if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, features, k, ldw, 256)) return -1;
             return launch_persistent<TOKENS_ON_M>(map_a, map_b, args, tiles_m, tiles_m * ((features + 255) / 256), splits, stream);
         }

@@ -484,6 +484,8 @@ def gemm_tcgen05_splits(tokens: int, features: int, k: int, sms: int | None = No
         if tokens >= PAIR_TOKENS:
             return 1
         tiles = -(-tokens // 128) * -(-features // 256)
+        if tiles * 8 <= sms:                  # tiles of 128 features where those of 256 fill at most an eighth of the SMs (the launcher does the same)
+            tiles = -(-tokens // 128) * -(-features // 128)
         splits = max(1, min(sms // tiles, k_blocks // PERSISTENT_SLICE_BLOCKS, 16))
         while splits > 1 and (splits - 1) * -(-k_blocks // splits) >= k_blocks:
             splits -= 1
