@@ -45,7 +45,8 @@ def test_tokens_on_m(tokens, features, k, splits):
     run(tokens, features, k, splits, with_bias=(features % 2 == 1))
 
 
-@pytest.mark.parametrize("tokens,features,k", [(2048, 3072, 2048), (1500, 2000, 1000), (3000, 1000, 136), (12345, 311, 72), (2048, 2048, 8192)])
+@pytest.mark.parametrize("tokens,features,k", [(2048, 3072, 2048), (1500, 2000, 1000), (3000, 1000, 136), (12345, 311, 72), (2048, 2048, 8192),
+                                               (2500, 1100, 72), (6000, 2052, 200)])
 def test_tokens_on_m_persistent(tokens, features, k):
     """Enough 128 x 256 tiles for the persistent kernel: tiles that hang over every edge,
     several tiles per CTA (two accumulators in turn), bias."""
@@ -71,7 +72,9 @@ def test_tokens_on_m_persistent_sliced(tokens, features, k, splits):
     (1500, 2000, 1000),          # persistent kernel, several tiles per CTA
     (700, 1001, 136),            # rows that are no multiple of four floats: element-wise loads and stores
     (2048, 2048, 2048),          # CTA pairs
-    (2500, 530, 8192),           # CTA pairs, ragged
+    (2500, 530, 8192),           # CTA pairs, ragged, rows that tiled copies cannot write (530 floats): stores from registers
+    (2500, 1100, 320),           # CTA pairs adding through tiled copies: the last pair half empty, the last box 12 columns wide
+    (2300, 2052, 192),           # the same with a bias and one column box of 4
 ])
 def test_product_added_into_its_output(tokens, features, k):
     """The accumulate form: out += x @ w.T (+ bias), every tile read and written once by its epilogue."""
@@ -95,6 +98,28 @@ def test_product_added_into_its_output(tokens, features, k):
     assert not api.gemm_tcgen05_accumulates(64, features, k) and not api.gemm_tcgen05_accumulates(512, 2048, 2048)   # few tokens; sliced k
     with pytest.raises(api.KernelError):
         api.gemm_tcgen05(x[:64], w, None, out[:, :64], status, accumulate=True)
+
+
+@pytest.mark.parametrize("accumulate", [False, True])
+def test_tiled_copies_of_the_output_stop_at_its_edges(accumulate):
+    """The CTA pairs' plain form writes its tiles with tiled copies whose boxes hang over the last rows and columns:
+    the output is a window of a larger matrix, and nothing around the window may change."""
+    tokens, features, k = 2100, 1100, 136
+    x, w = randn(tokens, k, seed=31), randn(features, k, seed=32)
+    whole = torch.full((tokens + 40, features + 36), 7.0, dtype=torch.float32, device=DEV)    # rows of 1,136 floats: a multiple of four
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    from ctypes import c_int, c_longlong, c_void_p
+    from thintensor_b200.kernels import build
+    fn = build.load("gemm_tcgen05").tt_gemm_tcgen05
+    fn.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+    fn.restype = c_int
+    assert fn(x.data_ptr(), k, w.data_ptr(), k, None, whole.data_ptr(), whole.stride(0), 0, tokens, features, k, 1, 2 if accumulate else 0,
+              status.data_ptr(), torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    want = x.double() @ w.double().T + (7.0 if accumulate else 0.0)
+    torch.testing.assert_close(whole[:tokens, :features].double(), want, rtol=1e-4, atol=1e-4 * k ** 0.5)
+    assert bool((whole[tokens:] == 7.0).all()) and bool((whole[:, features:] == 7.0).all())
 
 
 def test_split_policy_and_refusals():

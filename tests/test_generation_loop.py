@@ -176,18 +176,21 @@ def test_key_slices_fill_one_wave():
 
 def test_product_policies_need_no_device():
     """How a projection is run is decided on the host from its sizes alone: k-slices for few output
-    tiles, none for CTA pairs, and the product added into the residual stream by the kernel only where
-    every CTA has two tiles to hide the read under.  The number of multiprocessors is the device's at run
+    tiles, none for CTA pairs, and the product added into the residual stream by the kernel wherever k is in
+    one slice and tiled copies can do the adding (else only where every CTA has two tiles to hide the read under).  The number of multiprocessors is the device's at run
     time; here it is given (a B200 has 148)."""
     from thintensor_b200.kernels import api
 
     assert api.gemm_tcgen05_splits(8, 2048, 2048, sms=148) == 8 and api.gemm_tcgen05_splits(8, 128256, 2048, sms=148) == 1
     assert api.gemm_tcgen05_splits(512, 2048, 2048, sms=148) == 4 and api.gemm_tcgen05_splits(256, 2048, 2048, sms=148) == 4 and api.gemm_tcgen05_splits(2048, 2048, 8192, sms=148) == 1
-    for tokens in (1, 8, 64, 128, 512, 1024, 2048, 4096):
-        assert not api.gemm_tcgen05_accumulate_pays(tokens, 2048, 2048, sms=148), tokens       # 1B output projection: one tile per CTA pair or sliced k
-    assert api.gemm_tcgen05_accumulate_pays(4736, 2048, 2048, sms=148) and api.gemm_tcgen05_accumulate_pays(8192, 2048, 8192, sms=148)
-    assert api.gemm_tcgen05_accumulate_pays(4096, 4096, 14336, sms=148) and not api.gemm_tcgen05_accumulate_pays(2048, 4096, 14336, sms=148)
-    assert api.gemm_tcgen05_accumulates(2048, 2048, 2048, sms=148) and not api.gemm_tcgen05_accumulates(512, 2048, 2048, sms=148)   # can, but does not pay; cannot (sliced)
+    for tokens in (1, 8, 64, 128, 512, 1024):
+        assert not api.gemm_tcgen05_accumulate_pays(tokens, 2048, 2048, sms=148), tokens       # 1B output projection: few tokens, or k in slices
+    for tokens in (1536, 2048, 4096, 4736, 8192):                                              # one k-slice, rows that tiled copies can add to
+        assert api.gemm_tcgen05_accumulate_pays(tokens, 2048, 2048, sms=148) and api.gemm_tcgen05_accumulate_pays(tokens, 2048, 8192, sms=148), tokens
+    assert api.gemm_tcgen05_accumulate_pays(4096, 4096, 14336, sms=148) and api.gemm_tcgen05_accumulate_pays(2048, 4096, 14336, sms=148)
+    # rows of 2,050 floats are added from registers after a read: only where a CTA pair has two tiles to hide it under
+    assert not api.gemm_tcgen05_accumulate_pays(2048, 2050, 2048, sms=148) and api.gemm_tcgen05_accumulate_pays(4736, 2050, 2048, sms=148)
+    assert api.gemm_tcgen05_accumulates(2048, 2050, 2048, sms=148) and not api.gemm_tcgen05_accumulates(512, 2048, 2048, sms=148)   # can, but does not pay; cannot (sliced)
     # whatever pays can be done
     for tokens in range(129, 9000, 371):
         for features, k in ((2048, 2048), (3072, 8192), (200, 64), (4096, 14336)):

@@ -119,9 +119,9 @@ def test_float32_real_layer_sizes(tmp_path, shape):
 
 
 def test_long_prompt_whole_and_in_pieces(tmp_path):
-    """A 4,800-token prompt of the 1B layer sizes, whole (long enough for the output projections to add
-    their product into the residual stream inside the kernel) and in pieces of 2,048 tokens (short enough
-    for the norm kernel to do the addition): the same logits."""
+    """A 4,800-token prompt of the 1B layer sizes, whole (the output projections add their product into
+    the residual stream inside the kernel) and in pieces of 1,024 tokens (their k is cut into slices and
+    the norm kernel does the addition): the same logits."""
     import thintensor_b200
     from thintensor_b200.engine.engine import Entry
     from thintensor_b200.kernels import api
@@ -130,9 +130,9 @@ def test_long_prompt_whole_and_in_pieces(tmp_path):
     runtime = thintensor_b200.load_model(folder, dtype="bf16")
     tokens = token_ids(4099, 4800, 35)
     places = [0, 2047, 2048, 4095, 4700, 4799]
-    assert api.gemm_tcgen05_accumulate_pays(4800, 2048, 2048) and not api.gemm_tcgen05_accumulate_pays(2048, 2048, 8192)
+    assert api.gemm_tcgen05_accumulate_pays(4800, 2048, 2048) and not api.gemm_tcgen05_accumulate_pays(1024, 2048, 8192)
     results = []
-    for piece in (8192, 2048):
+    for piece in (8192, 1024):
         engine = runtime.new_engine(max_tokens=4864, max_sequences=1, max_step_tokens=piece)
         slot = engine.open()
         results.append(engine.step([Entry(slot, tokens, places)]).double().cpu())

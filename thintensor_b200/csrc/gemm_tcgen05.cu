@@ -89,6 +89,7 @@ struct Args {
     int k_blocks_per_split;
     int up_row_offset;       // SWIGLU: row of w where the up projection starts (= features of the output)
     int accumulate;          // persistent and pair kernels, plain form: out += product instead of out = product
+    int bulk_out;            // persistent and pair kernels, plain form: the tile leaves through shared memory and tiled copies (map_out is valid)
     QkvRope rope;            // qkv form only
     int rope_head_dim;       // 64 or 128
     int undelivered_bytes;   // 0 in every real call; tests: the first stage's barrier expects this many bytes that no copy brings
@@ -418,6 +419,45 @@ __device__ __forceinline__ void store_accumulator(uint32_t lane_addr, int token,
     }
 }
 
+// The plain form's epilogue through shared memory: a warp's 32 rows x 32 columns of the accumulator go into a 4 KB
+// slab (swizzled as the map says, so that the lanes, each with a row of its own, spread over all banks) and leave it
+// as one tiled copy, which stores them, or adds them to what the output holds, in whole lines.  With stores from
+// registers every lane wrote 16 bytes of another row: 32 sectors an instruction, 10,200 cycles for a tile of
+// 128 x 256, and the accumulate form had to read the old values first.  The warp alternates between two slabs;
+// `round` counts its copies so far (the slab a copy two rounds back read from is free once all but the latest
+// group have read).  The copies clip what hangs over the matrix's edges.  Warp-collective.
+template <int WIDE>
+__device__ __forceinline__ void store_accumulator_bulk(uint32_t lane_addr, int first_token, int f_base, int slice, const Args& args,
+                                                       const CUtensorMap* map_out, uint8_t* slabs, int lane, int& round) {
+    const float* bias = slice == 0 ? args.bias : nullptr;                      // a later k-slice: its own plane of the output, no bias
+#pragma unroll 1
+    for (int c = 0; c < WIDE; c += 32) {
+        float v[32];
+        tmem_load32(lane_addr + c, v);
+        const int f0 = f_base + c;
+        if (first_token >= args.tokens || f0 >= args.features) continue;       // the same for the whole warp
+        if (bias) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) if (f0 + e < args.features) v[e] += bias[f0 + e];
+        }
+        uint8_t* slab = slabs + (round & 1) * 4096;
+        ++round;
+        if (lane == 0) bulk_wait_group_read<1>();
+        __syncwarp();
+#pragma unroll
+        for (int piece = 0; piece < 8; ++piece)
+            *reinterpret_cast<float4*>(slab + lane * 128 + ((piece ^ (lane & 7)) << 4)) =
+                make_float4(v[4 * piece], v[4 * piece + 1], v[4 * piece + 2], v[4 * piece + 3]);
+        fence_async_shared();
+        __syncwarp();
+        if (lane == 0) {
+            if (args.accumulate) tma_reduce_add_3d(map_out, smem_u32(slab), f0, first_token, slice);
+            else tma_store_3d(map_out, smem_u32(slab), f0, first_token, slice);
+            bulk_commit_group();
+        }
+    }
+}
+
 // The qkv form's epilogue for one thread = one token's row of a 128 x WIDE accumulator, whose WIDE / HD
 // heads each lie inside the tile (HD = 64 or 128).  A head's rotation pairs dimension d with d + HD / 2:
 // the two come from tensor-memory chunks j and j + HD / 64 of the head, so a thread holds both.  The
@@ -553,12 +593,13 @@ __device__ __forceinline__ bool qkv_row_epilogue(uint32_t acc_bar, uint32_t pari
 // boundaries; the epilogue warps drain accumulator (j & 1) of the CTA's j-th tile while the
 // products of tile j + 1 fill the other one.
 constexpr int P_STAGES = 4;
+constexpr int OUT_SLAB_BYTES = 4 * 2 * 4096;     // plain form of the persistent and pair kernels: two slabs of 32 x 32 float32 for each epilogue warp
 constexpr int P_STAGE_BYTES = BM * BK * 2 + 256 * BK * 2;       // A tile + 256 rows of B
 
 template <int FORM, int WIDE = 256>
 __global__ void __launch_bounds__(THREADS)
-gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Args args,
-                               int tiles_m, int tiles_total, int splits) {
+gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                               const __grid_constant__ CUtensorMap map_out, const Args args, int tiles_m, int tiles_total, int splits) {
     constexpr bool dual = FORM == TOKENS_ON_M_SWIGLU;
     static_assert(WIDE == 256 || (!dual && WIDE == 128), "the SwiGLU form has no narrower tile");
     constexpr int TILE_N = dual ? 128 : WIDE;                   // output features per tile
@@ -668,11 +709,14 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
         tt_pdl_wait();
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
+        const bool bulk_out = FORM == TOKENS_ON_M && args.bulk_out;
+        uint8_t* slabs = smem + (size_t)P_STAGES * P_STAGE_BYTES + quarter * OUT_SLAB_BYTES / 4;     // plain form only
+        int round = 0;
         for (int j = 0; j < my_tiles; ++j) {
             const int buf = j & 1;
             const int item = (int)blockIdx.x + j * (int)gridDim.x, tile = item % tiles_total, slice = item / tiles_total;
             const int token = (tile % tiles_m) * BM + row, f_base = (tile / tiles_m) * TILE_N;
-            if (!dual) prefetch_output_row(token, f_base, args);
+            if (!dual && !bulk_out) prefetch_output_row(token, f_base, args);
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256;
             const uint32_t acc_bar = smem_u32(&acc_full[buf]), acc_parity = (uint32_t)((j >> 1) & 1);
             bool ok;
@@ -689,6 +733,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
             }
             if constexpr (FORM == TOKENS_ON_M_QKV) {
                 // stored by qkv_row_epilogue
+            } else if (bulk_out) {
+                if constexpr (FORM == TOKENS_ON_M) store_accumulator_bulk<WIDE>(lane_addr, token - lane, f_base, slice, args, &map_out, slabs, lane, round);
             } else if (dual || slice == 0) {
                 store_accumulator<dual, WIDE>(lane_addr, token, f_base, args);
             } else {                                            // a later k-slice: its own plane of the output, no bias
@@ -702,6 +748,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));
         }
+        if (bulk_out && lane == 0) bulk_wait_group_read<0>();   // the slabs stay until the last copies have read them
     }
     fence_before_sync();
     __syncthreads();
@@ -730,8 +777,8 @@ constexpr int PAIR_STAGE_BYTES = BM * BK * 2 + 128 * BK * 2;    // 128 rows of A
 // is a third full, or 128 tiles of 192, two rounds of three quarters the length.
 template <int FORM, int WIDE = 256>
 __global__ void __launch_bounds__(THREADS)
-gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Args args,
-                         int tiles_m, int tiles_total) {
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const __grid_constant__ CUtensorMap map_out, const Args args, int tiles_m, int tiles_total) {
     constexpr bool dual = FORM == TOKENS_ON_M_SWIGLU;
     static_assert(WIDE == 256 || (FORM == TOKENS_ON_M_QKV && WIDE == 192), "only the qkv form has a narrower tile");
     constexpr int TILE_N = dual ? 128 : WIDE;                   // output features per tile
@@ -825,11 +872,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         tt_pdl_wait();
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
+        const bool bulk_out = FORM == TOKENS_ON_M && args.bulk_out;
+        uint8_t* slabs = smem + (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + quarter * OUT_SLAB_BYTES / 4;   // plain form only
+        int round = 0;
         for (int j = 0; j < my_tiles; ++j) {
             const int buf = j & 1;
             const int tile = pair + j * n_pairs;
             const int token = (tile % tiles_m) * 2 * BM + rank * BM + row, f_base = (tile / tiles_m) * TILE_N;
-            if (!dual) prefetch_output_row(token, f_base, args);
+            if (!dual && !bulk_out) prefetch_output_row(token, f_base, args);
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256;
             const uint32_t acc_bar = smem_u32(&acc_full[buf]), acc_parity = (uint32_t)((j >> 1) & 1);
             bool ok;
@@ -845,12 +895,18 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 if (lane == 0) atomicOr(args.status, TT_STATUS_WAIT_EXPIRED);
                 break;
             }
-            if constexpr (FORM != TOKENS_ON_M_QKV) store_accumulator<dual>(lane_addr, token, f_base, args);     // the qkv form has stored its row
+            if constexpr (FORM == TOKENS_ON_M) {
+                if (bulk_out) store_accumulator_bulk<WIDE>(lane_addr, token - lane, f_base, 0, args, &map_out, slabs, lane, round);
+                else store_accumulator<dual>(lane_addr, token, f_base, args);
+            } else if constexpr (FORM != TOKENS_ON_M_QKV) {
+                store_accumulator<dual>(lane_addr, token, f_base, args);     // the qkv form has stored its row
+            }
             // this warp is done with the accumulator: tell the issuer, who sits in the even CTA
             fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_even_cta(smem_u32(&acc_empty[buf]));
         }
+        if (bulk_out && lane == 0) bulk_wait_group_read<0>();   // the slabs stay until the last copies have read them
     }
     fence_before_sync();
     __syncthreads();
@@ -882,9 +938,9 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const Args& args,
 }
 
 template <int FORM, int WIDE = 256>
-int launch_persistent(const CUtensorMap& map_a, const CUtensorMap& map_b, const Args& args, int tiles_m, int tiles_total,
+int launch_persistent(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_out, const Args& args, int tiles_m, int tiles_total,
                       int splits, cudaStream_t stream) {
-    constexpr int shared = P_STAGE_BYTES * P_STAGES + 1024;
+    constexpr int shared = P_STAGE_BYTES * P_STAGES + 1024 + (FORM == TOKENS_ON_M ? OUT_SLAB_BYTES : 0);
     static bool configured = false;
     static int sm_count = 0;
     auto kernel = gemm_tcgen05_persistent_kernel<FORM, WIDE>;
@@ -898,13 +954,14 @@ int launch_persistent(const CUtensorMap& map_a, const CUtensorMap& map_b, const 
     }
     const int items = tiles_total * splits;
     const int ctas = items < sm_count ? items : sm_count;
-    tt_launch_pdl(kernel, dim3(ctas), dim3(THREADS), shared, stream, map_a, map_b, args, tiles_m, tiles_total, splits);
+    tt_launch_pdl(kernel, dim3(ctas), dim3(THREADS), shared, stream, map_a, map_b, map_out, args, tiles_m, tiles_total, splits);
     return (int)cudaGetLastError();
 }
 
 template <int FORM, int WIDE = 256>
-int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const Args& args, int tiles_m, int tiles_total, cudaStream_t stream) {
-    constexpr int shared = PAIR_STAGE_BYTES * PAIR_STAGES + 1024;
+int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_out, const Args& args, int tiles_m, int tiles_total,
+                cudaStream_t stream) {
+    constexpr int shared = PAIR_STAGE_BYTES * PAIR_STAGES + 1024 + (FORM == TOKENS_ON_M ? OUT_SLAB_BYTES : 0);
     static bool configured = false;
     static int sm_count = 0;
     auto kernel = gemm_tcgen05_pair_kernel<FORM, WIDE>;
@@ -931,7 +988,7 @@ int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const Args& 
     attribute[1].val.clusterDim.z = 1;
     config.attrs = attribute;
     config.numAttrs = 2;
-    const cudaError_t err = cudaLaunchKernelEx(&config, kernel, map_a, map_b, args, tiles_m, tiles_total);
+    const cudaError_t err = cudaLaunchKernelEx(&config, kernel, map_a, map_b, map_out, args, tiles_m, tiles_total);
     return err != cudaSuccess ? (int)err : (int)cudaGetLastError();
 }
 
@@ -1000,10 +1057,10 @@ extern "C" int tt_gemm_tcgen05_qkv_rope(const void* x, long long ldx, const void
     if (tokens < PAIR_MIN_TOKENS) {
         if (qkv_rope_tile_width(tokens, features) == 128) {
             if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, features, k, ldw, 128)) return -1;
-            return launch_persistent<TOKENS_ON_M_QKV, 128>(map_a, map_b, args, tiles_m, tiles_m * ((features + 127) / 128), 1, stream);
+            return launch_persistent<TOKENS_ON_M_QKV, 128>(map_a, map_b, map_a, args, tiles_m, tiles_m * ((features + 127) / 128), 1, stream);
         }
         if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, features, k, ldw, 256)) return -1;
-        return launch_persistent<TOKENS_ON_M_QKV>(map_a, map_b, args, tiles_m, tiles_m * ((features + 255) / 256), 1, stream);
+        return launch_persistent<TOKENS_ON_M_QKV>(map_a, map_b, map_a, args, tiles_m, tiles_m * ((features + 255) / 256), 1, stream);
     }
     const int pair_tiles_m = (tokens + 2 * BM - 1) / (2 * BM);
     if (head_dim == 64) {
@@ -1014,11 +1071,11 @@ extern "C" int tt_gemm_tcgen05_qkv_rope(const void* x, long long ldx, const void
         auto cost = [&](int wide) { return ((long long)pair_tiles_m * ((features + wide - 1) / wide) + pairs - 1) / pairs * wide; };
         if (cost(192) < cost(256)) {
             if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, features, k, ldw, 96)) return -1;
-            return launch_pair<TOKENS_ON_M_QKV, 192>(map_a, map_b, args, pair_tiles_m, pair_tiles_m * ((features + 191) / 192), stream);
+            return launch_pair<TOKENS_ON_M_QKV, 192>(map_a, map_b, map_a, args, pair_tiles_m, pair_tiles_m * ((features + 191) / 192), stream);
         }
     }
     if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, features, k, ldw, 128)) return -1;
-    return launch_pair<TOKENS_ON_M_QKV>(map_a, map_b, args, pair_tiles_m, pair_tiles_m * ((features + 255) / 256), stream);
+    return launch_pair<TOKENS_ON_M_QKV>(map_a, map_b, map_a, args, pair_tiles_m, pair_tiles_m * ((features + 255) / 256), stream);
 }
 
 // How many tokens the features-on-m form takes at most.
@@ -1046,6 +1103,7 @@ extern "C" int tt_gemm_tcgen05(const void* x, long long ldx, const void* w, long
     args.up_row_offset = features; args.status = status;
     args.accumulate = form == 2 ? 1 : 0;
     args.undelivered_bytes = undelivered_bytes_for_tests;
+    args.bulk_out = 0;
     CUtensorMap map_a, map_b;
     const int tiles_m = (tokens + BM - 1) / BM;
     if (form == 2 && !(tokens > 128 && tiles_m * ((features + 255) / 256) >= 8 && splits == 1)) return (int)cudaErrorInvalidValue;
@@ -1065,10 +1123,10 @@ extern "C" int tt_gemm_tcgen05(const void* x, long long ldx, const void* w, long
             }
         }
         const int tiles = tiles_m * ((features + 127) / 128);
-        if (tiles >= 8 && tokens < PAIR_MIN_TOKENS_SWIGLU) return launch_persistent<TOKENS_ON_M_SWIGLU>(map_a, map_b, args, tiles_m, tiles, 1, stream);
+        if (tiles >= 8 && tokens < PAIR_MIN_TOKENS_SWIGLU) return launch_persistent<TOKENS_ON_M_SWIGLU>(map_a, map_b, map_a, args, tiles_m, tiles, 1, stream);
         if (tiles >= 8) {
             const int pair_tiles_m = (tokens + 2 * BM - 1) / (2 * BM);
-            return launch_pair<TOKENS_ON_M_SWIGLU>(map_a, map_b, args, pair_tiles_m, pair_tiles_m * ((features + 127) / 128), stream);
+            return launch_pair<TOKENS_ON_M_SWIGLU>(map_a, map_b, map_a, args, pair_tiles_m, pair_tiles_m * ((features + 127) / 128), stream);
         }
         const dim3 grid((features + 127) / 128, tiles_m, 1);
         return launch<TOKENS_ON_M_SWIGLU, 128, 4>(map_a, map_b, args, grid, stream);
@@ -1076,6 +1134,11 @@ extern "C" int tt_gemm_tcgen05(const void* x, long long ldx, const void* w, long
     // no slice may be empty in the persistent kernel (the generic kernel below writes zeros for one)
     const bool slices_full = (long long)(splits - 1) * args.k_blocks_per_split < k_blocks;
     if (tokens > 128 && tiles_m * ((features + 255) / 256) >= 8 && (splits == 1 || (tokens < PAIR_MIN_TOKENS && slices_full))) {
+        // The tiles leave through shared memory and tiled copies where those can write the output's rows: 16-byte aligned
+        // and a multiple of 16 bytes apart (the k-slices' planes too).
+        CUtensorMap map_out = {};
+        args.bulk_out = (ld_out % 4) == 0 && (splits == 1 || (split_stride % 4) == 0) && (((uintptr_t)out) & 15) == 0 &&
+                        make_map_f32_out(&map_out, out, splits, tokens, features, ld_out, split_stride) ? 1 : 0;
         // from 8 tiles of 128 x 256 on the persistent kernel wins (measured); fewer tiles than SMs are cut along k
         if (tokens < PAIR_MIN_TOKENS) {
             // Where tiles of 256 features would fill at most an eighth of the SMs (prompts of up to 256 tokens at the 1B
@@ -1088,14 +1151,14 @@ extern "C" int tt_gemm_tcgen05(const void* x, long long ldx, const void* w, long
             if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return -1;
             if (form == 0 && tiles_m * ((features + 255) / 256) * 8 <= sm_count) {
                 if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, features, k, ldw, 128)) return -1;
-                return launch_persistent<TOKENS_ON_M, 128>(map_a, map_b, args, tiles_m, tiles_m * ((features + 127) / 128), splits, stream);
+                return launch_persistent<TOKENS_ON_M, 128>(map_a, map_b, map_out, args, tiles_m, tiles_m * ((features + 127) / 128), splits, stream);
             }
             if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, features, k, ldw, 256)) return -1;
-            return launch_persistent<TOKENS_ON_M>(map_a, map_b, args, tiles_m, tiles_m * ((features + 255) / 256), splits, stream);
+            return launch_persistent<TOKENS_ON_M>(map_a, map_b, map_out, args, tiles_m, tiles_m * ((features + 255) / 256), splits, stream);
         }
         if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, features, k, ldw, 128)) return -1;
         const int pair_tiles_m = (tokens + 2 * BM - 1) / (2 * BM);
-        return launch_pair<TOKENS_ON_M>(map_a, map_b, args, pair_tiles_m, pair_tiles_m * ((features + 255) / 256), stream);
+        return launch_pair<TOKENS_ON_M>(map_a, map_b, map_out, args, pair_tiles_m, pair_tiles_m * ((features + 255) / 256), stream);
     }
     if (tokens > 128) {
         if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, features, k, ldw, 128)) return -1;

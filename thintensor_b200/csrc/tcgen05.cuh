@@ -72,6 +72,23 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
 }
 
+// Tiled copies from shared memory to a tensor in global memory, as a plain store and as an addition to what is
+// there (element type and swizzle come from the map); parts of the box outside the tensor are not written.  The x
+// coordinate times the element size must be a multiple of 16 bytes and no coordinate may be negative.  The copies of
+// a thread are grouped by bulk_commit_group; bulk_wait_group_read<N> returns when all but its N latest groups have
+// read their shared memory, which may then be written again (and must happen before the CTA ends).
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, uint32_t src, int x, int y, int z) {
+    asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+
 // Tensor memory: allocate (one whole warp; columns a power of two >= 32), free (the same warp).
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
@@ -257,6 +274,20 @@ inline bool make_map(CUtensorMap* map, const void* base, int rank, const cuuint6
     const cuuint32_t elem[3] = {1, 1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// `planes` float32 matrices [rows, cols] with `ld` elements between rows and `plane_stride` between matrices (both
+// multiples of 4), written in boxes of 32 x 32 of one matrix with the 128-byte swizzle: the 16-byte piece c of box
+// row r lies at piece c ^ (r & 7) of its 128 bytes of shared memory.
+inline bool make_map_f32_out(CUtensorMap* map, void* base, long long planes, long long rows, long long cols, long long ld, long long plane_stride) {
+    EncodeTiled fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)planes};
+    const cuuint64_t strides[2] = {(cuuint64_t)ld * 4, (cuuint64_t)(planes > 1 ? plane_stride : rows * ld) * 4};
+    const cuuint32_t box[3] = {32, 32, 1};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 }  // namespace tc

@@ -503,14 +503,17 @@ def gemm_tcgen05_accumulates(tokens: int, features: int, k: int, sms: int | None
 
 
 def gemm_tcgen05_accumulate_pays(tokens: int, features: int, k: int, sms: int | None = None) -> bool:
-    """Whether adding into the output inside the kernel is also the faster way: only where every CTA
-    (or CTA pair) has at least two tiles, so that a tile's epilogue, which now waits for the old
-    values, runs under the next tile's products.  Measured on a B200 with the 1B shape's output and
-    down projections: 2,048 tokens (one tile per CTA pair) 5.19 -> 5.27 ms per prefill, 8,192 tokens
-    (3.5 tiles per pair) 24.45 -> 24.13 ms."""
+    """Whether adding into the output inside the kernel is also the faster way.  Where the output's rows are a multiple
+    of 16 bytes the tiles are added by tiled copies from shared memory, which read nothing back, and the norm after the
+    product then reads the stream alone: taken wherever it can be (measured on a B200 with the 1B shape's output and down
+    projections, whole prefill: 2,048 tokens 3.98 -> 3.91 ms, 4,096 tokens 8.62 -> 8.51).  Other widths add from
+    registers after reading the old values, which pays only where every CTA (or CTA pair) has at least two tiles, so
+    that a tile's epilogue runs under the next tile's products."""
     sms = sm_count() if sms is None else sms
     if not gemm_tcgen05_accumulates(tokens, features, k, sms):
         return False
+    if features % 4 == 0:
+        return True
     if tokens >= PAIR_TOKENS:
         return -(-tokens // 256) * -(-features // 256) >= 2 * (sms // 2)
     return -(-tokens // 128) * -(-features // 256) >= 2 * sms
