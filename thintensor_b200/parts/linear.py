@@ -57,7 +57,8 @@ class Linear:
     def delta(self, ctx, x: torch.Tensor, name: str) -> Delta:
         """The product as an addition to the residual stream.  Where the step offers the stream
         (``ctx.residual``) and the tensor-core kernel can add into its output at no cost of its own
-        (long prompts), the product is added there at once and the delta is empty; otherwise the delta holds the product's k-slices."""
+        (prompts whose k is not cut into slices), the product is added there at once and the delta is
+        empty; otherwise the delta holds the product's k-slices."""
         residual = getattr(ctx, "residual", None)
         if (residual is not None and residual.shape == (x.shape[0], self.out_features) and api.gemm_tcgen05_usable(x, self.weight)
                 and api.gemm_tcgen05_accumulate_pays(x.shape[0], self.out_features, self.in_features)):
