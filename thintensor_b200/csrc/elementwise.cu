@@ -30,8 +30,23 @@ __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __r
         return;
     }
     const TW* row = table + (size_t)id * hidden;
+    float* out = residual + (size_t)t * hidden;
+    if constexpr (sizeof(TW) == 2) {
+        // rows of whole 16-byte pieces: eight numbers a load, two 16-byte stores
+        if ((hidden & 7) == 0 && (((uintptr_t)table | (uintptr_t)residual) & 15) == 0) {
+            for (int j = 8 * threadIdx.x; j < hidden; j += 8 * blockDim.x) {
+                const uint4 raw = __ldg(reinterpret_cast<const uint4*>(row + j));
+                const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+                const float2 a = __bfloat1622float2(pairs[0]), b = __bfloat1622float2(pairs[1]);
+                const float2 c = __bfloat1622float2(pairs[2]), d = __bfloat1622float2(pairs[3]);
+                *reinterpret_cast<float4*>(out + j) = make_float4(a.x * scale, a.y * scale, b.x * scale, b.y * scale);
+                *reinterpret_cast<float4*>(out + j + 4) = make_float4(c.x * scale, c.y * scale, d.x * scale, d.y * scale);
+            }
+            return;
+        }
+    }
     for (int j = threadIdx.x; j < hidden; j += blockDim.x)
-        residual[(size_t)t * hidden + j] = tt_to_float(row[j]) * scale;
+        out[j] = tt_to_float(row[j]) * scale;
 }
 
 extern "C" int tt_embed_gather(const void* table, int table_dtype, const int* tokens, float* residual, int n_tokens,
