@@ -139,3 +139,21 @@ def test_sequences_come_and_go():
     with pytest.raises(CacheError, match="cache is full"):
         d = cache.alloc_slot()
         cache.reserve(d, 64 * 9)
+
+
+def test_workspace_zeroes_its_zeroed_buffers_again():
+    """Buffers handed out zeroed (tickets, flags) are left zero by their users; after a kernel that gave up they are
+    zeroed again, and only they."""
+    import torch
+
+    from thintensor_b200.engine.context import Workspace
+
+    workspace = Workspace(torch.device("cpu"))
+    flags = workspace.get_zeroed("flags", (16,), torch.int32)
+    plain = workspace.get("scratch", (16,), torch.int32)
+    assert int(flags.abs().sum()) == 0
+    flags[3] = 1
+    plain.fill_(7)
+    workspace.zero_again()
+    assert int(flags.abs().sum()) == 0 and int(plain.sum()) == 7 * 16
+    assert workspace.get_zeroed("flags", (16,), torch.int32).data_ptr() == flags.data_ptr()       # still the same memory

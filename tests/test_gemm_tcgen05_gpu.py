@@ -111,15 +111,54 @@ def test_tiled_copies_of_the_output_stop_at_its_edges(accumulate):
     from ctypes import c_int, c_longlong, c_void_p
     from thintensor_b200.kernels import build
     fn = build.load("gemm_tcgen05").tt_gemm_tcgen05
-    fn.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+    fn.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                   c_void_p, c_longlong]
     fn.restype = c_int
     assert fn(x.data_ptr(), k, w.data_ptr(), k, None, whole.data_ptr(), whole.stride(0), 0, tokens, features, k, 1, 2 if accumulate else 0,
-              status.data_ptr(), torch.cuda.current_stream().cuda_stream) == 0
+              status.data_ptr(), torch.cuda.current_stream().cuda_stream, None, 0) == 0
     torch.cuda.synchronize()
     assert int(status.item()) == 0
     want = x.double() @ w.double().T + (7.0 if accumulate else 0.0)
     torch.testing.assert_close(whole[:tokens, :features].double(), want, rtol=1e-4, atol=1e-4 * k ** 0.5)
     assert bool((whole[tokens:] == 7.0).all()) and bool((whole[:, features:] == 7.0).all())
+
+
+@pytest.mark.parametrize("tokens,features,k,accumulate", [
+    (2560, 2048, 2048, False),   # 80 tiles for 74 pairs (two rounds, the second nearly empty): every pair a run of 34 or 35 of the 2,560 k-blocks
+    (2560, 2048, 8192, True),    # the same with long k, added into the output
+    (2560, 2050, 1024, False),   # rows of 2,050 floats: no tiled copies, so k is not dealt out and the shares are left alone
+    (2500, 2052, 1024, True),    # 10 x 9 = 90 tiles of 16 k-blocks: runs of 19 or 20 k-blocks over two or three tiles; ragged edges and a bias
+    (2100, 1100, 3072, False),   # 9 x 5 = 45 tiles: runs of 29 of a tile's 48 k-blocks, tiles shared by two or three pairs
+    (2048, 2048, 2048, False),   # 64 tiles fill most of one round: whole tiles, the shares are left alone
+])
+def test_k_dealt_out_among_the_cta_pairs(tokens, features, k, accumulate):
+    """With scratch memory for shares the CTA pairs' plain form deals the tiles' k-blocks out evenly where whole tiles
+    would leave pairs idle: the same product, the flags zero again afterwards, and the same bits from call to call
+    (the shares are added in a fixed order)."""
+    from thintensor_b200.kernels import api
+
+    x, w = randn(tokens, k, seed=41), randn(features, k, seed=42)
+    bias = torch.randn(features, device=DEV) if features % 3 == 0 else None
+    shares = torch.zeros(api.gemm_tcgen05_shares_words(), dtype=torch.int32, device=DEV)
+    flags = shares[-(shares.numel() // (32 * 256 + 1)):]
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    before = torch.randn(tokens, features, device=DEV) if accumulate else None
+    results = []
+    for _ in range(3):
+        out = before.clone().unsqueeze(0) if accumulate else torch.full((1, tokens, features), float("nan"), dtype=torch.float32, device=DEV)
+        api.gemm_tcgen05(x, w, bias, out, status, accumulate=accumulate, shares=shares)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        assert int(flags.abs().sum().item()) == 0, "a flag was left set"
+        results.append(out)
+    assert torch.equal(results[0], results[1]) and torch.equal(results[0], results[2])
+    want = x.double() @ w.double().T + (bias.double() if bias is not None else 0) + (before.double() if accumulate else 0)
+    assert torch.isfinite(results[0]).all()
+    torch.testing.assert_close(results[0][0].double(), want, rtol=1e-4, atol=1e-4 * k ** 0.5)
+    if features % 4 == 0 and tokens != 2048:
+        assert int(shares[:-flags.numel()].abs().sum().item()) != 0, "k was not dealt out"
+    else:
+        assert int(shares.abs().sum().item()) == 0
 
 
 def test_split_policy_and_refusals():

@@ -90,6 +90,7 @@ struct Args {
     int up_row_offset;       // SWIGLU: row of w where the up projection starts (= features of the output)
     int accumulate;          // persistent and pair kernels, plain form: out += product instead of out = product
     int bulk_out;            // persistent and pair kernels, plain form: the tile leaves through shared memory and tiled copies (map_out is valid)
+    float* shares;           // pair kernel, plain form: where CTA pairs leave their shares of tiles that several pairs work on (null: every tile has one pair)
     QkvRope rope;            // qkv form only
     int rope_head_dim;       // 64 or 128
     int undelivered_bytes;   // 0 in every real call; tests: the first stage's barrier expects this many bytes that no copy brings
@@ -428,7 +429,8 @@ __device__ __forceinline__ void store_accumulator(uint32_t lane_addr, int token,
 // group have read).  The copies clip what hangs over the matrix's edges.  Warp-collective.
 template <int WIDE>
 __device__ __forceinline__ void store_accumulator_bulk(uint32_t lane_addr, int first_token, int f_base, int slice, const Args& args,
-                                                       const CUtensorMap* map_out, uint8_t* slabs, int lane, int& round) {
+                                                       const CUtensorMap* map_out, uint8_t* slabs, int lane, int& round,
+                                                       const float* share_a = nullptr, const float* share_b = nullptr) {
     const float* bias = slice == 0 ? args.bias : nullptr;                      // a later k-slice: its own plane of the output, no bias
 #pragma unroll 1
     for (int c = 0; c < WIDE; c += 32) {
@@ -436,6 +438,15 @@ __device__ __forceinline__ void store_accumulator_bulk(uint32_t lane_addr, int f
         tmem_load32(lane_addr + c, v);
         const int f0 = f_base + c;
         if (first_token >= args.tokens || f0 >= args.features) continue;       // the same for the whole warp
+        // other pairs' shares of this tile's k (see store_share): added in a fixed order, first the one next in k
+        if (share_a) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] += __ldcg(share_a + (c + e) * 32 + lane);
+        }
+        if (share_b) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] += __ldcg(share_b + (c + e) * 32 + lane);
+        }
         if (bias) {
 #pragma unroll
             for (int e = 0; e < 32; ++e) if (f0 + e < args.features) v[e] += bias[f0 + e];
@@ -456,6 +467,49 @@ __device__ __forceinline__ void store_accumulator_bulk(uint32_t lane_addr, int f
             bulk_commit_group();
         }
     }
+}
+
+// A warp's 32 rows of an accumulator that holds only a share of the tile's k: column by column into the warp's own
+// 32 KB of scratch memory, the 32 lanes' numbers of a column side by side (whole lines a store; the layout is nobody
+// else's business).  The pair that holds the tile's first k-blocks adds it to its own share (store_accumulator_bulk).
+template <int WIDE>
+__device__ __forceinline__ void store_share(uint32_t lane_addr, float* share, int lane) {
+#pragma unroll 1
+    for (int c = 0; c < WIDE; c += 32) {
+        float v[32];
+        tmem_load32(lane_addr + c, v);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) __stcg(share + (c + e) * 32 + lane, v[e]);
+    }
+}
+
+// The work of CTA pair `pair` of `n_pairs` when the tiles' k-blocks are dealt out evenly (units = tiles * k-blocks in
+// tile order, every pair a contiguous run of them): item j of the pair is k-blocks kb0 .. kb1 - 1 of tile `tile`.
+// Only a pair's first item can start inside a tile (kb0 > 0: a share that the tile's first pair will add to its
+// own), only its last can end inside one (kb0 == 0, kb1 < all: this pair writes the tile, after the shares of the
+// pairs behind it have arrived).
+struct KRun {
+    long long begin, end;       // units
+    int k_blocks;               // per tile
+    __device__ int items() const { return end > begin ? (int)((end - 1) / k_blocks - begin / k_blocks) + 1 : 0; }
+    __device__ void item(int j, int& tile, int& kb0, int& kb1) const {
+        const long long t = begin / k_blocks + j;
+        tile = (int)t;
+        kb0 = j == 0 ? (int)(begin - t * k_blocks) : 0;
+        kb1 = end < (t + 1) * k_blocks ? (int)(end - t * k_blocks) : k_blocks;
+    }
+};
+__device__ __forceinline__ KRun k_run_of(int pair, int n_pairs, int tiles_total, int k_blocks) {
+    const long long units = (long long)tiles_total * k_blocks;
+    return KRun{units * pair / n_pairs, units * (pair + 1) / n_pairs, k_blocks};
+}
+constexpr int SHARE_FLOATS = 32 * 256;                   // one epilogue warp's share of a 256-wide tile
+// scratch memory of pair p, CTA r, epilogue warp w: its share, and behind all shares one flag word each
+__device__ __forceinline__ float* share_of(float* shares, int pair, int rank, int quarter) {
+    return shares + ((size_t)(pair * 2 + rank) * 4 + quarter) * SHARE_FLOATS;
+}
+__device__ __forceinline__ unsigned* share_flag_of(float* shares, int n_pairs, int pair, int rank, int quarter) {
+    return reinterpret_cast<unsigned*>(shares + (size_t)n_pairs * 8 * SHARE_FLOATS) + (pair * 2 + rank) * 4 + quarter;
 }
 
 // The qkv form's epilogue for one thread = one token's row of a 128 x WIDE accumulator, whose WIDE / HD
@@ -795,7 +849,15 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const int rank = (int)cluster.block_rank();                 // 0: the CTA that issues
     const int pair = (int)blockIdx.x >> 1, n_pairs = (int)gridDim.x >> 1;
     const int n_kb = (args.k + BK - 1) / BK;
-    const int my_tiles = pair < tiles_total ? (tiles_total - pair + n_pairs - 1) / n_pairs : 0;
+    // A pair's items: whole tiles pair, pair + n_pairs, ... or, where the launcher gave scratch memory for shares (plain
+    // form, fewer whole rounds of tiles than would fill the pairs), its run of the tiles' k-blocks dealt out evenly.
+    const bool dealt = FORM == TOKENS_ON_M && args.shares != nullptr;
+    const KRun run = k_run_of(pair, n_pairs, tiles_total, n_kb);
+    const int my_tiles = dealt ? run.items() : (pair < tiles_total ? (tiles_total - pair + n_pairs - 1) / n_pairs : 0);
+    auto item = [&](int j, int& tile, int& kb0, int& kb1) {
+        if (dealt) run.item(j, tile, kb0, kb1);
+        else { tile = pair + j * n_pairs; kb0 = 0; kb1 = n_kb; }
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < PAIR_STAGES; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
@@ -816,11 +878,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             long long it = 0;
             bool ok = true;
             for (int j = 0; j < my_tiles && ok; ++j) {
-                const int tile = pair + j * n_pairs;
+                int tile, kb0, kb1;
+                item(j, tile, kb0, kb1);
                 const int a_row = (tile % tiles_m) * 2 * BM + rank * BM;
                 const int b_row = dual ? (rank == 0 ? 0 : args.up_row_offset) + (tile / tiles_m) * TILE_N
                                        : (tile / tiles_m) * TILE_N + rank * B_ROWS;
-                for (int i = 0; i < n_kb; ++i, ++it) {
+                for (int i = kb0; i < kb1; ++i, ++it) {
                     const int s = (int)(it % PAIR_STAGES);
                     if (!mbar_wait(smem_u32(&empty_bar[s]), (uint32_t)(((it / PAIR_STAGES) & 1) ^ 1))) {
                         atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; break;
@@ -850,7 +913,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 }
                 fence_after_sync();
                 const uint32_t acc_addr = tmem_base + buf * 256;
-                for (int i = 0; i < n_kb; ++i, ++it) {
+                int tile, kb0, kb1;
+                item(j, tile, kb0, kb1);
+                for (int i = kb0; i < kb1; ++i, ++it) {
                     const int s = (int)(it % PAIR_STAGES);
                     if (!mbar_wait(smem_u32(&full_bar[s]), (uint32_t)((it / PAIR_STAGES) & 1))) {
                         atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; break;
@@ -861,7 +926,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #pragma unroll
                     for (int kk = 0; kk < BK / UMMA_K; ++kk)
                         umma_bf16_pair(acc_addr, smem_desc(a_addr + kk * UMMA_K * 2), smem_desc(b_addr + kk * UMMA_K * 2), idesc,
-                                       (i > 0 || kk > 0) ? 1u : 0u);
+                                       (i > kb0 || kk > 0) ? 1u : 0u);
                     umma_commit_pair(smem_u32(&empty_bar[s]), 3);          // the stage is free in both CTAs
                 }
                 if (ok) umma_commit_pair(smem_u32(&acc_full[buf]), 3);     // both CTAs' halves of the accumulator are complete
@@ -877,7 +942,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         int round = 0;
         for (int j = 0; j < my_tiles; ++j) {
             const int buf = j & 1;
-            const int tile = pair + j * n_pairs;
+            int tile, kb0, kb1;
+            item(j, tile, kb0, kb1);
             const int token = (tile % tiles_m) * 2 * BM + rank * BM + row, f_base = (tile / tiles_m) * TILE_N;
             if (!dual && !bulk_out) prefetch_output_row(token, f_base, args);
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256;
@@ -896,8 +962,40 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 break;
             }
             if constexpr (FORM == TOKENS_ON_M) {
-                if (bulk_out) store_accumulator_bulk<WIDE>(lane_addr, token - lane, f_base, 0, args, &map_out, slabs, lane, round);
-                else store_accumulator<dual>(lane_addr, token, f_base, args);
+                if (dealt && kb0 > 0) {
+                    // a share of a tile whose first k-blocks another pair has: into scratch memory, then the flag
+                    store_share<WIDE>(lane_addr, share_of(args.shares, pair, rank, quarter), lane);
+                    __threadfence();
+                    __syncwarp();
+                    if (lane == 0) flag_release(share_flag_of(args.shares, n_pairs, pair, rank, quarter), 1u);
+                } else if (dealt && kb1 < n_kb) {
+                    // this pair writes the tile; the pairs behind it hold the rest of its k (at most two of them: the launcher
+                    // deals k out only where a pair's run is at least half a tile long)
+                    const long long tile_end = (long long)(tile + 1) * n_kb;
+                    const float* share[2] = {nullptr, nullptr};
+                    bool arrived = true;
+                    for (int q = pair + 1, n = 0; q < n_pairs && k_run_of(q, n_pairs, tiles_total, n_kb).begin < tile_end; ++q, ++n) {
+                        if (n == 2) { if (lane == 0) atomicOr(args.status, TT_STATUS_BAD_SHAPE); break; }
+                        if (lane == 0) arrived = flag_wait(share_flag_of(args.shares, n_pairs, q, rank, quarter), 1u) && arrived;
+                        share[n] = share_of(args.shares, q, rank, quarter);
+                    }
+                    arrived = __shfl_sync(0xffffffffu, arrived ? 1 : 0, 0) != 0;
+                    __threadfence();
+                    if (!arrived) {
+                        if (lane == 0) atomicOr(args.status, TT_STATUS_WAIT_EXPIRED);
+                        share[0] = share[1] = nullptr;
+                    }
+                    store_accumulator_bulk<WIDE>(lane_addr, token - lane, f_base, 0, args, &map_out, slabs, lane, round, share[0], share[1]);
+                    __syncwarp();
+                    if (lane == 0 && arrived) {                       // the flags as they were found, for the next launch
+                        for (int q = pair + 1; q < n_pairs && k_run_of(q, n_pairs, tiles_total, n_kb).begin < tile_end; ++q)
+                            *share_flag_of(args.shares, n_pairs, q, rank, quarter) = 0u;
+                    }
+                } else if (bulk_out) {
+                    store_accumulator_bulk<WIDE>(lane_addr, token - lane, f_base, 0, args, &map_out, slabs, lane, round);
+                } else {
+                    store_accumulator<dual>(lane_addr, token, f_base, args);
+                }
             } else if constexpr (FORM != TOKENS_ON_M_QKV) {
                 store_accumulator<dual>(lane_addr, token, f_base, args);     // the qkv form has stored its row
             }
@@ -973,7 +1071,8 @@ int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtens
         if ((err = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device)) != cudaSuccess) return (int)err;
         configured = true;
     }
-    const int pairs = tiles_total < sm_count / 2 ? tiles_total : sm_count / 2;
+    // with the tiles' k-blocks dealt out (args.shares) every pair has work even where the tiles are fewer than the pairs
+    const int pairs = (tiles_total < sm_count / 2 && !args.shares) ? tiles_total : sm_count / 2;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(2 * pairs);
     config.blockDim = dim3(THREADS);
@@ -1088,9 +1187,32 @@ extern "C" int tt_gemm_tcgen05_max_skinny_tokens() { return 128; }
 // CTA-pair kernel with one k-slice only (every tile has one writer), anything else is refused.
 // Returns a cudaError_t value, or -1 if the driver's tensor-map encoder is unavailable
 // or refused the operands.
+// shares, shares_bytes: scratch memory of at least tt_gemm_tcgen05_shares_bytes() whose flag words (its tail) are zero,
+// or null.  With it, the CTA pairs' plain form deals the tiles' k-blocks out evenly where whole tiles would leave
+// pairs idle (see deals_k_out); the flags are zero again when the kernel ends.
+extern "C" long long tt_gemm_tcgen05_shares_bytes() {
+    int device = 0, sm_count = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+    return (long long)(sm_count / 2) * 8 * (SHARE_FLOATS * 4 + 4);
+}
+
+// Whether dealing k out pays: with whole tiles the pairs would work `rounds` rounds of which the last is part empty.
+// A tile's k may be shared by three pairs at most (its first pair adds two shares), so a pair's run must be at least
+// half a tile long; and a run needs a few k-blocks to be worth a share's trip through scratch memory.  While all
+// pairs are busy the products are bound by what the L2 delivers to the SMs together (64 KB per k-block and pair,
+// about 11 TB/s), not by the number of busy pairs, so only a last round that is mostly empty is worth filling.
+// Measured on a B200, whole prefill of the 1B shape (o and down dealt out / whole tiles, share of the pairs' rounds
+// that tiles fill): 2,560 tokens 5.17 / 5.54 ms (0.54), 3,000 tokens 6.20 / 6.32 (0.65), 4,864 tokens 10.91 / 11.01
+// (0.68), but 3,584 tokens 7.61 / 7.39 (0.76), 5,632 tokens 13.56 / 13.12 (0.79), 2,048 tokens 4.44 / 3.97 (0.86).
+static bool deals_k_out(int tiles, int pairs, int k_blocks) {
+    if (pairs < 2 || tiles * 2 <= pairs + 1 || k_blocks < 16) return false;
+    const int rounds = (tiles + pairs - 1) / pairs;
+    return (long long)tiles * 100 < (long long)rounds * pairs * 70;
+}
+
 extern "C" int tt_gemm_tcgen05(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* out,
                                long long ld_out, long long split_stride, int tokens, int features, int k, int splits,
-                               int form, unsigned* status, cudaStream_t stream) {
+                               int form, unsigned* status, cudaStream_t stream, void* shares, long long shares_bytes) {
     if (tokens <= 0 || features <= 0) return 0;
     if (k <= 0 || (k % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || splits < 1)
         return (int)cudaErrorInvalidValue;
@@ -1104,6 +1226,7 @@ extern "C" int tt_gemm_tcgen05(const void* x, long long ldx, const void* w, long
     args.accumulate = form == 2 ? 1 : 0;
     args.undelivered_bytes = undelivered_bytes_for_tests;
     args.bulk_out = 0;
+    args.shares = nullptr;
     CUtensorMap map_a, map_b;
     const int tiles_m = (tokens + BM - 1) / BM;
     if (form == 2 && !(tokens > 128 && tiles_m * ((features + 255) / 256) >= 8 && splits == 1)) return (int)cudaErrorInvalidValue;
@@ -1158,7 +1281,13 @@ extern "C" int tt_gemm_tcgen05(const void* x, long long ldx, const void* w, long
         }
         if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, features, k, ldw, 128)) return -1;
         const int pair_tiles_m = (tokens + 2 * BM - 1) / (2 * BM);
-        return launch_pair<TOKENS_ON_M>(map_a, map_b, map_out, args, pair_tiles_m, pair_tiles_m * ((features + 255) / 256), stream);
+        const int pair_tiles = pair_tiles_m * ((features + 255) / 256);
+        if (args.bulk_out && shares && (((uintptr_t)shares) & 15) == 0 && shares_bytes >= tt_gemm_tcgen05_shares_bytes()) {
+            int device = 0, sm_count = 0;
+            if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return -1;
+            if (deals_k_out(pair_tiles, sm_count / 2, k_blocks)) args.shares = (float*)shares;
+        }
+        return launch_pair<TOKENS_ON_M>(map_a, map_b, map_out, args, pair_tiles_m, pair_tiles, stream);
     }
     if (tokens > 128) {
         if (!make_map(&map_a, x, tokens, k, ldx, BM) || !make_map(&map_b, w, features, k, ldw, 128)) return -1;

@@ -54,6 +54,24 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         if (global_time_ns() - start > wait_limit_ns) return false;
     }
 }
+// A word in global memory that another CTA sets once: release by the setter after its stores (and their fence),
+// acquire by the waiter, who gives up after the same time limit as a barrier wait.
+__device__ __forceinline__ void flag_release(unsigned* flag, unsigned value) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(value) : "memory");
+}
+__device__ __forceinline__ bool flag_wait(const unsigned* flag, unsigned value) {
+    unsigned long long start = 0;
+    for (unsigned spins = 0;; ++spins) {
+        unsigned seen;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+        if (seen == value) return true;
+        if ((spins & 63) == 63) {
+            const unsigned long long now = global_time_ns();
+            if (start == 0) start = now;
+            else if (now - start > wait_limit_ns) return false;
+        }
+    }
+}
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }

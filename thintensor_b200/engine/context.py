@@ -25,6 +25,7 @@ class Workspace:
         self._buffers: dict[str, torch.Tensor] = {}
         self._views: dict[tuple, torch.Tensor] = {}   # (name, shape, dtype) -> the view handed out last time
         self.generation = 0  # bumped whenever a buffer moves
+        self._zeroed: set[str] = set()                # names handed out by get_zeroed
 
     def get(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         key = (name, shape, dtype)
@@ -57,7 +58,16 @@ class Workspace:
         view = self.get(name, shape, dtype)
         if self._buffers.get(name) is not buffer:
             self._buffers[name].zero_()
+        self._zeroed.add(name)
         return view
+
+    def zero_again(self) -> None:
+        """After a kernel gave up (a bounded wait that ran out, a size it refused) the users of these buffers may not
+        have left them as they found them: tickets half drawn, flags set by a CTA whose partner had stopped waiting."""
+        for name in self._zeroed:
+            buffer = self._buffers.get(name)
+            if buffer is not None:
+                buffer.zero_()
 
     def bytes(self) -> int:
         return sum(b.numel() for b in self._buffers.values())

@@ -210,6 +210,7 @@ class Engine:
         word = int(self.status.item())
         if word:
             self.status.zero_()
+            self.workspace.zero_again()         # tickets and flags that a kernel which gave up may have left set
             names = []
             if word & api.STATUS_BAD_TOKEN:
                 names.append("a token id outside the vocabulary reached the embedding")

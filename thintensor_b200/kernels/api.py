@@ -519,12 +519,24 @@ def gemm_tcgen05_accumulate_pays(tokens: int, features: int, k: int, sms: int | 
     return -(-tokens // 128) * -(-features // 256) >= 2 * sms
 
 
+def gemm_tcgen05_shares_words() -> int:
+    """int32 words of scratch memory with which the CTA pairs of a prompt's plain product may deal the tiles' k-blocks out
+    evenly among themselves (``shares`` of :func:`gemm_tcgen05`): a share of a tile per epilogue warp, and a flag word
+    each at the end, which must be zero before a call and is zero again after it."""
+    lib = build.load("gemm_tcgen05")
+    lib.tt_gemm_tcgen05_shares_bytes.argtypes = []
+    lib.tt_gemm_tcgen05_shares_bytes.restype = c_longlong
+    return int(lib.tt_gemm_tcgen05_shares_bytes()) // 4
+
+
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor, status: torch.Tensor,
-                 operands_checked: bool = False, accumulate: bool = False) -> None:
+                 operands_checked: bool = False, accumulate: bool = False, shares: torch.Tensor | None = None) -> None:
     """out[s] = x @ w[:, k-slice s].T on the tensor cores; bfloat16 operands, float32
     ``out`` [splits, tokens, features]; bias (float32) goes into slice 0.  ``operands_checked``: the
     caller has already called :func:`gemm_tcgen05_usable` on these operands.  ``accumulate``: the
-    product is added to ``out`` [1, tokens, features] (only where :func:`gemm_tcgen05_accumulates`)."""
+    product is added to ``out`` [1, tokens, features] (only where :func:`gemm_tcgen05_accumulates`).
+    ``shares``: zeroed int32 scratch memory of :func:`gemm_tcgen05_shares_words` words; with it, prompts on
+    CTA pairs whose tiles would leave pairs idle share the tiles' k among the pairs."""
     _need(out, torch.float32, "gemm output")
     tokens, k = x.shape
     features = w.shape[0]
@@ -536,10 +548,13 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, ou
         raise KernelError(f"{out.shape[0]} k-slices for k = {k}: a slice needs at least one block of 64")
     if bias is not None:
         _need(bias, torch.float32, "bias")
+    if shares is not None and (shares.dtype != torch.int32 or not shares.is_contiguous()):
+        raise KernelError("the shares of a tcgen05 gemm must be contiguous int32")
     fn = _fn("gemm_tcgen05", "tt_gemm_tcgen05", [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_longlong,
-                                                 c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+                                                 c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_longlong])
     _check(fn(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(bias), _ptr(out), out.stride(1), out.stride(0), tokens, features, k,
-              out.shape[0], 2 if accumulate else 0, _ptr(status), _stream()), "gemm_tcgen05")
+              out.shape[0], 2 if accumulate else 0, _ptr(status), _stream(), _ptr(shares), 0 if shares is None else shares.numel() * 4),
+           "gemm_tcgen05")
 
 
 def gemm_tcgen05_qkv_rope_takes(x: torch.Tensor, w: torch.Tensor, head_dim: int, rotary_dim: int) -> bool:
@@ -610,6 +625,6 @@ def gemm_tcgen05_swiglu(x: torch.Tensor, w: torch.Tensor, act: torch.Tensor, sta
     if not gemm_tcgen05_usable(x, w) or w.shape[1] != k or tuple(act.shape) != (tokens, inter):
         raise KernelError(f"tcgen05 swiglu gemm cannot take x {tuple(x.shape)} / w {tuple(w.shape)} / act {tuple(act.shape)}")
     fn = _fn("gemm_tcgen05", "tt_gemm_tcgen05", [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_longlong,
-                                                 c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+                                                 c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_longlong])
     _check(fn(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(None), _ptr(act), act.stride(0), 0, tokens, inter, k, 1, 1,
-              _ptr(status), _stream()), "gemm_tcgen05_swiglu")
+              _ptr(status), _stream(), _ptr(None), 0), "gemm_tcgen05_swiglu")

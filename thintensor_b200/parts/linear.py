@@ -47,12 +47,20 @@ class Linear:
                 out = into.unsqueeze(0)
             else:
                 out = ctx.scratch(name, (splits, tokens, self.out_features), torch.float32)
-            api.gemm_tcgen05(x, self.weight, self.bias, out, ctx.status, operands_checked=True)
+            api.gemm_tcgen05(x, self.weight, self.bias, out, ctx.status, operands_checked=True, shares=self.shares(ctx, tokens))
             return out
         out = into.unsqueeze(0) if into is not None else ctx.scratch(name, (1, tokens, self.out_features), torch.float32)
         api.gemm_simt(x, self.weight, self.bias, out)
         return out
 
+
+    @staticmethod
+    def shares(ctx, tokens: int):
+        """Scratch memory for prompts on CTA pairs, whose tiles' k the pairs may share among themselves (one buffer
+        for all products of the step: a product is done with it when the next one starts)."""
+        if tokens < api.PAIR_TOKENS:
+            return None
+        return ctx.workspace.get_zeroed("gemm.shares", (api.gemm_tcgen05_shares_words(),), torch.int32)
 
     def delta(self, ctx, x: torch.Tensor, name: str) -> Delta:
         """The product as an addition to the residual stream.  Where the step offers the stream
@@ -63,7 +71,8 @@ class Linear:
         if (residual is not None and residual.shape == (x.shape[0], self.out_features) and api.gemm_tcgen05_usable(x, self.weight)
                 and api.gemm_tcgen05_accumulate_pays(x.shape[0], self.out_features, self.in_features)):
             api.set_label(name)
-            api.gemm_tcgen05(x, self.weight, self.bias, residual.unsqueeze(0), ctx.status, operands_checked=True, accumulate=True)
+            api.gemm_tcgen05(x, self.weight, self.bias, residual.unsqueeze(0), ctx.status, operands_checked=True, accumulate=True,
+                             shares=self.shares(ctx, x.shape[0]))
             return Delta(None)
         return Delta(self(ctx, x, name))
 
