@@ -181,6 +181,8 @@ def test_split_policy_and_refusals():
 
 
 @pytest.mark.parametrize("tokens,inter,k", [(129, 128, 64), (300, 200, 72), (2048, 1024, 512), (257, 8192, 2048), (5000, 1100, 200), (2048, 8192, 2048),
+                                            # rows that tiled copies can write, edges inside a box of 64 features x 32 tokens: CTA pairs, one CTA
+                                            (5000, 1096, 200), (400, 1064, 136),
                                             # few tokens: features on the 128-row side, gate rows paired with up rows in one tile
                                             (1, 64, 64), (8, 8192, 2048), (3, 100, 72), (16, 1000, 520), (17, 328, 200), (40, 72, 2048),
                                             (64, 14336, 4096), (65, 130, 136), (128, 1100, 512)])

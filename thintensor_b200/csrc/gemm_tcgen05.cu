@@ -469,6 +469,57 @@ __device__ __forceinline__ void store_accumulator_bulk(uint32_t lane_addr, int f
     }
 }
 
+// The SwiGLU form's tile through shared memory: columns 0..127 of the accumulator are the gate and 128..255 the up
+// projection of 128 features from f_base; silu(gate) * up as bfloat16, 64 features (128 bytes) x 32 rows to a slab,
+// one tiled copy a slab.  The next chunk's gate and up are on their way while one is worked on, as in the register form.
+__device__ __forceinline__ void store_swiglu_bulk(uint32_t lane_addr, int first_token, int f_base, const Args& args, const CUtensorMap* map_out,
+                                                  uint8_t* slabs, int lane, int& round) {
+    uint32_t gate[2][32], up[2][32];
+    tmem_load32_issue(lane_addr, gate[0]);
+    tmem_load32_issue(lane_addr + 128, up[0]);
+    const bool wanted = first_token < args.tokens;                             // the same for the whole warp
+#pragma unroll
+    for (int ci = 0; ci < 4; ++ci) {
+        const int cur = ci & 1;
+        tmem_load_wait();
+        if (ci + 1 < 4) {
+            tmem_load32_issue(lane_addr + 32 * ci + 32, gate[cur ^ 1]);
+            tmem_load32_issue(lane_addr + 128 + 32 * ci + 32, up[cur ^ 1]);
+        }
+        const int f0 = f_base + 64 * (ci >> 1);                                // first feature of this chunk's slab
+        if (!wanted || f0 >= args.features) continue;
+        uint8_t* slab = slabs + (round & 1) * 4096;
+        if ((ci & 1) == 0) {
+            if (lane == 0) bulk_wait_group_read<1>();
+            __syncwarp();
+        }
+#pragma unroll
+        for (int e0 = 0; e0 < 32; e0 += 8) {
+            float y[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float g = tmem_loaded(gate[cur][e0 + e]), u = tmem_loaded(up[cur][e0 + e]);
+                y[e] = __fdividef(g, 1.0f + __expf(-g)) * u;
+            }
+            const __nv_bfloat162 p0 = __floats2bfloat162_rn(y[0], y[1]), p1 = __floats2bfloat162_rn(y[2], y[3]);
+            const __nv_bfloat162 p2 = __floats2bfloat162_rn(y[4], y[5]), p3 = __floats2bfloat162_rn(y[6], y[7]);
+            const int piece = (ci & 1) * 4 + (e0 >> 3);
+            *reinterpret_cast<uint4*>(slab + lane * 128 + ((piece ^ (lane & 7)) << 4)) =
+                make_uint4(*reinterpret_cast<const uint32_t*>(&p0), *reinterpret_cast<const uint32_t*>(&p1),
+                           *reinterpret_cast<const uint32_t*>(&p2), *reinterpret_cast<const uint32_t*>(&p3));
+        }
+        if (ci & 1) {
+            fence_async_shared();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_2d(map_out, smem_u32(slab), f0, first_token);
+                bulk_commit_group();
+            }
+            ++round;
+        }
+    }
+}
+
 // A warp's 32 rows of an accumulator that holds only a share of the tile's k: column by column into the warp's own
 // 32 KB of scratch memory, the 32 lanes' numbers of a column side by side (whole lines a store; the layout is nobody
 // else's business).  The pair that holds the tile's first k-blocks adds it to its own share (store_accumulator_bulk).
@@ -763,8 +814,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
         tt_pdl_wait();
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
-        const bool bulk_out = FORM == TOKENS_ON_M && args.bulk_out;
-        uint8_t* slabs = smem + (size_t)P_STAGES * P_STAGE_BYTES + quarter * OUT_SLAB_BYTES / 4;     // plain form only
+        const bool bulk_out = (FORM == TOKENS_ON_M || dual) && args.bulk_out;
+        uint8_t* slabs = smem + (size_t)P_STAGES * P_STAGE_BYTES + quarter * OUT_SLAB_BYTES / 4;     // plain and SwiGLU forms
         int round = 0;
         for (int j = 0; j < my_tiles; ++j) {
             const int buf = j & 1;
@@ -789,6 +840,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                 // stored by qkv_row_epilogue
             } else if (bulk_out) {
                 if constexpr (FORM == TOKENS_ON_M) store_accumulator_bulk<WIDE>(lane_addr, token - lane, f_base, slice, args, &map_out, slabs, lane, round);
+                else if constexpr (dual) store_swiglu_bulk(lane_addr, token - lane, f_base, args, &map_out, slabs, lane, round);
             } else if (dual || slice == 0) {
                 store_accumulator<dual, WIDE>(lane_addr, token, f_base, args);
             } else {                                            // a later k-slice: its own plane of the output, no bias
@@ -937,8 +989,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         tt_pdl_wait();
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
-        const bool bulk_out = FORM == TOKENS_ON_M && args.bulk_out;
-        uint8_t* slabs = smem + (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + quarter * OUT_SLAB_BYTES / 4;   // plain form only
+        const bool bulk_out = (FORM == TOKENS_ON_M || dual) && args.bulk_out;
+        uint8_t* slabs = smem + (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + quarter * OUT_SLAB_BYTES / 4;   // plain and SwiGLU forms
         int round = 0;
         for (int j = 0; j < my_tiles; ++j) {
             const int buf = j & 1;
@@ -996,9 +1048,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 } else {
                     store_accumulator<dual>(lane_addr, token, f_base, args);
                 }
-            } else if constexpr (FORM != TOKENS_ON_M_QKV) {
-                store_accumulator<dual>(lane_addr, token, f_base, args);     // the qkv form has stored its row
-            }
+            } else if constexpr (dual) {
+                if (bulk_out) store_swiglu_bulk(lane_addr, token - lane, f_base, args, &map_out, slabs, lane, round);
+                else store_accumulator<dual>(lane_addr, token, f_base, args);
+            }                                                                // the qkv form has stored its row
             // this warp is done with the accumulator: tell the issuer, who sits in the even CTA
             fence_before_sync();
             __syncwarp();
@@ -1038,7 +1091,7 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const Args& args,
 template <int FORM, int WIDE = 256>
 int launch_persistent(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_out, const Args& args, int tiles_m, int tiles_total,
                       int splits, cudaStream_t stream) {
-    constexpr int shared = P_STAGE_BYTES * P_STAGES + 1024 + (FORM == TOKENS_ON_M ? OUT_SLAB_BYTES : 0);
+    constexpr int shared = P_STAGE_BYTES * P_STAGES + 1024 + (FORM == TOKENS_ON_M || FORM == TOKENS_ON_M_SWIGLU ? OUT_SLAB_BYTES : 0);
     static bool configured = false;
     static int sm_count = 0;
     auto kernel = gemm_tcgen05_persistent_kernel<FORM, WIDE>;
@@ -1059,7 +1112,7 @@ int launch_persistent(const CUtensorMap& map_a, const CUtensorMap& map_b, const 
 template <int FORM, int WIDE = 256>
 int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_out, const Args& args, int tiles_m, int tiles_total,
                 cudaStream_t stream) {
-    constexpr int shared = PAIR_STAGE_BYTES * PAIR_STAGES + 1024 + (FORM == TOKENS_ON_M ? OUT_SLAB_BYTES : 0);
+    constexpr int shared = PAIR_STAGE_BYTES * PAIR_STAGES + 1024 + (FORM == TOKENS_ON_M || FORM == TOKENS_ON_M_SWIGLU ? OUT_SLAB_BYTES : 0);
     static bool configured = false;
     static int sm_count = 0;
     auto kernel = gemm_tcgen05_pair_kernel<FORM, WIDE>;
@@ -1246,10 +1299,19 @@ extern "C" int tt_gemm_tcgen05(const void* x, long long ldx, const void* w, long
             }
         }
         const int tiles = tiles_m * ((features + 127) / 128);
-        if (tiles >= 8 && tokens < PAIR_MIN_TOKENS_SWIGLU) return launch_persistent<TOKENS_ON_M_SWIGLU>(map_a, map_b, map_a, args, tiles_m, tiles, 1, stream);
+        // the activations leave through shared memory and tiled copies where those can write their rows (16-byte aligned,
+        // a multiple of 16 bytes apart): boxes of 64 features x 32 tokens
+        CUtensorMap map_out = map_a;
+        if (tiles >= 8 && (ld_out % 8) == 0 && (((uintptr_t)out) & 15) == 0) {
+            const cuuint64_t dims[2] = {(cuuint64_t)features, (cuuint64_t)tokens};
+            const cuuint64_t strides[1] = {(cuuint64_t)ld_out * 2};
+            const cuuint32_t box[2] = {64, 32};
+            args.bulk_out = tc::make_map(&map_out, out, 2, dims, strides, box) ? 1 : 0;
+        }
+        if (tiles >= 8 && tokens < PAIR_MIN_TOKENS_SWIGLU) return launch_persistent<TOKENS_ON_M_SWIGLU>(map_a, map_b, map_out, args, tiles_m, tiles, 1, stream);
         if (tiles >= 8) {
             const int pair_tiles_m = (tokens + 2 * BM - 1) / (2 * BM);
-            return launch_pair<TOKENS_ON_M_SWIGLU>(map_a, map_b, map_a, args, pair_tiles_m, pair_tiles_m * ((features + 127) / 128), stream);
+            return launch_pair<TOKENS_ON_M_SWIGLU>(map_a, map_b, map_out, args, pair_tiles_m, pair_tiles_m * ((features + 127) / 128), stream);
         }
         const dim3 grid((features + 127) / 128, tiles_m, 1);
         return launch<TOKENS_ON_M_SWIGLU, 128, 4>(map_a, map_b, args, grid, stream);

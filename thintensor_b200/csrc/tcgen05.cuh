@@ -95,6 +95,9 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
 // coordinate times the element size must be a multiple of 16 bytes and no coordinate may be negative.  The copies of
 // a thread are grouped by bulk_commit_group; bulk_wait_group_read<N> returns when all but its N latest groups have
 // read their shared memory, which may then be written again (and must happen before the CTA ends).
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int x, int y, int z) {
     asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
                  ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(z) : "memory");
