@@ -441,11 +441,17 @@ __device__ __forceinline__ void store_accumulator_bulk(uint32_t lane_addr, int f
         // other pairs' shares of this tile's k (see store_share): added in a fixed order, first the one next in k
         if (share_a) {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) v[e] += __ldcg(share_a + (c + e) * 32 + lane);
+            for (int e = 0; e < 32; e += 4) {
+                const float4 other = __ldcg(reinterpret_cast<const float4*>(share_a) + ((c + e) >> 2) * 32 + lane);
+                v[e] += other.x; v[e + 1] += other.y; v[e + 2] += other.z; v[e + 3] += other.w;
+            }
         }
         if (share_b) {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) v[e] += __ldcg(share_b + (c + e) * 32 + lane);
+            for (int e = 0; e < 32; e += 4) {
+                const float4 other = __ldcg(reinterpret_cast<const float4*>(share_b) + ((c + e) >> 2) * 32 + lane);
+                v[e] += other.x; v[e + 1] += other.y; v[e + 2] += other.z; v[e + 3] += other.w;
+            }
         }
         if (bias) {
 #pragma unroll
@@ -520,8 +526,8 @@ __device__ __forceinline__ void store_swiglu_bulk(uint32_t lane_addr, int first_
     }
 }
 
-// A warp's 32 rows of an accumulator that holds only a share of the tile's k: column by column into the warp's own
-// 32 KB of scratch memory, the 32 lanes' numbers of a column side by side (whole lines a store; the layout is nobody
+// A warp's 32 rows of an accumulator that holds only a share of the tile's k: four columns at a time into the warp's own
+// 32 KB of scratch memory, the 32 lanes' 16-byte pieces side by side (whole lines a store; the layout is nobody
 // else's business).  The pair that holds the tile's first k-blocks adds it to its own share (store_accumulator_bulk).
 template <int WIDE>
 __device__ __forceinline__ void store_share(uint32_t lane_addr, float* share, int lane) {
@@ -530,7 +536,8 @@ __device__ __forceinline__ void store_share(uint32_t lane_addr, float* share, in
         float v[32];
         tmem_load32(lane_addr + c, v);
 #pragma unroll
-        for (int e = 0; e < 32; ++e) __stcg(share + (c + e) * 32 + lane, v[e]);
+        for (int e = 0; e < 32; e += 4)
+            __stcg(reinterpret_cast<float4*>(share) + ((c + e) >> 2) * 32 + lane, make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]));
     }
 }
 
