@@ -138,6 +138,14 @@ def test_long_prompt_whole_and_in_pieces(tmp_path):
         results.append(engine.step([Entry(slot, tokens, places)]).double().cpu())
         engine.close(slot)
         engine.check_status()
+        if piece == 8192:
+            # 19 x 8 = 152 tiles of 256 x 256 fill two thirds of three rounds of a B200's 74 CTA pairs: the pairs share the tiles' k,
+            # which leaves their shares in the workspace and its flags zero
+            shares = engine.workspace.get_zeroed("gemm.shares", (api.gemm_tcgen05_shares_words(),), torch.int32)
+            flags = shares[-(shares.numel() // (32 * 256 + 1)):]
+            assert int(flags.abs().sum().item()) == 0
+            if api.sm_count() == 148:
+                assert int(shares.abs().sum().item()) != 0
     assert_close(results[0], results[1], "bfloat16", "whole against pieces")
     # and the first positions against the plain implementation (the whole prompt would take it minutes)
     want = plain_logits(folder, tokens[:300], [0, 299])

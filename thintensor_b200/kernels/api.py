@@ -519,14 +519,21 @@ def gemm_tcgen05_accumulate_pays(tokens: int, features: int, k: int, sms: int | 
     return -(-tokens // 128) * -(-features // 256) >= 2 * sms
 
 
+_shares_words: dict[int, int] = {}
+
+
 def gemm_tcgen05_shares_words() -> int:
     """int32 words of scratch memory with which the CTA pairs of a prompt's plain product may deal the tiles' k-blocks out
     evenly among themselves (``shares`` of :func:`gemm_tcgen05`): a share of a tile per epilogue warp, and a flag word
     each at the end, which must be zero before a call and is zero again after it."""
-    lib = build.load("gemm_tcgen05")
-    lib.tt_gemm_tcgen05_shares_bytes.argtypes = []
-    lib.tt_gemm_tcgen05_shares_bytes.restype = c_longlong
-    return int(lib.tt_gemm_tcgen05_shares_bytes()) // 4
+    device = torch.cuda.current_device()
+    words = _shares_words.get(device)
+    if words is None:
+        lib = build.load("gemm_tcgen05")
+        lib.tt_gemm_tcgen05_shares_bytes.argtypes = []
+        lib.tt_gemm_tcgen05_shares_bytes.restype = c_longlong
+        words = _shares_words[device] = int(lib.tt_gemm_tcgen05_shares_bytes()) // 4
+    return words
 
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor, status: torch.Tensor,
