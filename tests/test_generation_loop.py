@@ -196,3 +196,24 @@ def test_product_policies_need_no_device():
         for features, k in ((2048, 2048), (3072, 8192), (200, 64), (4096, 14336)):
             if api.gemm_tcgen05_accumulate_pays(tokens, features, k, sms=148):
                 assert api.gemm_tcgen05_accumulates(tokens, features, k, sms=148) and api.gemm_tcgen05_splits(tokens, features, k, sms=148) == 1
+
+
+def test_k_runs_of_cta_pairs_share_a_tile_among_at_most_three():
+    """The CTA pairs' plain product may deal the tiles' k-blocks out as contiguous runs (units = tiles * k-blocks,
+    pair p takes units [units * p // pairs, units * (p + 1) // pairs)).  The pair that holds a tile's first k-blocks adds
+    at most two other pairs' shares, which the launcher guarantees by dealing only where tiles * 2 > pairs + 1
+    (gemm_tcgen05.cu, deals_k_out and KRun): the arithmetic of that guarantee, for every size it admits."""
+    for pairs in (2, 3, 66, 74):
+        for k_blocks in (16, 17, 32, 48, 128, 224):
+            for tiles in range(1, 4 * pairs + 3):
+                if tiles * 2 <= pairs + 1:
+                    continue
+                units = tiles * k_blocks
+                begins = [units * p // pairs for p in range(pairs + 1)]
+                assert begins[0] == 0 and begins[-1] == units
+                for tile in range(tiles):
+                    lo, hi = tile * k_blocks, (tile + 1) * k_blocks
+                    holders = [p for p in range(pairs) if begins[p] < hi and begins[p + 1] > lo]
+                    assert 1 <= len(holders) <= 3, (pairs, k_blocks, tiles, tile, holders)
+                    # only a pair's first item starts inside a tile: every holder but the first begins inside this tile
+                    assert all(lo < begins[p] < hi for p in holders[1:])
