@@ -705,7 +705,7 @@ __device__ __forceinline__ bool qkv_row_epilogue(uint32_t acc_bar, uint32_t pari
 // boundaries; the epilogue warps drain accumulator (j & 1) of the CTA's j-th tile while the
 // products of tile j + 1 fill the other one.
 constexpr int P_STAGES = 4;
-constexpr int OUT_SLAB_BYTES = 4 * 2 * 4096;     // plain form of the persistent and pair kernels: two slabs of 32 x 32 float32 for each epilogue warp
+constexpr int OUT_SLAB_BYTES = 4 * 2 * 4096;     // plain and SwiGLU forms of the persistent and pair kernels: two slabs of 4 KB (32 rows of 128 bytes) for each epilogue warp
 constexpr int P_STAGE_BYTES = BM * BK * 2 + 256 * BK * 2;       // A tile + 256 rows of B
 
 template <int FORM, int WIDE = 256>
