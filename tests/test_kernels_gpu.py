@@ -321,6 +321,45 @@ def test_attention_mma_decode_many_sequences(splits):
     assert int(st.item()) == 0
 
 
+@pytest.mark.parametrize("window", [0, 200])
+@pytest.mark.parametrize("splits", [1, 2, 4])
+@pytest.mark.parametrize("sequences,heads,kv_heads,head_dim", [(120, 8, 4, 64), (80, 6, 2, 128), (150, 20, 2, 96), (40, 4, 4, 32)])
+def test_attention_mma_decode_in_several_rounds(sequences, heads, kv_heads, head_dim, splits, window):
+    """More (sequence, kv head, slice) CTAs than fit at once, at every head size: the grid runs in several rounds (at head
+    size 64 with the smaller CTAs, two to an SM).  Lengths from one token to 1,500 (so that slices have no block for some
+    warps, one block, or several rounds of the ring), sequences that end on a block's last and first slot, and in one
+    sequence a far key made to dominate."""
+    from thintensor_b200.kernels import api
+
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(60 + head_dim)
+    totals = [int(v) for v in torch.randint(1, 1500, (sequences,), generator=g)]
+    totals[0], totals[1], totals[2], totals[3], totals[-1] = 1400, 1, 64, 65, 1281
+    n = len(totals)
+    assert n * kv_heads * splits > (3 if head_dim == 64 else 1) * api.sm_count()
+    k_pool, v_pool, table, keys, values = make_cache(totals, kv_heads, head_dim, dtype, seed=61)
+    q = randn(n, heads, head_dim, dtype=dtype, seed=62)
+    far = 5 if not window else totals[0] - window
+    spike = (q[0, 0].float() * (24.0 * head_dim ** 0.5 / float(q[0, 0].float().norm()) ** 2)).to(dtype)
+    block, offset = int(table[0, far // 64]), far % 64
+    k_pool[block, 0, offset] = spike
+    keys[0][far, 0] = spike.float().cpu()
+    cu = torch.arange(n + 1, dtype=torch.int32, device=DEV)
+    before = torch.tensor([t - 1 for t in totals], dtype=torch.int32, device=DEV)
+    part_acc = torch.full((n * heads * splits * head_dim,), float("nan"), dtype=torch.float32, device=DEV)
+    part_ml = torch.full((n * heads * splits * 2,), float("nan"), dtype=torch.float32, device=DEV)
+    st = status()
+    scale = head_dim ** -0.5
+    want = attention_reference(q.float().cpu(), keys, values, [1] * n, heads, kv_heads, scale, window)
+    for _ in range(2):
+        out = torch.full((n, heads * head_dim), float("nan"), dtype=dtype, device=DEV)
+        api.attention_mma(q.view(n, -1), k_pool, v_pool, table, cu, before, n, n, heads, kv_heads, head_dim, scale, window, splits, out,
+                          part_acc, part_ml, st, one_token_each=True)
+        torch.testing.assert_close(out.double().cpu().view(n, heads, head_dim), want, **tol(dtype))
+        assert int(st.item()) == 0
+    assert torch.allclose(want[0, 0], values[0][far, 0].double(), atol=0.35)
+
+
 @pytest.mark.parametrize("write_cache", [True, False])
 @pytest.mark.parametrize("splits", [1, 3, 16])
 @pytest.mark.parametrize("window", [0, 100])
